@@ -1,0 +1,250 @@
+"""ctypes binding of the CPU oracle (``libsimp_oracle.so``) and of the reference's own
+compiled int8 kernels (``_ref/*.so``).
+
+TEST INFRASTRUCTURE ONLY: imported by ``tests/``, by ``__graft_entry__.smoke()`` and by the
+CPU-baseline / reference legs of ``bench.py`` -- as the checker, never as the thing shipped.
+The CUDA library must not import this package.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB = None
+_REF = {}
+
+i64 = C.c_int64
+_f32p = np.ctypeslib.ndpointer(dtype=np.float32, flags="C_CONTIGUOUS")
+_f64p = np.ctypeslib.ndpointer(dtype=np.float64, flags="C_CONTIGUOUS")
+_i32p = np.ctypeslib.ndpointer(dtype=np.int32, flags="C_CONTIGUOUS")
+_i8p = np.ctypeslib.ndpointer(dtype=np.int8, flags="C_CONTIGUOUS")
+_u8p = np.ctypeslib.ndpointer(dtype=np.uint8, flags="C_CONTIGUOUS")
+
+
+def build(with_ref: bool = True) -> None:
+    """Compile the oracle (and oracle/_ref when the reference checkout is present)."""
+    subprocess.run(["make", "-C", _HERE, "all" if with_ref else "oracle"], check=True,
+                   stdout=subprocess.DEVNULL)
+
+
+def lib() -> C.CDLL:
+    global _LIB
+    if _LIB is None:
+        path = os.path.join(_HERE, "libsimp_oracle.so")
+        if not os.path.exists(path):
+            build(with_ref=False)
+        _LIB = C.CDLL(path)
+        L = _LIB
+        L.simp_oracle_max_threads.restype = C.c_int
+        L.simp_oracle_matmul_f32.argtypes = [_f32p, i64, _f32p, i64, _f32p, i64, i64, i64, i64, C.c_int]
+        L.simp_oracle_tensor_matmul_f32.argtypes = [_f32p, _f32p, _f32p, i64, i64, i64, C.c_int, C.c_int]
+        L.simp_oracle_tensor_matmul_f64.argtypes = [_f64p, _f64p, _f64p, i64, i64, i64, C.c_int, C.c_int]
+        L.simp_oracle_tensor_matmul_i8.argtypes = [C.c_void_p, _i8p, _i32p, i64, i64, i64, C.c_int, C.c_int, C.c_int]
+        L.simp_oracle_checksum_i32.argtypes = [_i32p, i64]
+        L.simp_oracle_checksum_i32.restype = C.c_int32
+        L.simp_oracle_dequant_w4.argtypes = [_u8p, _f32p, C.c_void_p, i64, i64, i64, _f32p]
+        L.simp_oracle_matmul_quant.argtypes = [_u8p, _f32p, C.c_void_p, _f32p, _f32p, i64, i64, i64, i64, C.c_int, C.c_int]
+        L.simp_oracle_quantize_w4.argtypes = [_f32p, i64, i64, _u8p, _f32p, _f32p]
+        L.simp_oracle_rmsnorm.argtypes = [_f32p, _f32p, _f32p, i64, C.c_float, i64]
+        L.simp_oracle_softmax.argtypes = [_f32p, _f32p, i64, i64, i64]
+        L.simp_oracle_silu.argtypes = [_f32p, C.c_void_p, _f32p, i64]
+        L.simp_oracle_quantize_i8.argtypes = [_f32p, _i8p, i64, C.c_float, C.c_int]
+        L.simp_oracle_dequantize_i32.argtypes = [_i32p, _f32p, i64, C.c_float]
+        L.simp_oracle_llama_forward.argtypes = [C.c_void_p, i64, i64]
+        L.simp_oracle_llama_forward.restype = C.c_int
+        L.simp_oracle_argmax.argtypes = [_f32p, i64]
+        L.simp_oracle_argmax.restype = i64
+    return _LIB
+
+
+def _ptr(a):
+    return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+# --------------------------------------------------------------------------- numpy front-ends
+def matmul_f32(A, aoff, B, boff, Cbuf, coff, m, k, n, threads=1):
+    """In-place C += A.B on flat arrays with element offsets (simp.matmul)."""
+    lib().simp_oracle_matmul_f32(A, aoff, B, boff, Cbuf, coff, m, k, n, threads)
+    return Cbuf
+
+
+def tensor_matmul_f32(A, B, b_transposed=False, threads=1):
+    M, K = A.shape
+    N = B.shape[0] if b_transposed else B.shape[1]
+    out = np.empty((M, N), np.float32)
+    lib().simp_oracle_tensor_matmul_f32(np.ascontiguousarray(A), np.ascontiguousarray(B), out, M, K, N,
+                                        int(b_transposed), threads)
+    return out
+
+
+def tensor_matmul_f64(A, B, b_transposed=False, threads=1):
+    M, K = A.shape
+    N = B.shape[0] if b_transposed else B.shape[1]
+    out = np.empty((M, N), np.float64)
+    lib().simp_oracle_tensor_matmul_f64(np.ascontiguousarray(A), np.ascontiguousarray(B), out, M, K, N,
+                                        int(b_transposed), threads)
+    return out
+
+
+def tensor_matmul_i8(A, B, b_transposed=False, threads=0):
+    """A int8 (signed x signed) or uint8 (vpdpbusd form) [M,K]; B int8 [K,N] or [N,K]."""
+    M, K = A.shape
+    N = B.shape[0] if b_transposed else B.shape[1]
+    A = np.ascontiguousarray(A)
+    out = np.empty((M, N), np.int32)
+    lib().simp_oracle_tensor_matmul_i8(_ptr(A), np.ascontiguousarray(B), out, M, K, N,
+                                       int(A.dtype == np.uint8), int(b_transposed), threads)
+    return out
+
+
+def checksum_i32(Cm):
+    return int(lib().simp_oracle_checksum_i32(np.ascontiguousarray(Cm, np.int32).ravel(), Cm.size))
+
+
+def dequant_w4(qw, sc, zr, idx0, count, gs):
+    out = np.empty(count, np.float32)
+    lib().simp_oracle_dequant_w4(qw, sc, _ptr(zr), idx0, count, gs, out)
+    return out
+
+
+def matmul_quant(qw, sc, zr, x, rows, cols, gs, offset=0, scale_mode=0, threads=1):
+    out = np.empty(rows, np.float32)
+    lib().simp_oracle_matmul_quant(qw, sc, _ptr(zr), x, out, rows, cols, gs, offset, scale_mode, threads)
+    return out
+
+
+def quantize_w4(w, gs):
+    w = np.ascontiguousarray(w, np.float32).ravel()
+    ng = (w.size + gs - 1) // gs
+    qw = np.zeros((w.size + 1) // 2, np.uint8)
+    sc = np.empty(ng, np.float32)
+    zr = np.empty(ng, np.float32)
+    lib().simp_oracle_quantize_w4(w, w.size, gs, qw, sc, zr)
+    return qw, sc, zr
+
+
+def rmsnorm(x, w, eps=1e-5, woff=0):
+    y = np.empty(x.size, np.float32)
+    lib().simp_oracle_rmsnorm(x, w, y, x.size, eps, woff)
+    return y
+
+
+def softmax(x, n=None, xoff=0, yoff=0, out=None):
+    n = x.size if n is None else n
+    y = np.zeros(yoff + n, np.float32) if out is None else out
+    lib().simp_oracle_softmax(x, y, n, xoff, yoff)
+    return y
+
+
+def silu(x, mul=None):
+    y = np.empty(x.size, np.float32)
+    lib().simp_oracle_silu(x, _ptr(mul), y, x.size)
+    return y
+
+
+def quantize_i8(x, scale=127.0, clamp=True):
+    y = np.empty(x.size, np.int8)
+    lib().simp_oracle_quantize_i8(x, y, x.size, scale, int(clamp))
+    return y
+
+
+def dequantize_i32(acc, divisor=65536.0):
+    y = np.empty(acc.size, np.float32)
+    lib().simp_oracle_dequantize_i32(acc, y, acc.size, divisor)
+    return y
+
+
+def argmax(v):
+    return int(lib().simp_oracle_argmax(v, v.size))
+
+
+class LlamaStruct(C.Structure):
+    _fields_ = [(n, i64) for n in ("dim", "hidden_dim", "n_layers", "n_heads", "n_kv_heads", "vocab_size",
+                                   "seq_len", "w4", "group_size")] + \
+               [(n, C.c_void_p) for n in ("token_embedding", "rms_att_w", "rms_ffn_w", "rms_final_w", "wcls",
+                                          "wq", "wk", "wv", "wo", "w1", "w2", "w3",
+                                          "qweights", "scales", "zeros")] + \
+               [(n, i64) for n in ("wq_off", "wk_off", "wv_off", "wo_off", "w1_off", "w2_off", "w3_off")] + \
+               [(n, C.c_void_p) for n in ("key_cache", "value_cache", "logits")] + \
+               [("threads", C.c_int32)]
+
+
+class Llama:
+    """Whole-token forward of the f32 (stories110M.sl) or W4 (llama2_quant.sl) model on the CPU.
+
+    ``cfg``: dict with dim, hidden_dim, n_layers, n_heads, n_kv_heads, vocab_size, seq_len
+    (+ group_size for W4).  ``tensors``: dict of numpy arrays named like the struct fields.
+    """
+
+    def __init__(self, cfg, tensors, w4=False, offsets=None, threads=0):
+        self.cfg = dict(cfg)
+        self._keep = dict(tensors)
+        kv_dim = cfg["dim"] * cfg["n_kv_heads"] // cfg["n_heads"]
+        self.key_cache = np.zeros(cfg["n_layers"] * cfg["seq_len"] * kv_dim, np.float32)
+        self.value_cache = np.zeros_like(self.key_cache)
+        self.logits = np.zeros(cfg["vocab_size"], np.float32)
+        s = LlamaStruct()
+        for n in ("dim", "hidden_dim", "n_layers", "n_heads", "n_kv_heads", "vocab_size", "seq_len"):
+            setattr(s, n, cfg[n])
+        s.w4 = int(w4)
+        s.group_size = cfg.get("group_size", 0)
+        for n, a in tensors.items():
+            setattr(s, n, _ptr(a))
+        for n, v in (offsets or {}).items():
+            setattr(s, n, v)
+        s.key_cache, s.value_cache, s.logits = _ptr(self.key_cache), _ptr(self.value_cache), _ptr(self.logits)
+        s.threads = threads if threads > 0 else lib().simp_oracle_max_threads()
+        self._s = s
+
+    def forward(self, token, pos):
+        rc = lib().simp_oracle_llama_forward(C.byref(self._s), token, pos)
+        if rc != 0:
+            raise ValueError("token/pos out of range")
+        return self.logits
+
+
+# --------------------------------------------------------------------------- reference's own kernels
+def cpu_has_vnni() -> bool:
+    try:
+        with open("/proc/cpuinfo") as f:
+            flags = f.read()
+    except OSError:
+        return False
+    return all(x in flags for x in ("avx512_vnni", "avx512bw", "avx512vl", "avx512dq", "avx512cd"))
+
+
+def ref(unit: str):
+    """Load oracle/_ref/libref_<unit>.so, or return None when it is absent or the CPU lacks AVX512-VNNI."""
+    if unit not in _REF:
+        path = os.path.join(_HERE, "_ref", f"libref_{unit}.so")
+        _REF[unit] = C.CDLL(path) if (os.path.exists(path) and cpu_has_vnni()) else None
+    return _REF[unit]
+
+
+def ref_vnni_square(A, B_T, multicore=True):
+    """The reference's OpenMP VNNI GEMM (s8 x s8, B pre-transposed, N % 64 == 0)."""
+    L = ref("multicore")
+    N = A.shape[0]
+    out = np.empty((N, N), np.int32)
+    L.simp_ref_vnni_square.argtypes = [_i8p, _i8p, _i32p, C.c_int, C.c_int]
+    rc = L.simp_ref_vnni_square(np.ascontiguousarray(A), np.ascontiguousarray(B_T), out, N, int(multicore))
+    if rc != 0:
+        raise ValueError(f"size {N} not instantiated")
+    return out
+
+
+def ref_vnni_mnk(A, B_T, threads=1):
+    """The reference's non-square VNNI kernel: A [M,K] s8, B_T [N,K] s8, K % 64 == 0."""
+    L = ref("qkv")
+    M, K = A.shape
+    N = B_T.shape[0]
+    out = np.empty((M, N), np.int32)
+    L.simp_ref_vnni_mnk.argtypes = [_i8p, _i8p, _i32p, C.c_int, C.c_int, C.c_int, C.c_int]
+    rc = L.simp_ref_vnni_mnk(np.ascontiguousarray(A), np.ascontiguousarray(B_T), out, M, N, K, threads)
+    if rc != 0:
+        raise ValueError("K must be a multiple of 64")
+    return out
