@@ -1,0 +1,121 @@
+/* simp_gpu.h -- C ABI of the B200 (sm_100a) runtime library for SimpLang's tensor hot path.
+ *
+ * One shared library, libsimp_gpu.so.  Every entry point returns an int status
+ * (SIMP_OK == 0, negative on error, text via simp_gpu_last_error()) and never
+ * aborts, traps or throws across the boundary.  Pointers named *_dev are device
+ * pointers obtained from simp_gpu_alloc(); ops are enqueued on the library's
+ * stream of the calling thread's current library device and are asynchronous:
+ * call simp_gpu_sync() (or download) before reading results on the host.
+ *
+ * Each declaration cites the reference interface it replaces (paths relative
+ * to the reference project root).  The reference has no run-time library for
+ * these ops -- its compiler expands each `simp` dialect op into loops -- so
+ * "replaces" means: the call a GPU lowering pattern emits in place of the
+ * expansion cited.
+ */
+#ifndef SIMP_GPU_H_
+#define SIMP_GPU_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SIMP_OK 0
+#define SIMP_ERR_ARG (-1)         /* null pointer, negative size, bad flag              */
+#define SIMP_ERR_SHAPE (-2)       /* shape outside what the op supports                 */
+#define SIMP_ERR_CUDA (-3)        /* a CUDA runtime/driver call failed                  */
+#define SIMP_ERR_STATE (-4)       /* library not initialised / wrong call order         */
+#define SIMP_ERR_TIMEOUT (-5)     /* a bounded device-side wait gave up                 */
+#define SIMP_ERR_COMM (-6)        /* NCCL / multi-GPU set-up or collective failed       */
+#define SIMP_ERR_UNSUPPORTED (-7) /* valid request this build cannot serve              */
+
+/* ---- life cycle, memory, stream ------------------------------------------------------------
+ * Replaces: nothing in the op lowering; the reference hosts own all buffers as std::vector and
+ * pass host pointers (examples/llama2/generate_stories110M.cpp:236-251).  The loader they use is
+ * KernelRunner (runtime/include/kernel_runner.hpp:27-103). */
+int simp_gpu_init(int device);          /* select `device`, create the stream; idempotent      */
+int simp_gpu_shutdown(void);            /* free library-owned memory, destroy stream           */
+const char* simp_gpu_last_error(void);  /* message of the calling thread's last failure        */
+int simp_gpu_device_count(int* count);
+int simp_gpu_alloc(void** dptr, size_t bytes);
+int simp_gpu_free(void* dptr);
+int simp_gpu_upload(void* dst_dev, const void* src_host, size_t bytes);   /* async on the stream */
+int simp_gpu_download(void* dst_host, const void* src_dev, size_t bytes); /* synchronises        */
+int simp_gpu_memset(void* dptr, int value, size_t bytes);
+int simp_gpu_sync(void);
+void* simp_gpu_stream(void);            /* the cudaStream_t ops are enqueued on                 */
+/* Polls the device-side error word that bounded waits write; SIMP_OK or SIMP_ERR_TIMEOUT.      */
+int simp_gpu_check_device_status(void);
+
+/* ---- simp.matmul / tensor_matmul (f32) -----------------------------------------------------
+ * C[coff + i*n + j] (+)= sum_p A[aoff + i*k + p] * B[boff + p*n + j], row-major, element offsets.
+ * accumulate != 0: simp.matmul, C += A.B (MatMulOpLowering,
+ *   src/mlir/lowering/ConvertSimpToMemRef.cpp:1794-1920; callers zero C, stories110M.sl:66-83).
+ * accumulate == 0: tensor_matmul / tensor_matmul_into / tensor_matvecmul on f32, C = A.B
+ *   (ConvertSimpToMemRef.cpp:2884-2950, 3280-3291, 3490-3627, 3632-3792).
+ * b_transposed != 0: tensor_matmul_nt, B given as [n,k] (ConvertSimpToMemRef.cpp:3373-3486).
+ * n == 1 runs the streaming GEMV kernel; other shapes run the FFMA tile kernel.  f32 FMA
+ * arithmetic throughout (no TF32). */
+int simp_gpu_matmul_f32(const float* A_dev, int64_t aoff, const float* B_dev, int64_t boff,
+                        float* C_dev, int64_t coff, int64_t m, int64_t k, int64_t n,
+                        int accumulate, int b_transposed);
+
+/* ---- tensor_matmul on i8 -> i32 ------------------------------------------------------------
+ * C[M,N] (i32, wrap-around) = A[M,K] . B, bit-exact.
+ * a_unsigned == 0: signed x signed, the op as lowered (ConvertSimpToMemRef.cpp:3136-3279 and the
+ *   VNNI rewrite src/mlir/passes/VNNIPass.cpp:597-999).
+ * a_unsigned != 0: A is uint8 -- the raw vpdpbusd form
+ *   (simptensor/tests/test_vnni_correctness.cpp:28-42).
+ * b_transposed == 0: B is [K,N] (tensor_matmul / _into / tensor_matvecmul);
+ * b_transposed != 0: B is [N,K] (tensor_matmul_nt, ConvertSimpToMemRef.cpp:3373-3486).
+ * Shapes whose operand rows are 16-byte aligned run on the tcgen05 kind::i8 tensor-core kernel;
+ * any other shape runs an integer dot-product kernel with the same result. */
+int simp_gpu_matmul_i8(const void* A_dev, const int8_t* B_dev, int32_t* C_dev, int64_t M,
+                       int64_t K, int64_t N, int a_unsigned, int b_transposed);
+
+/* ---- matmul_quant / dequant_w4 (W4) --------------------------------------------------------
+ * out[rows] = W4[rows,cols] . x[cols]; nibbles packed two per byte, low nibble = even flat index,
+ * w = q*scale + zero (MatMulQuantOpLowering, ConvertSimpToMemRef.cpp:3853-4013;
+ * DequantW4OpLowering :2367-2429).  `offset` is in weights (elements) into qweights.
+ * scale_mode 0 ("reference"): scale index (i*cols)/gs + g, 128 weights visited per group -- the
+ *   lowering exactly as written (:3916-3936).
+ * scale_mode 1 ("per_matrix"): scale index (offset + i*cols)/gs + g, gs weights per group;
+ *   requires cols % gs == 0.
+ * zeros_dev == NULL: symmetric weights, zero = -8*scale (no zeros array is read). */
+int simp_gpu_matmul_w4(const uint8_t* qweights_dev, const float* scales_dev, const float* zeros_dev,
+                       const float* x_dev, float* out_dev, int64_t rows, int64_t cols,
+                       int64_t group_size, int64_t offset, int scale_mode);
+int simp_gpu_dequant_w4(const uint8_t* qweights_dev, const float* scales_dev,
+                        const float* zeros_dev, int64_t first_index, int64_t count,
+                        int64_t group_size, float* out_dev);
+
+/* ---- rmsnorm / softmax / silu --------------------------------------------------------------
+ * rmsnorm: y[r,i] = (x[r,i] / sqrt(mean_i(x[r,:]^2) + eps)) * w[woff + i]
+ *   (RMSNormOpLowering, ConvertSimpToMemRef.cpp:2157-2236).  The op is single-row; `rows` with
+ *   `row_stride` (elements) batches independent rows.  residual_dev != NULL fuses the preceding
+ *   residual add of the models (stories110M.sl:177-185): x[r,i] += residual[r,i] is written back
+ *   to x before normalising.
+ * softmax: per row, y[yoff + r*row_stride + i] = softmax(x[xoff + r*row_stride + i], i < n)
+ *   (SoftmaxOpLowering, ConvertSimpToMemRef.cpp:2239-2322).
+ * silu: y[i] = x[i] / (1 + expf(-x[i])), times mul[i] when mul_dev != NULL
+ *   (SiLUOpLowering, ConvertSimpToMemRef.cpp:2325-2360; the product is stories110M.sl:202-212). */
+int simp_gpu_rmsnorm_f32(float* x_dev, const float* w_dev, float* y_dev, int64_t rows, int64_t n,
+                         float eps, int64_t woff, int64_t row_stride, const float* residual_dev);
+int simp_gpu_softmax_f32(const float* x_dev, float* y_dev, int64_t rows, int64_t n, int64_t xoff,
+                         int64_t yoff, int64_t row_stride);
+int simp_gpu_silu_f32(const float* x_dev, const float* mul_dev, float* y_dev, int64_t n);
+
+/* ---- int8 quantise / dequantise ------------------------------------------------------------
+ * Scalar model code in the reference, not ops: y = (int8) trunc(clamp(x*scale, -128, 127))
+ * (examples/llama2/llama32_1b_int8_tensor.sl:96-103; without the clamp in
+ * llama32_1b_int8_prefill.sl:48) and y = float(acc) / divisor (llama32_1b_int8_tensor.sl:227). */
+int simp_gpu_quantize_i8(const float* x_dev, int8_t* y_dev, int64_t n, float scale, int clamp);
+int simp_gpu_dequantize_i32(const int32_t* acc_dev, float* y_dev, int64_t n, float divisor);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SIMP_GPU_H_ */

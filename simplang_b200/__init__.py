@@ -1,0 +1,193 @@
+"""simplang_b200 -- Python binding of ``libsimp_gpu.so``, the B200 (sm_100a) runtime library for
+SimpLang's tensor hot path.
+
+The product is the C-ABI library (``include/simp_gpu.h``); this module only loads it with ctypes and
+offers numpy conveniences for tests and benchmarks.  There is no CPU fallback: if the shared
+library is missing or an op fails, an exception is raised.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libsimp_gpu.so")
+_LIB = None
+
+i64 = C.c_int64
+vp = C.c_void_p
+
+
+class SimpGpuError(RuntimeError):
+    def __init__(self, code, msg):
+        super().__init__(f"simp_gpu error {code}: {msg}")
+        self.code = code
+
+
+_SIGNATURES = {
+    "simp_gpu_init": [C.c_int],
+    "simp_gpu_shutdown": [],
+    "simp_gpu_device_count": [C.POINTER(C.c_int)],
+    "simp_gpu_alloc": [C.POINTER(vp), C.c_size_t],
+    "simp_gpu_free": [vp],
+    "simp_gpu_upload": [vp, vp, C.c_size_t],
+    "simp_gpu_download": [vp, vp, C.c_size_t],
+    "simp_gpu_memset": [vp, C.c_int, C.c_size_t],
+    "simp_gpu_sync": [],
+    "simp_gpu_check_device_status": [],
+    "simp_gpu_matmul_f32": [vp, i64, vp, i64, vp, i64, i64, i64, i64, C.c_int, C.c_int],
+    "simp_gpu_matmul_i8": [vp, vp, vp, i64, i64, i64, C.c_int, C.c_int],
+    "simp_gpu_matmul_w4": [vp, vp, vp, vp, vp, i64, i64, i64, i64, C.c_int],
+    "simp_gpu_dequant_w4": [vp, vp, vp, i64, i64, i64, vp],
+    "simp_gpu_rmsnorm_f32": [vp, vp, vp, i64, i64, C.c_float, i64, i64, vp],
+    "simp_gpu_softmax_f32": [vp, vp, i64, i64, i64, i64, i64],
+    "simp_gpu_silu_f32": [vp, vp, vp, i64],
+    "simp_gpu_quantize_i8": [vp, vp, i64, C.c_float, C.c_int],
+    "simp_gpu_dequantize_i32": [vp, vp, i64, C.c_float],
+}
+
+
+def lib() -> C.CDLL:
+    """The loaded C-ABI library.  Raises if it has not been built (``python -m simplang_b200.build``)."""
+    global _LIB
+    if _LIB is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(f"{LIB_PATH} is missing: build it with `python -m simplang_b200.build`; "
+                              "there is no CPU fallback")
+        L = C.CDLL(LIB_PATH)
+        for name, args in _SIGNATURES.items():
+            fn = getattr(L, name)
+            fn.argtypes = args
+            fn.restype = C.c_int
+        L.simp_gpu_last_error.restype = C.c_char_p
+        L.simp_gpu_stream.restype = vp
+        _LIB = L
+    return _LIB
+
+
+def check(rc: int) -> None:
+    if rc != 0:
+        raise SimpGpuError(rc, lib().simp_gpu_last_error().decode())
+
+
+def init(device: int = 0) -> None:
+    check(lib().simp_gpu_init(device))
+
+
+def shutdown() -> None:
+    check(lib().simp_gpu_shutdown())
+
+
+def sync() -> None:
+    check(lib().simp_gpu_sync())
+
+
+def stream_handle() -> int:
+    return int(lib().simp_gpu_stream() or 0)
+
+
+class DeviceBuffer:
+    """Device memory owned through the C-ABI (simp_gpu_alloc / simp_gpu_free)."""
+
+    def __init__(self, nbytes: int):
+        p = vp()
+        check(lib().simp_gpu_alloc(C.byref(p), nbytes))
+        self.ptr = p.value
+        self.nbytes = nbytes
+
+    @classmethod
+    def from_numpy(cls, a: np.ndarray) -> "DeviceBuffer":
+        a = np.ascontiguousarray(a)
+        b = cls(max(a.nbytes, 16))
+        if a.nbytes:
+            check(lib().simp_gpu_upload(b.ptr, a.ctypes.data, a.nbytes))
+            sync()  # `a` may be a temporary
+        return b
+
+    def to_numpy(self, dtype, shape) -> np.ndarray:
+        out = np.empty(shape, dtype)
+        assert out.nbytes <= self.nbytes
+        check(lib().simp_gpu_download(out.ctypes.data, self.ptr, out.nbytes))
+        return out
+
+    def upload(self, a: np.ndarray) -> None:
+        a = np.ascontiguousarray(a)
+        assert a.nbytes <= self.nbytes
+        check(lib().simp_gpu_upload(self.ptr, a.ctypes.data, a.nbytes))
+        sync()
+
+    def zero(self) -> None:
+        check(lib().simp_gpu_memset(self.ptr, 0, self.nbytes))
+
+    def offset(self, nbytes: int) -> int:
+        return self.ptr + nbytes
+
+    def free(self) -> None:
+        if self.ptr:
+            lib().simp_gpu_free(self.ptr)
+            self.ptr = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+def _p(b):
+    if b is None:
+        return None
+    return b.ptr if isinstance(b, DeviceBuffer) else int(b)
+
+
+# ------------------------------------------------------------------------- device-pointer ops
+def matmul_f32(A, aoff, B, boff, Cb, coff, m, k, n, accumulate=True, b_transposed=False):
+    check(lib().simp_gpu_matmul_f32(_p(A), aoff, _p(B), boff, _p(Cb), coff, m, k, n, int(accumulate),
+                                    int(b_transposed)))
+
+
+def matmul_i8(A, B, Cb, M, K, N, a_unsigned=False, b_transposed=False):
+    check(lib().simp_gpu_matmul_i8(_p(A), _p(B), _p(Cb), M, K, N, int(a_unsigned), int(b_transposed)))
+
+
+def matmul_w4(qw, sc, zr, x, out, rows, cols, gs, offset=0, scale_mode=0):
+    check(lib().simp_gpu_matmul_w4(_p(qw), _p(sc), _p(zr), _p(x), _p(out), rows, cols, gs, offset, scale_mode))
+
+
+def dequant_w4(qw, sc, zr, first, count, gs, out):
+    check(lib().simp_gpu_dequant_w4(_p(qw), _p(sc), _p(zr), first, count, gs, _p(out)))
+
+
+def rmsnorm_f32(x, w, y, rows, n, eps=1e-5, woff=0, row_stride=0, residual=None):
+    check(lib().simp_gpu_rmsnorm_f32(_p(x), _p(w), _p(y), rows, n, eps, woff, row_stride, _p(residual)))
+
+
+def softmax_f32(x, y, rows, n, xoff=0, yoff=0, row_stride=0):
+    check(lib().simp_gpu_softmax_f32(_p(x), _p(y), rows, n, xoff, yoff, row_stride))
+
+
+def silu_f32(x, mul, y, n):
+    check(lib().simp_gpu_silu_f32(_p(x), _p(mul), _p(y), n))
+
+
+def quantize_i8(x, y, n, scale=127.0, clamp=True):
+    check(lib().simp_gpu_quantize_i8(_p(x), _p(y), n, scale, int(clamp)))
+
+
+def dequantize_i32(acc, y, n, divisor=65536.0):
+    check(lib().simp_gpu_dequantize_i32(_p(acc), _p(y), n, divisor))
+
+
+# ------------------------------------------------------------------------- numpy round trips (tests)
+def np_matmul_i8(A: np.ndarray, B: np.ndarray, b_transposed=False) -> np.ndarray:
+    """Upload, run the int8 GEMM, download.  A int8 or uint8 [M,K]; B int8 [K,N] or [N,K]."""
+    M, K = A.shape
+    N = B.shape[0] if b_transposed else B.shape[1]
+    dA, dB = DeviceBuffer.from_numpy(A), DeviceBuffer.from_numpy(B)
+    dC = DeviceBuffer(max(M * N * 4, 16))
+    matmul_i8(dA, dB, dC, M, K, N, a_unsigned=(A.dtype == np.uint8), b_transposed=b_transposed)
+    out = dC.to_numpy(np.int32, (M, N))
+    check(lib().simp_gpu_check_device_status())
+    return out

@@ -1,0 +1,112 @@
+// common.cuh -- shared host/device helpers of libsimp_gpu (sm_100a only).
+#pragma once
+#include <cuda_runtime.h>
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+
+#include "simp_gpu.h"
+
+#define SIMP_API extern "C" __attribute__((visibility("default")))
+
+namespace simp {
+
+// ---- per-process state (runtime.cu) ---------------------------------------------------------
+struct Context {
+  int device = -1;
+  cudaStream_t stream = nullptr;
+  int sm_count = 148;
+  int* dev_status = nullptr;   // device word written by bounded waits (0 = ok)
+  int* host_status = nullptr;  // pinned mirror for polling
+  bool ready = false;
+};
+Context& ctx();
+int set_error(int code, const char* fmt, ...) __attribute__((format(printf, 2, 3)));
+int ensure_ready();
+
+// Scratch arena owned by the library (grows, never shrinks until shutdown).
+void* scratch(size_t bytes, int slot);
+
+#define SIMP_CUDA(call)                                                                     \
+  do {                                                                                      \
+    cudaError_t e__ = (call);                                                               \
+    if (e__ != cudaSuccess)                                                                 \
+      return ::simp::set_error(SIMP_ERR_CUDA, "%s failed: %s (%s:%d)", #call,               \
+                               cudaGetErrorString(e__), __FILE__, __LINE__);                \
+  } while (0)
+
+#define SIMP_REQUIRE(cond, code, ...)                              \
+  do {                                                             \
+    if (!(cond)) return ::simp::set_error(code, __VA_ARGS__);      \
+  } while (0)
+
+#define SIMP_LAUNCH_CHECK()                                                                  \
+  do {                                                                                       \
+    cudaError_t e__ = cudaGetLastError();                                                    \
+    if (e__ != cudaSuccess)                                                                  \
+      return ::simp::set_error(SIMP_ERR_CUDA, "kernel launch failed: %s (%s:%d)",            \
+                               cudaGetErrorString(e__), __FILE__, __LINE__);                 \
+  } while (0)
+
+inline int64_t cdiv(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+// ---- device helpers -------------------------------------------------------------------------
+#ifdef __CUDACC__
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+// Block-wide sum / max over blockDim.x threads (multiple of 32, <= 1024); `red` holds 33 floats.
+// Every thread gets the result.  The same fixed tree each call, so results are run-to-run stable.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < nw ? red[lane] : 0.0f;
+    t = warp_sum(t);
+    if (lane == 0) red[32] = t;
+  }
+  __syncthreads();
+  return red[32];
+}
+__device__ __forceinline__ float block_max(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < nw ? red[lane] : -INFINITY;
+    t = warp_max(t);
+    if (lane == 0) red[32] = t;
+  }
+  __syncthreads();
+  return red[32];
+}
+// 128-bit streaming load that does not allocate in L1 (weights are read once per token).
+__device__ __forceinline__ uint4 ld_stream_u4(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+__device__ __forceinline__ float4 ld_stream_f4(const void* p) {
+  float4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.f32 {%0,%1,%2,%3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "l"(p));
+  return v;
+}
+#endif
+
+}  // namespace simp

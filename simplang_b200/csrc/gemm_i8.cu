@@ -1,0 +1,366 @@
+// gemm_i8.cu -- tensor_matmul on i8: C[M,N] (s32, wrap-around) = A[M,K] . B, bit-exact.
+//
+// Semantics: TensorMatMulOpLowering i8 branch (src/mlir/lowering/ConvertSimpToMemRef.cpp:3220-3247,
+// sign-extend both, multiply, add in i32) and its VNNI rewrite (src/mlir/passes/VNNIPass.cpp:731-906);
+// the unsigned-A form is raw vpdpbusd (simptensor/tests/test_vnni_correctness.cpp:28-42);
+// B as [N,K] is tensor_matmul_nt (ConvertSimpToMemRef.cpp:3417-3443).
+//
+// Tensor-core kernel (persistent, warp-specialised, one CTA per SM):
+//   warp 0      TMA producer: 128x128-byte A tile + 256x128-byte B tile per stage, 128-byte swizzle,
+//               4-stage ring, mbarrier complete_tx
+//   warp 1      issues tcgen05.mma.cta_group::1.kind::i8 (M128 x N256 x K32, s32 accumulators in
+//               TMEM), 4 per stage; tcgen05.commit releases the stage / publishes the accumulator
+//   warps 2..5  epilogue: tcgen05.ld 32x32b -> registers -> global, overlapped with the next
+//               tile's main loop through two 256-column TMEM accumulators
+// The unsigned/signed choice per operand is a bit of the instruction descriptor, so the u8 x s8
+// and s8 x s8 products need neither the sign flip nor the 128*sum(B) correction of the CPU code.
+// B given as [K,N] is consumed in place through an MN-major shared-memory descriptor: the
+// transpose the CPU lowering performs (ConvertSimpToMemRef.cpp:3168-3216) does not exist here.
+// Out-of-range parts of edge tiles are zero-filled by TMA and masked at the store.
+// Shapes whose operand rows are not 16-byte multiples (a TMA requirement) run the dp4a kernel.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace simp {
+
+using namespace ptx;
+
+constexpr int BM = 128, BN = 256, BK = 128;  // BK in bytes == elements
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * BK;            // 16 KB
+constexpr int B_BYTES = BN * BK;            // 32 KB
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int GEMM_THREADS = 192;
+constexpr int TMEM_COLS = 512;
+constexpr size_t GEMM_SMEM = size_t(STAGES) * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+
+struct GemmParams {
+  int M, N, K;
+  int tiles_m, tiles_n, num_kb;
+  int b_mn_major;   // 1: B is [K,N] (N contiguous), 0: B is [N,K]
+  uint32_t idesc;
+  int32_t* C;
+  int* status;
+};
+
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
+  // groups of 16 row-tiles, column-major inside a group: one wave of CTAs touches a compact block
+  constexpr int G = 16;
+  const int per_group = G * tiles_n;
+  const int group = tile / per_group;
+  const int first_m = group * G;
+  const int gsz = min(G, tiles_m - first_m);
+  const int in_group = tile - group * per_group;
+  tm = first_m + in_group % gsz;
+  tn = in_group / gsz;
+}
+
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+    gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                           const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bar_base = smem_base + STAGES * STAGE_BYTES;
+  // barrier layout (8 bytes each): full[STAGES], empty[STAGES], tfull[2], tempty[2]; then tmem slot, abort flag
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+  uint8_t* bar_generic = smem_raw + (bar_base - smem_u32(smem_raw));
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_generic + 8 * (2 * STAGES + 4));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_generic + 8 * (2 * STAGES + 4) + 8);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_tiles = p.tiles_m * p.tiles_n;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull_bar(a), 1);
+      mbar_init(tempty_bar(a), 4);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    prefetch_tensormap(&tmap_a);
+    prefetch_tensormap(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int tm, tn;
+        tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+        const int m0 = tm * BM, n0 = tn * BN;
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, 1)) { ok = false; break; }
+          const uint32_t sa = smem_base + stage * STAGE_BYTES;
+          const uint32_t sb = sa + A_BYTES;
+          mbar_arrive_expect_tx(full_bar(stage), STAGE_BYTES);
+          tma_load_2d(sa, &tmap_a, full_bar(stage), kb * BK, m0);
+          if (p.b_mn_major) {
+            tma_load_2d(sb, &tmap_b, full_bar(stage), n0, kb * BK);
+            tma_load_2d(sb + B_BYTES / 2, &tmap_b, full_bar(stage), n0 + 128, kb * BK);
+          } else {
+            tma_load_2d(sb, &tmap_b, full_bar(stage), kb * BK, n0);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok) {
+        // let copies already in flight land before the CTA retires (bounded)
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      const uint32_t b_lbo = p.b_mn_major ? uint32_t(B_BYTES / 2) : 16u;
+      const uint32_t b_kstep = p.b_mn_major ? (32u * 128u) >> 4 : 32u >> 4;  // descriptor units of 16 B
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, 2)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + uint32_t(acc * BN);
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, 3)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t sa = smem_base + stage * STAGE_BYTES;
+          const uint32_t sb = sa + A_BYTES;
+          const uint64_t a_desc = make_smem_desc_sw128(sa, 16u, 1024u);
+          const uint64_t b_desc = make_smem_desc_sw128(sb, b_lbo, 1024u);
+#pragma unroll
+          for (int j = 0; j < BK / 32; ++j) {
+            mma_i8_ss(d_tmem, a_desc + uint64_t(j * 2), b_desc + uint64_t(j) * b_kstep, p.idesc,
+                      (kb | j) != 0 ? 1u : 0u);
+          }
+          mma_commit(empty_bar(stage));
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        mma_commit(tfull_bar(acc));
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;  // TMEM lane quarter this warp may access
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    const bool vec_ok = (p.N % 4) == 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+      int tm, tn;
+      tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+      if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, 4)) break;
+      tc_fence_after_sync();
+      const int row = tm * BM + q * 32 + lane;
+      const int n0 = tn * BN;
+      int32_t* crow = p.C + int64_t(row) * p.N + n0;
+#pragma unroll 1
+      for (int ch = 0; ch < BN / 32; ++ch) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + (uint32_t(q * 32) << 16) + uint32_t(acc * BN + ch * 32), r);
+        tmem_ld_wait();
+        const int c0 = n0 + ch * 32;
+        if (row < p.M && c0 < p.N) {
+          if (vec_ok && c0 + 32 <= p.N) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              *reinterpret_cast<int4*>(crow + ch * 32 + 4 * j) =
+                  make_int4(int(r[4 * j]), int(r[4 * j + 1]), int(r[4 * j + 2]), int(r[4 * j + 3]));
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (c0 + j < p.N) crow[ch * 32 + j] = int(r[j]);
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar(acc));
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Integer dot-product kernel for shapes TMA cannot address (operand rows not 16-byte multiples)
+// and for tiny problems.  64x64 tile, K step 32, dp4a with per-operand signedness.
+template <bool A_UNSIGNED>
+__global__ void __launch_bounds__(256) gemm_i8_dp4a_kernel(const uint8_t* __restrict__ A, const int8_t* __restrict__ B,
+                                                           int32_t* __restrict__ C, int64_t M, int64_t K, int64_t N,
+                                                           int b_t) {
+  __shared__ uint32_t As[64][9];
+  __shared__ uint32_t Bs[64][9];
+  uint8_t* As8 = reinterpret_cast<uint8_t*>(&As[0][0]);
+  uint8_t* Bs8 = reinterpret_cast<uint8_t*>(&Bs[0][0]);
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  const int64_t m0 = int64_t(blockIdx.y) * 64, n0 = int64_t(blockIdx.x) * 64;
+  int32_t acc[4][4] = {};
+  for (int64_t p0 = 0; p0 < K; p0 += 32) {
+    for (int e = threadIdx.x; e < 64 * 32; e += 256) {
+      {
+        const int r = e >> 5, c = e & 31;
+        const int64_t gi = m0 + r, gp = p0 + c;
+        As8[r * 36 + c] = (gi < M && gp < K) ? A[gi * K + gp] : uint8_t(0);
+      }
+      if (b_t) {
+        const int r = e >> 5, c = e & 31;
+        const int64_t gj = n0 + r, gp = p0 + c;
+        Bs8[r * 36 + c] = (gj < N && gp < K) ? uint8_t(B[gj * K + gp]) : uint8_t(0);
+      } else {
+        const int c = e >> 6, r = e & 63;
+        const int64_t gj = n0 + r, gp = p0 + c;
+        Bs8[r * 36 + c] = (gj < N && gp < K) ? uint8_t(B[gp * N + gj]) : uint8_t(0);
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+      uint32_t a[4], b[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        a[u] = As[ty * 4 + u][w];
+        b[u] = Bs[tx * 4 + u][w];
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          if (A_UNSIGNED)
+            asm("dp4a.u32.s32 %0, %1, %2, %0;" : "+r"(acc[u][v]) : "r"(a[u]), "r"(b[v]));
+          else
+            asm("dp4a.s32.s32 %0, %1, %2, %0;" : "+r"(acc[u][v]) : "r"(a[u]), "r"(b[v]));
+        }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int u = 0; u < 4; ++u)
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+      const int64_t gi = m0 + ty * 4 + u, gj = n0 + tx * 4 + v;
+      if (gi < M && gj < N) C[gi * N + gj] = acc[u][v];
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  }
+  return fn;
+}
+
+// 2-D u8 tensor map: `inner` contiguous bytes per row, `outer` rows, 128-byte swizzle.
+static int make_map_u8(CUtensorMap* map, const void* base, int64_t inner, int64_t outer, int box_inner,
+                       int box_outer) {
+  EncodeTiledFn enc = get_encode_fn();
+  SIMP_REQUIRE(enc != nullptr, SIMP_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
+  cuuint64_t dims[2] = {cuuint64_t(inner), cuuint64_t(outer)};
+  cuuint64_t strides[1] = {cuuint64_t(inner)};
+  cuuint32_t box[2] = {cuuint32_t(box_inner), cuuint32_t(box_outer)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  SIMP_REQUIRE(r == CUDA_SUCCESS, SIMP_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", int(r));
+  return SIMP_OK;
+}
+
+}  // namespace simp
+
+using namespace simp;
+
+SIMP_API int simp_gpu_matmul_i8(const void* A, const int8_t* B, int32_t* C, int64_t M, int64_t K, int64_t N,
+                                int a_unsigned, int b_transposed) {
+  if (int rc = ensure_ready()) return rc;
+  SIMP_REQUIRE(M >= 0 && K >= 0 && N >= 0, SIMP_ERR_ARG, "matmul_i8: negative size");
+  if (M == 0 || N == 0) return SIMP_OK;
+  SIMP_REQUIRE(A && B && C, SIMP_ERR_ARG, "matmul_i8: null pointer");
+  SIMP_REQUIRE(M <= 0x7fffffff && N <= 0x7fffffff && K <= 0x7fffffff, SIMP_ERR_SHAPE, "matmul_i8: dimension too large");
+  cudaStream_t st = ctx().stream;
+  if (K == 0) {
+    SIMP_CUDA(cudaMemsetAsync(C, 0, size_t(M) * size_t(N) * sizeof(int32_t), st));
+    return SIMP_OK;
+  }
+  const bool a16 = (reinterpret_cast<uintptr_t>(A) & 15u) == 0, b16 = (reinterpret_cast<uintptr_t>(B) & 15u) == 0;
+  const bool tma_ok = a16 && b16 && (K % 16 == 0) && (b_transposed ? true : (N % 16 == 0)) &&
+                      ((reinterpret_cast<uintptr_t>(C) & 15u) == 0);
+  // The tensor-core kernel pays a fixed pipeline fill per tile; tiny problems stay on dp4a.
+  const bool tiny = M * N * K < int64_t(64) * 64 * 64;
+  if (tma_ok && !tiny) {
+    CUtensorMap ma, mb;
+    if (int rc = make_map_u8(&ma, A, K, M, BK, BM)) return rc;
+    if (b_transposed) {
+      if (int rc = make_map_u8(&mb, B, K, N, BK, BN)) return rc;
+    } else {
+      if (int rc = make_map_u8(&mb, B, N, K, 128, BK)) return rc;
+    }
+    GemmParams p;
+    p.M = int(M); p.N = int(N); p.K = int(K);
+    p.tiles_m = int(cdiv(M, BM)); p.tiles_n = int(cdiv(N, BN)); p.num_kb = int(cdiv(K, BK));
+    p.b_mn_major = b_transposed ? 0 : 1;
+    p.idesc = make_idesc_i8(BM, BN, /*a_signed=*/!a_unsigned, /*b_signed=*/true, false, !b_transposed);
+    p.C = C;
+    p.status = ctx().dev_status;
+    static bool attr_set = false;
+    if (!attr_set) {
+      SIMP_CUDA(cudaFuncSetAttribute(gemm_i8_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     int(GEMM_SMEM)));
+      attr_set = true;
+    }
+    const int64_t tiles = int64_t(p.tiles_m) * p.tiles_n;
+    SIMP_REQUIRE(tiles <= 0x7fffffff, SIMP_ERR_SHAPE, "matmul_i8: too many tiles");
+    const int grid = int(tiles < ctx().sm_count ? tiles : ctx().sm_count);
+    gemm_i8_tcgen05_kernel<<<grid, GEMM_THREADS, GEMM_SMEM, st>>>(ma, mb, p);
+  } else {
+    const int64_t gx = cdiv(N, 64), gy = cdiv(M, 64);
+    SIMP_REQUIRE(gy <= 65535, SIMP_ERR_SHAPE, "matmul_i8: M too large for the dp4a kernel");
+    dim3 grid{unsigned(gx), unsigned(gy)};
+    if (a_unsigned)
+      gemm_i8_dp4a_kernel<true><<<grid, 256, 0, st>>>(static_cast<const uint8_t*>(A), B, C, M, K, N, b_transposed);
+    else
+      gemm_i8_dp4a_kernel<false><<<grid, 256, 0, st>>>(static_cast<const uint8_t*>(A), B, C, M, K, N, b_transposed);
+  }
+  SIMP_LAUNCH_CHECK();
+  return SIMP_OK;
+}

@@ -1,0 +1,72 @@
+"""GPU parity: simp.matmul / tensor_matmul on f32 vs the CPU oracle.
+
+Tolerance (north star): max relative error 1e-4, taken against the row's scale
+sum_p |A[i,p]*B[p,j]| (the natural bound for a dot product whose summation order differs), and
+checked against an f64 product as well as the sequential-f32 oracle.
+"""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def check(gpu_out, A, B, ref32):
+    A64, B64 = A.astype(np.float64), B.astype(np.float64)
+    exact = A64 @ B64
+    scale = np.abs(A64) @ np.abs(B64) + 1e-30
+    assert np.max(np.abs(gpu_out - exact) / scale) <= 1e-4
+    assert np.max(np.abs(gpu_out - ref32) / scale) <= 1e-4
+
+
+@pytest.mark.parametrize("m,k", [(768, 768), (2048, 768), (768, 2048), (32000, 768), (3200, 8640), (5, 12), (33, 770),
+                                 (1, 4), (100, 3)])
+@pytest.mark.parametrize("accumulate", [True, False])
+def test_gemv(gpu, oracle, m, k, accumulate):
+    rng = np.random.default_rng(m + k)
+    aoff, coff = 8, 3
+    A = (0.02 * rng.standard_normal(aoff + m * k)).astype(np.float32)
+    x = rng.standard_normal(k).astype(np.float32)
+    c0 = rng.standard_normal(coff + m).astype(np.float32)
+    dA, dx, dC = (gpu.DeviceBuffer.from_numpy(a) for a in (A, x, c0))
+    gpu.matmul_f32(dA, aoff, dx, 0, dC, coff, m, k, 1, accumulate=accumulate)
+    out = dC.to_numpy(np.float32, coff + m)
+    assert np.array_equal(out[:coff], c0[:coff])
+    ref = c0.copy()
+    if not accumulate:
+        ref[coff:] = 0
+    oracle.matmul_f32(A, aoff, x, 0, ref, coff, m, k, 1, threads=0)
+    base = c0[coff:] if accumulate else 0
+    Am = A[aoff:].reshape(m, k)
+    check((out[coff:] - base)[:, None], Am, x[:, None], (ref[coff:] - base)[:, None])
+
+
+@pytest.mark.parametrize("m,k,n", [(64, 64, 64), (100, 37, 53), (4, 3, 2), (2, 2, 2), (512, 768, 96), (1, 300, 200)])
+@pytest.mark.parametrize("b_t", [False, True])
+def test_gemm_tile(gpu, oracle, m, k, n, b_t):
+    rng = np.random.default_rng(m * k + n)
+    A = rng.standard_normal((m, k)).astype(np.float32)
+    B = rng.standard_normal((k, n)).astype(np.float32)
+    Bg = np.ascontiguousarray(B.T) if b_t else B
+    dA, dB = gpu.DeviceBuffer.from_numpy(A), gpu.DeviceBuffer.from_numpy(Bg)
+    dC = gpu.DeviceBuffer(m * n * 4)
+    gpu.matmul_f32(dA, 0, dB, 0, dC, 0, m, k, n, accumulate=False, b_transposed=b_t)
+    out = dC.to_numpy(np.float32, (m, n))
+    check(out, A, B, oracle.tensor_matmul_f32(A, Bg, b_transposed=b_t))
+
+
+def test_known_answers(gpu):
+    # tests/mlir/integration/test_matmul_simple.sl:24-27: [[1,2],[3,4]] x [[5,6],[7,8]] -> C[0,0] = 19
+    A = np.array([[1, 2], [3, 4]], np.float32)
+    B = np.array([[5, 6], [7, 8]], np.float32)
+    dA, dB = gpu.DeviceBuffer.from_numpy(A), gpu.DeviceBuffer.from_numpy(B)
+    dC = gpu.DeviceBuffer(16)
+    dC.zero()
+    gpu.matmul_f32(dA, 0, dB, 0, dC, 0, 2, 2, 2, accumulate=True)
+    assert dC.to_numpy(np.float32, (2, 2))[0, 0] == 19.0
+    # tests/test_tensor_matmul.sl:4-65: A[i,j] = i*3+j+1 (4x3), B[i,j] = i*2+j+1 (3x2) -> C[0,0] = 22
+    A = (np.arange(12, dtype=np.float32) + 1).reshape(4, 3)
+    B = (np.arange(6, dtype=np.float32) + 1).reshape(3, 2)
+    dA, dB = gpu.DeviceBuffer.from_numpy(A), gpu.DeviceBuffer.from_numpy(B)
+    dC = gpu.DeviceBuffer(32)
+    gpu.matmul_f32(dA, 0, dB, 0, dC, 0, 4, 3, 2, accumulate=False)
+    assert dC.to_numpy(np.float32, (4, 2))[0, 0] == 22.0
