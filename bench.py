@@ -1,0 +1,322 @@
+#!/usr/bin/env python
+"""bench.py -- headline benchmark of the B200 back end for SimpLang's tensor hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--size S]
+
+Metric: int8 GEMM throughput (TOPS = 2*M*N*K / t / 1e12) of `tensor_matmul` on
+u8[M,K] x s8[K,N] -> i32[M,N], M = N = K = 8192, seeded uniform inputs -- the upper end of the
+reference's "INT8 tensor_matmul" sweep and the largest single-GPU cube the metric is quoted on.
+A step is one GEMM over device-resident operands (384 MB touched per step, larger than the 126 MB
+L2, so no flush is needed between steps).  At N > 1 the columns of B are sharded over the ranks
+(N/R columns each, A replicated) and the shards of C are all-gathered over NCCL: total work is
+fixed, so scaling is "strong".
+
+Prints ONE JSON line (rank 0).  `value` is the device-timed throughput (CUDA events on the stream the
+kernel runs on, max over ranks); `e2e` is the same metric through the host-pointer entry point
+(simp_host_tensor_matmul_i8: pinned host operands in, host result out, copies inside the timed
+region); `roofline` reports the tensor-core kernel against the calibrated int8 peak; `cpu_baseline`
+is the reference's own OpenMP VNNI kernel timed on this machine's host cores.
+
+`--impl reference` times only that CPU kernel (the reference has no GPU code).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+NOMINAL_INT8_TOPS = 4500.0  # B200 dense int8, vendor figure
+# dram__bytes_read.sum + dram__bytes_write.sum of one gemm_i8_tcgen05_kernel launch at 8192^3,
+# from the ncu capture summarised in profiles/gemm_i8_tcgen05_8192.md (null until captured).
+NCU_TRAFFIC_BYTES = {8192: None}
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"], "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks / throttle reasons while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index):
+        self.idx = device_index
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.idx)],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, power, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2])); power.append(float(f[3]))
+            except ValueError:
+                continue
+            for name, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        # "under load" = samples in the upper half of the power range seen
+        thr = (max(power) + min(power)) / 2
+        loaded = [s for s, p in zip(sm, power) if p >= thr] or sm
+        return {"sm_mhz": statistics.median(loaded), "sm_max_mhz": max(mx), "power_w_max": max(power),
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def gen_inputs(M, K, N, seed_a=1, seed_b=2, a_unsigned=True):
+    rng_a, rng_b = np.random.default_rng(seed_a), np.random.default_rng(seed_b)
+    if a_unsigned:
+        A = rng_a.integers(0, 256, (M, K), dtype=np.uint8)
+    else:
+        A = rng_a.integers(-128, 128, (M, K), dtype=np.int8)
+    B = rng_b.integers(-128, 128, (K, N), dtype=np.int8)
+    return A, B
+
+
+# --------------------------------------------------------------------------------------------- CPU legs
+def cpu_reference_gemm(n, repeats, warmup):
+    """Times the reference's own OpenMP VNNI GEMM (oracle/_ref, compiled from the reference checkout;
+    s8 x s8 with B pre-transposed) or, when AVX512-VNNI / the prebuilt object is missing, the oracle's
+    OpenMP restatement on a smaller cube.  Returns (tops, description, kind, cores)."""
+    import oracle
+    cores = oracle.lib().simp_oracle_max_threads()
+    rng = np.random.default_rng(3)
+    if oracle.ref("multicore") is not None:
+        A = rng.integers(-128, 128, (n, n), dtype=np.int8)
+        Bt = rng.integers(-128, 128, (n, n), dtype=np.int8)
+        for _ in range(warmup):
+            oracle.ref_vnni_square(A, Bt, multicore=True)
+        times = []
+        for _ in range(repeats):
+            t = time.perf_counter()
+            oracle.ref_vnni_square(A, Bt, multicore=True)
+            times.append(time.perf_counter() - t)
+        return 2.0 * n ** 3 / 1e12, times, f"reference vnni_matmul_multicore<{n}> (s8 x s8, B pre-transposed), {n}^3 per step", \
+            "reference", cores
+    n = min(n, 1024)
+    A = rng.integers(-128, 128, (n, n), dtype=np.int8)
+    Bt = rng.integers(-128, 128, (n, n), dtype=np.int8)
+    times = []
+    for i in range(warmup + repeats):
+        t = time.perf_counter()
+        oracle.tensor_matmul_i8(A, Bt, b_transposed=True, threads=0)
+        if i >= warmup:
+            times.append(time.perf_counter() - t)
+    return 2.0 * n ** 3 / 1e12, times, f"oracle OpenMP scalar loop (no AVX512-VNNI here), {n}^3 per step", "port", cores
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    n = 4096 if args.size >= 4096 else args.size
+    tera_ops, times, sample, kind, cores = cpu_reference_gemm(n, args.steps, args.warmup)
+    total = sum(times)
+    value = tera_ops * len(times) / total
+    line = {
+        "impl": "reference", "metric": "int8_gemm_tops", "value": value, "unit": "TOPS", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / len(times),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
+        "config": {"workload": f"int8 tensor_matmul {args.size}^3 u8 x s8 -> i32 (CPU arm: bounded sample, see cpu_baseline.sample)"},
+        "cpu_baseline": {"value": value, "unit": "TOPS", "cores": cores, "kind": kind, "sample": sample},
+        "e2e": {"value": value, "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------------------------- GPU arm
+def run_ours(args):
+    import simplang_b200 as sg
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    sg.init(local_rank)
+
+    S = args.size
+    M = K = N = S
+    assert N % world == 0 and (N // world) % 16 == 0, "N must split into 16-column multiples per rank"
+    Nl = N // world
+    A, B = gen_inputs(M, K, N)
+    B_local = np.ascontiguousarray(B[:, rank * Nl:(rank + 1) * Nl])
+
+    if world == 1:
+        dA, dB = sg.DeviceBuffer.from_numpy(A), sg.DeviceBuffer.from_numpy(B_local)
+        dC = sg.DeviceBuffer(M * Nl * 4)
+        a_ptr, b_ptr, c_ptr = dA.ptr, dB.ptr, dC.ptr
+
+        def step():
+            sg.matmul_i8(a_ptr, b_ptr, c_ptr, M, K, Nl, a_unsigned=True, b_transposed=False)
+    else:
+        import torch
+        ext = torch.cuda.ExternalStream(sg.stream_handle())
+        torch.cuda.set_stream(ext)
+        tA = torch.from_numpy(A).cuda()
+        tB = torch.from_numpy(B_local).cuda()
+        tC_local = torch.empty((M, Nl), dtype=torch.int32, device="cuda")
+        tC_all = torch.empty((world, M, Nl), dtype=torch.int32, device="cuda")  # shard r = C[:, r*Nl:(r+1)*Nl]
+        torch.cuda.synchronize()
+
+        def step():
+            sg.matmul_i8(tA.data_ptr(), tB.data_ptr(), tC_local.data_ptr(), M, K, Nl, a_unsigned=True,
+                         b_transposed=False)
+            dist.all_gather_into_tensor(tC_all, tC_local)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+            import torch
+            torch.cuda.synchronize()
+        sg.sync()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    barrier()
+    e0, e1 = sg.Event(), sg.Event()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    ms_total = e0.elapsed_ms(e1)
+    if dist is not None:
+        import torch
+        t = torch.tensor([ms_total], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+    clocks = sampler.stop() if rank == 0 else None
+    sg.check(sg.lib().simp_gpu_check_device_status())
+
+    ops = 2.0 * M * N * K
+    ms_step = ms_total / args.steps
+    tops = ops / (ms_step * 1e-3) / 1e12
+
+    # quick in-run parity spot check (rows of C against an exact numpy product)
+    if rank == 0:
+        rows = [0, 1, M // 2 + 1, M - 1]
+        if world == 1:
+            Cg = dC.to_numpy(np.int32, (M, Nl))[rows]
+        else:
+            Cg = tC_local[rows].cpu().numpy()
+        exact = (A[rows].astype(np.int64) @ B_local.astype(np.int64)).astype(np.int32)
+        if not np.array_equal(Cg, exact):
+            raise SystemExit("bench: GPU result differs from the exact product -- refusing to report a number")
+
+    # ---- e2e through the host-pointer entry point (every rank computes its shard; max over ranks)
+    hA = sg.pinned_empty((M, K), np.uint8); hA[...] = A
+    hB = sg.pinned_empty((K, Nl), np.int8); hB[...] = B_local
+    hC = sg.pinned_empty((M, Nl), np.int32)
+    e2e_steps = max(2, min(args.steps, 5))
+    sg.host_tensor_matmul_i8(hA, hB, hC)  # warm-up (allocates staging)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        sg.host_tensor_matmul_i8(hA, hB, hC)
+    t_e2e = (time.perf_counter() - t0) / e2e_steps
+    if dist is not None:
+        import torch
+        t = torch.tensor([t_e2e], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        t_e2e = float(t.item())
+    e2e_tops = ops / t_e2e / 1e12
+
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    peaks = measured_peaks()
+    peak_int8 = 2.0 * peaks["bf16_tflops"]
+    line = {
+        "metric": "int8_gemm_tops", "value": tops, "unit": "TOPS", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "u8", "data": "synthetic",
+        "config": {"workload": f"int8 tensor_matmul {S}^3: u8[M,K] x s8[K,N] -> i32, seeded uniform, row-major",
+                   "sharding": "single GPU" if world == 1 else f"N-sharded over {world} ranks + NCCL all-gather of C",
+                   "l2": "384 MB touched per step at 8192^3 (> 126 MB L2): no flush between steps"},
+        "clocks": clocks,
+        "e2e": {"value": e2e_tops, "unit": "TOPS", "h2d_bytes_per_step": int(M * K + K * Nl) * world,
+                "d2h_bytes_per_step": int(4 * M * Nl) * world, "ms_per_step": 1e3 * t_e2e, "steps": e2e_steps,
+                "api": "simp_host_tensor_matmul_i8 (pinned host operands, chunked upload/compute/download)"},
+        "gpu_launches": args.steps,
+        "roofline": {"bound": "tensor", "achieved": tops / world, "peak": peak_int8, "unit": "TOP/s",
+                     "frac": tops / world / peak_int8,
+                     "peak_basis": f"2 x cuBLAS bf16 burst ({peaks['bf16_tflops']} TFLOP/s, {peaks['source']}); "
+                                   "int8 MMA issues at twice the bf16 rate",
+                     "frac_of_nominal_4500": tops / world / NOMINAL_INT8_TOPS,
+                     "traffic": NCU_TRAFFIC_BYTES.get(S), "algorithmic_bytes": int(M * K + K * N + 4 * M * N),
+                     "kernel": "gemm_i8_tcgen05_kernel"},
+    }
+    if world == 1 and not args.no_cpu:
+        tera, times, sample, kind, cores = cpu_reference_gemm(min(S, 8192), 2, 1)
+        line["cpu_baseline"] = {"value": tera / min(times), "unit": "TOPS", "cores": cores, "kind": kind,
+                                "sample": sample + ", best of 2 after 1 warm-up"}
+    print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--size", type=int, default=8192)
+    ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

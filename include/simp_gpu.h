@@ -115,6 +115,41 @@ int simp_gpu_silu_f32(const float* x_dev, const float* mul_dev, float* y_dev, in
 int simp_gpu_quantize_i8(const float* x_dev, int8_t* y_dev, int64_t n, float scale, int clamp);
 int simp_gpu_dequantize_i32(const int32_t* acc_dev, float* y_dev, int64_t n, float divisor);
 
+/* ---- pinned host memory, resident operands, timing -----------------------------------------
+ * Replaces: the hosts' std::vector buffers and chrono timing (runtime/src/host.cpp:96-148).
+ * simp_gpu_register_host uploads [host, host+bytes) once; afterwards any simp_host_* call that is
+ * given a pointer inside that range uses the device copy instead of copying again (how the model
+ * weights of examples/llama2/generate_stories110M.cpp:142-202 stay resident between tokens). */
+int simp_gpu_host_alloc(void** hptr, size_t bytes);
+int simp_gpu_host_free(void* hptr);
+int simp_gpu_register_host(const void* host, size_t bytes);
+int simp_gpu_unregister_host(const void* host);
+int simp_gpu_event_create(void** event);
+int simp_gpu_event_record(void* event);                      /* on the library stream          */
+int simp_gpu_event_elapsed_ms(void* start, void* stop, float* ms);
+int simp_gpu_event_destroy(void* event);
+
+/* ---- the same ops on HOST pointers ---------------------------------------------------------
+ * What a compiled .sl kernel's host sees today: plain host arrays in, results in host arrays on
+ * return (hosts: simptensor/benchmarks/bench_prefill_matmul_runner.cpp:18-23, 77-120;
+ * examples/llama2/bench_llama_quant.cpp:10-28).  Each call copies operands that are not registered
+ * to the device, runs the device op declared above with the same arguments, and copies the result
+ * back.  The int8 GEMM pipelines upload / compute / download over row chunks of A. */
+int simp_host_tensor_matmul_i8(const void* A, const int8_t* B, int32_t* C, int64_t M, int64_t K,
+                               int64_t N, int a_unsigned, int b_transposed);
+int simp_host_matmul_f32(const float* A, int64_t aoff, const float* B, int64_t boff, float* C,
+                         int64_t coff, int64_t m, int64_t k, int64_t n, int accumulate,
+                         int b_transposed);
+int simp_host_matmul_quant(const uint8_t* qweights, size_t qweights_bytes, const float* scales,
+                           const float* zeros, size_t n_groups, const float* x, float* out,
+                           int64_t rows, int64_t cols, int64_t group_size, int64_t offset,
+                           int scale_mode);
+int simp_host_rmsnorm_f32(const float* x, const float* w, float* y, int64_t rows, int64_t n,
+                          float eps, int64_t woff);
+int simp_host_softmax_f32(const float* x, float* y, int64_t rows, int64_t n, int64_t xoff,
+                          int64_t yoff, int64_t row_stride);
+int simp_host_silu_f32(const float* x, const float* mul, float* y, int64_t n);
+
 #ifdef __cplusplus
 }
 #endif

@@ -46,6 +46,20 @@ _SIGNATURES = {
     "simp_gpu_silu_f32": [vp, vp, vp, i64],
     "simp_gpu_quantize_i8": [vp, vp, i64, C.c_float, C.c_int],
     "simp_gpu_dequantize_i32": [vp, vp, i64, C.c_float],
+    "simp_gpu_host_alloc": [C.POINTER(vp), C.c_size_t],
+    "simp_gpu_host_free": [vp],
+    "simp_gpu_register_host": [vp, C.c_size_t],
+    "simp_gpu_unregister_host": [vp],
+    "simp_gpu_event_create": [C.POINTER(vp)],
+    "simp_gpu_event_record": [vp],
+    "simp_gpu_event_elapsed_ms": [vp, vp, C.POINTER(C.c_float)],
+    "simp_gpu_event_destroy": [vp],
+    "simp_host_tensor_matmul_i8": [vp, vp, vp, i64, i64, i64, C.c_int, C.c_int],
+    "simp_host_matmul_f32": [vp, i64, vp, i64, vp, i64, i64, i64, i64, C.c_int, C.c_int],
+    "simp_host_matmul_quant": [vp, C.c_size_t, vp, vp, C.c_size_t, vp, vp, i64, i64, i64, i64, C.c_int],
+    "simp_host_rmsnorm_f32": [vp, vp, vp, i64, i64, C.c_float, i64],
+    "simp_host_softmax_f32": [vp, vp, i64, i64, i64, i64, i64],
+    "simp_host_silu_f32": [vp, vp, vp, i64],
 }
 
 
@@ -190,4 +204,55 @@ def np_matmul_i8(A: np.ndarray, B: np.ndarray, b_transposed=False) -> np.ndarray
     matmul_i8(dA, dB, dC, M, K, N, a_unsigned=(A.dtype == np.uint8), b_transposed=b_transposed)
     out = dC.to_numpy(np.int32, (M, N))
     check(lib().simp_gpu_check_device_status())
+    return out
+
+
+# ------------------------------------------------------------------------- timing, pinned memory
+class Event:
+    """CUDA event on the library stream (simp_gpu_event_*)."""
+
+    def __init__(self):
+        p = vp()
+        check(lib().simp_gpu_event_create(C.byref(p)))
+        self.ptr = p.value
+
+    def record(self):
+        check(lib().simp_gpu_event_record(self.ptr))
+        return self
+
+    def elapsed_ms(self, stop: "Event") -> float:
+        ms = C.c_float()
+        check(lib().simp_gpu_event_elapsed_ms(self.ptr, stop.ptr, C.byref(ms)))
+        return float(ms.value)
+
+    def __del__(self):
+        try:
+            lib().simp_gpu_event_destroy(self.ptr)
+        except Exception:
+            pass
+
+
+def pinned_empty(shape, dtype) -> np.ndarray:
+    """numpy array backed by pinned host memory from simp_gpu_host_alloc (kept alive by the array)."""
+    dtype = np.dtype(dtype)
+    n = int(np.prod(shape)) * dtype.itemsize
+    p = vp()
+    check(lib().simp_gpu_host_alloc(C.byref(p), max(n, 16)))
+    buf = (C.c_uint8 * max(n, 16)).from_address(p.value)
+    arr = np.frombuffer(buf, dtype=dtype, count=int(np.prod(shape))).reshape(shape)
+    _PINNED.append((p.value, buf))
+    return arr
+
+
+_PINNED = []
+
+
+# ------------------------------------------------------------------------- host-pointer ops (numpy in, numpy out)
+def host_tensor_matmul_i8(A: np.ndarray, B: np.ndarray, out: np.ndarray = None, b_transposed=False) -> np.ndarray:
+    M, K = A.shape
+    N = B.shape[0] if b_transposed else B.shape[1]
+    if out is None:
+        out = np.empty((M, N), np.int32)
+    check(lib().simp_host_tensor_matmul_i8(A.ctypes.data, B.ctypes.data, out.ctypes.data, M, K, N,
+                                           int(A.dtype == np.uint8), int(b_transposed)))
     return out

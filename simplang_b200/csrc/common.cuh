@@ -14,7 +14,9 @@ namespace simp {
 // ---- per-process state (runtime.cu) ---------------------------------------------------------
 struct Context {
   int device = -1;
-  cudaStream_t stream = nullptr;
+  cudaStream_t stream = nullptr;     // all ops
+  cudaStream_t copy_in = nullptr;    // host->device staging of the host-pointer entry points
+  cudaStream_t copy_out = nullptr;   // device->host staging
   int sm_count = 148;
   int* dev_status = nullptr;   // device word written by bounded waits (0 = ok)
   int* host_status = nullptr;  // pinned mirror for polling

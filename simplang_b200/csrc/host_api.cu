@@ -1,0 +1,272 @@
+// host_api.cu -- the reference-facing layer: entry points that take HOST pointers, as the
+// reference's compiled kernels do (its hosts pass std::vector::data() on every call,
+// examples/llama2/generate_stories110M.cpp:236-251; simptensor/benchmarks/bench_prefill_matmul_runner.cpp:18-23).
+//
+// Operands are copied to the device, the device op runs, results are copied back; the call
+// returns when the results are in host memory.  Long-lived operands (weights) can be registered
+// once with simp_gpu_register_host(): later calls that pass a pointer inside a registered range
+// use the resident device mirror instead of copying.
+// Also here: pinned host memory and CUDA-event timing for the host drivers.
+#include <map>
+#include <mutex>
+#include <vector>
+
+#include "common.cuh"
+
+namespace simp {
+
+struct Mirror {
+  size_t bytes;
+  void* dev;
+};
+static std::map<uintptr_t, Mirror> g_mirrors;  // keyed by host base address
+static std::mutex g_reg_mu;
+
+// Device address mirroring host pointer `h`, or nullptr when `h` is not inside a registered range.
+static void* lookup_mirror(const void* h, size_t bytes) {
+  std::lock_guard<std::mutex> lk(g_reg_mu);
+  const uintptr_t a = reinterpret_cast<uintptr_t>(h);
+  auto it = g_mirrors.upper_bound(a);
+  if (it == g_mirrors.begin()) return nullptr;
+  --it;
+  if (a >= it->first && a + bytes <= it->first + it->second.bytes)
+    return static_cast<uint8_t*>(it->second.dev) + (a - it->first);
+  return nullptr;
+}
+
+// Device copy of a host input: the registered mirror, or a staged copy in arena `slot`.
+static int stage_in(const void* h, size_t bytes, int slot, cudaStream_t st, void** dev) {
+  if (void* m = lookup_mirror(h, bytes)) {
+    *dev = m;
+    return SIMP_OK;
+  }
+  void* d = scratch(bytes ? bytes : 16, slot);
+  SIMP_REQUIRE(d != nullptr, SIMP_ERR_CUDA, "out of device memory staging %zu bytes", bytes);
+  if (bytes) SIMP_CUDA(cudaMemcpyAsync(d, h, bytes, cudaMemcpyHostToDevice, st));
+  *dev = d;
+  return SIMP_OK;
+}
+
+}  // namespace simp
+
+using namespace simp;
+
+// ---- pinned memory, registration, events ------------------------------------------------------
+SIMP_API int simp_gpu_host_alloc(void** hptr, size_t bytes) {
+  SIMP_REQUIRE(hptr != nullptr, SIMP_ERR_ARG, "host_alloc: null pointer");
+  if (int rc = ensure_ready()) return rc;
+  SIMP_CUDA(cudaMallocHost(hptr, bytes ? bytes : 16));
+  return SIMP_OK;
+}
+SIMP_API int simp_gpu_host_free(void* hptr) {
+  if (!hptr) return SIMP_OK;
+  SIMP_CUDA(cudaFreeHost(hptr));
+  return SIMP_OK;
+}
+SIMP_API int simp_gpu_register_host(const void* host, size_t bytes) {
+  SIMP_REQUIRE(host != nullptr && bytes > 0, SIMP_ERR_ARG, "register_host: null pointer or empty range");
+  if (int rc = ensure_ready()) return rc;
+  void* d = nullptr;
+  SIMP_CUDA(cudaMalloc(&d, bytes));
+  SIMP_CUDA(cudaMemcpyAsync(d, host, bytes, cudaMemcpyHostToDevice, ctx().stream));
+  SIMP_CUDA(cudaStreamSynchronize(ctx().stream));
+  std::lock_guard<std::mutex> lk(g_reg_mu);
+  auto old = g_mirrors.find(reinterpret_cast<uintptr_t>(host));
+  if (old != g_mirrors.end()) {
+    cudaFree(old->second.dev);
+    g_mirrors.erase(old);
+  }
+  g_mirrors[reinterpret_cast<uintptr_t>(host)] = Mirror{bytes, d};
+  return SIMP_OK;
+}
+SIMP_API int simp_gpu_unregister_host(const void* host) {
+  std::lock_guard<std::mutex> lk(g_reg_mu);
+  auto it = g_mirrors.find(reinterpret_cast<uintptr_t>(host));
+  SIMP_REQUIRE(it != g_mirrors.end(), SIMP_ERR_ARG, "unregister_host: pointer was not registered");
+  cudaStreamSynchronize(ctx().stream);
+  cudaFree(it->second.dev);
+  g_mirrors.erase(it);
+  return SIMP_OK;
+}
+SIMP_API int simp_gpu_event_create(void** ev) {
+  SIMP_REQUIRE(ev != nullptr, SIMP_ERR_ARG, "event_create: null pointer");
+  if (int rc = ensure_ready()) return rc;
+  cudaEvent_t e;
+  SIMP_CUDA(cudaEventCreate(&e));
+  *ev = e;
+  return SIMP_OK;
+}
+SIMP_API int simp_gpu_event_record(void* ev) {
+  SIMP_REQUIRE(ev != nullptr, SIMP_ERR_ARG, "event_record: null event");
+  SIMP_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(ev), ctx().stream));
+  return SIMP_OK;
+}
+SIMP_API int simp_gpu_event_elapsed_ms(void* start, void* stop, float* ms) {
+  SIMP_REQUIRE(start && stop && ms, SIMP_ERR_ARG, "event_elapsed_ms: null pointer");
+  SIMP_CUDA(cudaEventSynchronize(static_cast<cudaEvent_t>(stop)));
+  SIMP_CUDA(cudaEventElapsedTime(ms, static_cast<cudaEvent_t>(start), static_cast<cudaEvent_t>(stop)));
+  return SIMP_OK;
+}
+SIMP_API int simp_gpu_event_destroy(void* ev) {
+  if (ev) SIMP_CUDA(cudaEventDestroy(static_cast<cudaEvent_t>(ev)));
+  return SIMP_OK;
+}
+
+// ---- host-pointer ops -------------------------------------------------------------------------
+// tensor_matmul on i8 with host operands.  Rows of A are processed in chunks so that the upload of
+// chunk c+1, the GEMM of chunk c and the download of chunk c-1 overlap on three streams.
+SIMP_API int simp_host_tensor_matmul_i8(const void* A, const int8_t* B, int32_t* C, int64_t M, int64_t K,
+                                        int64_t N, int a_unsigned, int b_transposed) {
+  if (int rc = ensure_ready()) return rc;
+  SIMP_REQUIRE(M >= 0 && K >= 0 && N >= 0, SIMP_ERR_ARG, "host tensor_matmul_i8: negative size");
+  if (M == 0 || N == 0) return SIMP_OK;
+  SIMP_REQUIRE(A && B && C, SIMP_ERR_ARG, "host tensor_matmul_i8: null pointer");
+  Context& c = ctx();
+  void *dA = nullptr, *dB = nullptr;
+  const bool a_resident = lookup_mirror(A, size_t(M) * K) != nullptr;
+  if (int rc = stage_in(B, size_t(K) * N, 1, c.copy_in, &dB)) return rc;
+  int32_t* dC = static_cast<int32_t*>(scratch(size_t(M) * N * 4, 2));
+  SIMP_REQUIRE(dC != nullptr, SIMP_ERR_CUDA, "out of device memory for C");
+  if (a_resident) dA = lookup_mirror(A, size_t(M) * K);
+  else {
+    dA = scratch(size_t(M) * K + 16, 0);
+    SIMP_REQUIRE(dA != nullptr, SIMP_ERR_CUDA, "out of device memory for A");
+  }
+  int64_t chunk = ((cdiv(M, 8) + 127) / 128) * 128;
+  if (M * N * 4 < (int64_t(8) << 20)) chunk = M;  // small results: one piece
+  const int nchunks = int(cdiv(M, chunk));
+  std::vector<cudaEvent_t> ev_in(nchunks), ev_done(nchunks);
+  cudaEvent_t ev_b;
+  SIMP_CUDA(cudaEventCreateWithFlags(&ev_b, cudaEventDisableTiming));
+  SIMP_CUDA(cudaEventRecord(ev_b, c.copy_in));
+  SIMP_CUDA(cudaStreamWaitEvent(c.stream, ev_b, 0));
+  int rc = SIMP_OK;
+  for (int i = 0; i < nchunks && rc == SIMP_OK; ++i) {
+    const int64_t r0 = i * chunk, rows = (r0 + chunk <= M) ? chunk : M - r0;
+    cudaEventCreateWithFlags(&ev_in[i], cudaEventDisableTiming);
+    cudaEventCreateWithFlags(&ev_done[i], cudaEventDisableTiming);
+    const uint8_t* a_dev = static_cast<const uint8_t*>(dA) + r0 * K;
+    if (!a_resident)
+      cudaMemcpyAsync(const_cast<uint8_t*>(a_dev), static_cast<const uint8_t*>(A) + r0 * K, size_t(rows) * K,
+                      cudaMemcpyHostToDevice, c.copy_in);
+    cudaEventRecord(ev_in[i], c.copy_in);
+    cudaStreamWaitEvent(c.stream, ev_in[i], 0);
+    rc = simp_gpu_matmul_i8(a_dev, static_cast<const int8_t*>(dB), dC + r0 * N, rows, K, N, a_unsigned, b_transposed);
+    cudaEventRecord(ev_done[i], c.stream);
+    cudaStreamWaitEvent(c.copy_out, ev_done[i], 0);
+    cudaMemcpyAsync(C + r0 * N, dC + r0 * N, size_t(rows) * N * 4, cudaMemcpyDeviceToHost, c.copy_out);
+  }
+  cudaError_t e1 = cudaStreamSynchronize(c.copy_out);
+  cudaError_t e2 = cudaStreamSynchronize(c.stream);
+  for (int i = 0; i < nchunks; ++i) {
+    if (ev_in[i]) cudaEventDestroy(ev_in[i]);
+    if (ev_done[i]) cudaEventDestroy(ev_done[i]);
+  }
+  cudaEventDestroy(ev_b);
+  if (rc != SIMP_OK) return rc;
+  SIMP_REQUIRE(e1 == cudaSuccess && e2 == cudaSuccess, SIMP_ERR_CUDA, "host tensor_matmul_i8: %s",
+               cudaGetErrorString(e1 != cudaSuccess ? e1 : e2));
+  return SIMP_OK;
+}
+
+// simp.matmul with host operands (C is read when accumulating, then written back).
+SIMP_API int simp_host_matmul_f32(const float* A, int64_t aoff, const float* B, int64_t boff, float* C, int64_t coff,
+                                  int64_t m, int64_t k, int64_t n, int accumulate, int b_transposed) {
+  if (int rc = ensure_ready()) return rc;
+  SIMP_REQUIRE(m >= 0 && k >= 0 && n >= 0 && aoff >= 0 && boff >= 0 && coff >= 0, SIMP_ERR_ARG,
+               "host matmul_f32: negative size or offset");
+  if (m == 0 || n == 0) return SIMP_OK;
+  SIMP_REQUIRE(A && B && C, SIMP_ERR_ARG, "host matmul_f32: null pointer");
+  cudaStream_t st = ctx().stream;
+  void *dA, *dB, *dC;
+  if (int rc = stage_in(A + aoff, size_t(m) * k * 4, 0, st, &dA)) return rc;
+  if (int rc = stage_in(B + boff, size_t(k) * n * 4, 1, st, &dB)) return rc;
+  dC = scratch(size_t(m) * n * 4, 2);
+  SIMP_REQUIRE(dC != nullptr, SIMP_ERR_CUDA, "out of device memory for C");
+  if (accumulate) SIMP_CUDA(cudaMemcpyAsync(dC, C + coff, size_t(m) * n * 4, cudaMemcpyHostToDevice, st));
+  if (int rc = simp_gpu_matmul_f32(static_cast<float*>(dA), 0, static_cast<float*>(dB), 0, static_cast<float*>(dC), 0,
+                                   m, k, n, accumulate, b_transposed))
+    return rc;
+  SIMP_CUDA(cudaMemcpyAsync(C + coff, dC, size_t(m) * n * 4, cudaMemcpyDeviceToHost, st));
+  SIMP_CUDA(cudaStreamSynchronize(st));
+  return SIMP_OK;
+}
+
+// matmul_quant with host operands.  qweights/scales/zeros are normally registered (resident).
+SIMP_API int simp_host_matmul_quant(const uint8_t* qw, size_t qw_bytes, const float* sc, const float* zr,
+                                    size_t n_groups, const float* x, float* out, int64_t rows, int64_t cols,
+                                    int64_t gs, int64_t offset, int scale_mode) {
+  if (int rc = ensure_ready()) return rc;
+  SIMP_REQUIRE(qw && sc && x && out && rows >= 0 && cols >= 0, SIMP_ERR_ARG, "host matmul_quant: bad argument");
+  cudaStream_t st = ctx().stream;
+  void *dq, *ds, *dz = nullptr, *dx;
+  if (int rc = stage_in(qw, qw_bytes, 0, st, &dq)) return rc;
+  if (int rc = stage_in(sc, n_groups * 4, 1, st, &ds)) return rc;
+  if (zr)
+    if (int rc = stage_in(zr, n_groups * 4, 3, st, &dz)) return rc;
+  if (int rc = stage_in(x, size_t(cols) * 4, 4, st, &dx)) return rc;
+  float* dout = static_cast<float*>(scratch(size_t(rows) * 4 + 16, 2));
+  SIMP_REQUIRE(dout != nullptr, SIMP_ERR_CUDA, "out of device memory");
+  if (int rc = simp_gpu_matmul_w4(static_cast<uint8_t*>(dq), static_cast<float*>(ds), static_cast<float*>(dz),
+                                  static_cast<float*>(dx), dout, rows, cols, gs, offset, scale_mode))
+    return rc;
+  SIMP_CUDA(cudaMemcpyAsync(out, dout, size_t(rows) * 4, cudaMemcpyDeviceToHost, st));
+  SIMP_CUDA(cudaStreamSynchronize(st));
+  return SIMP_OK;
+}
+
+// rmsnorm / softmax / silu with host operands (single call = `rows` rows).
+SIMP_API int simp_host_rmsnorm_f32(const float* x, const float* w, float* y, int64_t rows, int64_t n, float eps,
+                                   int64_t woff) {
+  if (int rc = ensure_ready()) return rc;
+  SIMP_REQUIRE(rows >= 0 && n >= 0 && woff >= 0, SIMP_ERR_ARG, "host rmsnorm: negative size");
+  if (rows == 0 || n == 0) return SIMP_OK;
+  SIMP_REQUIRE(x && w && y, SIMP_ERR_ARG, "host rmsnorm: null pointer");
+  cudaStream_t st = ctx().stream;
+  void *dx, *dw;
+  if (int rc = stage_in(x, size_t(rows) * n * 4, 0, st, &dx)) return rc;
+  if (int rc = stage_in(w + woff, size_t(n) * 4, 1, st, &dw)) return rc;
+  float* dy = static_cast<float*>(scratch(size_t(rows) * n * 4, 2));
+  SIMP_REQUIRE(dy != nullptr, SIMP_ERR_CUDA, "out of device memory");
+  if (int rc = simp_gpu_rmsnorm_f32(static_cast<float*>(dx), static_cast<float*>(dw), dy, rows, n, eps, 0, n, nullptr))
+    return rc;
+  SIMP_CUDA(cudaMemcpyAsync(y, dy, size_t(rows) * n * 4, cudaMemcpyDeviceToHost, st));
+  SIMP_CUDA(cudaStreamSynchronize(st));
+  return SIMP_OK;
+}
+SIMP_API int simp_host_softmax_f32(const float* x, float* y, int64_t rows, int64_t n, int64_t xoff, int64_t yoff,
+                                   int64_t row_stride) {
+  if (int rc = ensure_ready()) return rc;
+  SIMP_REQUIRE(rows >= 0 && n >= 0 && xoff >= 0 && yoff >= 0, SIMP_ERR_ARG, "host softmax: negative size");
+  if (rows == 0 || n == 0) return SIMP_OK;
+  SIMP_REQUIRE(x && y, SIMP_ERR_ARG, "host softmax: null pointer");
+  if (row_stride == 0) row_stride = n;
+  const size_t span = size_t((rows - 1) * row_stride + n) * 4;
+  cudaStream_t st = ctx().stream;
+  void* dx;
+  if (int rc = stage_in(x + xoff, span, 0, st, &dx)) return rc;
+  float* dy = static_cast<float*>(scratch(span, 2));
+  SIMP_REQUIRE(dy != nullptr, SIMP_ERR_CUDA, "out of device memory");
+  if (row_stride != n) SIMP_CUDA(cudaMemcpyAsync(dy, y + yoff, span, cudaMemcpyHostToDevice, st));
+  if (int rc = simp_gpu_softmax_f32(static_cast<float*>(dx), dy, rows, n, 0, 0, row_stride)) return rc;
+  SIMP_CUDA(cudaMemcpyAsync(y + yoff, dy, span, cudaMemcpyDeviceToHost, st));
+  SIMP_CUDA(cudaStreamSynchronize(st));
+  return SIMP_OK;
+}
+SIMP_API int simp_host_silu_f32(const float* x, const float* mul, float* y, int64_t n) {
+  if (int rc = ensure_ready()) return rc;
+  SIMP_REQUIRE(n >= 0, SIMP_ERR_ARG, "host silu: negative size");
+  if (n == 0) return SIMP_OK;
+  SIMP_REQUIRE(x && y, SIMP_ERR_ARG, "host silu: null pointer");
+  cudaStream_t st = ctx().stream;
+  void *dx, *dm = nullptr;
+  if (int rc = stage_in(x, size_t(n) * 4, 0, st, &dx)) return rc;
+  if (mul)
+    if (int rc = stage_in(mul, size_t(n) * 4, 1, st, &dm)) return rc;
+  float* dy = static_cast<float*>(scratch(size_t(n) * 4, 2));
+  SIMP_REQUIRE(dy != nullptr, SIMP_ERR_CUDA, "out of device memory");
+  if (int rc = simp_gpu_silu_f32(static_cast<float*>(dx), static_cast<float*>(dm), dy, n)) return rc;
+  SIMP_CUDA(cudaMemcpyAsync(y, dy, size_t(n) * 4, cudaMemcpyDeviceToHost, st));
+  SIMP_CUDA(cudaStreamSynchronize(st));
+  return SIMP_OK;
+}

@@ -18,7 +18,7 @@ struct Arena {
   void* p = nullptr;
   size_t cap = 0;
 };
-static Arena g_arena[8];
+static Arena g_arena[16];
 
 Context& ctx() { return g_ctx; }
 
@@ -76,6 +76,8 @@ SIMP_API int simp_gpu_init(int device) {
                prop.minor);
   g_ctx.sm_count = prop.multiProcessorCount;
   SIMP_CUDA(cudaStreamCreateWithFlags(&g_ctx.stream, cudaStreamNonBlocking));
+  SIMP_CUDA(cudaStreamCreateWithFlags(&g_ctx.copy_in, cudaStreamNonBlocking));
+  SIMP_CUDA(cudaStreamCreateWithFlags(&g_ctx.copy_out, cudaStreamNonBlocking));
   SIMP_CUDA(cudaMalloc(&g_ctx.dev_status, 64));
   SIMP_CUDA(cudaMemset(g_ctx.dev_status, 0, 64));
   SIMP_CUDA(cudaMallocHost(&g_ctx.host_status, 64));
@@ -97,6 +99,8 @@ SIMP_API int simp_gpu_shutdown(void) {
   cudaFree(g_ctx.dev_status);
   cudaFreeHost(g_ctx.host_status);
   cudaStreamDestroy(g_ctx.stream);
+  cudaStreamDestroy(g_ctx.copy_in);
+  cudaStreamDestroy(g_ctx.copy_out);
   g_ctx = Context{};
   return SIMP_OK;
 }
