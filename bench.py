@@ -50,52 +50,61 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks / throttle reasons while the timed region runs."""
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """Samples SM clock, power and throttle reasons through NVML (read-only) while the timed region runs."""
 
-    def __init__(self, device_index):
+    def __init__(self, device_index, period_s=0.01):
         self.idx = device_index
-        self.proc = None
+        self.period = period_s
+        self.samples = []
+        self._stop = False
+        self._thread = None
+        self._nvml = None
 
     def start(self):
+        import threading
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "100", "-i", str(self.idx)],
-                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-        except OSError:
-            self.proc = None
+            import pynvml
+            pynvml.nvmlInit()
+            self._nvml = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(self.idx)
+            self._max = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nvml = None
+            return
+        self._thread = threading.Thread(target=self._run, daemon=True)
+        self._thread.start()
+
+    def _run(self):
+        n = self._nvml
+        while not self._stop:
+            try:
+                sm = n.nvmlDeviceGetClockInfo(self._h, n.NVML_CLOCK_SM)
+                pw = n.nvmlDeviceGetPowerUsage(self._h) / 1000.0
+                rs = n.nvmlDeviceGetCurrentClocksEventReasons(self._h)
+                self.samples.append((sm, pw, rs))
+            except Exception:
+                pass
+            time.sleep(self.period)
 
     def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            out, _ = self.proc.communicate(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-            out, _ = self.proc.communicate()
-        sm, mx, power, reasons = [], [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in out.strip().splitlines():
-            f = [x.strip() for x in line.split(",")]
-            if len(f) < 9:
-                continue
-            try:
-                sm.append(float(f[1])); mx.append(float(f[2])); power.append(float(f[3]))
-            except ValueError:
-                continue
-            for name, v in zip(names, f[5:9]):
-                if v.lower().startswith("active"):
-                    reasons.add(name)
-        if not sm:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
-        # "under load" = samples in the upper half of the power range seen
+        if self._nvml is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["NVML unavailable"]}
+        self._stop = True
+        self._thread.join(timeout=2)
+        n = self._nvml
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": float(self._max), "reasons": ["no samples"]}
+        names = {"hw_slowdown": n.nvmlClocksEventReasonHwSlowdown,
+                 "hw_thermal_slowdown": n.nvmlClocksEventReasonHwThermalSlowdown,
+                 "sw_thermal_slowdown": n.nvmlClocksEventReasonSwThermalSlowdown,
+                 "sw_power_cap": n.nvmlClocksEventReasonSwPowerCap}
+        power = [p for _, p, _ in self.samples]
         thr = (max(power) + min(power)) / 2
-        loaded = [s for s, p in zip(sm, power) if p >= thr] or sm
-        return {"sm_mhz": statistics.median(loaded), "sm_max_mhz": max(mx), "power_w_max": max(power),
-                "samples": len(sm), "reasons": sorted(reasons)}
+        loaded = [s for s in self.samples if s[1] >= thr] or self.samples
+        reasons = sorted(k for k, bit in names.items() if any(r & bit for _, _, r in loaded))
+        return {"sm_mhz": statistics.median(s for s, _, _ in loaded), "sm_max_mhz": float(self._max),
+                "power_w_max": max(power), "samples": len(self.samples), "samples_under_load": len(loaded),
+                "reasons": reasons}
 
 
 def gen_inputs(M, K, N, seed_a=1, seed_b=2, a_unsigned=True):
@@ -144,7 +153,13 @@ def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    # bounded sample per step: the largest cube <= 4096 that keeps the whole run within ~2.5 minutes
     n = 4096 if args.size >= 4096 else args.size
+    while n > 1024:
+        _, probe, _, _, _ = cpu_reference_gemm(n, 1, 1)
+        if probe[0] * (args.steps + args.warmup) <= 150.0:
+            break
+        n //= 2
     tera_ops, times, sample, kind, cores = cpu_reference_gemm(n, args.steps, args.warmup)
     total = sum(times)
     value = tera_ops * len(times) / total
@@ -217,7 +232,6 @@ def run_ours(args):
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-        time.sleep(0.3)
     barrier()
     e0, e1 = sg.Event(), sg.Event()
     e0.record()
@@ -306,7 +320,7 @@ def run_ours(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=1000)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--size", type=int, default=8192)
