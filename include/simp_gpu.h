@@ -150,6 +150,32 @@ int simp_host_softmax_f32(const float* x, float* y, int64_t rows, int64_t n, int
                           int64_t yoff, int64_t row_stride);
 int simp_host_silu_f32(const float* x, const float* mul, float* y, int64_t n);
 
+/* ---- whole-token LLaMA decode --------------------------------------------------------------
+ * Replaces: the compiled model kernels stories110M_forward (examples/llama2/stories110M.sl:5-247)
+ * and llama2_quant_forward (examples/llama2/llama2_quant.sl:7-198) together with the host loop
+ * around them (examples/llama2/generate_stories110M.cpp:236-260, greedy argmax :73-83).
+ * Tensors are loaded by the .sl argument names: token_embedding, rms_att_w, rms_ffn_w, rms_final_w,
+ * wcls, and either wq wk wv wo w1 w2 w3 (f32, stacked [n_layers, rows, cols]) or qweights, scales
+ * [, zeros] plus the seven element offsets of wq wk wv wo w1 w2 w3 inside qweights
+ * (examples/llama2/bench_llama_quant.cpp:189-209).  KV cache and activations stay on the device;
+ * one CUDA graph is replayed per token. */
+typedef struct simp_llama_config {
+  int64_t dim, hidden_dim, n_layers, n_heads, n_kv_heads, vocab_size, seq_len;
+  int64_t w4;          /* 0: f32 projections, 1: W4 projections (scale_mode 1) */
+  int64_t group_size;  /* W4 only: 32, 64, ... 1024 */
+} simp_llama_config;
+int simp_llama_create(const simp_llama_config* cfg, void** model);
+int simp_llama_load(void* model, const char* name, const void* host, size_t bytes);
+int simp_llama_set_w4_offsets(void* model, const int64_t* offsets7);
+/* One token at `pos`; logits_host (vocab floats) may be NULL. */
+int simp_llama_forward(void* model, int64_t token, int64_t pos, float* logits_host);
+/* Teacher-forces prompt[0..n_prompt), then greedily generates n_new tokens into tokens_out.
+ * logits_trace (optional) receives (n_prompt + n_new - 1) x vocab logits; ms_out (optional) the
+ * device time of the whole generation in milliseconds. */
+int simp_llama_generate(void* model, const int32_t* prompt, int64_t n_prompt, int64_t n_new,
+                        int32_t* tokens_out, float* logits_trace, float* ms_out);
+int simp_llama_destroy(void* model);
+
 #ifdef __cplusplus
 }
 #endif

@@ -60,6 +60,12 @@ _SIGNATURES = {
     "simp_host_rmsnorm_f32": [vp, vp, vp, i64, i64, C.c_float, i64],
     "simp_host_softmax_f32": [vp, vp, i64, i64, i64, i64, i64],
     "simp_host_silu_f32": [vp, vp, vp, i64],
+    "simp_llama_create": [vp, C.POINTER(vp)],
+    "simp_llama_load": [vp, C.c_char_p, vp, C.c_size_t],
+    "simp_llama_set_w4_offsets": [vp, C.POINTER(i64)],
+    "simp_llama_forward": [vp, i64, i64, vp],
+    "simp_llama_generate": [vp, vp, i64, i64, vp, vp, C.POINTER(C.c_float)],
+    "simp_llama_destroy": [vp],
 }
 
 
@@ -256,3 +262,57 @@ def host_tensor_matmul_i8(A: np.ndarray, B: np.ndarray, out: np.ndarray = None, 
     check(lib().simp_host_tensor_matmul_i8(A.ctypes.data, B.ctypes.data, out.ctypes.data, M, K, N,
                                            int(A.dtype == np.uint8), int(b_transposed)))
     return out
+
+
+# ------------------------------------------------------------------------- LLaMA decode driver
+class LlamaConfig(C.Structure):
+    _fields_ = [(n, i64) for n in ("dim", "hidden_dim", "n_layers", "n_heads", "n_kv_heads", "vocab_size", "seq_len",
+                                   "w4", "group_size")]
+
+
+W4_FAMILIES = ("wq", "wk", "wv", "wo", "w1", "w2", "w3")
+
+
+class Llama:
+    """Device-resident LLaMA decoder (simp_llama_*).  ``tensors`` maps the .sl argument names to numpy arrays;
+    for W4 pass qweights / scales [/ zeros] and ``offsets`` = {family: element offset}."""
+
+    def __init__(self, cfg: dict, tensors: dict, w4=False, offsets=None):
+        c = LlamaConfig(**{k: cfg[k] for k in ("dim", "hidden_dim", "n_layers", "n_heads", "n_kv_heads", "vocab_size",
+                                                "seq_len")}, w4=int(w4), group_size=cfg.get("group_size", 0))
+        h = vp()
+        check(lib().simp_llama_create(C.byref(c), C.byref(h)))
+        self.h = h
+        self.vocab = cfg["vocab_size"]
+        for name, arr in tensors.items():
+            arr = np.ascontiguousarray(arr)
+            check(lib().simp_llama_load(self.h, name.encode(), arr.ctypes.data, arr.nbytes))
+        if w4:
+            off = (i64 * 7)(*[offsets[f] if isinstance(offsets, dict) else offsets[i] for i, f in enumerate(W4_FAMILIES)])
+            check(lib().simp_llama_set_w4_offsets(self.h, off))
+
+    def forward(self, token: int, pos: int) -> np.ndarray:
+        out = np.empty(self.vocab, np.float32)
+        check(lib().simp_llama_forward(self.h, token, pos, out.ctypes.data))
+        return out
+
+    def generate(self, prompt, n_new: int, trace_logits=False):
+        prompt = np.ascontiguousarray(prompt, np.int32)
+        toks = np.empty(n_new, np.int32)
+        steps = len(prompt) + n_new - 1
+        trace = np.empty((steps, self.vocab), np.float32) if trace_logits else None
+        ms = C.c_float()
+        check(lib().simp_llama_generate(self.h, prompt.ctypes.data, len(prompt), n_new, toks.ctypes.data,
+                                        trace.ctypes.data if trace_logits else None, C.byref(ms)))
+        return toks, trace, float(ms.value)
+
+    def close(self):
+        if self.h:
+            lib().simp_llama_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

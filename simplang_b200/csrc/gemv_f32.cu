@@ -9,70 +9,9 @@
 // Semantics: MatMulOpLowering (src/mlir/lowering/ConvertSimpToMemRef.cpp:1890-1913, accumulates)
 // and TensorMatMulOpLowering f32 (ConvertSimpToMemRef.cpp:2926-2933, 3280-3291, fresh result).
 #include "common.cuh"
+#include "gemv_f32_core.cuh"
 
 namespace simp {
-
-constexpr int GEMV_WARPS = 8;  // warps per block
-
-// A rows 16-byte aligned.  W warps share a row (W in {1,2,4,8}); row partials are combined in
-// warp order through shared memory, so the summation tree is fixed for a given (k, W).
-template <int W>
-__global__ void __launch_bounds__(GEMV_WARPS * 32) gemv_f32_kernel(const float* __restrict__ A,
-                                                                   const float* __restrict__ x,
-                                                                   float* __restrict__ C, int64_t m, int k4,
-                                                                   int accumulate) {
-  __shared__ float part[GEMV_WARPS];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  constexpr int ROWS = GEMV_WARPS / W;
-  const int64_t row = int64_t(blockIdx.x) * ROWS + warp / W;
-  const int kp = warp % W;
-  const int chunk = (k4 + W - 1) / W;
-  const int c0 = kp * chunk;
-  const int c1 = min(k4, c0 + chunk);
-  float acc = 0.0f;
-  if (row < m) {
-    const float4* a = reinterpret_cast<const float4*>(A) + row * int64_t(k4);
-    const float4* xv = reinterpret_cast<const float4*>(x);
-    int i = c0 + lane;
-    for (; i + 7 * 32 < c1; i += 8 * 32) {
-      float4 v[8];
-#pragma unroll
-      for (int u = 0; u < 8; ++u) v[u] = ld_stream_f4(a + i + u * 32);
-#pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        const float4 b = __ldg(xv + i + u * 32);
-        acc = fmaf(v[u].x, b.x, acc); acc = fmaf(v[u].y, b.y, acc);
-        acc = fmaf(v[u].z, b.z, acc); acc = fmaf(v[u].w, b.w, acc);
-      }
-    }
-    {
-      float4 v[8];
-#pragma unroll
-      for (int u = 0; u < 8; ++u)
-        if (i + u * 32 < c1) v[u] = ld_stream_f4(a + i + u * 32);
-#pragma unroll
-      for (int u = 0; u < 8; ++u)
-        if (i + u * 32 < c1) {
-          const float4 b = __ldg(xv + i + u * 32);
-          acc = fmaf(v[u].x, b.x, acc); acc = fmaf(v[u].y, b.y, acc);
-          acc = fmaf(v[u].z, b.z, acc); acc = fmaf(v[u].w, b.w, acc);
-        }
-    }
-  }
-  acc = warp_sum(acc);
-  if (W == 1) {
-    if (lane == 0 && row < m) C[row] = accumulate ? C[row] + acc : acc;
-  } else {
-    if (lane == 0) part[warp] = acc;
-    __syncthreads();
-    if (lane == 0 && kp == 0 && row < m) {
-      float s = part[warp];
-#pragma unroll
-      for (int u = 1; u < W; ++u) s += part[warp + u];
-      C[row] = accumulate ? C[row] + s : s;
-    }
-  }
-}
 
 // Any alignment, n == 1: one warp per row, scalar loads.
 __global__ void __launch_bounds__(256) gemv_f32_any_kernel(const float* __restrict__ A, const float* __restrict__ x,
@@ -167,20 +106,15 @@ SIMP_API int simp_gpu_matmul_f32(const float* A, int64_t aoff, const float* B, i
     const bool vec = (k % 4 == 0) && ((reinterpret_cast<uintptr_t>(a) & 15u) == 0) &&
                      ((reinterpret_cast<uintptr_t>(b) & 15u) == 0) && k / 4 <= 0x7fffffff;
     if (vec) {
-      const int k4 = int(k / 4);
-      // Enough warps to keep ~16 per SM busy, but never fewer than 32 float4 per warp.
-      const int64_t want = int64_t(ctx().sm_count) * 16;
-      int W = 1;
-      while (W < 8 && m * W < want && k4 / (W * 2) >= 64) W *= 2;
-      const int rows_per_block = GEMV_WARPS / W;
-      const int64_t grid = cdiv(m, rows_per_block);
-      SIMP_REQUIRE(grid <= 0x7fffffff, SIMP_ERR_SHAPE, "matmul_f32: too many rows");
-      switch (W) {
-        case 1: gemv_f32_kernel<1><<<int(grid), GEMV_WARPS * 32, 0, st>>>(a, b, c, m, k4, accumulate); break;
-        case 2: gemv_f32_kernel<2><<<int(grid), GEMV_WARPS * 32, 0, st>>>(a, b, c, m, k4, accumulate); break;
-        case 4: gemv_f32_kernel<4><<<int(grid), GEMV_WARPS * 32, 0, st>>>(a, b, c, m, k4, accumulate); break;
-        default: gemv_f32_kernel<8><<<int(grid), GEMV_WARPS * 32, 0, st>>>(a, b, c, m, k4, accumulate); break;
-      }
+      GemvArgs g{};
+      g.seg[0] = GemvSeg{a, c, int(m)};
+      g.nseg = 1;
+      g.k4 = int(k / 4);
+      g.x = b;
+      SIMP_REQUIRE(m <= 0x7fffffff, SIMP_ERR_SHAPE, "matmul_f32: too many rows");
+      if (int rc = accumulate ? gemv_f32_launch<GEMV_ACCUM>(g, st, ctx().sm_count)
+                              : gemv_f32_launch<GEMV_STORE>(g, st, ctx().sm_count))
+        return rc;
     } else {
       const int64_t grid = cdiv(m, 8);
       SIMP_REQUIRE(grid <= 0x7fffffff, SIMP_ERR_SHAPE, "matmul_f32: too many rows");

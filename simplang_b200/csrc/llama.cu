@@ -1,0 +1,565 @@
+// llama.cu -- whole-token LLaMA decode on the device: the model drivers that define the f32 110M and
+// W4 3B decode workloads (examples/llama2/stories110M.sl:5-247, examples/llama2/llama2_quant.sl:7-198)
+// as one CUDA graph of this library's kernels per token.
+//
+// Per layer: rmsnorm -> q/k/v GEMV (one launch, three matrices) -> RoPE + KV-cache store ->
+// decode attention (scores, softmax, weighted sum per head, split over the sequence) -> wo GEMV with
+// the residual add fused -> rmsnorm -> gate/up GEMV pair with silu*mul fused -> down GEMV with the
+// residual add fused; then final rmsnorm, classifier GEMV, greedy argmax (strict '>', lowest index
+// wins ties as examples/llama2/generate_stories110M.cpp:73-83).  Token id and position live in device
+// memory, so the same graph is replayed for every token and the host never synchronises inside a
+// generation.
+//
+// Deviations from the .sl text (all mirrored by the CPU oracle): the score divisor is sqrt(head_size)
+// rather than the literal 8.0 (identical for head_size 64); the W4 model applies RoPE like the f32
+// one (the reference's W4 model has none); W4 projections use scale_mode 1 (per-matrix scale index).
+#include <cstring>
+#include <string>
+
+#include "common.cuh"
+#include "gemv_f32_core.cuh"
+#include "w4_core.cuh"
+
+namespace simp {
+
+struct LlamaModel {
+  simp_llama_config cfg;
+  int64_t kv_dim, head_size;
+  // weights (device)
+  float *tok_emb = nullptr, *rms_att = nullptr, *rms_ffn = nullptr, *rms_final = nullptr, *wcls = nullptr;
+  float *wq = nullptr, *wk = nullptr, *wv = nullptr, *wo = nullptr, *w1 = nullptr, *w2 = nullptr, *w3 = nullptr;
+  uint8_t* qweights = nullptr;
+  float *scales = nullptr, *zeros = nullptr;
+  int64_t off[7] = {0, 0, 0, 0, 0, 0, 0};  // wq wk wv wo w1 w2 w3 element offsets (W4)
+  // state (device)
+  float *x = nullptr, *xb = nullptr, *hb = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *logits = nullptr;
+  float *kc = nullptr, *vc = nullptr, *attn_part = nullptr;
+  uint8_t* xp = nullptr;  // packed activations for the W4 kernels
+  int* ctl = nullptr;     // [0] token, [1] pos, [2] n_prompt, [3] step, [4] next (argmax)
+  int32_t *prompt = nullptr, *out_tokens = nullptr;
+  int64_t prompt_cap = 0, out_cap = 0;
+  int nsplit = 1;
+  cudaGraphExec_t graph = nullptr;
+  bool loaded_any = false;
+};
+
+// ---------------------------------------------------------------------------------------------
+__global__ void embed_kernel(float* __restrict__ x, const float* __restrict__ table, const int* __restrict__ ctl,
+                             int dim) {
+  const int64_t token = ctl[0];
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < dim; i += gridDim.x * blockDim.x)
+    x[i] = table[token * dim + i];
+}
+
+// rmsnorm of one row (+ optional packing of the result for the W4 kernels).  Same arithmetic as
+// rmsnorm_any_kernel: y = (x / sqrt(ss/n + eps)) * w.  blockDim = 256, n % 32 == 0 when packing.
+__global__ void __launch_bounds__(256) dec_rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                                          float* __restrict__ y, uint8_t* __restrict__ xp, int n,
+                                                          float eps) {
+  __shared__ float red[33];
+  float ss = 0.0f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) ss += x[i] * x[i];
+  ss = block_sum(ss, red);
+  const float r = sqrtf(ss / float(n) + eps);
+  const int lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float o = (x[i] / r) * w[i];
+    y[i] = o;
+    if (xp) w4_pack_chunk(o, lane, xp + size_t(i >> 5) * (W4_CHUNK_U4 * 16));
+  }
+}
+
+// RoPE on (even, odd) pairs of q and k, then store k and v into the caches at `pos`
+// (examples/llama2/stories110M.sl:86-121): freq = 1 / 10000^((i % hs)/hs), angle = pos * freq.
+__global__ void rope_kv_kernel(float* __restrict__ q, float* __restrict__ k, const float* __restrict__ v,
+                               float* __restrict__ kc, float* __restrict__ vc, const int* __restrict__ ctl, int dim,
+                               int kv_dim, int hs, int seq_len, int layer) {
+  const int pos = ctl[1];
+  const int p = blockIdx.x * blockDim.x + threadIdx.x;  // pair index
+  const int i = 2 * p;
+  if (i >= dim) return;
+  const float freq = 1.0f / powf(10000.0f, float(i % hs) / float(hs));
+  const float val = float(pos) * freq;
+  const float fcr = cosf(val), fci = sinf(val);
+  const float q0 = q[i], q1 = q[i + 1];
+  q[i] = q0 * fcr - q1 * fci;
+  q[i + 1] = q0 * fci + q1 * fcr;
+  if (i < kv_dim) {
+    const float k0 = k[i], k1 = k[i + 1];
+    const float r0 = k0 * fcr - k1 * fci, r1 = k0 * fci + k1 * fcr;
+    const int64_t base = (int64_t(layer) * seq_len + pos) * kv_dim + i;
+    kc[base] = r0;
+    kc[base + 1] = r1;
+    vc[base] = v[i];
+    vc[base + 1] = v[i + 1];
+  }
+}
+
+// Decode attention for one head and one slice of the sequence.  Each warp walks timesteps
+// t = t0 + warp, t0 + warp + 4, ...; lanes split the head dimension (hs <= 128); the softmax is
+// carried online (running max m, running sum s, running weighted value acc).  Partials
+// (m, s, acc[hs]) of every (head, split) go to `part` and are merged by attn_combine_kernel.
+constexpr int ATT_WARPS = 4;
+constexpr int ATT_MAX_PER_LANE = 4;
+__global__ void __launch_bounds__(ATT_WARPS * 32)
+    attn_decode_kernel(const float* __restrict__ q, const float* __restrict__ kc, const float* __restrict__ vc,
+                       float* __restrict__ part, const int* __restrict__ ctl, int hs, int kv_dim, int kv_mul,
+                       int seq_len, int layer, int nsplit) {
+  __shared__ float sm_m[ATT_WARPS], sm_s[ATT_WARPS];
+  __shared__ float sm_acc[ATT_WARPS][128];
+  const int h = blockIdx.x, sp = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int len = ctl[1] + 1;
+  const int per = (len + nsplit - 1) / nsplit;
+  const int t0 = sp * per, t1 = min(len, t0 + per);
+  const int kvo = (h / kv_mul) * hs;
+  const float inv_div = sqrtf(float(hs));
+  float qr[ATT_MAX_PER_LANE], acc[ATT_MAX_PER_LANE];
+#pragma unroll
+  for (int e = 0; e < ATT_MAX_PER_LANE; ++e) {
+    const int i = lane + 32 * e;
+    qr[e] = i < hs ? q[h * hs + i] : 0.0f;
+    acc[e] = 0.0f;
+  }
+  float m = -INFINITY, s = 0.0f;
+  const float* kbase = kc + int64_t(layer) * seq_len * kv_dim + kvo;
+  const float* vbase = vc + int64_t(layer) * seq_len * kv_dim + kvo;
+  for (int t = t0 + warp; t < t1; t += ATT_WARPS) {
+    const float* kr = kbase + int64_t(t) * kv_dim;
+    float d = 0.0f;
+#pragma unroll
+    for (int e = 0; e < ATT_MAX_PER_LANE; ++e) {
+      const int i = lane + 32 * e;
+      if (i < hs) d = fmaf(qr[e], kr[i], d);
+    }
+    const float score = warp_sum(d) / inv_div;
+    const float m_new = fmaxf(m, score);
+    const float corr = expf(m - m_new);  // 0 on the first step (m = -inf)
+    const float p = expf(score - m_new);
+    s = s * corr + p;
+    const float* vr = vbase + int64_t(t) * kv_dim;
+#pragma unroll
+    for (int e = 0; e < ATT_MAX_PER_LANE; ++e) {
+      const int i = lane + 32 * e;
+      if (i < hs) acc[e] = acc[e] * corr + p * vr[i];
+    }
+    m = m_new;
+  }
+  if (lane == 0) {
+    sm_m[warp] = m;
+    sm_s[warp] = s;
+  }
+#pragma unroll
+  for (int e = 0; e < ATT_MAX_PER_LANE; ++e) {
+    const int i = lane + 32 * e;
+    if (i < hs) sm_acc[warp][i] = acc[e];
+  }
+  __syncthreads();
+  if (warp == 0) {
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < ATT_WARPS; ++w) M = fmaxf(M, sm_m[w]);
+    float S = 0.0f;
+    float sc[ATT_WARPS];
+#pragma unroll
+    for (int w = 0; w < ATT_WARPS; ++w) {
+      sc[w] = sm_m[w] == -INFINITY ? 0.0f : expf(sm_m[w] - M);
+      S += sm_s[w] * sc[w];
+    }
+    float* o = part + (int64_t(h) * nsplit + sp) * (hs + 2);
+    if (lane == 0) {
+      o[0] = M;
+      o[1] = S;
+    }
+#pragma unroll
+    for (int e = 0; e < ATT_MAX_PER_LANE; ++e) {
+      const int i = lane + 32 * e;
+      if (i < hs) {
+        float a = 0.0f;
+#pragma unroll
+        for (int w = 0; w < ATT_WARPS; ++w) a += sm_acc[w][i] * sc[w];
+        o[2 + i] = a;
+      }
+    }
+  }
+}
+
+// Merges the nsplit partials of each head and writes the normalised head output (+ packed form).
+__global__ void __launch_bounds__(128) attn_combine_kernel(const float* __restrict__ part, float* __restrict__ out,
+                                                           int hs, int nsplit) {
+  const int h = blockIdx.x;
+  const float* p = part + int64_t(h) * nsplit * (hs + 2);
+  float M = -INFINITY;
+  for (int sp = 0; sp < nsplit; ++sp) M = fmaxf(M, p[sp * (hs + 2)]);
+  float S = 0.0f;
+  for (int sp = 0; sp < nsplit; ++sp) {
+    const float mm = p[sp * (hs + 2)];
+    S += mm == -INFINITY ? 0.0f : p[sp * (hs + 2) + 1] * expf(mm - M);
+  }
+  for (int i = threadIdx.x; i < hs; i += blockDim.x) {
+    float a = 0.0f;
+    for (int sp = 0; sp < nsplit; ++sp) {
+      const float mm = p[sp * (hs + 2)];
+      if (mm != -INFINITY) a += p[sp * (hs + 2) + 2 + i] * expf(mm - M);
+    }
+    out[h * hs + i] = a / S;
+  }
+}
+
+// Greedy argmax (strict '>', lowest index wins) + bookkeeping for the next step:
+// step++, pos++, token = pos < n_prompt ? prompt[pos] : argmax; generated tokens are recorded.
+__global__ void __launch_bounds__(1024) argmax_advance_kernel(const float* __restrict__ logits, int n, int* ctl,
+                                                              const int32_t* __restrict__ prompt,
+                                                              int32_t* __restrict__ out_tokens) {
+  __shared__ float bv[32];
+  __shared__ int bi[32];
+  float best = -INFINITY;
+  int idx = 0x7fffffff;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float v = logits[i];
+    if (v > best || (v == best && i < idx)) {
+      best = v;
+      idx = i;
+    }
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+    if (ov > best || (ov == best && oi < idx)) {
+      best = ov;
+      idx = oi;
+    }
+  }
+  if (lane == 0) {
+    bv[warp] = best;
+    bi[warp] = idx;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    best = lane < (blockDim.x >> 5) ? bv[lane] : -INFINITY;
+    idx = lane < (blockDim.x >> 5) ? bi[lane] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+      if (ov > best || (ov == best && oi < idx)) {
+        best = ov;
+        idx = oi;
+      }
+    }
+    if (lane == 0) {
+      if (idx == 0x7fffffff) idx = 0;  // all-NaN logits: the host loop would keep index 0
+      const int pos = ctl[1] + 1, n_prompt = ctl[2], step = ctl[3];
+      ctl[4] = idx;
+      if (out_tokens && pos >= n_prompt) out_tokens[pos - n_prompt] = idx;
+      ctl[0] = (prompt && pos < n_prompt) ? prompt[pos] : idx;
+      ctl[1] = pos;
+      ctl[3] = step + 1;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+static int dev_alloc(void** p, size_t bytes) {
+  SIMP_CUDA(cudaMalloc(p, bytes ? bytes : 16));
+  return SIMP_OK;
+}
+
+static int enqueue_token(LlamaModel& m, cudaStream_t st) {
+  const simp_llama_config& c = m.cfg;
+  const int dim = int(c.dim), hd = int(c.hidden_dim), kv = int(m.kv_dim), hs = int(m.head_size);
+  const int sms = ctx().sm_count;
+  const bool w4 = c.w4 != 0;
+  const int log2_cpg = w4 ? __builtin_ctzll(uint64_t(c.group_size / 32)) : 0;
+  embed_kernel<<<(dim + 255) / 256, 256, 0, st>>>(m.x, m.tok_emb, m.ctl, dim);
+  auto w4seg = [&](int fam, int64_t layer, int64_t rows, int64_t cols, float* out) {
+    const int64_t o = m.off[fam] + layer * rows * cols;
+    return W4Seg{m.qweights + o / 2, m.scales + o / c.group_size, m.zeros ? m.zeros + o / c.group_size : nullptr, out,
+                 int(rows)};
+  };
+  for (int64_t l = 0; l < c.n_layers; ++l) {
+    dec_rmsnorm_kernel<<<1, 256, 0, st>>>(m.x, m.rms_att + l * dim, m.xb, w4 ? m.xp : nullptr, dim, 1e-5f);
+    if (w4) {
+      W4Args a{};
+      a.seg[0] = w4seg(0, l, dim, dim, m.q);
+      a.seg[1] = w4seg(1, l, kv, dim, m.k);
+      a.seg[2] = w4seg(2, l, kv, dim, m.v);
+      a.nseg = 3; a.cols = dim; a.log2_cpg = log2_cpg; a.groups_per_row = int(dim / c.group_size); a.xp = m.xp;
+      if (int rc = w4_launch<W4_STORE>(a, st, sms)) return rc;
+    } else {
+      GemvArgs g{};
+      g.seg[0] = GemvSeg{m.wq + l * dim * dim, m.q, dim};
+      g.seg[1] = GemvSeg{m.wk + l * int64_t(kv) * dim, m.k, kv};
+      g.seg[2] = GemvSeg{m.wv + l * int64_t(kv) * dim, m.v, kv};
+      g.nseg = 3; g.k4 = dim / 4; g.x = m.xb;
+      if (int rc = gemv_f32_launch<GEMV_STORE>(g, st, sms)) return rc;
+    }
+    rope_kv_kernel<<<(dim / 2 + 127) / 128, 128, 0, st>>>(m.q, m.k, m.v, m.kc, m.vc, m.ctl, dim, kv, hs,
+                                                          int(c.seq_len), int(l));
+    attn_decode_kernel<<<dim3(unsigned(c.n_heads), unsigned(m.nsplit)), ATT_WARPS * 32, 0, st>>>(
+        m.q, m.kc, m.vc, m.attn_part, m.ctl, hs, kv, int(c.n_heads / c.n_kv_heads), int(c.seq_len), int(l), m.nsplit);
+    attn_combine_kernel<<<unsigned(c.n_heads), 128, 0, st>>>(m.attn_part, m.xb, hs, m.nsplit);
+    if (w4) {
+      w4_pack_x_kernel<<<(dim / 32 + 7) / 8, 256, 0, st>>>(m.xb, m.xp, dim / 32);
+      W4Args a{};
+      a.seg[0] = w4seg(3, l, dim, dim, m.x);
+      a.nseg = 1; a.cols = dim; a.log2_cpg = log2_cpg; a.groups_per_row = int(dim / c.group_size); a.xp = m.xp;
+      a.res = m.x;
+      if (int rc = w4_launch<W4_ADD>(a, st, sms)) return rc;
+    } else {
+      GemvArgs g{};
+      g.seg[0] = GemvSeg{m.wo + l * dim * dim, m.x, dim};
+      g.nseg = 1; g.k4 = dim / 4; g.x = m.xb;
+      if (int rc = gemv_f32_launch<GEMV_ACCUM>(g, st, sms)) return rc;
+    }
+    dec_rmsnorm_kernel<<<1, 256, 0, st>>>(m.x, m.rms_ffn + l * dim, m.xb, w4 ? m.xp : nullptr, dim, 1e-5f);
+    if (w4) {
+      W4Args a{};
+      a.seg[0] = w4seg(4, l, hd, dim, m.hb);
+      a.seg[1] = w4seg(6, l, hd, dim, nullptr);
+      a.nseg = 2; a.cols = dim; a.log2_cpg = log2_cpg; a.groups_per_row = int(dim / c.group_size); a.xp = m.xp;
+      if (int rc = w4_launch<W4_GATE_UP>(a, st, sms)) return rc;
+      w4_pack_x_kernel<<<(hd / 32 + 7) / 8, 256, 0, st>>>(m.hb, m.xp, hd / 32);
+      W4Args d{};
+      d.seg[0] = w4seg(5, l, dim, hd, m.x);
+      d.nseg = 1; d.cols = hd; d.log2_cpg = log2_cpg; d.groups_per_row = int(hd / c.group_size); d.xp = m.xp;
+      d.res = m.x;
+      if (int rc = w4_launch<W4_ADD>(d, st, sms)) return rc;
+    } else {
+      GemvArgs g{};
+      g.seg[0] = GemvSeg{m.w1 + l * int64_t(hd) * dim, m.hb, hd};
+      g.seg[1] = GemvSeg{m.w3 + l * int64_t(hd) * dim, nullptr, hd};
+      g.nseg = 2; g.k4 = dim / 4; g.x = m.xb;
+      if (int rc = gemv_f32_launch<GEMV_GATE_UP>(g, st, sms)) return rc;
+      GemvArgs d{};
+      d.seg[0] = GemvSeg{m.w2 + l * int64_t(dim) * hd, m.x, dim};
+      d.nseg = 1; d.k4 = hd / 4; d.x = m.hb;
+      if (int rc = gemv_f32_launch<GEMV_ACCUM>(d, st, sms)) return rc;
+    }
+  }
+  dec_rmsnorm_kernel<<<1, 256, 0, st>>>(m.x, m.rms_final, m.xb, nullptr, dim, 1e-5f);
+  {
+    GemvArgs g{};
+    g.seg[0] = GemvSeg{m.wcls, m.logits, int(c.vocab_size)};
+    g.nseg = 1; g.k4 = dim / 4; g.x = m.xb;
+    if (int rc = gemv_f32_launch<GEMV_STORE>(g, st, sms)) return rc;
+  }
+  argmax_advance_kernel<<<1, 1024, 0, st>>>(m.logits, int(c.vocab_size), m.ctl, m.prompt, m.out_tokens);
+  SIMP_LAUNCH_CHECK();
+  return SIMP_OK;
+}
+
+static int ensure_graph(LlamaModel& m) {
+  if (m.graph) return SIMP_OK;
+  cudaStream_t st = ctx().stream;
+  // one eager pass first (sets function attributes, surfaces launch errors outside capture); it
+  // rewrites the same cache row the replay will write, so it is harmless
+  int ctl_save[5];
+  SIMP_CUDA(cudaMemcpyAsync(ctl_save, m.ctl, sizeof(ctl_save), cudaMemcpyDeviceToHost, st));
+  SIMP_CUDA(cudaStreamSynchronize(st));
+  if (int rc = enqueue_token(m, st)) return rc;
+  SIMP_CUDA(cudaStreamSynchronize(st));
+  SIMP_CUDA(cudaMemcpyAsync(m.ctl, ctl_save, sizeof(ctl_save), cudaMemcpyHostToDevice, st));
+  SIMP_CUDA(cudaStreamSynchronize(st));
+  cudaGraph_t g = nullptr;
+  SIMP_CUDA(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
+  const int rc = enqueue_token(m, st);
+  cudaError_t e = cudaStreamEndCapture(st, &g);
+  if (rc != SIMP_OK) {
+    if (g) cudaGraphDestroy(g);
+    return rc;
+  }
+  SIMP_REQUIRE(e == cudaSuccess, SIMP_ERR_CUDA, "graph capture failed: %s", cudaGetErrorString(e));
+  e = cudaGraphInstantiate(&m.graph, g, 0);
+  cudaGraphDestroy(g);
+  SIMP_REQUIRE(e == cudaSuccess, SIMP_ERR_CUDA, "graph instantiate failed: %s", cudaGetErrorString(e));
+  return SIMP_OK;
+}
+
+}  // namespace simp
+
+using namespace simp;
+
+SIMP_API int simp_llama_create(const simp_llama_config* cfg, void** model) {
+  SIMP_REQUIRE(cfg && model, SIMP_ERR_ARG, "llama_create: null pointer");
+  if (int rc = ensure_ready()) return rc;
+  const simp_llama_config& c = *cfg;
+  SIMP_REQUIRE(c.dim > 0 && c.hidden_dim > 0 && c.n_layers > 0 && c.n_heads > 0 && c.n_kv_heads > 0 &&
+                   c.vocab_size > 0 && c.seq_len > 0,
+               SIMP_ERR_ARG, "llama_create: non-positive dimension");
+  SIMP_REQUIRE(c.dim % c.n_heads == 0 && c.n_heads % c.n_kv_heads == 0, SIMP_ERR_SHAPE,
+               "llama_create: dim %% n_heads or n_heads %% n_kv_heads != 0");
+  const int64_t hs = c.dim / c.n_heads;
+  SIMP_REQUIRE(hs % 2 == 0 && hs <= 128, SIMP_ERR_SHAPE, "llama_create: head_size %lld must be even and <= 128",
+               (long long)hs);
+  SIMP_REQUIRE(c.dim % 4 == 0 && c.hidden_dim % 4 == 0, SIMP_ERR_SHAPE, "llama_create: dim, hidden_dim must be multiples of 4");
+  if (c.w4) {
+    const int64_t gs = c.group_size;
+    SIMP_REQUIRE(gs == 32 || gs == 64 || gs == 128 || gs == 256 || gs == 512 || gs == 1024, SIMP_ERR_SHAPE,
+                 "llama_create: W4 group_size must be 32..1024 and a power of two");
+    SIMP_REQUIRE(c.dim % gs == 0 && c.hidden_dim % gs == 0 && c.dim <= 16384 && c.hidden_dim <= 16384, SIMP_ERR_SHAPE,
+                 "llama_create: W4 needs dim and hidden_dim to be multiples of group_size and <= 16384");
+  }
+  LlamaModel* m = new LlamaModel();
+  m->cfg = c;
+  m->head_size = hs;
+  m->kv_dim = c.dim * c.n_kv_heads / c.n_heads;
+  m->nsplit = int(c.seq_len >= 1024 ? 8 : (c.seq_len >= 256 ? 4 : 1));
+  int rc = SIMP_OK;
+  auto A = [&](void** p, size_t n) { if (rc == SIMP_OK) rc = dev_alloc(p, n); };
+  const size_t mx = size_t(c.dim > c.hidden_dim ? c.dim : c.hidden_dim);
+  A((void**)&m->x, c.dim * 4); A((void**)&m->xb, mx * 4); A((void**)&m->hb, c.hidden_dim * 4);
+  A((void**)&m->q, c.dim * 4); A((void**)&m->k, m->kv_dim * 4); A((void**)&m->v, m->kv_dim * 4);
+  A((void**)&m->logits, c.vocab_size * 4);
+  A((void**)&m->kc, size_t(c.n_layers) * c.seq_len * m->kv_dim * 4);
+  A((void**)&m->vc, size_t(c.n_layers) * c.seq_len * m->kv_dim * 4);
+  A((void**)&m->attn_part, size_t(c.n_heads) * m->nsplit * (hs + 2) * 4);
+  A((void**)&m->xp, w4_packed_bytes(int64_t(mx) + 32));
+  A((void**)&m->ctl, 64);
+  if (rc != SIMP_OK) { simp_llama_destroy(m); return rc; }
+  cudaMemsetAsync(m->ctl, 0, 64, ctx().stream);
+  cudaMemsetAsync(m->kc, 0, size_t(c.n_layers) * c.seq_len * m->kv_dim * 4, ctx().stream);
+  cudaMemsetAsync(m->vc, 0, size_t(c.n_layers) * c.seq_len * m->kv_dim * 4, ctx().stream);
+  *model = m;
+  return SIMP_OK;
+}
+
+SIMP_API int simp_llama_load(void* model, const char* name, const void* host, size_t bytes) {
+  SIMP_REQUIRE(model && name && host, SIMP_ERR_ARG, "llama_load: null pointer");
+  LlamaModel& m = *static_cast<LlamaModel*>(model);
+  const simp_llama_config& c = m.cfg;
+  const std::string n(name);
+  const size_t d = c.dim, h = c.hidden_dim, L = c.n_layers, V = c.vocab_size, kv = m.kv_dim;
+  void** slot = nullptr;
+  size_t want = 0;
+  if (n == "token_embedding") { slot = (void**)&m.tok_emb; want = V * d * 4; }
+  else if (n == "rms_att_w") { slot = (void**)&m.rms_att; want = L * d * 4; }
+  else if (n == "rms_ffn_w") { slot = (void**)&m.rms_ffn; want = L * d * 4; }
+  else if (n == "rms_final_w") { slot = (void**)&m.rms_final; want = d * 4; }
+  else if (n == "wcls") { slot = (void**)&m.wcls; want = V * d * 4; }
+  else if (n == "wq") { slot = (void**)&m.wq; want = L * d * d * 4; }
+  else if (n == "wk") { slot = (void**)&m.wk; want = L * kv * d * 4; }
+  else if (n == "wv") { slot = (void**)&m.wv; want = L * kv * d * 4; }
+  else if (n == "wo") { slot = (void**)&m.wo; want = L * d * d * 4; }
+  else if (n == "w1") { slot = (void**)&m.w1; want = L * h * d * 4; }
+  else if (n == "w2") { slot = (void**)&m.w2; want = L * d * h * 4; }
+  else if (n == "w3") { slot = (void**)&m.w3; want = L * h * d * 4; }
+  else if (n == "qweights") { slot = (void**)&m.qweights; want = bytes; }
+  else if (n == "scales") { slot = (void**)&m.scales; want = bytes; }
+  else if (n == "zeros") { slot = (void**)&m.zeros; want = bytes; }
+  SIMP_REQUIRE(slot != nullptr, SIMP_ERR_ARG, "llama_load: unknown tensor name '%s'", name);
+  SIMP_REQUIRE(bytes == want, SIMP_ERR_SHAPE, "llama_load: '%s' needs %zu bytes, got %zu", name, want, bytes);
+  if (*slot) { cudaStreamSynchronize(ctx().stream); cudaFree(*slot); *slot = nullptr; }
+  if (int rc = dev_alloc(slot, bytes)) return rc;
+  SIMP_CUDA(cudaMemcpyAsync(*slot, host, bytes, cudaMemcpyHostToDevice, ctx().stream));
+  SIMP_CUDA(cudaStreamSynchronize(ctx().stream));
+  if (m.graph) { cudaGraphExecDestroy(m.graph); m.graph = nullptr; }
+  return SIMP_OK;
+}
+
+SIMP_API int simp_llama_set_w4_offsets(void* model, const int64_t* offsets7) {
+  SIMP_REQUIRE(model && offsets7, SIMP_ERR_ARG, "llama_set_w4_offsets: null pointer");
+  LlamaModel& m = *static_cast<LlamaModel*>(model);
+  for (int i = 0; i < 7; ++i) {
+    SIMP_REQUIRE(offsets7[i] >= 0 && offsets7[i] % m.cfg.group_size == 0 && offsets7[i] % 32 == 0, SIMP_ERR_SHAPE,
+                 "llama_set_w4_offsets: offset %d (%lld) must be a multiple of group_size and of 32", i,
+                 (long long)offsets7[i]);
+    m.off[i] = offsets7[i];
+  }
+  if (m.graph) { cudaGraphExecDestroy(m.graph); m.graph = nullptr; }
+  return SIMP_OK;
+}
+
+static int check_loaded(const LlamaModel& m) {
+  const bool common = m.tok_emb && m.rms_att && m.rms_ffn && m.rms_final && m.wcls;
+  const bool proj = m.cfg.w4 ? (m.qweights && m.scales) : (m.wq && m.wk && m.wv && m.wo && m.w1 && m.w2 && m.w3);
+  SIMP_REQUIRE(common && proj, SIMP_ERR_STATE, "llama: not all tensors are loaded");
+  return SIMP_OK;
+}
+
+SIMP_API int simp_llama_forward(void* model, int64_t token, int64_t pos, float* logits_host) {
+  SIMP_REQUIRE(model != nullptr, SIMP_ERR_ARG, "llama_forward: null model");
+  LlamaModel& m = *static_cast<LlamaModel*>(model);
+  SIMP_REQUIRE(token >= 0 && token < m.cfg.vocab_size && pos >= 0 && pos < m.cfg.seq_len, SIMP_ERR_ARG,
+               "llama_forward: token %lld or pos %lld out of range", (long long)token, (long long)pos);
+  if (int rc = check_loaded(m)) return rc;
+  cudaStream_t st = ctx().stream;
+  const int ctl[5] = {int(token), int(pos), 0, 0, 0};
+  if (m.out_tokens || m.prompt) {  // a forward() is not part of a generation: detach the buffers
+    cudaStreamSynchronize(st);
+    cudaFree(m.out_tokens); cudaFree(m.prompt);
+    m.out_tokens = nullptr; m.prompt = nullptr; m.out_cap = m.prompt_cap = 0;
+    if (m.graph) { cudaGraphExecDestroy(m.graph); m.graph = nullptr; }
+  }
+  SIMP_CUDA(cudaMemcpyAsync(m.ctl, ctl, sizeof(ctl), cudaMemcpyHostToDevice, st));
+  if (int rc = ensure_graph(m)) return rc;
+  SIMP_CUDA(cudaGraphLaunch(m.graph, st));
+  if (logits_host)
+    SIMP_CUDA(cudaMemcpyAsync(logits_host, m.logits, size_t(m.cfg.vocab_size) * 4, cudaMemcpyDeviceToHost, st));
+  SIMP_CUDA(cudaStreamSynchronize(st));
+  return SIMP_OK;
+}
+
+// Teacher-forces `prompt` (positions 0..n_prompt-1), then generates n_new tokens greedily.
+// tokens_out[n_new] receives the generated ids; logits_trace (optional, host) receives the logits of
+// every step, (n_prompt + n_new - 1) x vocab.  ms_out (optional) = device time of the whole generation.
+SIMP_API int simp_llama_generate(void* model, const int32_t* prompt, int64_t n_prompt, int64_t n_new,
+                                 int32_t* tokens_out, float* logits_trace, float* ms_out) {
+  SIMP_REQUIRE(model && prompt && tokens_out, SIMP_ERR_ARG, "llama_generate: null pointer");
+  LlamaModel& m = *static_cast<LlamaModel*>(model);
+  SIMP_REQUIRE(n_prompt >= 1 && n_new >= 1 && n_prompt + n_new - 1 <= m.cfg.seq_len, SIMP_ERR_ARG,
+               "llama_generate: need n_prompt >= 1, n_new >= 1, n_prompt + n_new - 1 <= seq_len");
+  for (int64_t i = 0; i < n_prompt; ++i)
+    SIMP_REQUIRE(prompt[i] >= 0 && prompt[i] < m.cfg.vocab_size, SIMP_ERR_ARG, "llama_generate: prompt token out of range");
+  if (int rc = check_loaded(m)) return rc;
+  cudaStream_t st = ctx().stream;
+  if (m.prompt_cap < n_prompt || m.out_cap < n_new) {
+    cudaStreamSynchronize(st);
+    cudaFree(m.prompt); cudaFree(m.out_tokens);
+    m.prompt = nullptr; m.out_tokens = nullptr;
+    m.prompt_cap = n_prompt > 64 ? n_prompt : 64;
+    m.out_cap = n_new > 2048 ? n_new : 2048;
+    if (int rc = dev_alloc((void**)&m.prompt, size_t(m.prompt_cap) * 4)) return rc;
+    if (int rc = dev_alloc((void**)&m.out_tokens, size_t(m.out_cap) * 4)) return rc;
+    if (m.graph) { cudaGraphExecDestroy(m.graph); m.graph = nullptr; }
+  }
+  SIMP_CUDA(cudaMemcpyAsync(m.prompt, prompt, size_t(n_prompt) * 4, cudaMemcpyHostToDevice, st));
+  const int ctl[5] = {int(prompt[0]), 0, int(n_prompt), 0, 0};
+  SIMP_CUDA(cudaMemcpyAsync(m.ctl, ctl, sizeof(ctl), cudaMemcpyHostToDevice, st));
+  if (int rc = ensure_graph(m)) return rc;
+  SIMP_CUDA(cudaMemcpyAsync(m.ctl, ctl, sizeof(ctl), cudaMemcpyHostToDevice, st));
+  const int64_t steps = n_prompt + n_new - 1;
+  cudaEvent_t e0, e1;
+  SIMP_CUDA(cudaEventCreate(&e0));
+  SIMP_CUDA(cudaEventCreate(&e1));
+  SIMP_CUDA(cudaEventRecord(e0, st));
+  for (int64_t s = 0; s < steps; ++s) {
+    SIMP_CUDA(cudaGraphLaunch(m.graph, st));
+    if (logits_trace)
+      SIMP_CUDA(cudaMemcpyAsync(logits_trace + s * m.cfg.vocab_size, m.logits, size_t(m.cfg.vocab_size) * 4,
+                                cudaMemcpyDeviceToHost, st));
+  }
+  SIMP_CUDA(cudaEventRecord(e1, st));
+  SIMP_CUDA(cudaMemcpyAsync(tokens_out, m.out_tokens, size_t(n_new) * 4, cudaMemcpyDeviceToHost, st));
+  SIMP_CUDA(cudaStreamSynchronize(st));
+  if (ms_out) SIMP_CUDA(cudaEventElapsedTime(ms_out, e0, e1));
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  return SIMP_OK;
+}
+
+SIMP_API int simp_llama_destroy(void* model) {
+  if (!model) return SIMP_OK;
+  LlamaModel* m = static_cast<LlamaModel*>(model);
+  if (ctx().ready) cudaStreamSynchronize(ctx().stream);
+  if (m->graph) cudaGraphExecDestroy(m->graph);
+  void* ptrs[] = {m->tok_emb, m->rms_att, m->rms_ffn, m->rms_final, m->wcls, m->wq, m->wk, m->wv, m->wo, m->w1, m->w2,
+                  m->w3, m->qweights, m->scales, m->zeros, m->x, m->xb, m->hb, m->q, m->k, m->v, m->logits, m->kc,
+                  m->vc, m->attn_part, m->xp, m->ctl, m->prompt, m->out_tokens};
+  for (void* p : ptrs)
+    if (p) cudaFree(p);
+  delete m;
+  return SIMP_OK;
+}

@@ -1,0 +1,149 @@
+"""Per-op sweep of the bandwidth-bound kernels (f32 GEMV, W4 GEMV, rmsnorm, softmax, silu) and of the
+int8 GEMM at the configured shapes.  Prints one JSON line per case with the achieved GB/s (or TOPS), the
+algorithmic bytes used, and the fraction of the measured roofline.
+
+    python -m simplang_b200.opbench [--iters 50] [--only gemv_f32,w4,...]
+
+Each case rotates over enough independent operand copies that the working set exceeds twice the
+126 MB L2, so every iteration streams from HBM the way consecutive layers of a decode step do.
+Timing: CUDA events on the library stream, 3 warm-up passes, mean over `iters` launches.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import numpy as np
+
+import simplang_b200 as sg
+
+L2_BYTES = 126 << 20
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def hbm_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        return json.load(open(p))["hbm_gbs"], "measured"
+    return 6650.0, "fallback"
+
+
+def copies_for(nbytes):
+    return max(2, min(256, int(2 * L2_BYTES // max(nbytes, 1)) + 1))
+
+
+def timed(fn, ncopies, iters):
+    for i in range(3 * min(ncopies, 4)):
+        fn(i % ncopies)
+    sg.sync()
+    e0, e1 = sg.Event(), sg.Event()
+    e0.record()
+    for i in range(iters):
+        fn(i % ncopies)
+    e1.record()
+    sg.sync()
+    return e0.elapsed_ms(e1) / iters
+
+
+def emit(op, shape, ms, nbytes, extra=None):
+    peak, src = hbm_peak()
+    gbs = nbytes / (ms * 1e-3) / 1e9
+    line = {"op": op, "shape": shape, "us": round(ms * 1e3, 3), "algorithmic_bytes": int(nbytes),
+            "gb_s": round(gbs, 1), "frac_of_hbm_peak": round(gbs / peak, 4), "peak_gb_s": peak, "peak": src}
+    if extra:
+        line.update(extra)
+    print(json.dumps(line), flush=True)
+
+
+def bench_gemv_f32(iters):
+    rng = np.random.default_rng(0)
+    for rows, cols in [(768, 768), (2048, 768), (768, 2048), (32000, 768), (3200, 3200), (32000, 3200), (65536, 4096)]:
+        nb = 4 * (rows * cols + cols + rows)
+        nc = copies_for(nb)
+        A = sg.DeviceBuffer.from_numpy((0.02 * rng.standard_normal(rows * cols)).astype(np.float32))
+        bufs = [A] + [sg.DeviceBuffer(rows * cols * 4) for _ in range(nc - 1)]
+        for b in bufs[1:]:
+            sg.check(sg.lib().simp_gpu_memset(b.ptr, 0, b.nbytes))
+        x = sg.DeviceBuffer.from_numpy(rng.standard_normal(cols).astype(np.float32))
+        y = sg.DeviceBuffer(rows * 4)
+        ms = timed(lambda i: sg.matmul_f32(bufs[i], 0, x, 0, y, 0, rows, cols, 1, accumulate=False), nc, iters)
+        emit("gemv_f32", [rows, cols], ms, nb, {"copies": nc})
+        del bufs
+
+
+def bench_w4(iters):
+    rng = np.random.default_rng(1)
+    gs = 64
+    for rows, cols in [(3200, 3200), (9600, 3200), (8640, 3200), (3200, 8640), (26 * 8640, 3200), (65536, 8192)]:
+        nb = rows * cols // 2 + 4 * rows * cols // gs + 4 * cols + 4 * rows
+        nc = copies_for(nb)
+        qbytes, ngroups = rows * cols // 2, rows * cols // gs
+        q = sg.DeviceBuffer.from_numpy(rng.integers(0, 256, nc * qbytes, dtype=np.uint8))
+        s = sg.DeviceBuffer.from_numpy((0.01 * rng.random(nc * ngroups)).astype(np.float32))
+        x = sg.DeviceBuffer.from_numpy(rng.standard_normal(cols).astype(np.float32))
+        y = sg.DeviceBuffer(rows * 4)
+        ms = timed(lambda i: sg.matmul_w4(q, s, None, x, y, rows, cols, gs, i * rows * cols, scale_mode=1), nc, iters)
+        emit("gemv_w4_sym_gs64", [rows, cols], ms, nb, {"copies": nc})
+        del q, s
+
+
+def bench_rowops(iters):
+    rng = np.random.default_rng(2)
+    for rows, n in [(4096, 768), (4096, 3200), (4096, 4096), (16384, 4096)]:
+        nb = 4 * (2 * rows * n + n)
+        nc = copies_for(nb)
+        xs = [sg.DeviceBuffer.from_numpy(rng.standard_normal(rows * n).astype(np.float32)) for _ in range(min(nc, 8))]
+        ys = [sg.DeviceBuffer(rows * n * 4) for _ in range(len(xs))]
+        w = sg.DeviceBuffer.from_numpy(np.ones(n, np.float32))
+        ms = timed(lambda i: sg.rmsnorm_f32(xs[i], w, ys[i], rows, n), len(xs), iters)
+        emit("rmsnorm", [rows, n], ms, nb, {"copies": len(xs)})
+        ms = timed(lambda i: sg.softmax_f32(xs[i], ys[i], rows, n), len(xs), iters)
+        emit("softmax", [rows, n], ms, 8 * rows * n, {"copies": len(xs)})
+        ms = timed(lambda i: sg.silu_f32(xs[i], None, ys[i], rows * n), len(xs), iters)
+        emit("silu", [rows * n], ms, 8 * rows * n, {"copies": len(xs)})
+        ms = timed(lambda i: sg.silu_f32(xs[i], xs[(i + 1) % len(xs)], ys[i], rows * n), len(xs), iters)
+        emit("silu_mul", [rows * n], ms, 12 * rows * n, {"copies": len(xs)})
+        del xs, ys
+
+
+def bench_gemm_i8(iters):
+    rng = np.random.default_rng(3)
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    peak = 2 * (json.load(open(peaks_path))["bf16_tflops"] if os.path.exists(peaks_path) else 1590.0)
+    cases = [(1024, 1024, 1024), (2048, 2048, 2048), (4096, 4096, 4096), (8192, 8192, 8192), (16384, 16384, 16384),
+             (512, 3200, 9600), (512, 3200, 8640), (512, 8640, 3200)]
+    for M, K, N in cases:
+        A = sg.DeviceBuffer.from_numpy(rng.integers(0, 256, (M, K), dtype=np.uint8))
+        for b_t in (False, True):
+            B = sg.DeviceBuffer.from_numpy(rng.integers(-128, 128, (K, N), dtype=np.int8))
+            Cd = sg.DeviceBuffer(M * N * 4)
+            it = max(3, min(iters, int(2e14 / (2.0 * M * N * K))))
+            ms = timed(lambda i: sg.matmul_i8(A, B, Cd, M, K, N, a_unsigned=True, b_transposed=b_t), 1, it)
+            tops = 2.0 * M * N * K / (ms * 1e-3) / 1e12
+            print(json.dumps({"op": "gemm_i8", "shape": [M, K, N], "b_transposed": b_t, "us": round(ms * 1e3, 2),
+                              "tops": round(tops, 1), "frac_of_2x_bf16_burst": round(tops / peak, 4),
+                              "frac_of_nominal_4500": round(tops / 4500, 4)}), flush=True)
+            del B, Cd
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--iters", type=int, default=50)
+    ap.add_argument("--only", default="gemv_f32,w4,rowops,gemm_i8")
+    args = ap.parse_args()
+    sg.init(int(os.environ.get("LOCAL_RANK", "0")))
+    which = set(args.only.split(","))
+    if "gemv_f32" in which:
+        bench_gemv_f32(args.iters)
+    if "w4" in which:
+        bench_w4(args.iters)
+    if "rowops" in which:
+        bench_rowops(args.iters)
+    if "gemm_i8" in which:
+        bench_gemm_i8(args.iters)
+    sg.check(sg.lib().simp_gpu_check_device_status())
+
+
+if __name__ == "__main__":
+    main()
