@@ -63,7 +63,10 @@ SIMP_API int simp_gpu_matmul_w4(const uint8_t* qw, const float* sc, const float*
     if (gs == (int64_t(32) << s)) log2_cpg = s;
   const bool mode_ok = scale_mode == 1 ? (offset % gs == 0) : (gs == 128);
   const uint8_t* base = qw + offset / 2;
-  const bool fast = log2_cpg >= 0 && mode_ok && cols > 0 && cols % gs == 0 && cols <= 16384 && offset % 32 == 0 &&
+  const int64_t soff_chk = scale_mode == 1 ? offset / gs : 0;
+  const bool sc_aligned = ((reinterpret_cast<uintptr_t>(sc + soff_chk) & 15u) == 0) &&
+                          (!zr || (reinterpret_cast<uintptr_t>(zr + soff_chk) & 15u) == 0);
+  const bool fast = sc_aligned && log2_cpg >= 0 && mode_ok && cols > 0 && cols % gs == 0 && cols <= 16384 && offset % 32 == 0 &&
                     ((reinterpret_cast<uintptr_t>(base) & 15u) == 0) && rows <= 0x7fffffff;
   if (fast) {
     // scratch: the packed form of x (80 bytes per 32 inputs), produced by one small kernel

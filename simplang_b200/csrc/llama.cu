@@ -34,7 +34,8 @@ struct LlamaModel {
   // state (device)
   float *x = nullptr, *xb = nullptr, *hb = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *logits = nullptr;
   float *kc = nullptr, *vc = nullptr, *attn_part = nullptr;
-  uint8_t* xp = nullptr;  // packed activations for the W4 kernels
+  uint8_t *xpA = nullptr, *xpB = nullptr;  // packed activations for the W4 kernels (ping-pong)
+  float* ss = nullptr;                      // per-tile partial sums of squares (deferred rmsnorm)
   int* ctl = nullptr;     // [0] token, [1] pos, [2] n_prompt, [3] step, [4] next (argmax)
   int32_t *prompt = nullptr, *out_tokens = nullptr;
   int64_t prompt_cap = 0, out_cap = 0;
@@ -44,28 +45,22 @@ struct LlamaModel {
 };
 
 // ---------------------------------------------------------------------------------------------
-__global__ void embed_kernel(float* __restrict__ x, const float* __restrict__ table, const int* __restrict__ ctl,
-                             int dim) {
+// x = embedding row of the current token.  For the W4 path one warp per 32-element chunk also emits the
+// packed form of x * norm_w (input of the first q/k/v GEMV) and the chunk's sum of squares.
+__global__ void __launch_bounds__(256) embed_kernel(float* __restrict__ x, const float* __restrict__ table,
+                                                    const int* __restrict__ ctl, int dim, const float* __restrict__ norm_w,
+                                                    uint8_t* __restrict__ xp, float* __restrict__ ss) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int64_t token = ctl[0];
-  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < dim; i += gridDim.x * blockDim.x)
-    x[i] = table[token * dim + i];
-}
-
-// rmsnorm of one row (+ optional packing of the result for the W4 kernels).  Same arithmetic as
-// rmsnorm_any_kernel: y = (x / sqrt(ss/n + eps)) * w.  blockDim = 256, n % 32 == 0 when packing.
-__global__ void __launch_bounds__(256) dec_rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w,
-                                                          float* __restrict__ y, uint8_t* __restrict__ xp, int n,
-                                                          float eps) {
-  __shared__ float red[33];
-  float ss = 0.0f;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) ss += x[i] * x[i];
-  ss = block_sum(ss, red);
-  const float r = sqrtf(ss / float(n) + eps);
   const int lane = threadIdx.x & 31;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    const float o = (x[i] / r) * w[i];
-    y[i] = o;
-    if (xp) w4_pack_chunk(o, lane, xp + size_t(i >> 5) * (W4_CHUNK_U4 * 16));
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  const float v = i < dim ? table[token * dim + i] : 0.0f;
+  if (i < dim) x[i] = v;
+  if (xp && (i - lane) < dim) {
+    w4_pack_chunk(i < dim ? v * norm_w[i] : 0.0f, lane, xp + size_t(i >> 5) * (W4_CHUNK_U4 * 16));
+    const float q = warp_sum(v * v);
+    if (lane == 0) ss[i >> 5] = q;
   }
 }
 
@@ -74,6 +69,8 @@ __global__ void __launch_bounds__(256) dec_rmsnorm_kernel(const float* __restric
 __global__ void rope_kv_kernel(float* __restrict__ q, float* __restrict__ k, const float* __restrict__ v,
                                float* __restrict__ kc, float* __restrict__ vc, const int* __restrict__ ctl, int dim,
                                int kv_dim, int hs, int seq_len, int layer) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int pos = ctl[1];
   const int p = blockIdx.x * blockDim.x + threadIdx.x;  // pair index
   const int i = 2 * p;
@@ -109,6 +106,8 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
   __shared__ float sm_acc[ATT_WARPS][128];
   const int h = blockIdx.x, sp = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  pdl_launch_dependents();
+  pdl_wait();
   const int len = ctl[1] + 1;
   const int per = (len + nsplit - 1) / nsplit;
   const int t0 = sp * per, t1 = min(len, t0 + per);
@@ -184,26 +183,34 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
   }
 }
 
-// Merges the nsplit partials of each head and writes the normalised head output (+ packed form).
-__global__ void __launch_bounds__(128) attn_combine_kernel(const float* __restrict__ part, float* __restrict__ out,
-                                                           int hs, int nsplit) {
-  const int h = blockIdx.x;
-  const float* p = part + int64_t(h) * nsplit * (hs + 2);
-  float M = -INFINITY;
-  for (int sp = 0; sp < nsplit; ++sp) M = fmaxf(M, p[sp * (hs + 2)]);
-  float S = 0.0f;
-  for (int sp = 0; sp < nsplit; ++sp) {
-    const float mm = p[sp * (hs + 2)];
-    S += mm == -INFINITY ? 0.0f : p[sp * (hs + 2) + 1] * expf(mm - M);
-  }
-  for (int i = threadIdx.x; i < hs; i += blockDim.x) {
-    float a = 0.0f;
+// Merges the nsplit partials of every head into the normalised attention output.  One warp per 32
+// consecutive output elements, so the W4 path can emit the packed form for the wo GEMV in the same pass.
+__global__ void __launch_bounds__(256) attn_combine_kernel(const float* __restrict__ part, float* __restrict__ out,
+                                                           uint8_t* __restrict__ xp, int dim, int hs, int nsplit) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i - lane >= dim) return;
+  float val = 0.0f;
+  if (i < dim) {
+    const int h = i / hs, e = i - h * hs;
+    const float* p = part + int64_t(h) * nsplit * (hs + 2);
+    float M = -INFINITY;
+    for (int sp = 0; sp < nsplit; ++sp) M = fmaxf(M, p[sp * (hs + 2)]);
+    float S = 0.0f, a = 0.0f;
     for (int sp = 0; sp < nsplit; ++sp) {
       const float mm = p[sp * (hs + 2)];
-      if (mm != -INFINITY) a += p[sp * (hs + 2) + 2 + i] * expf(mm - M);
+      if (mm != -INFINITY) {
+        const float w = expf(mm - M);
+        S += p[sp * (hs + 2) + 1] * w;
+        a += p[sp * (hs + 2) + 2 + e] * w;
+      }
     }
-    out[h * hs + i] = a / S;
+    val = a / S;
+    out[i] = val;
   }
+  if (xp) w4_pack_chunk(val, lane, xp + size_t(i >> 5) * (W4_CHUNK_U4 * 16));
 }
 
 // Greedy argmax (strict '>', lowest index wins) + bookkeeping for the next step:
@@ -213,6 +220,8 @@ __global__ void __launch_bounds__(1024) argmax_advance_kernel(const float* __res
                                                               int32_t* __restrict__ out_tokens) {
   __shared__ float bv[32];
   __shared__ int bi[32];
+  pdl_launch_dependents();
+  pdl_wait();
   float best = -INFINITY;
   int idx = 0x7fffffff;
   for (int i = threadIdx.x; i < n; i += blockDim.x) {
@@ -267,87 +276,98 @@ static int dev_alloc(void** p, size_t bytes) {
   return SIMP_OK;
 }
 
+#define LAUNCH_OR_FAIL(...)                                                                         \
+  do {                                                                                              \
+    cudaError_t e__ = launch_kernel(__VA_ARGS__);                                                   \
+    if (e__ != cudaSuccess)                                                                         \
+      return set_error(SIMP_ERR_CUDA, "decode launch failed: %s (%s:%d)", cudaGetErrorString(e__), __FILE__, __LINE__); \
+  } while (0)
+
+// Enqueues one token.  Every launch after the first uses programmatic dependent launch: each kernel
+// requests its first weights, then waits for its predecessor before touching activations.
 static int enqueue_token(LlamaModel& m, cudaStream_t st) {
   const simp_llama_config& c = m.cfg;
   const int dim = int(c.dim), hd = int(c.hidden_dim), kv = int(m.kv_dim), hs = int(m.head_size);
   const int sms = ctx().sm_count;
   const bool w4 = c.w4 != 0;
+  const bool pdl = true;
   const int log2_cpg = w4 ? __builtin_ctzll(uint64_t(c.group_size / 32)) : 0;
-  embed_kernel<<<(dim + 255) / 256, 256, 0, st>>>(m.x, m.tok_emb, m.ctl, dim);
+  const int n_ss = dim / 32;
+  LAUNCH_OR_FAIL(embed_kernel, dim3((dim + 255) / 256), dim3(256), 0, st, false, m.x, m.tok_emb, m.ctl, dim,
+                 w4 ? m.rms_att : nullptr, w4 ? m.xpA : nullptr, m.ss);
   auto w4seg = [&](int fam, int64_t layer, int64_t rows, int64_t cols, float* out) {
     const int64_t o = m.off[fam] + layer * rows * cols;
     return W4Seg{m.qweights + o / 2, m.scales + o / c.group_size, m.zeros ? m.zeros + o / c.group_size : nullptr, out,
                  int(rows)};
   };
+  auto w4args = [&](int cols, const uint8_t* xp) {
+    W4Args a{};
+    a.cols = cols; a.log2_cpg = log2_cpg; a.groups_per_row = int(cols / c.group_size); a.xp = xp;
+    a.eps = 1e-5f; a.ss_div = float(dim);
+    return a;
+  };
   for (int64_t l = 0; l < c.n_layers; ++l) {
-    dec_rmsnorm_kernel<<<1, 256, 0, st>>>(m.x, m.rms_att + l * dim, m.xb, w4 ? m.xp : nullptr, dim, 1e-5f);
     if (w4) {
-      W4Args a{};
+      W4Args a = w4args(dim, m.xpA);
       a.seg[0] = w4seg(0, l, dim, dim, m.q);
       a.seg[1] = w4seg(1, l, kv, dim, m.k);
       a.seg[2] = w4seg(2, l, kv, dim, m.v);
-      a.nseg = 3; a.cols = dim; a.log2_cpg = log2_cpg; a.groups_per_row = int(dim / c.group_size); a.xp = m.xp;
-      if (int rc = w4_launch<W4_STORE>(a, st, sms)) return rc;
+      a.nseg = 3; a.ss_part = m.ss; a.n_ss = n_ss;
+      if (int rc = w4_launch<W4_STORE>(a, st, sms, pdl)) return rc;
     } else {
-      GemvArgs g{};
+      GemvDecArgs g{};
       g.seg[0] = GemvSeg{m.wq + l * dim * dim, m.q, dim};
       g.seg[1] = GemvSeg{m.wk + l * int64_t(kv) * dim, m.k, kv};
       g.seg[2] = GemvSeg{m.wv + l * int64_t(kv) * dim, m.v, kv};
-      g.nseg = 3; g.k4 = dim / 4; g.x = m.xb;
-      if (int rc = gemv_f32_launch<GEMV_STORE>(g, st, sms)) return rc;
+      g.nseg = 3; g.k4 = dim / 4; g.x = m.x; g.norm_w = m.rms_att + l * dim; g.eps = 1e-5f;
+      if (int rc = gemv_f32_dec_launch<GEMV_STORE>(g, st, sms, pdl)) return rc;
     }
-    rope_kv_kernel<<<(dim / 2 + 127) / 128, 128, 0, st>>>(m.q, m.k, m.v, m.kc, m.vc, m.ctl, dim, kv, hs,
-                                                          int(c.seq_len), int(l));
-    attn_decode_kernel<<<dim3(unsigned(c.n_heads), unsigned(m.nsplit)), ATT_WARPS * 32, 0, st>>>(
-        m.q, m.kc, m.vc, m.attn_part, m.ctl, hs, kv, int(c.n_heads / c.n_kv_heads), int(c.seq_len), int(l), m.nsplit);
-    attn_combine_kernel<<<unsigned(c.n_heads), 128, 0, st>>>(m.attn_part, m.xb, hs, m.nsplit);
+    LAUNCH_OR_FAIL(rope_kv_kernel, dim3((dim / 2 + 127) / 128), dim3(128), 0, st, pdl, m.q, m.k, m.v, m.kc, m.vc,
+                   m.ctl, dim, kv, hs, int(c.seq_len), int(l));
+    LAUNCH_OR_FAIL(attn_decode_kernel, dim3(unsigned(c.n_heads), unsigned(m.nsplit)), dim3(ATT_WARPS * 32), 0, st, pdl,
+                   m.q, m.kc, m.vc, m.attn_part, m.ctl, hs, kv, int(c.n_heads / c.n_kv_heads), int(c.seq_len), int(l),
+                   m.nsplit);
+    LAUNCH_OR_FAIL(attn_combine_kernel, dim3((dim + 255) / 256), dim3(256), 0, st, pdl, m.attn_part, m.xb,
+                   w4 ? m.xpB : nullptr, dim, hs, m.nsplit);
     if (w4) {
-      w4_pack_x_kernel<<<(dim / 32 + 7) / 8, 256, 0, st>>>(m.xb, m.xp, dim / 32);
-      W4Args a{};
+      W4Args a = w4args(dim, m.xpB);
       a.seg[0] = w4seg(3, l, dim, dim, m.x);
-      a.nseg = 1; a.cols = dim; a.log2_cpg = log2_cpg; a.groups_per_row = int(dim / c.group_size); a.xp = m.xp;
-      a.res = m.x;
-      if (int rc = w4_launch<W4_ADD>(a, st, sms)) return rc;
-    } else {
-      GemvArgs g{};
-      g.seg[0] = GemvSeg{m.wo + l * dim * dim, m.x, dim};
-      g.nseg = 1; g.k4 = dim / 4; g.x = m.xb;
-      if (int rc = gemv_f32_launch<GEMV_ACCUM>(g, st, sms)) return rc;
-    }
-    dec_rmsnorm_kernel<<<1, 256, 0, st>>>(m.x, m.rms_ffn + l * dim, m.xb, w4 ? m.xp : nullptr, dim, 1e-5f);
-    if (w4) {
-      W4Args a{};
-      a.seg[0] = w4seg(4, l, hd, dim, m.hb);
-      a.seg[1] = w4seg(6, l, hd, dim, nullptr);
-      a.nseg = 2; a.cols = dim; a.log2_cpg = log2_cpg; a.groups_per_row = int(dim / c.group_size); a.xp = m.xp;
-      if (int rc = w4_launch<W4_GATE_UP>(a, st, sms)) return rc;
-      w4_pack_x_kernel<<<(hd / 32 + 7) / 8, 256, 0, st>>>(m.hb, m.xp, hd / 32);
-      W4Args d{};
+      a.nseg = 1; a.res = m.x; a.xp_out = m.xpA; a.out_scale = m.rms_ffn + l * dim; a.ss_out = m.ss;
+      if (int rc = w4_launch<W4_ADD>(a, st, sms, pdl)) return rc;
+      W4Args g = w4args(dim, m.xpA);
+      g.seg[0] = w4seg(4, l, hd, dim, nullptr);
+      g.seg[1] = w4seg(6, l, hd, dim, nullptr);
+      g.nseg = 2; g.ss_part = m.ss; g.n_ss = n_ss; g.xp_out = m.xpB;
+      if (int rc = w4_launch<W4_GATE_UP>(g, st, sms, pdl)) return rc;
+      W4Args d = w4args(hd, m.xpB);
       d.seg[0] = w4seg(5, l, dim, hd, m.x);
-      d.nseg = 1; d.cols = hd; d.log2_cpg = log2_cpg; d.groups_per_row = int(hd / c.group_size); d.xp = m.xp;
-      d.res = m.x;
-      if (int rc = w4_launch<W4_ADD>(d, st, sms)) return rc;
+      d.nseg = 1; d.res = m.x; d.ss_out = m.ss;
+      if (l + 1 < c.n_layers) { d.xp_out = m.xpA; d.out_scale = m.rms_att + (l + 1) * dim; }
+      if (int rc = w4_launch<W4_ADD>(d, st, sms, pdl)) return rc;
     } else {
-      GemvArgs g{};
+      GemvDecArgs o{};
+      o.seg[0] = GemvSeg{m.wo + l * dim * dim, m.x, dim};
+      o.nseg = 1; o.k4 = dim / 4; o.x = m.xb;
+      if (int rc = gemv_f32_dec_launch<GEMV_ACCUM>(o, st, sms, pdl)) return rc;
+      GemvDecArgs g{};
       g.seg[0] = GemvSeg{m.w1 + l * int64_t(hd) * dim, m.hb, hd};
       g.seg[1] = GemvSeg{m.w3 + l * int64_t(hd) * dim, nullptr, hd};
-      g.nseg = 2; g.k4 = dim / 4; g.x = m.xb;
-      if (int rc = gemv_f32_launch<GEMV_GATE_UP>(g, st, sms)) return rc;
-      GemvArgs d{};
+      g.nseg = 2; g.k4 = dim / 4; g.x = m.x; g.norm_w = m.rms_ffn + l * dim; g.eps = 1e-5f;
+      if (int rc = gemv_f32_dec_launch<GEMV_GATE_UP>(g, st, sms, pdl)) return rc;
+      GemvDecArgs d{};
       d.seg[0] = GemvSeg{m.w2 + l * int64_t(dim) * hd, m.x, dim};
       d.nseg = 1; d.k4 = hd / 4; d.x = m.hb;
-      if (int rc = gemv_f32_launch<GEMV_ACCUM>(d, st, sms)) return rc;
+      if (int rc = gemv_f32_dec_launch<GEMV_ACCUM>(d, st, sms, pdl)) return rc;
     }
   }
-  dec_rmsnorm_kernel<<<1, 256, 0, st>>>(m.x, m.rms_final, m.xb, nullptr, dim, 1e-5f);
   {
-    GemvArgs g{};
+    GemvDecArgs g{};
     g.seg[0] = GemvSeg{m.wcls, m.logits, int(c.vocab_size)};
-    g.nseg = 1; g.k4 = dim / 4; g.x = m.xb;
-    if (int rc = gemv_f32_launch<GEMV_STORE>(g, st, sms)) return rc;
+    g.nseg = 1; g.k4 = dim / 4; g.x = m.x; g.norm_w = m.rms_final; g.eps = 1e-5f;
+    if (int rc = gemv_f32_dec_launch<GEMV_STORE>(g, st, sms, pdl)) return rc;
   }
-  argmax_advance_kernel<<<1, 1024, 0, st>>>(m.logits, int(c.vocab_size), m.ctl, m.prompt, m.out_tokens);
-  SIMP_LAUNCH_CHECK();
+  LAUNCH_OR_FAIL(argmax_advance_kernel, dim3(1), dim3(1024), 0, st, pdl, (const float*)m.logits, int(c.vocab_size),
+                 m.ctl, (const int32_t*)m.prompt, m.out_tokens);
   return SIMP_OK;
 }
 
@@ -416,7 +436,9 @@ SIMP_API int simp_llama_create(const simp_llama_config* cfg, void** model) {
   A((void**)&m->kc, size_t(c.n_layers) * c.seq_len * m->kv_dim * 4);
   A((void**)&m->vc, size_t(c.n_layers) * c.seq_len * m->kv_dim * 4);
   A((void**)&m->attn_part, size_t(c.n_heads) * m->nsplit * (hs + 2) * 4);
-  A((void**)&m->xp, w4_packed_bytes(int64_t(mx) + 32));
+  A((void**)&m->xpA, w4_packed_bytes(int64_t(mx) + 32));
+  A((void**)&m->xpB, w4_packed_bytes(int64_t(mx) + 32));
+  A((void**)&m->ss, (mx / 32 + 1) * 4);
   A((void**)&m->ctl, 64);
   if (rc != SIMP_OK) { simp_llama_destroy(m); return rc; }
   cudaMemsetAsync(m->ctl, 0, 64, ctx().stream);
@@ -557,7 +579,7 @@ SIMP_API int simp_llama_destroy(void* model) {
   if (m->graph) cudaGraphExecDestroy(m->graph);
   void* ptrs[] = {m->tok_emb, m->rms_att, m->rms_ffn, m->rms_final, m->wcls, m->wq, m->wk, m->wv, m->wo, m->w1, m->w2,
                   m->w3, m->qweights, m->scales, m->zeros, m->x, m->xb, m->hb, m->q, m->k, m->v, m->logits, m->kc,
-                  m->vc, m->attn_part, m->xp, m->ctl, m->prompt, m->out_tokens};
+                  m->vc, m->attn_part, m->xpA, m->xpB, m->ss, m->ctl, m->prompt, m->out_tokens};
   for (void* p : ptrs)
     if (p) cudaFree(p);
   delete m;

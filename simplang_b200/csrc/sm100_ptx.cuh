@@ -52,6 +52,7 @@ constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;  // 2 s: far above any legitim
 // Bounded wait.  `abort_flag` (shared memory) lets the roles of a CTA give up together.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           int* status, int site) {
+  if (*abort_flag) return false;
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = globaltimer_ns();
   for (uint32_t spin = 1;; ++spin) {
@@ -78,6 +79,13 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const CUtensorMap
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       ::"r"(dst_smem), "l"(m), "r"(bar), "r"(x), "r"(y)
       : "memory");
+}
+// 1-D bulk copy global -> shared (both addresses 16-byte aligned, size a multiple of 16), completion
+// counted in bytes on `bar`.
+__device__ __forceinline__ void bulk_load(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst_smem), "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
 }
 // 2-D tiled store shared -> global (bulk async group).
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, uint32_t src_smem, int x, int y) {

@@ -19,6 +19,7 @@
 // The 80-byte stride makes the 128-bit shared-memory reads of 8 neighbouring lanes conflict-free.
 #pragma once
 #include "common.cuh"
+#include "sm100_ptx.cuh"
 
 namespace simp {
 
@@ -80,19 +81,20 @@ __device__ __forceinline__ uint32_t dp4a_uu(uint32_t a, uint32_t b, uint32_t c) 
 
 // sum_j q_j * x16_j over one 32-weight chunk: weights `w` (4 words), packed inputs `xq` (4 uint4).
 __device__ __forceinline__ int w4_chunk_dot(const uint4& w, const uint4* xq) {
-  int ah = 0;
-  uint32_t al = 0;
+  // four independent accumulation chains (high/low byte x low/high nibble) keep the dp4a pipe fed
+  int ah0 = 0, ah1 = 0;
+  uint32_t al0 = 0, al1 = 0;
   const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
   for (int wd = 0; wd < 4; ++wd) {
     const uint32_t lo = ws[wd] & 0x0F0F0F0Fu;
     const uint32_t hi = (ws[wd] >> 4) & 0x0F0F0F0Fu;
-    ah = dp4a_us(lo, xq[wd].x, ah);
-    ah = dp4a_us(hi, xq[wd].y, ah);
-    al = dp4a_uu(lo, xq[wd].z, al);
-    al = dp4a_uu(hi, xq[wd].w, al);
+    ah0 = dp4a_us(lo, xq[wd].x, ah0);
+    ah1 = dp4a_us(hi, xq[wd].y, ah1);
+    al0 = dp4a_uu(lo, xq[wd].z, al0);
+    al1 = dp4a_uu(hi, xq[wd].w, al1);
   }
-  return ah * 256 + int(al);
+  return (ah0 + ah1) * 256 + int(al0 + al1);
 }
 
 // One matrix segment of a launch.  All segments share cols / group size / the packed input.
@@ -100,7 +102,7 @@ struct W4Seg {
   const uint8_t* qw;   // first byte of the matrix (16-byte aligned)
   const float* sc;     // first group scale of the matrix
   const float* zr;     // first group zero, or nullptr (symmetric: zero = -8*scale)
-  float* out;
+  float* out;          // f32 result rows (may be nullptr for W4_GATE_UP's second matrix)
   int rows;
 };
 enum W4Mode { W4_STORE = 0, W4_ADD = 1, W4_GATE_UP = 2 };
@@ -108,59 +110,152 @@ struct W4Args {
   W4Seg seg[3];
   int nseg;
   int cols, log2_cpg, groups_per_row;
-  const uint8_t* xp;     // packed input
-  const float* res;      // W4_ADD: out[i] = res[i] + dot   (segment 0 only)
-  int total_groups;      // row groups over all segments (W4_GATE_UP: over segment 0)
-  int seg_group_start[4];
+  const uint8_t* xp;       // packed input
+  // Deferred rmsnorm of the input: when ss_part != nullptr the packed input holds x[i]*w_norm[i] and every
+  // dot product is multiplied by 1/sqrt(sum(ss_part[0..n_ss)) / ss_div + eps).
+  const float* ss_part;
+  int n_ss;
+  float ss_div, eps;
+  const float* res;        // W4_ADD: new = res[i] + dot (segment 0 only); written to seg[0].out
+  // Packed output for the next GEMV, one chunk per 32-row tile (W4_ADD / W4_GATE_UP), may be nullptr:
+  // W4_ADD packs new*out_scale[i] (the next rmsnorm's weight; nullptr = 1), W4_GATE_UP packs silu(a)*b.
+  uint8_t* xp_out;
+  const float* out_scale;
+  float* ss_out;           // W4_ADD: per-tile sum of new^2 (deterministic partials of the next rmsnorm), may be nullptr
+  int total_tiles;         // 32-row tiles over all segments (W4_GATE_UP: over segment 0)
+  int* status;             // device error word for bounded waits
+  int seg_tile_start[4];
 };
 
-constexpr int W4_R = 2;                       // rows per warp per pass
-constexpr int W4_ROWS_PER_GROUP = W4_WARPS * W4_R;
+constexpr int W4_TILE = 32;  // rows per tile = one packed output chunk
 
-template <int MODE>
+// Shared-memory footprint of one pipeline stage: 8*RW rows of every streamed matrix with their scales (+zeros).
+inline size_t w4_stage_bytes(int cols, int groups_per_row, int nm, bool zeros, int rw) {
+  return size_t(nm) * size_t(8 * rw) * (size_t(cols / 2) + size_t(groups_per_row) * 4 * (zeros ? 2 : 1));
+}
+
+// Streaming kernel.  A block owns 32-row tiles; each tile is fetched in stages of 8*RW consecutive rows by
+// ONE bulk async copy per matrix (cp.async.bulk global -> shared, completion on an mbarrier; rows of a
+// row-major matrix are contiguous) plus one for their scales, two stages in flight.  The copies of the
+// first two stages are issued before the kernel waits for the producer of its input vector, so under
+// programmatic dependent launch the weights of layer n+1 are already streaming while layer n finishes.
+// Warps then read weights, scales and the packed input from shared memory only.
+template <int MODE, int RW>
 __global__ void __launch_bounds__(W4_WARPS * 32, 3) w4_gemv_kernel(const W4Args a) {
-  extern __shared__ __align__(16) uint4 xs[];
+  extern __shared__ __align__(128) uint8_t smem[];
+  __shared__ float ytile[2][W4_TILE];  // [0] value to pack, [1] new residual (for the sum of squares)
+  __shared__ float sh_inv_r;
+  __shared__ __align__(8) uint64_t bars[2];
+  __shared__ int abort_flag;
+  constexpr int NM = MODE == W4_GATE_UP ? 2 : 1;
+  constexpr int S_ROWS = 8 * RW;
+  constexpr int SPT = W4_TILE / S_ROWS;  // stages per tile
   const int nchunks = a.cols >> 5;
-  for (int i = threadIdx.x; i < nchunks * W4_CHUNK_U4; i += blockDim.x)
-    xs[i] = __ldg(reinterpret_cast<const uint4*>(a.xp) + i);
-  __syncthreads();
+  const int row_bytes = a.cols >> 1;
+  const int sc_row = a.groups_per_row;  // floats of scale per row
+  const bool has_z = a.seg[0].zr != nullptr;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_it = (nchunks + 31) >> 5;
-  const int64_t row_u4 = nchunks;  // uint4 of weights per row
-  constexpr int NM = MODE == W4_GATE_UP ? 2 : 1;  // matrices streamed together
-  for (int grp = blockIdx.x; grp < a.total_groups; grp += gridDim.x) {
-    int s = 0;
-    if (MODE != W4_GATE_UP) {
-      while (s + 1 < a.nseg && grp >= a.seg_group_start[s + 1]) ++s;
+  const size_t xs_bytes = size_t(nchunks) * (W4_CHUNK_U4 * 16);
+  const size_t mat_w = size_t(S_ROWS) * row_bytes, mat_s = size_t(S_ROWS) * sc_row * 4;
+  const size_t mat_bytes = mat_w + mat_s * (has_z ? 2 : 1);
+  const size_t stage_bytes = mat_bytes * NM;
+  uint4* xs = reinterpret_cast<uint4*>(smem);
+  auto stage_ptr = [&](int st, int m) { return smem + xs_bytes + st * stage_bytes + m * mat_bytes; };
+
+  const int my_tiles = int(blockIdx.x) < a.total_tiles ? (a.total_tiles - 1 - int(blockIdx.x)) / int(gridDim.x) + 1 : 0;
+  const int my_steps = my_tiles * SPT;
+  auto locate = [&](int q, int& s, int& row0, int& rows, int& tile) {
+    tile = int(blockIdx.x) + (q / SPT) * int(gridDim.x);
+    s = 0;
+    if (MODE != W4_GATE_UP)
+      while (s + 1 < a.nseg && tile >= a.seg_tile_start[s + 1]) ++s;
+    row0 = (tile - a.seg_tile_start[s]) * W4_TILE + (q % SPT) * S_ROWS;
+    rows = a.seg[s].rows;
+  };
+  // Requests stage q.  Full stages: one elected thread issues bulk copies; a ragged last stage is copied
+  // with plain loads by every thread (bulk copies need 16-byte multiples) and published by the same barrier.
+  auto issue = [&](int q) {
+    if (q >= my_steps) return;
+    int s, row0, rows, tile;
+    locate(q, s, row0, rows, tile);
+    const int st = q & 1;
+    const int vr = min(S_ROWS, rows - row0);
+    const uint32_t bar = ptx::smem_u32(&bars[st]);
+    if (vr <= 0) {
+      if (threadIdx.x == 0) ptx::mbar_arrive(bar);
+      return;
     }
-    const int row0 = (grp - a.seg_group_start[s]) * W4_ROWS_PER_GROUP + warp * W4_R;
-    const int rows = a.seg[s].rows;
-    if (row0 >= rows) continue;
-    float acc[NM][W4_R];
+    if (vr == S_ROWS) {
+      if (threadIdx.x == 0) {
+        ptx::mbar_arrive_expect_tx(bar, uint32_t(stage_bytes));
+#pragma unroll
+        for (int m = 0; m < NM; ++m) {
+          const W4Seg& sg = a.seg[MODE == W4_GATE_UP ? m : s];
+          uint8_t* dst = stage_ptr(st, m);
+          ptx::bulk_load(ptx::smem_u32(dst), sg.qw + size_t(row0) * row_bytes, uint32_t(mat_w), bar);
+          ptx::bulk_load(ptx::smem_u32(dst + mat_w), sg.sc + size_t(row0) * sc_row, uint32_t(mat_s), bar);
+          if (has_z) ptx::bulk_load(ptx::smem_u32(dst + mat_w + mat_s), sg.zr + size_t(row0) * sc_row, uint32_t(mat_s), bar);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int m = 0; m < NM; ++m) {
+        const W4Seg& sg = a.seg[MODE == W4_GATE_UP ? m : s];
+        uint8_t* dst = stage_ptr(st, m);
+        const uint4* src = reinterpret_cast<const uint4*>(sg.qw + size_t(row0) * row_bytes);
+        for (int i = threadIdx.x; i < vr * (row_bytes >> 4); i += blockDim.x) reinterpret_cast<uint4*>(dst)[i] = src[i];
+        for (int i = threadIdx.x; i < vr * sc_row; i += blockDim.x) {
+          reinterpret_cast<float*>(dst + mat_w)[i] = sg.sc[size_t(row0) * sc_row + i];
+          if (has_z) reinterpret_cast<float*>(dst + mat_w + mat_s)[i] = sg.zr[size_t(row0) * sc_row + i];
+        }
+      }
+      __syncthreads();
+      if (threadIdx.x == 0) ptx::mbar_arrive(bar);
+    }
+  };
+
+  if (threadIdx.x == 0) {
+    ptx::mbar_init(ptx::smem_u32(&bars[0]), 1);
+    ptx::mbar_init(ptx::smem_u32(&bars[1]), 1);
+    abort_flag = 0;
+    ptx::fence_barrier_init();
+  }
+  __syncthreads();
+  // Weights never change: the first two stages are requested before waiting for the producer of the input.
+  issue(0);
+  issue(1);
+  pdl_launch_dependents();
+  pdl_wait();
+  for (int i = threadIdx.x; i < nchunks * W4_CHUNK_U4; i += blockDim.x)
+    xs[i] = __ldg(reinterpret_cast<const uint4*>(a.xp) + i);
+  if (warp == 0) {
+    float inv_r = 1.0f;
+    if (a.ss_part) {
+      float ss = 0.0f;
+      for (int i = lane; i < a.n_ss; i += 32) ss += a.ss_part[i];
+      ss = warp_sum(ss);
+      inv_r = 1.0f / sqrtf(ss / a.ss_div + a.eps);
+    }
+    if (lane == 0) sh_inv_r = inv_r;
+  }
+  __syncthreads();
+  const float inv_r = sh_inv_r;
+
+  for (int q = 0; q < my_steps; ++q) {
+    int s, row0, rows, tile;
+    locate(q, s, row0, rows, tile);
+    const int st = q & 1;
+    if (!ptx::mbar_wait(ptx::smem_u32(&bars[st]), uint32_t(q >> 1) & 1u, &abort_flag, a.status, 10)) break;
+    float acc[NM][RW];
 #pragma unroll
     for (int m = 0; m < NM; ++m)
 #pragma unroll
-      for (int r = 0; r < W4_R; ++r) acc[m][r] = 0.0f;
-    constexpr int U = MODE == W4_GATE_UP ? 2 : 4;  // chunk-steps whose loads are issued together
-    for (int it0 = 0; it0 < n_it; it0 += U) {
-      uint4 wv[U][NM][W4_R];
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const int c = lane + ((it0 + u) << 5);
-#pragma unroll
-        for (int m = 0; m < NM; ++m)
-#pragma unroll
-          for (int r = 0; r < W4_R; ++r) {
-            const W4Seg& sg = a.seg[MODE == W4_GATE_UP ? m : s];
-            if (c < nchunks && row0 + r < rows)
-              wv[u][m][r] = ldg_nc_u4(reinterpret_cast<const uint4*>(sg.qw) + int64_t(row0 + r) * row_u4 + c);
-            else
-              wv[u][m][r] = make_uint4(0, 0, 0, 0);
-          }
-      }
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const int c = lane + ((it0 + u) << 5);
+      for (int r = 0; r < RW; ++r) acc[m][r] = 0.0f;
+    const int wr0 = warp * RW;  // first row of this warp inside the stage
+    if (row0 + wr0 < rows) {
+      for (int it = 0; it < n_it; ++it) {
+        const int c = lane + (it << 5);
         if (c < nchunks) {
           uint4 xq[4];
 #pragma unroll
@@ -170,59 +265,112 @@ __global__ void __launch_bounds__(W4_WARPS * 32, 3) w4_gemv_kernel(const W4Args 
           const int sum16 = int(meta.z);
           const int g = c >> a.log2_cpg;
 #pragma unroll
-          for (int m = 0; m < NM; ++m)
+          for (int m = 0; m < NM; ++m) {
+            const uint8_t* base = stage_ptr(st, m);
 #pragma unroll
-            for (int r = 0; r < W4_R; ++r) {
-              if (row0 + r < rows) {
-                const W4Seg& sg = a.seg[MODE == W4_GATE_UP ? m : s];
-                const int tot = w4_chunk_dot(wv[u][m][r], xq);
-                const int64_t sidx = int64_t(row0 + r) * a.groups_per_row + g;
-                const float scale = __ldg(sg.sc + sidx);
-                if (sg.zr == nullptr) {
+            for (int r = 0; r < RW; ++r) {
+              if (row0 + wr0 + r < rows) {
+                const uint4 w = *reinterpret_cast<const uint4*>(base + size_t(wr0 + r) * row_bytes + size_t(c) * 16);
+                const int tot = w4_chunk_dot(w, xq);
+                const float scale = reinterpret_cast<const float*>(base + mat_w)[(wr0 + r) * sc_row + g];
+                if (!has_z) {
                   acc[m][r] = fmaf(float(tot - 8 * sum16) * sx, scale, acc[m][r]);
                 } else {
-                  acc[m][r] = fmaf(float(tot) * sx, scale, fmaf(__ldg(sg.zr + sidx), sumx, acc[m][r]));
+                  const float z = reinterpret_cast<const float*>(base + mat_w + mat_s)[(wr0 + r) * sc_row + g];
+                  acc[m][r] = fmaf(float(tot) * sx, scale, fmaf(z, sumx, acc[m][r]));
                 }
               }
             }
+          }
         }
       }
     }
 #pragma unroll
-    for (int r = 0; r < W4_R; ++r) {
-      float v0 = warp_sum(acc[0][r]);
-      float v1 = NM == 2 ? warp_sum(acc[NM - 1][r]) : 0.0f;
-      if (lane == 0 && row0 + r < rows) {
-        if (MODE == W4_STORE) a.seg[s].out[row0 + r] = v0;
-        if (MODE == W4_ADD) a.seg[s].out[row0 + r] = a.res[row0 + r] + v0;
-        if (MODE == W4_GATE_UP) a.seg[0].out[row0 + r] = (v0 / (1.0f + expf(-v0))) * v1;
+    for (int r = 0; r < RW; ++r) {
+      const float v0 = warp_sum(acc[0][r]) * inv_r;
+      const float v1 = NM == 2 ? warp_sum(acc[NM - 1][r]) * inv_r : 0.0f;
+      if (lane == 0) {
+        const int row = row0 + wr0 + r;
+        const int slot = (q % SPT) * S_ROWS + wr0 + r;
+        float pack_v = 0.0f, new_v = 0.0f;
+        if (row < rows) {
+          if (MODE == W4_STORE) a.seg[s].out[row] = v0;
+          if (MODE == W4_ADD) {
+            new_v = a.res[row] + v0;
+            a.seg[s].out[row] = new_v;
+            pack_v = a.out_scale ? new_v * a.out_scale[row] : new_v;
+          }
+          if (MODE == W4_GATE_UP) {
+            pack_v = (v0 / (1.0f + expf(-v0))) * v1;
+            if (a.seg[0].out) a.seg[0].out[row] = pack_v;
+          }
+        }
+        ytile[0][slot] = pack_v;
+        ytile[1][slot] = new_v;
       }
     }
+    __syncthreads();  // every warp is done with stage st; ytile complete for this stage
+    if (MODE != W4_STORE && (q % SPT) == SPT - 1 && (a.xp_out || a.ss_out)) {
+      if (warp == 0) {
+        const int t_in_seg = tile - a.seg_tile_start[0];
+        if (a.xp_out) w4_pack_chunk(ytile[0][lane], lane, a.xp_out + size_t(t_in_seg) * (W4_CHUNK_U4 * 16));
+        if (MODE == W4_ADD && a.ss_out) {
+          const float qq = warp_sum(ytile[1][lane] * ytile[1][lane]);
+          if (lane == 0) a.ss_out[t_in_seg] = qq;
+        }
+      }
+      __syncthreads();
+    }
+    issue(q + 2);
   }
 }
 
-// Fills the group bookkeeping and launches.  All pointers are device pointers.
+// Fills the tile bookkeeping, sizes the stages and launches.  All pointers are device pointers.
 template <int MODE>
-inline int w4_launch(W4Args a, cudaStream_t st, int sm_count) {
+inline int w4_launch(W4Args a, cudaStream_t st, int sm_count, bool pdl = false) {
   int g = 0;
-  const int nseg_groups = MODE == W4_GATE_UP ? 1 : a.nseg;
-  for (int s = 0; s < nseg_groups; ++s) {
-    a.seg_group_start[s] = g;
-    g += (a.seg[s].rows + W4_ROWS_PER_GROUP - 1) / W4_ROWS_PER_GROUP;
+  const int nseg_tiles = MODE == W4_GATE_UP ? 1 : a.nseg;
+  for (int s = 0; s < nseg_tiles; ++s) {
+    a.seg_tile_start[s] = g;
+    g += (a.seg[s].rows + W4_TILE - 1) / W4_TILE;
   }
-  a.seg_group_start[nseg_groups] = g;
-  a.total_groups = g;
+  a.seg_tile_start[nseg_tiles] = g;
+  a.total_tiles = g;
   if (g == 0) return SIMP_OK;
-  const size_t smem = w4_packed_bytes(a.cols);
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaFuncSetAttribute(w4_gemv_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
-    attr_set = true;
+  a.status = ctx().dev_status;
+  constexpr int NM = MODE == W4_GATE_UP ? 2 : 1;
+  const bool zeros = a.seg[0].zr != nullptr;
+  for (int s = 0; s < a.nseg; ++s) {
+    const bool ok = (reinterpret_cast<uintptr_t>(a.seg[s].qw) & 15u) == 0 && (reinterpret_cast<uintptr_t>(a.seg[s].sc) & 15u) == 0 &&
+                    (!zeros || (reinterpret_cast<uintptr_t>(a.seg[s].zr) & 15u) == 0) && ((a.seg[s].zr != nullptr) == zeros);
+    if (!ok) return set_error(SIMP_ERR_SHAPE, "w4_gemv: weights, scales and zeros of every matrix must be 16-byte aligned");
   }
-  const int cap = sm_count * 3;
+  const size_t xs_bytes = w4_packed_bytes(a.cols);
+  const size_t budget = 74 * 1024;  // three blocks per SM when the row is short enough, else two
+  int rw = 4;
+  while (rw > 1 && xs_bytes + 2 * w4_stage_bytes(a.cols, a.groups_per_row, NM, zeros, rw) > budget) rw >>= 1;
+  if (rw == 1 && xs_bytes + 2 * w4_stage_bytes(a.cols, a.groups_per_row, NM, zeros, 2) <= 112 * 1024) rw = 2;
+  const size_t smem = xs_bytes + 2 * w4_stage_bytes(a.cols, a.groups_per_row, NM, zeros, rw);
+  if (smem > 220 * 1024) return set_error(SIMP_ERR_SHAPE, "w4_gemv: row too long for the shared-memory pipeline");
+  int per_sm = int((227 * 1024) / (smem + 1024));
+  per_sm = per_sm < 1 ? 1 : (per_sm > 3 ? 3 : per_sm);
+  const int cap = sm_count * per_sm;
   const int grid = g < cap ? g : cap;
-  w4_gemv_kernel<MODE><<<grid, W4_WARPS * 32, smem, st>>>(a);
-  SIMP_LAUNCH_CHECK();
+  cudaError_t e;
+#define W4_LAUNCH_RW(RWV)                                                                                   \
+  do {                                                                                                      \
+    static bool attr_set = false;                                                                           \
+    if (!attr_set) {                                                                                        \
+      cudaFuncSetAttribute(w4_gemv_kernel<MODE, RWV>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024); \
+      attr_set = true;                                                                                      \
+    }                                                                                                       \
+    e = launch_kernel(w4_gemv_kernel<MODE, RWV>, dim3(grid), dim3(W4_WARPS * 32), smem, st, pdl, a);        \
+  } while (0)
+  if (rw == 4) W4_LAUNCH_RW(4);
+  else if (rw == 2) W4_LAUNCH_RW(2);
+  else W4_LAUNCH_RW(1);
+#undef W4_LAUNCH_RW
+  if (e != cudaSuccess) return set_error(SIMP_ERR_CUDA, "w4_gemv launch failed: %s", cudaGetErrorString(e));
   return SIMP_OK;
 }
 

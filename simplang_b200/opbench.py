@@ -127,6 +127,38 @@ def bench_gemm_i8(iters):
             del B, Cd
 
 
+def bench_decode(which, n_new=128):
+    """Greedy decode tokens/s of the two model configurations (random init), device-timed over the
+    whole generation (prompt of 16 teacher-forced tokens + n_new generated)."""
+    from simplang_b200 import synth
+    peak, src = hbm_peak()
+    if which == "110m":
+        cfg = synth.STORIES_110M
+        m = sg.Llama(cfg, synth.llama_f32_tensors(cfg, 0))
+        d, h, L, V = cfg["dim"], cfg["hidden_dim"], cfg["n_layers"], cfg["vocab_size"]
+        wbytes = 4 * (L * (4 * d * d + 3 * d * h) + V * d)
+        name = "llama 110M f32 decode"
+    else:
+        cfg = synth.LLAMA_3B_W4
+        t, off = synth.llama_w4_tensors(cfg, 0, threads=16)
+        m = sg.Llama(cfg, t, w4=True, offsets=off)
+        d, h, L, V, gs = cfg["dim"], cfg["hidden_dim"], cfg["n_layers"], cfg["vocab_size"], cfg["group_size"]
+        nw = L * (4 * d * d + 3 * d * h)
+        wbytes = nw // 2 + 4 * nw // gs + 4 * V * d
+        name = "llama 3B W4 decode"
+    prompt = synth.prompt_tokens(16, cfg["vocab_size"])
+    m.generate(prompt, 8)
+    toks, _, ms = m.generate(prompt, n_new)
+    steps = 16 + n_new - 1
+    us = ms * 1e3 / steps
+    kv = 2 * cfg["n_layers"] * cfg["dim"] * 4 * (steps / 2)
+    print(json.dumps({"op": name, "tokens": steps, "us_per_token": round(us, 1), "tok_s": round(1e6 / us, 1),
+                      "weight_bytes_per_token": int(wbytes), "avg_kv_bytes_per_token": int(kv),
+                      "gb_s": round((wbytes + kv) / us / 1e3, 1), "frac_of_hbm_peak": round((wbytes + kv) / us / 1e3 / peak, 4),
+                      "peak_gb_s": peak, "peak": src}), flush=True)
+    m.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--iters", type=int, default=50)
@@ -142,6 +174,10 @@ def main():
         bench_rowops(args.iters)
     if "gemm_i8" in which:
         bench_gemm_i8(args.iters)
+    if "decode110m" in which:
+        bench_decode("110m")
+    if "decode3b" in which:
+        bench_decode("3b")
     sg.check(sg.lib().simp_gpu_check_device_status())
 
 
