@@ -176,6 +176,26 @@ int simp_llama_generate(void* model, const int32_t* prompt, int64_t n_prompt, in
                         int32_t* tokens_out, float* logits_trace, float* ms_out);
 int simp_llama_destroy(void* model);
 
+/* ---- multi-GPU (one process per GPU, NCCL over NVLink / NVSwitch) ---------------------------
+ * Replaces: the reference's only parallel schemes, OpenMP row tiles (src/mlir/mlir_pipeline.cpp:265-364)
+ * and host-side row chunks sharing B (simptensor/benchmarks/bench_int8_parallel_runner.cpp:70-91).
+ * Rank 0 creates the NCCL unique id (128 bytes); the host carries it to the other ranks.  Collectives run
+ * on the library stream.  With world == 1 every call degenerates to a local copy / no-op. */
+#define SIMP_DIST_ID_BYTES 128
+int simp_dist_unique_id(void* id_out, size_t bytes);
+int simp_dist_init(int rank, int world, const void* id, size_t bytes);
+int simp_dist_shutdown(void);
+int simp_dist_rank(void);
+int simp_dist_world(void);
+int simp_dist_allgather(const void* send_dev, void* recv_dev, size_t bytes_per_rank);
+int simp_dist_allreduce_f32(float* buf_dev, size_t count);
+/* N-sharded tensor_matmul on i8: A[M,K] replicated, this rank's column block of B ([K,N_local], or
+ * [N_local,K] when b_transposed); C_blocks_dev receives world blocks of M x N_local i32, block r being
+ * columns [r*N_local, (r+1)*N_local) of C.  One all-gather, no reduction: results stay bit-exact. */
+int simp_dist_matmul_i8_nsharded(const void* A_dev, const int8_t* B_local_dev, int32_t* C_blocks_dev,
+                                 int64_t M, int64_t K, int64_t N_local, int a_unsigned,
+                                 int b_transposed);
+
 #ifdef __cplusplus
 }
 #endif

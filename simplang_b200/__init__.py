@@ -66,6 +66,14 @@ _SIGNATURES = {
     "simp_llama_forward": [vp, i64, i64, vp],
     "simp_llama_generate": [vp, vp, i64, i64, vp, vp, C.POINTER(C.c_float)],
     "simp_llama_destroy": [vp],
+    "simp_dist_unique_id": [vp, C.c_size_t],
+    "simp_dist_init": [C.c_int, C.c_int, vp, C.c_size_t],
+    "simp_dist_shutdown": [],
+    "simp_dist_rank": [],
+    "simp_dist_world": [],
+    "simp_dist_allgather": [vp, vp, C.c_size_t],
+    "simp_dist_allreduce_f32": [vp, C.c_size_t],
+    "simp_dist_matmul_i8_nsharded": [vp, vp, vp, i64, i64, i64, C.c_int, C.c_int],
 }
 
 

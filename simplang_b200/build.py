@@ -59,7 +59,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
             if log:
                 print(log)
     if force or not _newer(LIB, objs):
-        cmd = [NVCC, "-shared", "-ccbin", HOST_CXX, "-o", LIB] + objs + ["-lcudart_static", "-ldl", "-lpthread", "-lrt"]
+        cmd = [NVCC, "-shared", "-ccbin", HOST_CXX, "-o", LIB] + objs + ["-lcudart_static", "-ldl", "-lpthread", "-lrt"]  # NCCL is dlopen-ed
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")

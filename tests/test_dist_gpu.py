@@ -1,0 +1,61 @@
+"""GPU test of the N-sharded int8 GEMM over NCCL (needs >= 2 GPUs; skipped otherwise): every rank must end
+with all column blocks, bit-exact against the oracle."""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank))
+    import torch
+    import torch.distributed as dist
+    import oracle
+    import simplang_b200 as sg
+    from simplang_b200 import dist as sd
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        sg.init(rank)
+        sd.init_from_env(sg)
+        M, K, N = 256, 512, 1024
+        rng = np.random.default_rng(3)
+        A = rng.integers(0, 256, (M, K), dtype=np.uint8)
+        B = rng.integers(-128, 128, (K, N), dtype=np.int8)
+        lo, hi = sd.column_shard(N, world, rank)
+        dA = sg.DeviceBuffer.from_numpy(A)
+        dB = sg.DeviceBuffer.from_numpy(np.ascontiguousarray(B[:, lo:hi]))
+        dC = sg.DeviceBuffer(world * M * (hi - lo) * 4)
+        sg.check(sg.lib().simp_dist_matmul_i8_nsharded(dA.ptr, dB.ptr, dC.ptr, M, K, hi - lo, 1, 0))
+        full = sd.assemble_column_blocks(dC.to_numpy(np.int32, (world, M, hi - lo)))
+        assert np.array_equal(full, oracle.tensor_matmul_i8(A, B))
+        np.save(os.path.join(out_dir, f"ok{rank}.npy"), np.array([1]))
+        sg.check(sg.lib().simp_dist_shutdown())
+    finally:
+        dist.destroy_process_group()
+
+
+def test_nsharded_gemm_two_ranks(gpu, tmp_path):
+    import ctypes
+    n = ctypes.c_int()
+    gpu.check(gpu.lib().simp_gpu_device_count(ctypes.byref(n)))
+    if n.value < 2:
+        pytest.skip("needs at least 2 GPUs")
+    import torch.multiprocessing as mp
+    mp.spawn(_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    assert all(os.path.exists(tmp_path / f"ok{r}.npy") for r in range(2))
