@@ -20,6 +20,9 @@
 // Shapes whose operand rows are not 16-byte multiples (a TMA requirement) run the dp4a kernel.
 #include <cuda.h>
 
+#include <cstdlib>
+#include <cstring>
+
 #include "common.cuh"
 #include "sm100_ptx.cuh"
 
@@ -34,7 +37,8 @@ constexpr int B_BYTES = BN * BK;            // 32 KB
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int GEMM_THREADS = 192;
 constexpr int TMEM_COLS = 512;
-constexpr size_t GEMM_SMEM = size_t(STAGES) * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int EPI_BYTES = 4 * 2 * 4096;      // per epilogue warp: two 32x32 i32 staging tiles for TMA stores
+constexpr size_t GEMM_SMEM = size_t(STAGES) * STAGE_BYTES + EPI_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 
 struct GemmParams {
   int M, N, K;
@@ -43,6 +47,7 @@ struct GemmParams {
   uint32_t idesc;
   int32_t* C;
   int* status;
+  int tma_store;    // 1: epilogue goes through shared memory + TMA stores (needs N % 4 == 0)
 };
 
 __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
@@ -57,12 +62,68 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
   tn = in_group / gsz;
 }
 
+
+// Epilogue of one 128 x 256 accumulator for the 32 rows owned by this warp: TMEM -> registers ->
+// (a) 128-byte-swizzled shared-memory tile -> TMA store of full 128-byte lines, two tiles in flight, or
+// (b) direct global stores when C's row pitch is not a 16-byte multiple.
+// Returns after the last tcgen05.ld has completed (the accumulator may then be reused).
+__device__ __forceinline__ void epilogue_rows(const CUtensorMap* tmap_c, const GemmParams& p, uint32_t tmem_acc,
+                                              int q, int lane, int row0, int n0, uint32_t stage_smem,
+                                              uint32_t& nstore) {
+  const int row = row0 + lane;
+  int32_t* crow = p.C + int64_t(row) * p.N + n0;
+  const bool vec_ok = (p.N % 4) == 0;
+#pragma unroll 1
+  for (int ch = 0; ch < BN / 32; ++ch) {
+    uint32_t r[32];
+    const int c0 = n0 + ch * 32;
+    if (p.tma_store) {
+      if (lane == 0) tma_store_wait_read<1>();  // at most the previous store (other buffer) is still reading
+      __syncwarp();
+    }
+    tmem_ld_32x32(tmem_acc + (uint32_t(q * 32) << 16) + uint32_t(ch * 32), r);
+    tmem_ld_wait();
+    if (p.tma_store) {
+      if (row0 < p.M && c0 < p.N) {
+        const uint32_t buf = stage_smem + (nstore & 1u) * 4096u;
+        ++nstore;
+        const uint32_t rowaddr = buf + uint32_t(lane) * 128u;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const uint32_t addr = rowaddr + (uint32_t(j ^ (lane & 7)) << 4);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(r[4 * j]), "r"(r[4 * j + 1]),
+                       "r"(r[4 * j + 2]), "r"(r[4 * j + 3])
+                       : "memory");
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          tma_store_2d(tmap_c, buf, c0, row0);
+          tma_store_commit();
+        }
+      }
+    } else if (row < p.M && c0 < p.N) {
+      if (vec_ok && c0 + 32 <= p.N) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          *reinterpret_cast<int4*>(crow + ch * 32 + 4 * j) =
+              make_int4(int(r[4 * j]), int(r[4 * j + 1]), int(r[4 * j + 2]), int(r[4 * j + 3]));
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (c0 + j < p.N) crow[ch * 32 + j] = int(r[j]);
+      }
+    }
+  }
+}
+
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
     gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                           const GemmParams p) {
+                           const __grid_constant__ CUtensorMap tmap_c, const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t bar_base = smem_base + STAGES * STAGE_BYTES;
+  const uint32_t epi_base = smem_base + STAGES * STAGE_BYTES;
+  const uint32_t bar_base = epi_base + EPI_BYTES;
   // barrier layout (8 bytes each): full[STAGES], empty[STAGES], tfull[2], tempty[2]; then tmem slot, abort flag
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
@@ -168,40 +229,21 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     const int q = warp & 3;  // TMEM lane quarter this warp may access
     int acc = 0;
     uint32_t acc_phase = 0;
-    const bool vec_ok = (p.N % 4) == 0;
+    const uint32_t my_stage = epi_base + uint32_t(warp - 2) * 8192u;
+    uint32_t nstore = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
       int tm, tn;
       tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
       if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, 4)) break;
       tc_fence_after_sync();
-      const int row = tm * BM + q * 32 + lane;
-      const int n0 = tn * BN;
-      int32_t* crow = p.C + int64_t(row) * p.N + n0;
-#pragma unroll 1
-      for (int ch = 0; ch < BN / 32; ++ch) {
-        uint32_t r[32];
-        tmem_ld_32x32(tmem_base + (uint32_t(q * 32) << 16) + uint32_t(acc * BN + ch * 32), r);
-        tmem_ld_wait();
-        const int c0 = n0 + ch * 32;
-        if (row < p.M && c0 < p.N) {
-          if (vec_ok && c0 + 32 <= p.N) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j)
-              *reinterpret_cast<int4*>(crow + ch * 32 + 4 * j) =
-                  make_int4(int(r[4 * j]), int(r[4 * j + 1]), int(r[4 * j + 2]), int(r[4 * j + 3]));
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (c0 + j < p.N) crow[ch * 32 + j] = int(r[j]);
-          }
-        }
-      }
+      epilogue_rows(&tmap_c, p, tmem_base + uint32_t(acc * BN), q, lane, tm * BM + q * 32, tn * BN, my_stage, nstore);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty_bar(acc));
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
     }
+    if (p.tma_store && lane == 0) tma_store_wait_all<0>();
   }
 
   tc_fence_before_sync();
@@ -209,6 +251,151 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// 2-CTA variant (cta_group::2): a pair of CTAs on neighbouring SMs owns one 256x256 tile.  Each CTA
+// loads its own 128 rows of A and its own 128 columns of B (no multicast; the tensor cores read the
+// peer's half of B over the cluster's shared-memory network), so a stage is 32 KB instead of 48 KB:
+// one third less L2->SM traffic per MAC and six stages of look-ahead instead of four.  The even CTA
+// issues tcgen05.mma.cta_group::2 (M = 256 across the pair); its commits are multicast to the
+// barriers of both CTAs.  Both CTAs run a TMA producer and four epilogue warps.
+constexpr int P_STAGES = 6;
+constexpr int P_A_BYTES = 128 * BK, P_B_BYTES = 128 * BK;
+constexpr int P_STAGE_BYTES = P_A_BYTES + P_B_BYTES;
+constexpr size_t GEMM2_SMEM = size_t(P_STAGES) * P_STAGE_BYTES + EPI_BYTES + 1024 + 256;
+
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+    gemm_i8_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                                const __grid_constant__ CUtensorMap tmap_c, const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t epi_base = smem_base + P_STAGES * P_STAGE_BYTES;
+  const uint32_t bar_base = epi_base + EPI_BYTES;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (P_STAGES + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * P_STAGES + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * P_STAGES + 2 + a); };
+  uint8_t* bar_generic = smem_raw + (bar_base - smem_u32(smem_raw));
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_generic + 8 * (2 * P_STAGES + 4));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_generic + 8 * (2 * P_STAGES + 4) + 8);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t cta_rank = cluster_ctarank();  // 0: even CTA (issues MMAs), 1: odd CTA
+  const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  const int num_tiles = p.tiles_m * p.tiles_n;  // 256 x 256 tiles
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < P_STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull_bar(a), 1);
+      mbar_init(tempty_bar(a), 8);  // 4 epilogue warps in each CTA of the pair
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    prefetch_tensormap(&tmap_a);
+    prefetch_tensormap(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(smem_u32(tmem_slot), TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();  // the peer's barriers are initialised before anything signals them
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        int tm, tn;
+        tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+        const int m0 = tm * 256 + int(cta_rank) * 128, n0 = tn * 256 + int(cta_rank) * 128;
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, 11)) { ok = false; break; }
+          const uint32_t sa = smem_base + stage * P_STAGE_BYTES;
+          const uint32_t sb = sa + P_A_BYTES;
+          if (cta_rank == 0) mbar_arrive_expect_tx(full_bar(stage), 2 * P_STAGE_BYTES);
+          tma_load_2d_pair(sa, &tmap_a, full_bar(stage), kb * BK, m0);
+          if (p.b_mn_major) tma_load_2d_pair(sb, &tmap_b, full_bar(stage), n0, kb * BK);
+          else tma_load_2d_pair(sb, &tmap_b, full_bar(stage), kb * BK, n0);
+          if (++stage == P_STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok)
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (even CTA only)
+    if (lane == 0 && cta_rank == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      const uint32_t b_kstep = p.b_mn_major ? (32u * 128u) >> 4 : 32u >> 4;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, 12)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + uint32_t(acc * BN);
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, 13)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t sa = smem_base + stage * P_STAGE_BYTES;
+          const uint32_t sb = sa + P_A_BYTES;
+          const uint64_t a_desc = make_smem_desc_sw128(sa, 16u, 1024u);
+          const uint64_t b_desc = make_smem_desc_sw128(sb, 16u, 1024u);
+#pragma unroll
+          for (int j = 0; j < BK / 32; ++j)
+            mma_i8_ss_pair(d_tmem, a_desc + uint64_t(j * 2), b_desc + uint64_t(j) * b_kstep, p.idesc,
+                           (kb | j) != 0 ? 1u : 0u);
+          mma_commit_pair(empty_bar(stage));
+          if (++stage == P_STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        mma_commit_pair(tfull_bar(acc));
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
+    const int q = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    const uint32_t my_stage = epi_base + uint32_t(warp - 2) * 8192u;
+    uint32_t nstore = 0;
+    for (int tile = pair; tile < num_tiles; tile += num_pairs) {
+      int tm, tn;
+      tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+      if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, 14)) break;
+      tc_fence_after_sync();
+      epilogue_rows(&tmap_c, p, tmem_base + uint32_t(acc * BN), q, lane, tm * 256 + int(cta_rank) * 128 + q * 32, tn * BN,
+                    my_stage, nstore);
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_even_cta(tempty_bar(acc));
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+    if (p.tma_store && lane == 0) tma_store_wait_all<0>();
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();  // no CTA of the pair retires while the other may still signal or read it
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, TMEM_COLS);
   }
 }
 
@@ -291,6 +478,21 @@ static EncodeTiledFn get_encode_fn() {
 }
 
 // 2-D u8 tensor map: `inner` contiguous bytes per row, `outer` rows, 128-byte swizzle.
+// 2-D i32 tensor map for C stores: 32 x 32 boxes (128-byte rows), 128-byte swizzle.
+static int make_map_c_i32(CUtensorMap* map, const void* base, int64_t n, int64_t m) {
+  EncodeTiledFn enc = get_encode_fn();
+  SIMP_REQUIRE(enc != nullptr, SIMP_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
+  cuuint64_t dims[2] = {cuuint64_t(n), cuuint64_t(m)};
+  cuuint64_t strides[1] = {cuuint64_t(n) * 4};
+  cuuint32_t box[2] = {32, 32};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_INT32, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  SIMP_REQUIRE(r == CUDA_SUCCESS, SIMP_ERR_CUDA, "cuTensorMapEncodeTiled (C) failed with CUresult %d", int(r));
+  return SIMP_OK;
+}
+
 static int make_map_u8(CUtensorMap* map, const void* base, int64_t inner, int64_t outer, int box_inner,
                        int box_outer) {
   EncodeTiledFn enc = get_encode_fn();
@@ -328,20 +530,66 @@ SIMP_API int simp_gpu_matmul_i8(const void* A, const int8_t* B, int32_t* C, int6
   // The tensor-core kernel pays a fixed pipeline fill per tile; tiny problems stay on dp4a.
   const bool tiny = M * N * K < int64_t(64) * 64 * 64;
   if (tma_ok && !tiny) {
+    // Kernel choice: the 2-CTA kernel for problems with at least one full wave of 256x256 tiles on the
+    // 74 CTA pairs; the 1-CTA kernel otherwise.  SIMP_GEMM_I8_KERNEL=1cta|2cta overrides (testing).
+    const int64_t tiles2 = cdiv(M, 256) * cdiv(N, 256);
+    bool use_pair = tiles2 >= (ctx().sm_count / 2) && ctx().sm_count >= 2;
+    if (const char* env = getenv("SIMP_GEMM_I8_KERNEL")) {
+      if (!strcmp(env, "1cta")) use_pair = false;
+      if (!strcmp(env, "2cta")) use_pair = true;
+    }
     CUtensorMap ma, mb;
-    if (int rc = make_map_u8(&ma, A, K, M, BK, BM)) return rc;
+    if (int rc = make_map_u8(&ma, A, K, M, BK, 128)) return rc;
     if (b_transposed) {
-      if (int rc = make_map_u8(&mb, B, K, N, BK, BN)) return rc;
+      if (int rc = make_map_u8(&mb, B, K, N, BK, use_pair ? 128 : BN)) return rc;
     } else {
       if (int rc = make_map_u8(&mb, B, N, K, 128, BK)) return rc;
     }
     GemmParams p;
     p.M = int(M); p.N = int(N); p.K = int(K);
-    p.tiles_m = int(cdiv(M, BM)); p.tiles_n = int(cdiv(N, BN)); p.num_kb = int(cdiv(K, BK));
+    p.num_kb = int(cdiv(K, BK));
     p.b_mn_major = b_transposed ? 0 : 1;
-    p.idesc = make_idesc_i8(BM, BN, /*a_signed=*/!a_unsigned, /*b_signed=*/true, false, !b_transposed);
     p.C = C;
     p.status = ctx().dev_status;
+    p.tma_store = (N % 4 == 0) ? 1 : 0;
+    if (const char* env = getenv("SIMP_GEMM_I8_EPILOGUE"))
+      if (!strcmp(env, "direct")) p.tma_store = 0;
+    CUtensorMap mc;
+    if (p.tma_store) {
+      if (int rc = make_map_c_i32(&mc, C, N, M)) return rc;
+    } else {
+      mc = ma;  // unused by the kernel
+    }
+    if (use_pair) {
+      p.tiles_m = int(cdiv(M, 256)); p.tiles_n = int(cdiv(N, BN));
+      p.idesc = make_idesc_i8(256, BN, /*a_signed=*/!a_unsigned, /*b_signed=*/true, false, !b_transposed);
+      static bool attr2_set = false;
+      if (!attr2_set) {
+        SIMP_CUDA(cudaFuncSetAttribute(gemm_i8_tcgen05_2cta_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       int(GEMM2_SMEM)));
+        attr2_set = true;
+      }
+      const int64_t tiles = int64_t(p.tiles_m) * p.tiles_n;
+      SIMP_REQUIRE(tiles <= 0x7fffffff, SIMP_ERR_SHAPE, "matmul_i8: too many tiles");
+      const int max_pairs = ctx().sm_count / 2;
+      const int pairs = int(tiles < max_pairs ? tiles : max_pairs);
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(unsigned(2 * pairs));
+      cfg.blockDim = dim3(GEMM_THREADS);
+      cfg.dynamicSmemBytes = GEMM2_SMEM;
+      cfg.stream = st;
+      cudaLaunchAttribute at[1];
+      at[0].id = cudaLaunchAttributeClusterDimension;
+      at[0].val.clusterDim.x = 2;
+      at[0].val.clusterDim.y = 1;
+      at[0].val.clusterDim.z = 1;
+      cfg.attrs = at;
+      cfg.numAttrs = 1;
+      SIMP_CUDA(cudaLaunchKernelEx(&cfg, gemm_i8_tcgen05_2cta_kernel, ma, mb, mc, p));
+      return SIMP_OK;
+    }
+    p.tiles_m = int(cdiv(M, BM)); p.tiles_n = int(cdiv(N, BN));
+    p.idesc = make_idesc_i8(BM, BN, /*a_signed=*/!a_unsigned, /*b_signed=*/true, false, !b_transposed);
     static bool attr_set = false;
     if (!attr_set) {
       SIMP_CUDA(cudaFuncSetAttribute(gemm_i8_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -351,7 +599,7 @@ SIMP_API int simp_gpu_matmul_i8(const void* A, const int8_t* B, int32_t* C, int6
     const int64_t tiles = int64_t(p.tiles_m) * p.tiles_n;
     SIMP_REQUIRE(tiles <= 0x7fffffff, SIMP_ERR_SHAPE, "matmul_i8: too many tiles");
     const int grid = int(tiles < ctx().sm_count ? tiles : ctx().sm_count);
-    gemm_i8_tcgen05_kernel<<<grid, GEMM_THREADS, GEMM_SMEM, st>>>(ma, mb, p);
+    gemm_i8_tcgen05_kernel<<<grid, GEMM_THREADS, GEMM_SMEM, st>>>(ma, mb, mc, p);
   } else {
     const int64_t gx = cdiv(N, 64), gy = cdiv(M, 64);
     SIMP_REQUIRE(gy <= 65535, SIMP_ERR_SHAPE, "matmul_i8: M too large for the dp4a kernel");
