@@ -196,6 +196,33 @@ int simp_dist_matmul_i8_nsharded(const void* A_dev, const int8_t* B_local_dev, i
                                  int64_t M, int64_t K, int64_t N_local, int a_unsigned,
                                  int b_transposed);
 
+/* ---- memref-ABI shims ----------------------------------------------------------------------
+ * What a GPU lowering pattern calls from compiled .sl code.  Arguments follow MLIR 14's std->LLVM
+ * expansion of memref operands: a 1-D dynamic memref (what `!simp.array<T>` becomes,
+ * src/mlir/lowering/ConvertSimpToMemRef.cpp:43-46) is (allocated, aligned, offset, size, stride); a
+ * static rank-2 memref (a `!simp.tensor`) is (allocated, aligned, offset, size0, size1, stride0, stride1) --
+ * the expansion the reference hosts write by hand (examples/llama2/generate_stories110M.cpp:12-22).
+ * Data pointers are HOST pointers; each shim forwards to the simp_host_* entry point of the op.  Scalars
+ * after the memrefs are the op's own operands in the order of the .sl builtin
+ * (src/mlir/mlir_codegen.cpp:1388-1530, 2068-2260).  Return value: status as above. */
+#define SIMP_MEMREF1(T, n) T* n##_allocated, T* n##_aligned, int64_t n##_offset, int64_t n##_size, int64_t n##_stride
+#define SIMP_MEMREF2(T, n)                                                                        \
+  T* n##_allocated, T* n##_aligned, int64_t n##_offset, int64_t n##_size0, int64_t n##_size1, \
+      int64_t n##_stride0, int64_t n##_stride1
+int32_t simp_rt_matmul_f32(SIMP_MEMREF1(float, lhs), SIMP_MEMREF1(float, rhs), SIMP_MEMREF1(float, out),
+                           int64_t m, int64_t k, int64_t n, int64_t lhs_off, int64_t rhs_off, int64_t out_off);
+int32_t simp_rt_rmsnorm_f32(SIMP_MEMREF1(float, x), SIMP_MEMREF1(float, w), SIMP_MEMREF1(float, y), int64_t n,
+                            float eps, int64_t weight_offset);
+int32_t simp_rt_softmax_f32(SIMP_MEMREF1(float, x), SIMP_MEMREF1(float, y), int64_t n, int64_t input_offset,
+                            int64_t output_offset);
+int32_t simp_rt_silu_f32(SIMP_MEMREF1(float, x), SIMP_MEMREF1(float, y), int64_t n);
+int32_t simp_rt_matmul_quant(SIMP_MEMREF1(int8_t, qweights), SIMP_MEMREF1(float, scales),
+                             SIMP_MEMREF1(float, zeros), SIMP_MEMREF1(float, x), SIMP_MEMREF1(float, out),
+                             int64_t rows, int64_t cols, int64_t group_size, int64_t offset);
+int32_t simp_rt_tensor_matmul_i8(SIMP_MEMREF2(int8_t, a), SIMP_MEMREF2(int8_t, b), SIMP_MEMREF2(int32_t, c));
+int32_t simp_rt_tensor_matmul_nt_i8(SIMP_MEMREF2(int8_t, a), SIMP_MEMREF2(int8_t, bt), SIMP_MEMREF2(int32_t, c));
+int32_t simp_rt_tensor_matmul_f32(SIMP_MEMREF2(float, a), SIMP_MEMREF2(float, b), SIMP_MEMREF2(float, c));
+
 #ifdef __cplusplus
 }
 #endif
