@@ -91,6 +91,20 @@ int simp_gpu_matmul_w4(const uint8_t* qweights_dev, const float* scales_dev, con
 int simp_gpu_dequant_w4(const uint8_t* qweights_dev, const float* scales_dev,
                         const float* zeros_dev, int64_t first_index, int64_t count,
                         int64_t group_size, float* out_dev);
+/* Same result as simp_gpu_matmul_w4, for callers that must not allocate device memory (a host that gave its
+ * whole memory budget to its own pool at start-up, or code running where the runtime forbids allocation).
+ * This entry point has no counterpart in the reference.  The packed copy of x that the streaming kernel
+ * needs lives in a fixed 40 KB device array inside the library instead of the growable arena, so:
+ *   - cols may not exceed SIMP_W4_NOALLOC_MAX_COLS (larger shapes are rejected with SIMP_ERR_SHAPE);
+ *   - the library must already be initialised (simp_gpu_init allocates; this call returns SIMP_ERR_STATE
+ *     rather than initialising on demand);
+ *   - the first call on a device looks the array's address up (cudaGetSymbolAddress): make that first
+ *     call before starting any stream capture;
+ *   - all calls share the array: calls whose kernels overlap on the GPU race, keep them on one stream. */
+#define SIMP_W4_NOALLOC_MAX_COLS 16384
+int simp_gpu_matmul_w4_noalloc(const uint8_t* qweights_dev, const float* scales_dev,
+                               const float* zeros_dev, const float* x_dev, float* out_dev, int64_t rows,
+                               int64_t cols, int64_t group_size, int64_t offset, int scale_mode);
 
 /* ---- rmsnorm / softmax / silu --------------------------------------------------------------
  * rmsnorm: y[r,i] = (x[r,i] / sqrt(mean_i(x[r,:]^2) + eps)) * w[woff + i]

@@ -41,6 +41,7 @@ _SIGNATURES = {
     "simp_gpu_matmul_i8": [vp, vp, vp, i64, i64, i64, C.c_int, C.c_int],
     "simp_gpu_matmul_w4": [vp, vp, vp, vp, vp, i64, i64, i64, i64, C.c_int],
     "simp_gpu_dequant_w4": [vp, vp, vp, i64, i64, i64, vp],
+    "simp_gpu_matmul_w4_noalloc": [vp, vp, vp, vp, vp, i64, i64, i64, i64, C.c_int],
     "simp_gpu_rmsnorm_f32": [vp, vp, vp, i64, i64, C.c_float, i64, i64, vp],
     "simp_gpu_softmax_f32": [vp, vp, i64, i64, i64, i64, i64],
     "simp_gpu_silu_f32": [vp, vp, vp, i64],

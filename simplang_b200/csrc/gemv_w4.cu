@@ -96,3 +96,89 @@ SIMP_API int simp_gpu_matmul_w4(const uint8_t* qw, const float* sc, const float*
   SIMP_LAUNCH_CHECK();
   return SIMP_OK;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant of simp_gpu_matmul_w4.
+//
+// Some hosts may not allocate device memory when they call into this library: a serving process
+// that hands its whole memory budget to its own pool at start-up (a later cudaMalloc then fails or
+// fragments the pool), or code running where the CUDA runtime forbids allocation altogether.  The
+// regular entry point keeps the packed copy of x in a library arena that is created on first use
+// and grows on demand; this one keeps it in a fixed device array that is part of the library image.
+//
+// The array holds the packed form of at most SIMP_W4_NOALLOC_MAX_COLS inputs (80 bytes per 32
+// inputs = 40 KB).  Every GPU that loads the library carries it until the process exits.  All calls
+// share it: the pack kernel rewrites the part a call uses before the GEMV reads it, so nothing has
+// to be cleared, but two calls whose kernels overlap on the GPU (different streams or threads) race
+// on it -- keep calls on one stream.
+constexpr int64_t W4_NOALLOC_MAX_COLS = 16384;
+static __device__ __align__(256) uint8_t w4_noalloc_scratch[(W4_NOALLOC_MAX_COLS / 32) * (simp::W4_CHUNK_U4 * 16)];
+
+// Device address of the array for the current device.  The symbol's name is only a host-side handle;
+// kernels need the address cudaGetSymbolAddress reports, looked up once per device.
+static int w4_noalloc_scratch_ptr(uint8_t** out) {
+  static uint8_t* cached[64] = {};
+  int dev = -1;
+  SIMP_CUDA(cudaGetDevice(&dev));
+  SIMP_REQUIRE(dev >= 0 && dev < 64, SIMP_ERR_STATE, "matmul_w4_noalloc: unexpected device index %d", dev);
+  if (!cached[dev]) {
+    void* p = nullptr;
+    SIMP_CUDA(cudaGetSymbolAddress(&p, w4_noalloc_scratch));
+    cached[dev] = static_cast<uint8_t*>(p);
+  }
+  *out = cached[dev];
+  return SIMP_OK;
+}
+
+SIMP_API int simp_gpu_matmul_w4_noalloc(const uint8_t* qw, const float* sc, const float* zr, const float* x,
+                                        float* out, int64_t rows, int64_t cols, int64_t gs, int64_t offset,
+                                        int scale_mode) {
+  SIMP_REQUIRE(ctx().ready, SIMP_ERR_STATE,
+               "matmul_w4_noalloc: call simp_gpu_init first (initialisation allocates; this entry point must not)");
+  SIMP_REQUIRE(rows >= 0 && cols >= 0 && offset >= 0, SIMP_ERR_ARG, "matmul_w4_noalloc: negative size or offset");
+  SIMP_REQUIRE(gs > 0, SIMP_ERR_ARG, "matmul_w4_noalloc: group_size must be positive");
+  SIMP_REQUIRE(scale_mode == 0 || scale_mode == 1, SIMP_ERR_ARG, "matmul_w4_noalloc: scale_mode must be 0 or 1");
+  SIMP_REQUIRE(cols <= W4_NOALLOC_MAX_COLS, SIMP_ERR_SHAPE,
+               "matmul_w4_noalloc: cols %lld exceeds the built-in scratch (max %lld); use simp_gpu_matmul_w4",
+               (long long)cols, (long long)W4_NOALLOC_MAX_COLS);
+  if (rows == 0) return SIMP_OK;
+  SIMP_REQUIRE(qw && sc && x && out, SIMP_ERR_ARG, "matmul_w4_noalloc: null pointer");
+  SIMP_REQUIRE(scale_mode == 0 || cols % gs == 0, SIMP_ERR_SHAPE,
+               "matmul_w4_noalloc: scale_mode 1 needs cols %% group_size == 0");
+  cudaStream_t st = ctx().stream;
+  int log2_cpg = -1;
+  for (int s = 0; s <= 5; ++s)
+    if (gs == (int64_t(32) << s)) log2_cpg = s;
+  const bool mode_ok = scale_mode == 1 ? (offset % gs == 0) : (gs == 128);
+  const uint8_t* base = qw + offset / 2;
+  const int64_t soff = scale_mode == 1 ? offset / gs : 0;
+  const bool sc_aligned = ((reinterpret_cast<uintptr_t>(sc + soff) & 15u) == 0) &&
+                          (!zr || (reinterpret_cast<uintptr_t>(zr + soff) & 15u) == 0);
+  const bool fast = sc_aligned && log2_cpg >= 0 && mode_ok && cols > 0 && cols % gs == 0 && offset % 32 == 0 &&
+                    ((reinterpret_cast<uintptr_t>(base) & 15u) == 0) && rows <= 0x7fffffff;
+  if (fast) {
+    uint8_t* xp = nullptr;
+    if (int rc = w4_noalloc_scratch_ptr(&xp)) return rc;
+    const int nchunks = int(cols / 32);
+    w4_pack_x_kernel<<<int(cdiv(nchunks, 8)), 256, 0, st>>>(x, xp, nchunks);
+    SIMP_LAUNCH_CHECK();
+    W4Args a{};
+    a.seg[0] = W4Seg{base, sc + soff, zr ? zr + soff : nullptr, out, int(rows)};
+    a.nseg = 1;
+    a.cols = int(cols);
+    a.log2_cpg = log2_cpg;
+    a.groups_per_row = int(cols / gs);
+    a.xp = xp;
+    return w4_launch<W4_STORE>(a, st, ctx().sm_count);
+  }
+  // shapes outside the streaming kernel's domain use the general kernel, which needs no scratch at all
+  if (cols == 0) {
+    SIMP_CUDA(cudaMemsetAsync(out, 0, size_t(rows) * sizeof(float), st));
+    return SIMP_OK;
+  }
+  const int64_t grid = cdiv(rows, 8);
+  SIMP_REQUIRE(grid <= 0x7fffffff, SIMP_ERR_SHAPE, "matmul_w4_noalloc: too many rows");
+  w4_gemv_general_kernel<<<int(grid), 256, 0, st>>>(qw, sc, zr, x, out, rows, cols, gs, offset, scale_mode);
+  SIMP_LAUNCH_CHECK();
+  return SIMP_OK;
+}
