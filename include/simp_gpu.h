@@ -177,6 +177,13 @@ typedef struct simp_llama_config {
   int64_t dim, hidden_dim, n_layers, n_heads, n_kv_heads, vocab_size, seq_len;
   int64_t w4;          /* 0: f32 projections, 1: W4 projections (scale_mode 1) */
   int64_t group_size;  /* W4 only: 32, 64, ... 1024 */
+  /* Tensor parallelism over the ranks of simp_dist_init (W4 model only; 0 or 1 = single GPU).  Every
+   * projection is split by output rows (q/k/v by heads, gate/up/down/wo and the classifier by rows); each
+   * rank keeps the KV cache of its heads; the row slices are exchanged with in-place NCCL all-gathers
+   * (four per layer + one for the logits), so every output element is still computed by one rank with
+   * the single-GPU reduction order.  simp_llama_load takes the FULL tensors on every rank and keeps
+   * this rank's rows; call simp_llama_set_w4_offsets before loading qweights / scales / zeros. */
+  int64_t tp_size;
 } simp_llama_config;
 int simp_llama_create(const simp_llama_config* cfg, void** model);
 int simp_llama_load(void* model, const char* name, const void* host, size_t bytes);

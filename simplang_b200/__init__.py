@@ -276,7 +276,7 @@ def host_tensor_matmul_i8(A: np.ndarray, B: np.ndarray, out: np.ndarray = None, 
 # ------------------------------------------------------------------------- LLaMA decode driver
 class LlamaConfig(C.Structure):
     _fields_ = [(n, i64) for n in ("dim", "hidden_dim", "n_layers", "n_heads", "n_kv_heads", "vocab_size", "seq_len",
-                                   "w4", "group_size")]
+                                   "w4", "group_size", "tp_size")]
 
 
 W4_FAMILIES = ("wq", "wk", "wv", "wo", "w1", "w2", "w3")
@@ -286,19 +286,20 @@ class Llama:
     """Device-resident LLaMA decoder (simp_llama_*).  ``tensors`` maps the .sl argument names to numpy arrays;
     for W4 pass qweights / scales [/ zeros] and ``offsets`` = {family: element offset}."""
 
-    def __init__(self, cfg: dict, tensors: dict, w4=False, offsets=None):
+    def __init__(self, cfg: dict, tensors: dict, w4=False, offsets=None, tp_size=1):
         c = LlamaConfig(**{k: cfg[k] for k in ("dim", "hidden_dim", "n_layers", "n_heads", "n_kv_heads", "vocab_size",
-                                                "seq_len")}, w4=int(w4), group_size=cfg.get("group_size", 0))
+                                                "seq_len")}, w4=int(w4), group_size=cfg.get("group_size", 0),
+                        tp_size=tp_size)
         h = vp()
         check(lib().simp_llama_create(C.byref(c), C.byref(h)))
         self.h = h
         self.vocab = cfg["vocab_size"]
+        if w4:  # offsets first: under tensor parallelism the loader slices the shared arrays with them
+            off = (i64 * 7)(*[offsets[f] if isinstance(offsets, dict) else offsets[i] for i, f in enumerate(W4_FAMILIES)])
+            check(lib().simp_llama_set_w4_offsets(self.h, off))
         for name, arr in tensors.items():
             arr = np.ascontiguousarray(arr)
             check(lib().simp_llama_load(self.h, name.encode(), arr.ctypes.data, arr.nbytes))
-        if w4:
-            off = (i64 * 7)(*[offsets[f] if isinstance(offsets, dict) else offsets[i] for i, f in enumerate(W4_FAMILIES)])
-            check(lib().simp_llama_set_w4_offsets(self.h, off))
 
     def forward(self, token: int, pos: int) -> np.ndarray:
         out = np.empty(self.vocab, np.float32)

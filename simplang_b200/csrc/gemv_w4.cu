@@ -73,7 +73,7 @@ SIMP_API int simp_gpu_matmul_w4(const uint8_t* qw, const float* sc, const float*
     uint8_t* xp = static_cast<uint8_t*>(scratch(w4_packed_bytes(cols), 5));
     SIMP_REQUIRE(xp != nullptr, SIMP_ERR_CUDA, "matmul_w4: out of device memory for the packed input");
     const int nchunks = int(cols / 32);
-    w4_pack_x_kernel<<<int(cdiv(nchunks, 8)), 256, 0, st>>>(x, xp, nchunks);
+    w4_pack_x_kernel<<<int(cdiv(nchunks, 8)), 256, 0, st>>>(x, xp, nchunks, nullptr, nullptr);
     SIMP_LAUNCH_CHECK();
     const int64_t soff = scale_mode == 1 ? offset / gs : 0;
     W4Args a{};
@@ -160,7 +160,7 @@ SIMP_API int simp_gpu_matmul_w4_noalloc(const uint8_t* qw, const float* sc, cons
     uint8_t* xp = nullptr;
     if (int rc = w4_noalloc_scratch_ptr(&xp)) return rc;
     const int nchunks = int(cols / 32);
-    w4_pack_x_kernel<<<int(cdiv(nchunks, 8)), 256, 0, st>>>(x, xp, nchunks);
+    w4_pack_x_kernel<<<int(cdiv(nchunks, 8)), 256, 0, st>>>(x, xp, nchunks, nullptr, nullptr);
     SIMP_LAUNCH_CHECK();
     W4Args a{};
     a.seg[0] = W4Seg{base, sc + soff, zr ? zr + soff : nullptr, out, int(rows)};

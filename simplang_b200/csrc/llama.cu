@@ -30,7 +30,10 @@ struct LlamaModel {
   float *wq = nullptr, *wk = nullptr, *wv = nullptr, *wo = nullptr, *w1 = nullptr, *w2 = nullptr, *w3 = nullptr;
   uint8_t* qweights = nullptr;
   float *scales = nullptr, *zeros = nullptr;
-  int64_t off[7] = {0, 0, 0, 0, 0, 0, 0};  // wq wk wv wo w1 w2 w3 element offsets (W4)
+  int64_t off[7] = {0, 0, 0, 0, 0, 0, 0};   // wq wk wv wo w1 w2 w3 element offsets in the caller's arrays (W4)
+  int64_t loff[7] = {0, 0, 0, 0, 0, 0, 0};  // the same for the device copy (differs under tensor parallelism)
+  bool offsets_set = false;
+  int tp = 1, rank = 0;                      // tensor-parallel degree and this rank
   // state (device)
   float *x = nullptr, *xb = nullptr, *hb = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *logits = nullptr;
   float *kc = nullptr, *vc = nullptr, *attn_part = nullptr;
@@ -296,7 +299,7 @@ static int enqueue_token(LlamaModel& m, cudaStream_t st) {
   LAUNCH_OR_FAIL(embed_kernel, dim3((dim + 255) / 256), dim3(256), 0, st, false, m.x, m.tok_emb, m.ctl, dim,
                  w4 ? m.rms_att : nullptr, w4 ? m.xpA : nullptr, m.ss);
   auto w4seg = [&](int fam, int64_t layer, int64_t rows, int64_t cols, float* out) {
-    const int64_t o = m.off[fam] + layer * rows * cols;
+    const int64_t o = m.loff[fam] + layer * rows * cols;
     return W4Seg{m.qweights + o / 2, m.scales + o / c.group_size, m.zeros ? m.zeros + o / c.group_size : nullptr, out,
                  int(rows)};
   };
@@ -371,6 +374,92 @@ static int enqueue_token(LlamaModel& m, cudaStream_t st) {
   return SIMP_OK;
 }
 
+// Tensor-parallel token (W4 model): every projection computes this rank's output rows from the full,
+// replicated input vector, and the row slices are exchanged with in-place all-gathers.  Packing of a
+// gathered vector (and the partial sums of the following rmsnorm) is done by the small pack kernel on
+// every rank, so each output element keeps the single-GPU arithmetic.
+static int enqueue_token_tp(LlamaModel& m, cudaStream_t st) {
+  const simp_llama_config& c = m.cfg;
+  const int R = m.tp, rk = m.rank;
+  const int dim = int(c.dim), hd = int(c.hidden_dim), kv = int(m.kv_dim), hs = int(m.head_size);
+  const int dim_l = dim / R, kv_l = kv / R, hd_l = hd / R, V_l = int(c.vocab_size) / R, heads_l = int(c.n_heads) / R;
+  const int sms = ctx().sm_count;
+  const int log2_cpg = __builtin_ctzll(uint64_t(c.group_size / 32));
+  const int n_ss = dim / 32;
+  LAUNCH_OR_FAIL(embed_kernel, dim3((dim + 255) / 256), dim3(256), 0, st, false, m.x, m.tok_emb, m.ctl, dim, m.rms_att,
+                 m.xpA, m.ss);
+  auto w4seg = [&](int fam, int64_t layer, int64_t rows_l, int64_t cols, float* out) {
+    const int64_t o = m.loff[fam] + layer * rows_l * cols;
+    return W4Seg{m.qweights + o / 2, m.scales + o / c.group_size, m.zeros ? m.zeros + o / c.group_size : nullptr, out,
+                 int(rows_l)};
+  };
+  auto w4args = [&](int cols, const uint8_t* xp) {
+    W4Args a{};
+    a.cols = cols; a.log2_cpg = log2_cpg; a.groups_per_row = int(cols / c.group_size); a.xp = xp;
+    a.eps = 1e-5f; a.ss_div = float(dim);
+    return a;
+  };
+  auto pack = [&](const float* x, uint8_t* xp, int n, const float* mul, float* ss, bool pdl) {
+    return launch_kernel(w4_pack_x_kernel, dim3((n / 32 + 7) / 8), dim3(256), 0, st, pdl, x, xp, n / 32, mul, ss);
+  };
+#define TP_CUDA(e) do { cudaError_t e__ = (e); if (e__ != cudaSuccess) return set_error(SIMP_ERR_CUDA, "tp decode launch failed: %s", cudaGetErrorString(e__)); } while (0)
+  for (int64_t l = 0; l < c.n_layers; ++l) {
+    {
+      W4Args a = w4args(dim, m.xpA);
+      a.seg[0] = w4seg(0, l, dim_l, dim, m.q);
+      a.seg[1] = w4seg(1, l, kv_l, dim, m.k);
+      a.seg[2] = w4seg(2, l, kv_l, dim, m.v);
+      a.nseg = 3; a.ss_part = m.ss; a.n_ss = n_ss;
+      if (int rc = w4_launch<W4_STORE>(a, st, sms, true)) return rc;
+    }
+    LAUNCH_OR_FAIL(rope_kv_kernel, dim3((dim_l / 2 + 127) / 128), dim3(128), 0, st, true, m.q, m.k, m.v, m.kc, m.vc,
+                   m.ctl, dim_l, kv_l, hs, int(c.seq_len), int(l));
+    LAUNCH_OR_FAIL(attn_decode_kernel, dim3(unsigned(heads_l), unsigned(m.nsplit)), dim3(ATT_WARPS * 32), 0, st, true,
+                   m.q, m.kc, m.vc, m.attn_part, m.ctl, hs, kv_l, int(c.n_heads / c.n_kv_heads), int(c.seq_len), int(l),
+                   m.nsplit);
+    LAUNCH_OR_FAIL(attn_combine_kernel, dim3((dim_l + 255) / 256), dim3(256), 0, st, true, m.attn_part,
+                   m.xb + rk * dim_l, (uint8_t*)nullptr, dim_l, hs, m.nsplit);
+    if (int rc = simp_dist_allgather(m.xb + rk * dim_l, m.xb, size_t(dim_l) * 4)) return rc;
+    TP_CUDA(pack(m.xb, m.xpB, dim, nullptr, nullptr, false));
+    {
+      W4Args a = w4args(dim, m.xpB);
+      a.seg[0] = w4seg(3, l, dim_l, dim, m.x + rk * dim_l);
+      a.nseg = 1; a.res = m.x + rk * dim_l;
+      if (int rc = w4_launch<W4_ADD>(a, st, sms, true)) return rc;
+    }
+    if (int rc = simp_dist_allgather(m.x + rk * dim_l, m.x, size_t(dim_l) * 4)) return rc;
+    TP_CUDA(pack(m.x, m.xpA, dim, m.rms_ffn + l * dim, m.ss, false));
+    {
+      W4Args g = w4args(dim, m.xpA);
+      g.seg[0] = w4seg(4, l, hd_l, dim, m.hb + rk * hd_l);
+      g.seg[1] = w4seg(6, l, hd_l, dim, nullptr);
+      g.nseg = 2; g.ss_part = m.ss; g.n_ss = n_ss;
+      if (int rc = w4_launch<W4_GATE_UP>(g, st, sms, true)) return rc;
+    }
+    if (int rc = simp_dist_allgather(m.hb + rk * hd_l, m.hb, size_t(hd_l) * 4)) return rc;
+    TP_CUDA(pack(m.hb, m.xpB, hd, nullptr, nullptr, false));
+    {
+      W4Args d = w4args(hd, m.xpB);
+      d.seg[0] = w4seg(5, l, dim_l, hd, m.x + rk * dim_l);
+      d.nseg = 1; d.res = m.x + rk * dim_l;
+      if (int rc = w4_launch<W4_ADD>(d, st, sms, true)) return rc;
+    }
+    if (int rc = simp_dist_allgather(m.x + rk * dim_l, m.x, size_t(dim_l) * 4)) return rc;
+    if (l + 1 < c.n_layers) TP_CUDA(pack(m.x, m.xpA, dim, m.rms_att + (l + 1) * dim, m.ss, false));
+  }
+  {
+    GemvDecArgs g{};
+    g.seg[0] = GemvSeg{m.wcls, m.logits + int64_t(rk) * V_l, V_l};
+    g.nseg = 1; g.k4 = dim / 4; g.x = m.x; g.norm_w = m.rms_final; g.eps = 1e-5f;
+    if (int rc = gemv_f32_dec_launch<GEMV_STORE>(g, st, sms, false)) return rc;
+  }
+  if (int rc = simp_dist_allgather(m.logits + int64_t(rk) * V_l, m.logits, size_t(V_l) * 4)) return rc;
+  LAUNCH_OR_FAIL(argmax_advance_kernel, dim3(1), dim3(1024), 0, st, false, (const float*)m.logits, int(c.vocab_size),
+                 m.ctl, (const int32_t*)m.prompt, m.out_tokens);
+#undef TP_CUDA
+  return SIMP_OK;
+}
+
 static int ensure_graph(LlamaModel& m) {
   if (m.graph) return SIMP_OK;
   cudaStream_t st = ctx().stream;
@@ -379,13 +468,13 @@ static int ensure_graph(LlamaModel& m) {
   int ctl_save[5];
   SIMP_CUDA(cudaMemcpyAsync(ctl_save, m.ctl, sizeof(ctl_save), cudaMemcpyDeviceToHost, st));
   SIMP_CUDA(cudaStreamSynchronize(st));
-  if (int rc = enqueue_token(m, st)) return rc;
+  if (int rc = (m.tp > 1 ? enqueue_token_tp(m, st) : enqueue_token(m, st))) return rc;
   SIMP_CUDA(cudaStreamSynchronize(st));
   SIMP_CUDA(cudaMemcpyAsync(m.ctl, ctl_save, sizeof(ctl_save), cudaMemcpyHostToDevice, st));
   SIMP_CUDA(cudaStreamSynchronize(st));
   cudaGraph_t g = nullptr;
   SIMP_CUDA(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
-  const int rc = enqueue_token(m, st);
+  const int rc = m.tp > 1 ? enqueue_token_tp(m, st) : enqueue_token(m, st);
   cudaError_t e = cudaStreamEndCapture(st, &g);
   if (rc != SIMP_OK) {
     if (g) cudaGraphDestroy(g);
@@ -422,8 +511,21 @@ SIMP_API int simp_llama_create(const simp_llama_config* cfg, void** model) {
     SIMP_REQUIRE(c.dim % gs == 0 && c.hidden_dim % gs == 0 && c.dim <= 16384 && c.hidden_dim <= 16384, SIMP_ERR_SHAPE,
                  "llama_create: W4 needs dim and hidden_dim to be multiples of group_size and <= 16384");
   }
+  const int tp = c.tp_size > 1 ? int(c.tp_size) : 1;
+  if (tp > 1) {
+    SIMP_REQUIRE(c.w4 != 0, SIMP_ERR_UNSUPPORTED, "llama_create: tensor parallelism is implemented for the W4 model only");
+    SIMP_REQUIRE(tp == simp_dist_world(), SIMP_ERR_STATE, "llama_create: tp_size %d but simp_dist_init world is %d", tp,
+                 simp_dist_world());
+    SIMP_REQUIRE(c.n_heads % tp == 0 && c.n_kv_heads % tp == 0 && c.hidden_dim % tp == 0 && c.vocab_size % tp == 0,
+                 SIMP_ERR_SHAPE, "llama_create: heads, kv heads, hidden_dim and vocab_size must be multiples of tp_size");
+    SIMP_REQUIRE(((c.dim / tp) * (c.dim / c.group_size)) % 4 == 0 && ((c.hidden_dim / tp) * (c.dim / c.group_size)) % 4 == 0 &&
+                     ((c.dim / tp) * (c.hidden_dim / c.group_size)) % 4 == 0,
+                 SIMP_ERR_SHAPE, "llama_create: row slices leave the scale arrays misaligned (need 16-byte multiples)");
+  }
   LlamaModel* m = new LlamaModel();
   m->cfg = c;
+  m->tp = tp;
+  m->rank = tp > 1 ? simp_dist_rank() : 0;
   m->head_size = hs;
   m->kv_dim = c.dim * c.n_kv_heads / c.n_heads;
   m->nsplit = int(c.seq_len >= 1024 ? 8 : (c.seq_len >= 256 ? 4 : 1));
@@ -433,8 +535,9 @@ SIMP_API int simp_llama_create(const simp_llama_config* cfg, void** model) {
   A((void**)&m->x, c.dim * 4); A((void**)&m->xb, mx * 4); A((void**)&m->hb, c.hidden_dim * 4);
   A((void**)&m->q, c.dim * 4); A((void**)&m->k, m->kv_dim * 4); A((void**)&m->v, m->kv_dim * 4);
   A((void**)&m->logits, c.vocab_size * 4);
-  A((void**)&m->kc, size_t(c.n_layers) * c.seq_len * m->kv_dim * 4);
-  A((void**)&m->vc, size_t(c.n_layers) * c.seq_len * m->kv_dim * 4);
+  const size_t kv_bytes = size_t(c.n_layers) * c.seq_len * (m->kv_dim / tp) * 4;  // this rank's heads only
+  A((void**)&m->kc, kv_bytes);
+  A((void**)&m->vc, kv_bytes);
   A((void**)&m->attn_part, size_t(c.n_heads) * m->nsplit * (hs + 2) * 4);
   A((void**)&m->xpA, w4_packed_bytes(int64_t(mx) + 32));
   A((void**)&m->xpB, w4_packed_bytes(int64_t(mx) + 32));
@@ -442,8 +545,8 @@ SIMP_API int simp_llama_create(const simp_llama_config* cfg, void** model) {
   A((void**)&m->ctl, 64);
   if (rc != SIMP_OK) { simp_llama_destroy(m); return rc; }
   cudaMemsetAsync(m->ctl, 0, 64, ctx().stream);
-  cudaMemsetAsync(m->kc, 0, size_t(c.n_layers) * c.seq_len * m->kv_dim * 4, ctx().stream);
-  cudaMemsetAsync(m->vc, 0, size_t(c.n_layers) * c.seq_len * m->kv_dim * 4, ctx().stream);
+  cudaMemsetAsync(m->kc, 0, kv_bytes, ctx().stream);
+  cudaMemsetAsync(m->vc, 0, kv_bytes, ctx().stream);
   *model = m;
   return SIMP_OK;
 }
@@ -473,6 +576,45 @@ SIMP_API int simp_llama_load(void* model, const char* name, const void* host, si
   else if (n == "zeros") { slot = (void**)&m.zeros; want = bytes; }
   SIMP_REQUIRE(slot != nullptr, SIMP_ERR_ARG, "llama_load: unknown tensor name '%s'", name);
   SIMP_REQUIRE(bytes == want, SIMP_ERR_SHAPE, "llama_load: '%s' needs %zu bytes, got %zu", name, want, bytes);
+  if (m.tp > 1 && (n == "qweights" || n == "scales" || n == "zeros" || n == "wcls")) {
+    // keep this rank's rows only
+    cudaStream_t st = ctx().stream;
+    if (*slot) { cudaStreamSynchronize(st); cudaFree(*slot); *slot = nullptr; }
+    if (n == "wcls") {
+      const size_t rows_l = V / m.tp;
+      if (int rc = dev_alloc(slot, rows_l * d * 4)) return rc;
+      SIMP_CUDA(cudaMemcpyAsync(*slot, static_cast<const float*>(host) + size_t(m.rank) * rows_l * d, rows_l * d * 4,
+                                cudaMemcpyHostToDevice, st));
+    } else {
+      SIMP_REQUIRE(m.offsets_set, SIMP_ERR_STATE, "llama_load: call simp_llama_set_w4_offsets before loading '%s'", name);
+      const size_t fam_rows[7] = {d, kv, kv, d, h, d, h}, fam_cols[7] = {d, d, d, d, d, h, d};
+      const size_t gs = size_t(c.group_size);
+      size_t total_l = 0;
+      for (int f = 0; f < 7; ++f) total_l += L * (fam_rows[f] / m.tp) * fam_cols[f];
+      const bool is_q = n == "qweights";
+      if (int rc = dev_alloc(slot, is_q ? total_l / 2 : total_l / gs * 4)) return rc;
+      for (int f = 0; f < 7; ++f) {
+        const size_t rows_l = fam_rows[f] / m.tp, cols = fam_cols[f];
+        for (size_t l = 0; l < L; ++l) {
+          const size_t src = size_t(m.off[f]) + l * fam_rows[f] * cols + size_t(m.rank) * rows_l * cols;  // elements
+          const size_t dst = size_t(m.loff[f]) + l * rows_l * cols;
+          const size_t cnt = rows_l * cols;
+          if (is_q) {
+            SIMP_REQUIRE((src + cnt) / 2 <= bytes, SIMP_ERR_SHAPE, "llama_load: qweights shorter than the offsets imply");
+            SIMP_CUDA(cudaMemcpyAsync(static_cast<uint8_t*>(*slot) + dst / 2, static_cast<const uint8_t*>(host) + src / 2,
+                                      cnt / 2, cudaMemcpyHostToDevice, st));
+          } else {
+            SIMP_REQUIRE((src + cnt) / gs * 4 <= bytes, SIMP_ERR_SHAPE, "llama_load: '%s' shorter than the offsets imply", name);
+            SIMP_CUDA(cudaMemcpyAsync(static_cast<float*>(*slot) + dst / gs, static_cast<const float*>(host) + src / gs,
+                                      cnt / gs * 4, cudaMemcpyHostToDevice, st));
+          }
+        }
+      }
+    }
+    SIMP_CUDA(cudaStreamSynchronize(st));
+    if (m.graph) { cudaGraphExecDestroy(m.graph); m.graph = nullptr; }
+    return SIMP_OK;
+  }
   if (*slot) { cudaStreamSynchronize(ctx().stream); cudaFree(*slot); *slot = nullptr; }
   if (int rc = dev_alloc(slot, bytes)) return rc;
   SIMP_CUDA(cudaMemcpyAsync(*slot, host, bytes, cudaMemcpyHostToDevice, ctx().stream));
@@ -490,6 +632,18 @@ SIMP_API int simp_llama_set_w4_offsets(void* model, const int64_t* offsets7) {
                  (long long)offsets7[i]);
     m.off[i] = offsets7[i];
   }
+  if (m.tp > 1) {
+    const int64_t d = m.cfg.dim, h = m.cfg.hidden_dim, kv = m.kv_dim, L = m.cfg.n_layers;
+    const int64_t fam_rows[7] = {d, kv, kv, d, h, d, h}, fam_cols[7] = {d, d, d, d, d, h, d};
+    int64_t acc = 0;
+    for (int f = 0; f < 7; ++f) {
+      m.loff[f] = acc;
+      acc += L * (fam_rows[f] / m.tp) * fam_cols[f];
+    }
+  } else {
+    for (int i = 0; i < 7; ++i) m.loff[i] = m.off[i];
+  }
+  m.offsets_set = true;
   if (m.graph) { cudaGraphExecDestroy(m.graph); m.graph = nullptr; }
   return SIMP_OK;
 }
@@ -498,6 +652,7 @@ static int check_loaded(const LlamaModel& m) {
   const bool common = m.tok_emb && m.rms_att && m.rms_ffn && m.rms_final && m.wcls;
   const bool proj = m.cfg.w4 ? (m.qweights && m.scales) : (m.wq && m.wk && m.wv && m.wo && m.w1 && m.w2 && m.w3);
   SIMP_REQUIRE(common && proj, SIMP_ERR_STATE, "llama: not all tensors are loaded");
+  SIMP_REQUIRE(!m.cfg.w4 || m.offsets_set, SIMP_ERR_STATE, "llama: call simp_llama_set_w4_offsets for the W4 model");
   return SIMP_OK;
 }
 

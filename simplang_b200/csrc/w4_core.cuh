@@ -54,11 +54,21 @@ __device__ __forceinline__ void w4_pack_chunk(float xv, int lane, uint8_t* chunk
   }
 }
 
+// Packs x (optionally x[i]*mul[i], the next rmsnorm's weight) chunk by chunk; ss_out (optional) receives the
+// sum of squares of the unscaled x per chunk -- the deterministic partials of that rmsnorm.
 static __global__ void __launch_bounds__(256) w4_pack_x_kernel(const float* __restrict__ x, uint8_t* __restrict__ xp,
-                                                        int nchunks) {
+                                                               int nchunks, const float* __restrict__ mul,
+                                                               float* __restrict__ ss_out) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (warp >= nchunks) return;
-  w4_pack_chunk(x[warp * 32 + lane], lane, xp + size_t(warp) * (W4_CHUNK_U4 * 16));
+  const float v = x[warp * 32 + lane];
+  w4_pack_chunk(mul ? v * mul[warp * 32 + lane] : v, lane, xp + size_t(warp) * (W4_CHUNK_U4 * 16));
+  if (ss_out) {
+    const float q = warp_sum(v * v);
+    if (lane == 0) ss_out[warp] = q;
+  }
 }
 
 __device__ __forceinline__ uint4 ldg_nc_u4(const uint4* p) {

@@ -59,3 +59,63 @@ def test_nsharded_gemm_two_ranks(gpu, tmp_path):
     import torch.multiprocessing as mp
     mp.spawn(_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
     assert all(os.path.exists(tmp_path / f"ok{r}.npy") for r in range(2))
+
+
+def _tp_worker(rank, world, port, out_dir, which):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank))
+    import torch
+    import torch.distributed as dist
+    import oracle
+    import simplang_b200 as sg
+    from simplang_b200 import dist as sd, synth
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        sg.init(rank)
+        sd.init_from_env(sg)
+        if which == "tiny":
+            cfg = dict(dim=256, hidden_dim=512, n_layers=3, n_heads=8, n_kv_heads=8, vocab_size=320, seq_len=64,
+                       group_size=64)
+            n_prompt, n_new = 4, 24
+        else:
+            cfg = synth.LLAMA_3B_W4
+            n_prompt, n_new = 16, 16
+        t, off = synth.llama_w4_tensors(cfg, 11, threads=8)
+        prompt = synth.prompt_tokens(n_prompt, cfg["vocab_size"])
+        m = sg.Llama(cfg, t, w4=True, offsets=off, tp_size=world)
+        toks, trace, ms = m.generate(prompt, n_new, trace_logits=True)
+        if rank == 0:
+            om = oracle.Llama(cfg, t, w4=True, offsets={k + "_off": v for k, v in off.items()}, threads=0)
+            tok, ref, worst = int(prompt[0]), [], 0.0
+            for pos in range(n_prompt + n_new - 1):
+                lg = om.forward(tok, pos)
+                worst = max(worst, float(np.max(np.abs(trace[pos] - lg)) / np.max(np.abs(lg))))
+                nxt = oracle.argmax(lg)
+                tok = int(prompt[pos + 1]) if pos + 1 < n_prompt else nxt
+                if pos + 1 >= n_prompt:
+                    ref.append(nxt)
+            assert worst <= 1e-3, worst
+            assert list(toks) == ref
+            print(f"TP{world} {which}: worst logit err {worst:.2e}, {(n_prompt + n_new - 1) / ms * 1e3:.0f} tok/s")
+        allt = [None] * world
+        dist.all_gather_object(allt, toks.tolist())
+        assert all(a == allt[0] for a in allt)  # every rank generated the same sequence
+        np.save(os.path.join(out_dir, f"tp_{which}_{rank}.npy"), np.array([1]))
+        m.close()
+        sg.check(sg.lib().simp_dist_shutdown())
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("which", ["tiny", "3b"])
+def test_tensor_parallel_w4_decode_two_ranks(gpu, tmp_path, which):
+    import ctypes
+    n = ctypes.c_int()
+    gpu.check(gpu.lib().simp_gpu_device_count(ctypes.byref(n)))
+    if n.value < 2:
+        pytest.skip("needs at least 2 GPUs")
+    import torch.multiprocessing as mp
+    mp.spawn(_tp_worker, args=(2, _free_port(), str(tmp_path), which), nprocs=2, join=True)
+    assert all(os.path.exists(tmp_path / f"tp_{which}_{r}.npy") for r in range(2))
