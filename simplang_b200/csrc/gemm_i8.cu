@@ -48,6 +48,8 @@ struct GemmParams {
   int32_t* C;
   int* status;
   int tma_store;    // 1: epilogue goes through shared memory + TMA stores (needs N % 4 == 0)
+  int bn;           // tile width in columns (multiple of 32, <= 256); the 2-CTA kernel always uses 256
+  uint32_t stage_tx;  // bytes one stage's TMA loads deliver (1-CTA kernel)
 };
 
 __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
@@ -74,7 +76,7 @@ __device__ __forceinline__ void epilogue_rows(const CUtensorMap* tmap_c, const G
   int32_t* crow = p.C + int64_t(row) * p.N + n0;
   const bool vec_ok = (p.N % 4) == 0;
 #pragma unroll 1
-  for (int ch = 0; ch < BN / 32; ++ch) {
+  for (int ch = 0; ch < p.bn / 32; ++ch) {
     uint32_t r[32];
     const int c0 = n0 + ch * 32;
     if (p.tma_store) {
@@ -168,16 +170,16 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         int tm, tn;
         tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
-        const int m0 = tm * BM, n0 = tn * BN;
+        const int m0 = tm * BM, n0 = tn * p.bn;
         for (int kb = 0; kb < p.num_kb; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, 1)) { ok = false; break; }
           const uint32_t sa = smem_base + stage * STAGE_BYTES;
           const uint32_t sb = sa + A_BYTES;
-          mbar_arrive_expect_tx(full_bar(stage), STAGE_BYTES);
+          mbar_arrive_expect_tx(full_bar(stage), p.stage_tx);
           tma_load_2d(sa, &tmap_a, full_bar(stage), kb * BK, m0);
           if (p.b_mn_major) {
             tma_load_2d(sb, &tmap_b, full_bar(stage), n0, kb * BK);
-            tma_load_2d(sb + B_BYTES / 2, &tmap_b, full_bar(stage), n0 + 128, kb * BK);
+            if (p.bn > 128) tma_load_2d(sb + B_BYTES / 2, &tmap_b, full_bar(stage), n0 + 128, kb * BK);
           } else {
             tma_load_2d(sb, &tmap_b, full_bar(stage), kb * BK, n0);
           }
@@ -236,7 +238,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
       tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
       if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, 4)) break;
       tc_fence_after_sync();
-      epilogue_rows(&tmap_c, p, tmem_base + uint32_t(acc * BN), q, lane, tm * BM + q * 32, tn * BN, my_stage, nstore);
+      epilogue_rows(&tmap_c, p, tmem_base + uint32_t(acc * BN), q, lane, tm * BM + q * 32, tn * p.bn, my_stage, nstore);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty_bar(acc));
@@ -561,6 +563,8 @@ SIMP_API int simp_gpu_matmul_i8(const void* A, const int8_t* B, int32_t* C, int6
       mc = ma;  // unused by the kernel
     }
     if (use_pair) {
+      p.bn = BN;
+      p.stage_tx = 0;
       p.tiles_m = int(cdiv(M, 256)); p.tiles_n = int(cdiv(N, BN));
       p.idesc = make_idesc_i8(256, BN, /*a_signed=*/!a_unsigned, /*b_signed=*/true, false, !b_transposed);
       static bool attr2_set = false;
@@ -588,8 +592,24 @@ SIMP_API int simp_gpu_matmul_i8(const void* A, const int8_t* B, int32_t* C, int6
       SIMP_CUDA(cudaLaunchKernelEx(&cfg, gemm_i8_tcgen05_2cta_kernel, ma, mb, mc, p));
       return SIMP_OK;
     }
-    p.tiles_m = int(cdiv(M, BM)); p.tiles_n = int(cdiv(N, BN));
-    p.idesc = make_idesc_i8(BM, BN, /*a_signed=*/!a_unsigned, /*b_signed=*/true, false, !b_transposed);
+    // Tile width.  Measured on B200: a kind::i8 MMA of M = 128 takes the same ~128 clocks for every N <= 256
+    // (the array is 256 columns wide and narrower tiles leave it idle), so narrower tiles never pay back in
+    // math time; the width only shrinks for matrices narrower than one tile, to avoid loading padding.
+    int bn = BN;
+    {
+      if (N < BN) bn = int(cdiv(N, 32) * 32);
+      if (const char* env = getenv("SIMP_GEMM_I8_BN")) {
+        const int v = atoi(env);
+        if (v >= 32 && v <= 256 && v % 32 == 0) bn = v;
+      }
+    }
+    if (b_transposed) {  // the K-major B box height follows the tile width
+      if (int rc = make_map_u8(&mb, B, K, N, BK, bn)) return rc;
+    }
+    p.bn = bn;
+    p.stage_tx = uint32_t(A_BYTES + (b_transposed ? bn * BK : (bn > 128 ? 2 : 1) * 128 * BK));
+    p.tiles_m = int(cdiv(M, BM)); p.tiles_n = int(cdiv(N, bn));
+    p.idesc = make_idesc_i8(BM, bn, /*a_signed=*/!a_unsigned, /*b_signed=*/true, false, !b_transposed);
     static bool attr_set = false;
     if (!attr_set) {
       SIMP_CUDA(cudaFuncSetAttribute(gemm_i8_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
