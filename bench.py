@@ -35,9 +35,10 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 NOMINAL_INT8_TOPS = 4500.0  # B200 dense int8, vendor figure
-# dram__bytes_read.sum + dram__bytes_write.sum of one gemm_i8_tcgen05_kernel launch at 8192^3,
-# from the ncu capture summarised in profiles/gemm_i8_tcgen05_8192.md (null until captured).
-NCU_TRAFFIC_BYTES = {8192: None}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch.  4096^3 is the ncu capture summarised in
+# profiles/gemm_i8_tcgen05_2cta_8192.md; 8192^3 is too large to capture under the profiling size rule and is
+# scaled from it by the units processed (reads x4, plus the full 256 MB result, which no longer stays in L2).
+NCU_TRAFFIC_BYTES = {4096: 52_200_000, 8192: 393_000_000}
 
 
 def measured_peaks():
@@ -291,7 +292,7 @@ def run_ours(args):
                                    "int8 MMA issues at twice the bf16 rate",
                      "frac_of_nominal_4500": tops / world / NOMINAL_INT8_TOPS,
                      "traffic": NCU_TRAFFIC_BYTES.get(S), "algorithmic_bytes": int(M * K + K * N + 4 * M * N),
-                     "kernel": "gemm_i8_tcgen05_kernel"},
+                     "kernel": "gemm_i8_tcgen05_2cta_kernel" if (M // 256) * (N // world // 256) >= 74 else "gemm_i8_tcgen05_kernel"},
     }
     if world == 1 and not args.no_cpu:
         tera, times, sample, kind, cores = cpu_reference_gemm(min(S, 8192), 2, 1)
