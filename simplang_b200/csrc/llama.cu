@@ -67,6 +67,19 @@ __global__ void __launch_bounds__(256) embed_kernel(float* __restrict__ x, const
   }
 }
 
+// rmsnorm of one row before the classifier: y = (x / sqrt(ss/n + eps)) * w (the arithmetic of rmsnorm_any_kernel).
+__global__ void __launch_bounds__(1024) dec_rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                                           float* __restrict__ y, int n, float eps) {
+  __shared__ float red[33];
+  pdl_launch_dependents();
+  pdl_wait();
+  float ss = 0.0f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) ss += x[i] * x[i];
+  ss = block_sum(ss, red);
+  const float r = sqrtf(ss / float(n) + eps);
+  for (int i = threadIdx.x; i < n; i += blockDim.x) y[i] = (x[i] / r) * w[i];
+}
+
 // RoPE on (even, odd) pairs of q and k, then store k and v into the caches at `pos`
 // (examples/llama2/stories110M.sl:86-121): freq = 1 / 10000^((i % hs)/hs), angle = pos * freq.
 __global__ void rope_kv_kernel(float* __restrict__ q, float* __restrict__ k, const float* __restrict__ v,
@@ -288,36 +301,18 @@ static int dev_alloc(void** p, size_t bytes) {
 
 // Enqueues one token.  Every launch after the first uses programmatic dependent launch: each kernel
 // requests its first weights, then waits for its predecessor before touching activations.
+static int enqueue_token_tp(LlamaModel& m, cudaStream_t st);
+
 static int enqueue_token(LlamaModel& m, cudaStream_t st) {
   const simp_llama_config& c = m.cfg;
+  if (c.w4) return enqueue_token_tp(m, st);  // the W4 model shares one path for 1 and R ranks
   const int dim = int(c.dim), hd = int(c.hidden_dim), kv = int(m.kv_dim), hs = int(m.head_size);
   const int sms = ctx().sm_count;
-  const bool w4 = c.w4 != 0;
   const bool pdl = true;
-  const int log2_cpg = w4 ? __builtin_ctzll(uint64_t(c.group_size / 32)) : 0;
-  const int n_ss = dim / 32;
   LAUNCH_OR_FAIL(embed_kernel, dim3((dim + 255) / 256), dim3(256), 0, st, false, m.x, m.tok_emb, m.ctl, dim,
-                 w4 ? m.rms_att : nullptr, w4 ? m.xpA : nullptr, m.ss);
-  auto w4seg = [&](int fam, int64_t layer, int64_t rows, int64_t cols, float* out) {
-    const int64_t o = m.loff[fam] + layer * rows * cols;
-    return W4Seg{m.qweights + o / 2, m.scales + o / c.group_size, m.zeros ? m.zeros + o / c.group_size : nullptr, out,
-                 int(rows)};
-  };
-  auto w4args = [&](int cols, const uint8_t* xp) {
-    W4Args a{};
-    a.cols = cols; a.log2_cpg = log2_cpg; a.groups_per_row = int(cols / c.group_size); a.xp = xp;
-    a.eps = 1e-5f; a.ss_div = float(dim);
-    return a;
-  };
+                 (const float*)nullptr, (uint8_t*)nullptr, m.ss);
   for (int64_t l = 0; l < c.n_layers; ++l) {
-    if (w4) {
-      W4Args a = w4args(dim, m.xpA);
-      a.seg[0] = w4seg(0, l, dim, dim, m.q);
-      a.seg[1] = w4seg(1, l, kv, dim, m.k);
-      a.seg[2] = w4seg(2, l, kv, dim, m.v);
-      a.nseg = 3; a.ss_part = m.ss; a.n_ss = n_ss;
-      if (int rc = w4_launch<W4_STORE>(a, st, sms, pdl)) return rc;
-    } else {
+    {
       GemvDecArgs g{};
       g.seg[0] = GemvSeg{m.wq + l * dim * dim, m.q, dim};
       g.seg[1] = GemvSeg{m.wk + l * int64_t(kv) * dim, m.k, kv};
@@ -331,23 +326,8 @@ static int enqueue_token(LlamaModel& m, cudaStream_t st) {
                    m.q, m.kc, m.vc, m.attn_part, m.ctl, hs, kv, int(c.n_heads / c.n_kv_heads), int(c.seq_len), int(l),
                    m.nsplit);
     LAUNCH_OR_FAIL(attn_combine_kernel, dim3((dim + 255) / 256), dim3(256), 0, st, pdl, m.attn_part, m.xb,
-                   w4 ? m.xpB : nullptr, dim, hs, m.nsplit);
-    if (w4) {
-      W4Args a = w4args(dim, m.xpB);
-      a.seg[0] = w4seg(3, l, dim, dim, m.x);
-      a.nseg = 1; a.res = m.x; a.xp_out = m.xpA; a.out_scale = m.rms_ffn + l * dim; a.ss_out = m.ss;
-      if (int rc = w4_launch<W4_ADD>(a, st, sms, pdl)) return rc;
-      W4Args g = w4args(dim, m.xpA);
-      g.seg[0] = w4seg(4, l, hd, dim, nullptr);
-      g.seg[1] = w4seg(6, l, hd, dim, nullptr);
-      g.nseg = 2; g.ss_part = m.ss; g.n_ss = n_ss; g.xp_out = m.xpB;
-      if (int rc = w4_launch<W4_GATE_UP>(g, st, sms, pdl)) return rc;
-      W4Args d = w4args(hd, m.xpB);
-      d.seg[0] = w4seg(5, l, dim, hd, m.x);
-      d.nseg = 1; d.res = m.x; d.ss_out = m.ss;
-      if (l + 1 < c.n_layers) { d.xp_out = m.xpA; d.out_scale = m.rms_att + (l + 1) * dim; }
-      if (int rc = w4_launch<W4_ADD>(d, st, sms, pdl)) return rc;
-    } else {
+                   (uint8_t*)nullptr, dim, hs, m.nsplit);
+    {
       GemvDecArgs o{};
       o.seg[0] = GemvSeg{m.wo + l * dim * dim, m.x, dim};
       o.nseg = 1; o.k4 = dim / 4; o.x = m.xb;
@@ -363,18 +343,20 @@ static int enqueue_token(LlamaModel& m, cudaStream_t st) {
       if (int rc = gemv_f32_dec_launch<GEMV_ACCUM>(d, st, sms, pdl)) return rc;
     }
   }
+  LAUNCH_OR_FAIL(dec_rmsnorm_kernel, dim3(1), dim3(1024), 0, st, pdl, (const float*)m.x, (const float*)m.rms_final, m.xb,
+                 dim, 1e-5f);
   {
-    GemvDecArgs g{};
+    GemvArgs g{};
     g.seg[0] = GemvSeg{m.wcls, m.logits, int(c.vocab_size)};
-    g.nseg = 1; g.k4 = dim / 4; g.x = m.x; g.norm_w = m.rms_final; g.eps = 1e-5f;
-    if (int rc = gemv_f32_dec_launch<GEMV_STORE>(g, st, sms, pdl)) return rc;
+    g.nseg = 1; g.k4 = dim / 4; g.x = m.xb;
+    if (int rc = gemv_f32_launch<GEMV_STORE>(g, st, sms)) return rc;
   }
-  LAUNCH_OR_FAIL(argmax_advance_kernel, dim3(1), dim3(1024), 0, st, pdl, (const float*)m.logits, int(c.vocab_size),
+  LAUNCH_OR_FAIL(argmax_advance_kernel, dim3(1), dim3(1024), 0, st, false, (const float*)m.logits, int(c.vocab_size),
                  m.ctl, (const int32_t*)m.prompt, m.out_tokens);
   return SIMP_OK;
 }
 
-// Tensor-parallel token (W4 model): every projection computes this rank's output rows from the full,
+// W4 token, single GPU (R = 1) or tensor-parallel: every projection computes this rank's output rows from the full,
 // replicated input vector, and the row slices are exchanged with in-place all-gathers.  Packing of a
 // gathered vector (and the partial sums of the following rmsnorm) is done by the small pack kernel on
 // every rank, so each output element keeps the single-GPU arithmetic.
@@ -386,6 +368,7 @@ static int enqueue_token_tp(LlamaModel& m, cudaStream_t st) {
   const int sms = ctx().sm_count;
   const int log2_cpg = __builtin_ctzll(uint64_t(c.group_size / 32));
   const int n_ss = dim / 32;
+  const bool chain = R == 1;  // no NCCL kernels in between: every launch can be a programmatic dependent
   LAUNCH_OR_FAIL(embed_kernel, dim3((dim + 255) / 256), dim3(256), 0, st, false, m.x, m.tok_emb, m.ctl, dim, m.rms_att,
                  m.xpA, m.ss);
   auto w4seg = [&](int fam, int64_t layer, int64_t rows_l, int64_t cols, float* out) {
@@ -420,7 +403,7 @@ static int enqueue_token_tp(LlamaModel& m, cudaStream_t st) {
     LAUNCH_OR_FAIL(attn_combine_kernel, dim3((dim_l + 255) / 256), dim3(256), 0, st, true, m.attn_part,
                    m.xb + rk * dim_l, (uint8_t*)nullptr, dim_l, hs, m.nsplit);
     if (int rc = simp_dist_allgather(m.xb + rk * dim_l, m.xb, size_t(dim_l) * 4)) return rc;
-    TP_CUDA(pack(m.xb, m.xpB, dim, nullptr, nullptr, false));
+    TP_CUDA(pack(m.xb, m.xpB, dim, nullptr, nullptr, chain));
     {
       W4Args a = w4args(dim, m.xpB);
       a.seg[0] = w4seg(3, l, dim_l, dim, m.x + rk * dim_l);
@@ -428,7 +411,7 @@ static int enqueue_token_tp(LlamaModel& m, cudaStream_t st) {
       if (int rc = w4_launch<W4_ADD>(a, st, sms, true)) return rc;
     }
     if (int rc = simp_dist_allgather(m.x + rk * dim_l, m.x, size_t(dim_l) * 4)) return rc;
-    TP_CUDA(pack(m.x, m.xpA, dim, m.rms_ffn + l * dim, m.ss, false));
+    TP_CUDA(pack(m.x, m.xpA, dim, m.rms_ffn + l * dim, m.ss, chain));
     {
       W4Args g = w4args(dim, m.xpA);
       g.seg[0] = w4seg(4, l, hd_l, dim, m.hb + rk * hd_l);
@@ -437,7 +420,7 @@ static int enqueue_token_tp(LlamaModel& m, cudaStream_t st) {
       if (int rc = w4_launch<W4_GATE_UP>(g, st, sms, true)) return rc;
     }
     if (int rc = simp_dist_allgather(m.hb + rk * hd_l, m.hb, size_t(hd_l) * 4)) return rc;
-    TP_CUDA(pack(m.hb, m.xpB, hd, nullptr, nullptr, false));
+    TP_CUDA(pack(m.hb, m.xpB, hd, nullptr, nullptr, chain));
     {
       W4Args d = w4args(hd, m.xpB);
       d.seg[0] = w4seg(5, l, dim_l, hd, m.x + rk * dim_l);
@@ -445,13 +428,15 @@ static int enqueue_token_tp(LlamaModel& m, cudaStream_t st) {
       if (int rc = w4_launch<W4_ADD>(d, st, sms, true)) return rc;
     }
     if (int rc = simp_dist_allgather(m.x + rk * dim_l, m.x, size_t(dim_l) * 4)) return rc;
-    if (l + 1 < c.n_layers) TP_CUDA(pack(m.x, m.xpA, dim, m.rms_att + (l + 1) * dim, m.ss, false));
+    if (l + 1 < c.n_layers) TP_CUDA(pack(m.x, m.xpA, dim, m.rms_att + (l + 1) * dim, m.ss, chain));
   }
+  LAUNCH_OR_FAIL(dec_rmsnorm_kernel, dim3(1), dim3(1024), 0, st, chain, (const float*)m.x, (const float*)m.rms_final,
+                 m.xb, dim, 1e-5f);
   {
-    GemvDecArgs g{};
+    GemvArgs g{};
     g.seg[0] = GemvSeg{m.wcls, m.logits + int64_t(rk) * V_l, V_l};
-    g.nseg = 1; g.k4 = dim / 4; g.x = m.x; g.norm_w = m.rms_final; g.eps = 1e-5f;
-    if (int rc = gemv_f32_dec_launch<GEMV_STORE>(g, st, sms, false)) return rc;
+    g.nseg = 1; g.k4 = dim / 4; g.x = m.xb;
+    if (int rc = gemv_f32_launch<GEMV_STORE>(g, st, sms)) return rc;
   }
   if (int rc = simp_dist_allgather(m.logits + int64_t(rk) * V_l, m.logits, size_t(V_l) * 4)) return rc;
   LAUNCH_OR_FAIL(argmax_advance_kernel, dim3(1), dim3(1024), 0, st, false, (const float*)m.logits, int(c.vocab_size),

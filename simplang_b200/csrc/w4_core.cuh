@@ -110,9 +110,9 @@ __device__ __forceinline__ int w4_chunk_dot(const uint4& w, const uint4* xq) {
 // One matrix segment of a launch.  All segments share cols / group size / the packed input.
 struct W4Seg {
   const uint8_t* qw;   // first byte of the matrix (16-byte aligned)
-  const float* sc;     // first group scale of the matrix
+  const float* sc;     // first group scale of the matrix (16-byte aligned)
   const float* zr;     // first group zero, or nullptr (symmetric: zero = -8*scale)
-  float* out;          // f32 result rows (may be nullptr for W4_GATE_UP's second matrix)
+  float* out;          // f32 result rows
   int rows;
 };
 enum W4Mode { W4_STORE = 0, W4_ADD = 1, W4_GATE_UP = 2 };
@@ -126,40 +126,32 @@ struct W4Args {
   const float* ss_part;
   int n_ss;
   float ss_div, eps;
-  const float* res;        // W4_ADD: new = res[i] + dot (segment 0 only); written to seg[0].out
-  // Packed output for the next GEMV, one chunk per 32-row tile (W4_ADD / W4_GATE_UP), may be nullptr:
-  // W4_ADD packs new*out_scale[i] (the next rmsnorm's weight; nullptr = 1), W4_GATE_UP packs silu(a)*b.
-  uint8_t* xp_out;
-  const float* out_scale;
-  float* ss_out;           // W4_ADD: per-tile sum of new^2 (deterministic partials of the next rmsnorm), may be nullptr
-  int total_tiles;         // 32-row tiles over all segments (W4_GATE_UP: over segment 0)
+  const float* res;        // W4_ADD: out[i] = res[i] + dot (segment 0 only)
+  int total_tiles;         // row tiles over all segments (W4_GATE_UP: over segment 0)
   int* status;             // device error word for bounded waits
   int seg_tile_start[4];
 };
-
-constexpr int W4_TILE = 32;  // rows per tile = one packed output chunk
 
 // Shared-memory footprint of one pipeline stage: 8*RW rows of every streamed matrix with their scales (+zeros).
 inline size_t w4_stage_bytes(int cols, int groups_per_row, int nm, bool zeros, int rw) {
   return size_t(nm) * size_t(8 * rw) * (size_t(cols / 2) + size_t(groups_per_row) * 4 * (zeros ? 2 : 1));
 }
 
-// Streaming kernel.  A block owns 32-row tiles; each tile is fetched in stages of 8*RW consecutive rows by
-// ONE bulk async copy per matrix (cp.async.bulk global -> shared, completion on an mbarrier; rows of a
-// row-major matrix are contiguous) plus one for their scales, two stages in flight.  The copies of the
-// first two stages are issued before the kernel waits for the producer of its input vector, so under
-// programmatic dependent launch the weights of layer n+1 are already streaming while layer n finishes.
-// Warps then read weights, scales and the packed input from shared memory only.
+// Streaming kernel.  A block owns tiles of 8*RW consecutive rows; a tile is fetched by ONE bulk async copy
+// per matrix (cp.async.bulk global -> shared, completion on an mbarrier; rows of a row-major matrix are
+// contiguous) plus one for its scales, two tiles in flight.  The copies of the first two tiles are issued
+// before the kernel waits for the producer of its input vector, so under programmatic dependent launch
+// the weights of the next projection are already streaming while the previous kernel finishes.
+// Warps then read weights, scales and the packed input from shared memory only; warp w owns rows
+// w*RW .. w*RW+RW-1 of the tile, lanes split the 32-weight chunks, one shuffle reduction per row.
 template <int MODE, int RW>
 __global__ void __launch_bounds__(W4_WARPS * 32, 3) w4_gemv_kernel(const W4Args a) {
   extern __shared__ __align__(128) uint8_t smem[];
-  __shared__ float ytile[2][W4_TILE];  // [0] value to pack, [1] new residual (for the sum of squares)
   __shared__ float sh_inv_r;
   __shared__ __align__(8) uint64_t bars[2];
   __shared__ int abort_flag;
   constexpr int NM = MODE == W4_GATE_UP ? 2 : 1;
   constexpr int S_ROWS = 8 * RW;
-  constexpr int SPT = W4_TILE / S_ROWS;  // stages per tile
   const int nchunks = a.cols >> 5;
   const int row_bytes = a.cols >> 1;
   const int sc_row = a.groups_per_row;  // floats of scale per row
@@ -173,29 +165,24 @@ __global__ void __launch_bounds__(W4_WARPS * 32, 3) w4_gemv_kernel(const W4Args 
   uint4* xs = reinterpret_cast<uint4*>(smem);
   auto stage_ptr = [&](int st, int m) { return smem + xs_bytes + st * stage_bytes + m * mat_bytes; };
 
-  const int my_tiles = int(blockIdx.x) < a.total_tiles ? (a.total_tiles - 1 - int(blockIdx.x)) / int(gridDim.x) + 1 : 0;
-  const int my_steps = my_tiles * SPT;
-  auto locate = [&](int q, int& s, int& row0, int& rows, int& tile) {
-    tile = int(blockIdx.x) + (q / SPT) * int(gridDim.x);
+  const int my_steps = int(blockIdx.x) < a.total_tiles ? (a.total_tiles - 1 - int(blockIdx.x)) / int(gridDim.x) + 1 : 0;
+  auto locate = [&](int q, int& s, int& row0, int& rows) {
+    const int tile = int(blockIdx.x) + q * int(gridDim.x);
     s = 0;
     if (MODE != W4_GATE_UP)
       while (s + 1 < a.nseg && tile >= a.seg_tile_start[s + 1]) ++s;
-    row0 = (tile - a.seg_tile_start[s]) * W4_TILE + (q % SPT) * S_ROWS;
+    row0 = (tile - a.seg_tile_start[s]) * S_ROWS;
     rows = a.seg[s].rows;
   };
-  // Requests stage q.  Full stages: one elected thread issues bulk copies; a ragged last stage is copied
-  // with plain loads by every thread (bulk copies need 16-byte multiples) and published by the same barrier.
+  // Requests tile q.  Full tiles: one elected thread issues bulk copies; a ragged last tile is copied with
+  // plain loads by every thread (bulk copies need 16-byte multiples) and published by the same barrier.
   auto issue = [&](int q) {
     if (q >= my_steps) return;
-    int s, row0, rows, tile;
-    locate(q, s, row0, rows, tile);
+    int s, row0, rows;
+    locate(q, s, row0, rows);
     const int st = q & 1;
     const int vr = min(S_ROWS, rows - row0);
     const uint32_t bar = ptx::smem_u32(&bars[st]);
-    if (vr <= 0) {
-      if (threadIdx.x == 0) ptx::mbar_arrive(bar);
-      return;
-    }
     if (vr == S_ROWS) {
       if (threadIdx.x == 0) {
         ptx::mbar_arrive_expect_tx(bar, uint32_t(stage_bytes));
@@ -232,7 +219,7 @@ __global__ void __launch_bounds__(W4_WARPS * 32, 3) w4_gemv_kernel(const W4Args 
     ptx::fence_barrier_init();
   }
   __syncthreads();
-  // Weights never change: the first two stages are requested before waiting for the producer of the input.
+  // Weights never change: the first two tiles are requested before waiting for the producer of the input.
   issue(0);
   issue(1);
   pdl_launch_dependents();
@@ -253,8 +240,8 @@ __global__ void __launch_bounds__(W4_WARPS * 32, 3) w4_gemv_kernel(const W4Args 
   const float inv_r = sh_inv_r;
 
   for (int q = 0; q < my_steps; ++q) {
-    int s, row0, rows, tile;
-    locate(q, s, row0, rows, tile);
+    int s, row0, rows;
+    locate(q, s, row0, rows);
     const int st = q & 1;
     if (!ptx::mbar_wait(ptx::smem_u32(&bars[st]), uint32_t(q >> 1) & 1u, &abort_flag, a.status, 10)) break;
     float acc[NM][RW];
@@ -262,7 +249,7 @@ __global__ void __launch_bounds__(W4_WARPS * 32, 3) w4_gemv_kernel(const W4Args 
     for (int m = 0; m < NM; ++m)
 #pragma unroll
       for (int r = 0; r < RW; ++r) acc[m][r] = 0.0f;
-    const int wr0 = warp * RW;  // first row of this warp inside the stage
+    const int wr0 = warp * RW;  // first row of this warp inside the tile
     if (row0 + wr0 < rows) {
       for (int it = 0; it < n_it; ++it) {
         const int c = lane + (it << 5);
@@ -299,38 +286,14 @@ __global__ void __launch_bounds__(W4_WARPS * 32, 3) w4_gemv_kernel(const W4Args 
     for (int r = 0; r < RW; ++r) {
       const float v0 = warp_sum(acc[0][r]) * inv_r;
       const float v1 = NM == 2 ? warp_sum(acc[NM - 1][r]) * inv_r : 0.0f;
-      if (lane == 0) {
-        const int row = row0 + wr0 + r;
-        const int slot = (q % SPT) * S_ROWS + wr0 + r;
-        float pack_v = 0.0f, new_v = 0.0f;
-        if (row < rows) {
-          if (MODE == W4_STORE) a.seg[s].out[row] = v0;
-          if (MODE == W4_ADD) {
-            new_v = a.res[row] + v0;
-            a.seg[s].out[row] = new_v;
-            pack_v = a.out_scale ? new_v * a.out_scale[row] : new_v;
-          }
-          if (MODE == W4_GATE_UP) {
-            pack_v = (v0 / (1.0f + expf(-v0))) * v1;
-            if (a.seg[0].out) a.seg[0].out[row] = pack_v;
-          }
-        }
-        ytile[0][slot] = pack_v;
-        ytile[1][slot] = new_v;
+      const int row = row0 + wr0 + r;
+      if (lane == 0 && row < rows) {
+        if (MODE == W4_STORE) a.seg[s].out[row] = v0;
+        if (MODE == W4_ADD) a.seg[s].out[row] = a.res[row] + v0;
+        if (MODE == W4_GATE_UP) a.seg[0].out[row] = (v0 / (1.0f + expf(-v0))) * v1;
       }
     }
-    __syncthreads();  // every warp is done with stage st; ytile complete for this stage
-    if (MODE != W4_STORE && (q % SPT) == SPT - 1 && (a.xp_out || a.ss_out)) {
-      if (warp == 0) {
-        const int t_in_seg = tile - a.seg_tile_start[0];
-        if (a.xp_out) w4_pack_chunk(ytile[0][lane], lane, a.xp_out + size_t(t_in_seg) * (W4_CHUNK_U4 * 16));
-        if (MODE == W4_ADD && a.ss_out) {
-          const float qq = warp_sum(ytile[1][lane] * ytile[1][lane]);
-          if (lane == 0) a.ss_out[t_in_seg] = qq;
-        }
-      }
-      __syncthreads();
-    }
+    __syncthreads();  // every warp is done with stage st before it is refilled
     issue(q + 2);
   }
 }
@@ -338,30 +301,35 @@ __global__ void __launch_bounds__(W4_WARPS * 32, 3) w4_gemv_kernel(const W4Args 
 // Fills the tile bookkeeping, sizes the stages and launches.  All pointers are device pointers.
 template <int MODE>
 inline int w4_launch(W4Args a, cudaStream_t st, int sm_count, bool pdl = false) {
-  int g = 0;
-  const int nseg_tiles = MODE == W4_GATE_UP ? 1 : a.nseg;
-  for (int s = 0; s < nseg_tiles; ++s) {
-    a.seg_tile_start[s] = g;
-    g += (a.seg[s].rows + W4_TILE - 1) / W4_TILE;
-  }
-  a.seg_tile_start[nseg_tiles] = g;
-  a.total_tiles = g;
-  if (g == 0) return SIMP_OK;
   a.status = ctx().dev_status;
   constexpr int NM = MODE == W4_GATE_UP ? 2 : 1;
   const bool zeros = a.seg[0].zr != nullptr;
+  const int nseg_tiles = MODE == W4_GATE_UP ? 1 : a.nseg;
+  int64_t total_rows = 0;
   for (int s = 0; s < a.nseg; ++s) {
     const bool ok = (reinterpret_cast<uintptr_t>(a.seg[s].qw) & 15u) == 0 && (reinterpret_cast<uintptr_t>(a.seg[s].sc) & 15u) == 0 &&
                     (!zeros || (reinterpret_cast<uintptr_t>(a.seg[s].zr) & 15u) == 0) && ((a.seg[s].zr != nullptr) == zeros);
     if (!ok) return set_error(SIMP_ERR_SHAPE, "w4_gemv: weights, scales and zeros of every matrix must be 16-byte aligned");
+    if (s < nseg_tiles) total_rows += a.seg[s].rows;
   }
+  if (total_rows == 0) return SIMP_OK;
+  // Rows per warp (tile = 8*RW rows).  More rows per tile reuse the packed input better (less shared-memory
+  // traffic per weight); fewer keep every SM busy on the short matrices of batch-1 decode.  Two tiles must
+  // fit in shared memory next to the packed input, with room for 2-3 blocks per SM.
   const size_t xs_bytes = w4_packed_bytes(a.cols);
-  const size_t budget = 74 * 1024;  // three blocks per SM when the row is short enough, else two
   int rw = 4;
-  while (rw > 1 && xs_bytes + 2 * w4_stage_bytes(a.cols, a.groups_per_row, NM, zeros, rw) > budget) rw >>= 1;
+  while (rw > 1 && xs_bytes + 2 * w4_stage_bytes(a.cols, a.groups_per_row, NM, zeros, rw) > 74 * 1024) rw >>= 1;
   if (rw == 1 && xs_bytes + 2 * w4_stage_bytes(a.cols, a.groups_per_row, NM, zeros, 2) <= 112 * 1024) rw = 2;
+  while (rw > 1 && total_rows / (8 * rw) < 2 * int64_t(sm_count)) rw >>= 1;
   const size_t smem = xs_bytes + 2 * w4_stage_bytes(a.cols, a.groups_per_row, NM, zeros, rw);
   if (smem > 220 * 1024) return set_error(SIMP_ERR_SHAPE, "w4_gemv: row too long for the shared-memory pipeline");
+  int g = 0;
+  for (int s = 0; s < nseg_tiles; ++s) {
+    a.seg_tile_start[s] = g;
+    g += (a.seg[s].rows + 8 * rw - 1) / (8 * rw);
+  }
+  a.seg_tile_start[nseg_tiles] = g;
+  a.total_tiles = g;
   int per_sm = int((227 * 1024) / (smem + 1024));
   per_sm = per_sm < 1 ? 1 : (per_sm > 3 ? 3 : per_sm);
   const int cap = sm_count * per_sm;
