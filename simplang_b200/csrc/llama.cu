@@ -37,6 +37,7 @@ struct LlamaModel {
   // state (device)
   float *x = nullptr, *xb = nullptr, *hb = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *logits = nullptr;
   float *kc = nullptr, *vc = nullptr, *attn_part = nullptr;
+  int* attn_cnt = nullptr;  // per-head arrival counters of the attention kernel (zero between launches)
   uint8_t *xpA = nullptr, *xpB = nullptr;  // packed activations for the W4 kernels (ping-pong)
   float* ss = nullptr;                      // per-tile partial sums of squares (deferred rmsnorm)
   int* ctl = nullptr;     // [0] token, [1] pos, [2] n_prompt, [3] step, [4] next (argmax)
@@ -80,96 +81,120 @@ __global__ void __launch_bounds__(1024) dec_rmsnorm_kernel(const float* __restri
   for (int i = threadIdx.x; i < n; i += blockDim.x) y[i] = (x[i] / r) * w[i];
 }
 
-// RoPE on (even, odd) pairs of q and k, then store k and v into the caches at `pos`
-// (examples/llama2/stories110M.sl:86-121): freq = 1 / 10000^((i % hs)/hs), angle = pos * freq.
-__global__ void rope_kv_kernel(float* __restrict__ q, float* __restrict__ k, const float* __restrict__ v,
-                               float* __restrict__ kc, float* __restrict__ vc, const int* __restrict__ ctl, int dim,
-                               int kv_dim, int hs, int seq_len, int layer) {
-  pdl_launch_dependents();
-  pdl_wait();
-  const int pos = ctl[1];
-  const int p = blockIdx.x * blockDim.x + threadIdx.x;  // pair index
-  const int i = 2 * p;
-  if (i >= dim) return;
-  const float freq = 1.0f / powf(10000.0f, float(i % hs) / float(hs));
-  const float val = float(pos) * freq;
-  const float fcr = cosf(val), fci = sinf(val);
-  const float q0 = q[i], q1 = q[i + 1];
-  q[i] = q0 * fcr - q1 * fci;
-  q[i + 1] = q0 * fci + q1 * fcr;
-  if (i < kv_dim) {
-    const float k0 = k[i], k1 = k[i + 1];
-    const float r0 = k0 * fcr - k1 * fci, r1 = k0 * fci + k1 * fcr;
-    const int64_t base = (int64_t(layer) * seq_len + pos) * kv_dim + i;
-    kc[base] = r0;
-    kc[base + 1] = r1;
-    vc[base] = v[i];
-    vc[base + 1] = v[i + 1];
-  }
-}
-
-// Decode attention for one head and one slice of the sequence.  Each warp walks timesteps
-// t = t0 + warp, t0 + warp + 4, ...; lanes split the head dimension (hs <= 128); the softmax is
-// carried online (running max m, running sum s, running weighted value acc).  Partials
-// (m, s, acc[hs]) of every (head, split) go to `part` and are merged by attn_combine_kernel.
+// Decode attention of one layer in a single launch: grid (heads, nsplit), one block per head and
+// slice of the sequence.
+//   * RoPE on (even, odd) pairs of this head's q and k (examples/llama2/stories110M.sl:86-112:
+//     freq = 1 / 10000^((i % hs)/hs), angle = pos * freq), held in shared memory; the block (split 0, first
+//     head of a KV group) stores the rotated k and v into the caches at `pos` (stories110M.sl:115-121);
+//   * each warp walks timesteps t0+warp, t0+warp+4, ... four at a time (all k and v rows of a batch are
+//     requested before the first use); lanes split the head dimension (hs <= 128); the softmax is carried
+//     online (running max, running sum, running weighted value); timestep `pos` itself is served from the
+//     shared-memory copy, so no block depends on another block's cache write;
+//   * partials (m, s, acc[hs]) go to `part`; the last block of a head to finish (atomic counter, no
+//     waiting) merges the nsplit partials in split order and writes the normalised head output.
 constexpr int ATT_WARPS = 4;
-constexpr int ATT_MAX_PER_LANE = 4;
+constexpr int ATT_E = 4;   // head elements per lane (hs <= 128)
+constexpr int ATT_UB = 4;  // timesteps per batch
 __global__ void __launch_bounds__(ATT_WARPS * 32)
-    attn_decode_kernel(const float* __restrict__ q, const float* __restrict__ kc, const float* __restrict__ vc,
-                       float* __restrict__ part, const int* __restrict__ ctl, int hs, int kv_dim, int kv_mul,
-                       int seq_len, int layer, int nsplit) {
+    attn_fused_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
+                      float* __restrict__ kc, float* __restrict__ vc, float* __restrict__ part, int* __restrict__ counters,
+                      float* __restrict__ out, const int* __restrict__ ctl, int hs, int kv_dim, int kv_mul, int seq_len,
+                      int layer, int nsplit) {
+  __shared__ float qs[128], ks[128], vs[128];
   __shared__ float sm_m[ATT_WARPS], sm_s[ATT_WARPS];
   __shared__ float sm_acc[ATT_WARPS][128];
+  __shared__ int is_last;
   const int h = blockIdx.x, sp = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   pdl_launch_dependents();
   pdl_wait();
-  const int len = ctl[1] + 1;
+  const int pos = ctl[1];
+  const int len = pos + 1;
+  const int kvh = h / kv_mul;
+  if (int(threadIdx.x) < hs / 2) {
+    const int i = 2 * threadIdx.x;
+    const float freq = 1.0f / powf(10000.0f, float(i) / float(hs));
+    const float val = float(pos) * freq;
+    const float fcr = cosf(val), fci = sinf(val);
+    const float q0 = q[h * hs + i], q1 = q[h * hs + i + 1];
+    qs[i] = q0 * fcr - q1 * fci;
+    qs[i + 1] = q0 * fci + q1 * fcr;
+    const float k0 = k[kvh * hs + i], k1 = k[kvh * hs + i + 1];
+    ks[i] = k0 * fcr - k1 * fci;
+    ks[i + 1] = k0 * fci + k1 * fcr;
+    vs[i] = v[kvh * hs + i];
+    vs[i + 1] = v[kvh * hs + i + 1];
+  }
+  __syncthreads();
+  float* kbase = kc + int64_t(layer) * seq_len * kv_dim + kvh * hs;
+  float* vbase = vc + int64_t(layer) * seq_len * kv_dim + kvh * hs;
+  if (sp == 0 && h % kv_mul == 0) {
+    for (int i = threadIdx.x; i < hs; i += blockDim.x) {
+      kbase[int64_t(pos) * kv_dim + i] = ks[i];
+      vbase[int64_t(pos) * kv_dim + i] = vs[i];
+    }
+  }
   const int per = (len + nsplit - 1) / nsplit;
   const int t0 = sp * per, t1 = min(len, t0 + per);
-  const int kvo = (h / kv_mul) * hs;
-  const float inv_div = sqrtf(float(hs));
-  float qr[ATT_MAX_PER_LANE], acc[ATT_MAX_PER_LANE];
+  const float div = sqrtf(float(hs));
+  float qr[ATT_E], acc[ATT_E];
 #pragma unroll
-  for (int e = 0; e < ATT_MAX_PER_LANE; ++e) {
+  for (int e = 0; e < ATT_E; ++e) {
     const int i = lane + 32 * e;
-    qr[e] = i < hs ? q[h * hs + i] : 0.0f;
+    qr[e] = i < hs ? qs[i] : 0.0f;
     acc[e] = 0.0f;
   }
   float m = -INFINITY, s = 0.0f;
-  const float* kbase = kc + int64_t(layer) * seq_len * kv_dim + kvo;
-  const float* vbase = vc + int64_t(layer) * seq_len * kv_dim + kvo;
-  for (int t = t0 + warp; t < t1; t += ATT_WARPS) {
-    const float* kr = kbase + int64_t(t) * kv_dim;
-    float d = 0.0f;
+  for (int tb = t0 + warp; tb < t1; tb += ATT_WARPS * ATT_UB) {
+    float kr[ATT_UB][ATT_E], vr[ATT_UB][ATT_E];
 #pragma unroll
-    for (int e = 0; e < ATT_MAX_PER_LANE; ++e) {
-      const int i = lane + 32 * e;
-      if (i < hs) d = fmaf(qr[e], kr[i], d);
-    }
-    const float score = warp_sum(d) / inv_div;
-    const float m_new = fmaxf(m, score);
-    const float corr = expf(m - m_new);  // 0 on the first step (m = -inf)
-    const float p = expf(score - m_new);
-    s = s * corr + p;
-    const float* vr = vbase + int64_t(t) * kv_dim;
+    for (int u = 0; u < ATT_UB; ++u) {
+      const int t = tb + u * ATT_WARPS;
 #pragma unroll
-    for (int e = 0; e < ATT_MAX_PER_LANE; ++e) {
-      const int i = lane + 32 * e;
-      if (i < hs) acc[e] = acc[e] * corr + p * vr[i];
+      for (int e = 0; e < ATT_E; ++e) {
+        const int i = lane + 32 * e;
+        kr[u][e] = 0.0f;
+        vr[u][e] = 0.0f;
+        if (t < t1 && i < hs) {
+          if (t == pos) {
+            kr[u][e] = ks[i];
+            vr[u][e] = vs[i];
+          } else {
+            kr[u][e] = kbase[int64_t(t) * kv_dim + i];
+            vr[u][e] = vbase[int64_t(t) * kv_dim + i];
+          }
+        }
+      }
     }
-    m = m_new;
+#pragma unroll
+    for (int u = 0; u < ATT_UB; ++u) {
+      const int t = tb + u * ATT_WARPS;
+      if (t < t1) {  // warp-uniform
+        float d = 0.0f;
+#pragma unroll
+        for (int e = 0; e < ATT_E; ++e) d = fmaf(qr[e], kr[u][e], d);
+        const float score = warp_sum(d) / div;
+        const float m_new = fmaxf(m, score);
+        const float corr = expf(m - m_new);  // 0 on the first step (m = -inf)
+        const float p = expf(score - m_new);
+        s = s * corr + p;
+#pragma unroll
+        for (int e = 0; e < ATT_E; ++e) acc[e] = acc[e] * corr + p * vr[u][e];
+        m = m_new;
+      }
+    }
   }
   if (lane == 0) {
     sm_m[warp] = m;
     sm_s[warp] = s;
   }
 #pragma unroll
-  for (int e = 0; e < ATT_MAX_PER_LANE; ++e) {
+  for (int e = 0; e < ATT_E; ++e) {
     const int i = lane + 32 * e;
     if (i < hs) sm_acc[warp][i] = acc[e];
   }
   __syncthreads();
+  float* mine = part + (int64_t(h) * nsplit + sp) * (hs + 2);
   if (warp == 0) {
     float M = -INFINITY;
 #pragma unroll
@@ -181,52 +206,45 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
       sc[w] = sm_m[w] == -INFINITY ? 0.0f : expf(sm_m[w] - M);
       S += sm_s[w] * sc[w];
     }
-    float* o = part + (int64_t(h) * nsplit + sp) * (hs + 2);
     if (lane == 0) {
-      o[0] = M;
-      o[1] = S;
+      mine[0] = M;
+      mine[1] = S;
     }
 #pragma unroll
-    for (int e = 0; e < ATT_MAX_PER_LANE; ++e) {
+    for (int e = 0; e < ATT_E; ++e) {
       const int i = lane + 32 * e;
       if (i < hs) {
         float a = 0.0f;
 #pragma unroll
         for (int w = 0; w < ATT_WARPS; ++w) a += sm_acc[w][i] * sc[w];
-        o[2 + i] = a;
+        mine[2 + i] = a;
       }
     }
   }
-}
-
-// Merges the nsplit partials of every head into the normalised attention output.  One warp per 32
-// consecutive output elements, so the W4 path can emit the packed form for the wo GEMV in the same pass.
-__global__ void __launch_bounds__(256) attn_combine_kernel(const float* __restrict__ part, float* __restrict__ out,
-                                                           uint8_t* __restrict__ xp, int dim, int hs, int nsplit) {
-  pdl_launch_dependents();
-  pdl_wait();
-  const int lane = threadIdx.x & 31;
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i - lane >= dim) return;
-  float val = 0.0f;
-  if (i < dim) {
-    const int h = i / hs, e = i - h * hs;
-    const float* p = part + int64_t(h) * nsplit * (hs + 2);
-    float M = -INFINITY;
-    for (int sp = 0; sp < nsplit; ++sp) M = fmaxf(M, p[sp * (hs + 2)]);
-    float S = 0.0f, a = 0.0f;
-    for (int sp = 0; sp < nsplit; ++sp) {
-      const float mm = p[sp * (hs + 2)];
-      if (mm != -INFINITY) {
-        const float w = expf(mm - M);
-        S += p[sp * (hs + 2) + 1] * w;
-        a += p[sp * (hs + 2) + 2 + e] * w;
-      }
-    }
-    val = a / S;
-    out[i] = val;
+  // last block of this head merges (writes above are published by the fence + atomic)
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) is_last = (atomicAdd(&counters[h], 1) == nsplit - 1);
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  const float* p = part + int64_t(h) * nsplit * (hs + 2);
+  float M = -INFINITY;
+  for (int x = 0; x < nsplit; ++x) M = fmaxf(M, __ldcg(p + x * (hs + 2)));
+  float S = 0.0f;
+  for (int x = 0; x < nsplit; ++x) {
+    const float mm = __ldcg(p + x * (hs + 2));
+    if (mm != -INFINITY) S += __ldcg(p + x * (hs + 2) + 1) * expf(mm - M);
   }
-  if (xp) w4_pack_chunk(val, lane, xp + size_t(i >> 5) * (W4_CHUNK_U4 * 16));
+  for (int i = threadIdx.x; i < hs; i += blockDim.x) {
+    float a = 0.0f;
+    for (int x = 0; x < nsplit; ++x) {
+      const float mm = __ldcg(p + x * (hs + 2));
+      if (mm != -INFINITY) a += __ldcg(p + x * (hs + 2) + 2 + i) * expf(mm - M);
+    }
+    out[h * hs + i] = a / S;
+  }
+  if (threadIdx.x == 0) counters[h] = 0;
 }
 
 // Greedy argmax (strict '>', lowest index wins) + bookkeeping for the next step:
@@ -320,13 +338,9 @@ static int enqueue_token(LlamaModel& m, cudaStream_t st) {
       g.nseg = 3; g.k4 = dim / 4; g.x = m.x; g.norm_w = m.rms_att + l * dim; g.eps = 1e-5f;
       if (int rc = gemv_f32_dec_launch<GEMV_STORE>(g, st, sms, pdl)) return rc;
     }
-    LAUNCH_OR_FAIL(rope_kv_kernel, dim3((dim / 2 + 127) / 128), dim3(128), 0, st, pdl, m.q, m.k, m.v, m.kc, m.vc,
-                   m.ctl, dim, kv, hs, int(c.seq_len), int(l));
-    LAUNCH_OR_FAIL(attn_decode_kernel, dim3(unsigned(c.n_heads), unsigned(m.nsplit)), dim3(ATT_WARPS * 32), 0, st, pdl,
-                   m.q, m.kc, m.vc, m.attn_part, m.ctl, hs, kv, int(c.n_heads / c.n_kv_heads), int(c.seq_len), int(l),
-                   m.nsplit);
-    LAUNCH_OR_FAIL(attn_combine_kernel, dim3((dim + 255) / 256), dim3(256), 0, st, pdl, m.attn_part, m.xb,
-                   (uint8_t*)nullptr, dim, hs, m.nsplit);
+    LAUNCH_OR_FAIL(attn_fused_kernel, dim3(unsigned(c.n_heads), unsigned(m.nsplit)), dim3(ATT_WARPS * 32), 0, st, pdl,
+                   (const float*)m.q, (const float*)m.k, (const float*)m.v, m.kc, m.vc, m.attn_part, m.attn_cnt, m.xb,
+                   (const int*)m.ctl, hs, kv, int(c.n_heads / c.n_kv_heads), int(c.seq_len), int(l), m.nsplit);
     {
       GemvDecArgs o{};
       o.seg[0] = GemvSeg{m.wo + l * dim * dim, m.x, dim};
@@ -395,13 +409,10 @@ static int enqueue_token_tp(LlamaModel& m, cudaStream_t st) {
       a.nseg = 3; a.ss_part = m.ss; a.n_ss = n_ss;
       if (int rc = w4_launch<W4_STORE>(a, st, sms, true)) return rc;
     }
-    LAUNCH_OR_FAIL(rope_kv_kernel, dim3((dim_l / 2 + 127) / 128), dim3(128), 0, st, true, m.q, m.k, m.v, m.kc, m.vc,
-                   m.ctl, dim_l, kv_l, hs, int(c.seq_len), int(l));
-    LAUNCH_OR_FAIL(attn_decode_kernel, dim3(unsigned(heads_l), unsigned(m.nsplit)), dim3(ATT_WARPS * 32), 0, st, true,
-                   m.q, m.kc, m.vc, m.attn_part, m.ctl, hs, kv_l, int(c.n_heads / c.n_kv_heads), int(c.seq_len), int(l),
+    LAUNCH_OR_FAIL(attn_fused_kernel, dim3(unsigned(heads_l), unsigned(m.nsplit)), dim3(ATT_WARPS * 32), 0, st, true,
+                   (const float*)m.q, (const float*)m.k, (const float*)m.v, m.kc, m.vc, m.attn_part, m.attn_cnt,
+                   m.xb + rk * dim_l, (const int*)m.ctl, hs, kv_l, int(c.n_heads / c.n_kv_heads), int(c.seq_len), int(l),
                    m.nsplit);
-    LAUNCH_OR_FAIL(attn_combine_kernel, dim3((dim_l + 255) / 256), dim3(256), 0, st, true, m.attn_part,
-                   m.xb + rk * dim_l, (uint8_t*)nullptr, dim_l, hs, m.nsplit);
     if (int rc = simp_dist_allgather(m.xb + rk * dim_l, m.xb, size_t(dim_l) * 4)) return rc;
     TP_CUDA(pack(m.xb, m.xpB, dim, nullptr, nullptr, chain));
     {
@@ -524,12 +535,14 @@ SIMP_API int simp_llama_create(const simp_llama_config* cfg, void** model) {
   A((void**)&m->kc, kv_bytes);
   A((void**)&m->vc, kv_bytes);
   A((void**)&m->attn_part, size_t(c.n_heads) * m->nsplit * (hs + 2) * 4);
+  A((void**)&m->attn_cnt, size_t(c.n_heads) * 4);
   A((void**)&m->xpA, w4_packed_bytes(int64_t(mx) + 32));
   A((void**)&m->xpB, w4_packed_bytes(int64_t(mx) + 32));
   A((void**)&m->ss, (mx / 32 + 1) * 4);
   A((void**)&m->ctl, 64);
   if (rc != SIMP_OK) { simp_llama_destroy(m); return rc; }
   cudaMemsetAsync(m->ctl, 0, 64, ctx().stream);
+  cudaMemsetAsync(m->attn_cnt, 0, size_t(c.n_heads) * 4, ctx().stream);
   cudaMemsetAsync(m->kc, 0, kv_bytes, ctx().stream);
   cudaMemsetAsync(m->vc, 0, kv_bytes, ctx().stream);
   *model = m;
@@ -719,7 +732,7 @@ SIMP_API int simp_llama_destroy(void* model) {
   if (m->graph) cudaGraphExecDestroy(m->graph);
   void* ptrs[] = {m->tok_emb, m->rms_att, m->rms_ffn, m->rms_final, m->wcls, m->wq, m->wk, m->wv, m->wo, m->w1, m->w2,
                   m->w3, m->qweights, m->scales, m->zeros, m->x, m->xb, m->hb, m->q, m->k, m->v, m->logits, m->kc,
-                  m->vc, m->attn_part, m->xpA, m->xpB, m->ss, m->ctl, m->prompt, m->out_tokens};
+                  m->vc, m->attn_part, m->attn_cnt, m->xpA, m->xpB, m->ss, m->ctl, m->prompt, m->out_tokens};
   for (void* p : ptrs)
     if (p) cudaFree(p);
   delete m;
