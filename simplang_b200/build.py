@@ -63,7 +63,20 @@ def build(force: bool = False, verbose: bool = False) -> str:
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+    build_host()
     return LIB
+
+
+def build_host() -> str:
+    """Compiles the C++ host example (plain g++, links only -ldl: it dlopen()s the runtime library)."""
+    host_dir = os.path.join(HERE, "host")
+    src = os.path.join(host_dir, "bench_int8_gemm_host.cpp")
+    exe = os.path.join(host_dir, "bench_int8_gemm_host")
+    if not _newer(exe, [src, os.path.join(host_dir, "gpu_kernel_runner.hpp")]):
+        r = subprocess.run([HOST_CXX, "-O2", "-std=c++17", "-o", exe, src, "-ldl"], capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"host build failed:\n{r.stdout}\n{r.stderr}")
+    return exe
 
 
 if __name__ == "__main__":

@@ -50,3 +50,11 @@ def test_product_does_not_import_the_oracle():
         if path.endswith((".py", ".cu", ".cuh", ".cpp", ".hpp", ".h")):
             text = open(path, errors="ignore").read()
             assert "import oracle" not in text and "simp_oracle" not in text and "oracle/" not in text, path
+
+
+def test_cpp_host_builds_and_reports_a_missing_library():
+    import subprocess
+    from simplang_b200 import build as b
+    exe = b.build_host()
+    r = subprocess.run([exe, "/nonexistent/libsimp_gpu.so"], capture_output=True, text=True)
+    assert r.returncode == 1 and "Failed to load library" in r.stderr

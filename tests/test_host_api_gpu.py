@@ -112,3 +112,16 @@ def test_host_gemm_chunked_pipeline_and_registered_weights(gpu, oracle):
     finally:
         gpu.check(gpu.lib().simp_gpu_unregister_host(Bt.ctypes.data))
     assert gpu.lib().simp_gpu_unregister_host(Bt.ctypes.data) != 0
+
+
+def test_cpp_host_driver(gpu):
+    """The C++ host (GpuKernelRunner / ProfiledGpuKernelRunner) loads the library, runs and verifies a GEMM."""
+    import os
+    import subprocess
+    from simplang_b200 import build as b
+    exe = b.build_host()
+    r = subprocess.run([exe, gpu.LIB_PATH, "256", "512", "384", "5"], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "verification passed" in r.stdout and "GIOP/s" in r.stdout
+    r = subprocess.run([exe, os.path.join(os.path.dirname(gpu.LIB_PATH), "missing.so")], capture_output=True, text=True)
+    assert r.returncode == 1 and "Failed to load library" in r.stderr
