@@ -29,6 +29,13 @@ def hbm_peak():
     return 6650.0, "fallback"
 
 
+SHAPE_FILTER = None  # e.g. [32000, 3200]: run only the case with this shape (for single-kernel ncu captures)
+
+
+def want(shape):
+    return SHAPE_FILTER is None or list(shape) == SHAPE_FILTER
+
+
 def copies_for(nbytes):
     return max(2, min(256, int(2 * L2_BYTES // max(nbytes, 1)) + 1))
 
@@ -59,6 +66,8 @@ def emit(op, shape, ms, nbytes, extra=None):
 def bench_gemv_f32(iters):
     rng = np.random.default_rng(0)
     for rows, cols in [(768, 768), (2048, 768), (768, 2048), (32000, 768), (3200, 3200), (32000, 3200), (65536, 4096)]:
+        if not want((rows, cols)):
+            continue
         nb = 4 * (rows * cols + cols + rows)
         nc = copies_for(nb)
         A = sg.DeviceBuffer.from_numpy((0.02 * rng.standard_normal(rows * cols)).astype(np.float32))
@@ -76,6 +85,8 @@ def bench_w4(iters):
     rng = np.random.default_rng(1)
     gs = 64
     for rows, cols in [(3200, 3200), (9600, 3200), (8640, 3200), (3200, 8640), (26 * 8640, 3200), (65536, 8192)]:
+        if not want((rows, cols)):
+            continue
         nb = rows * cols // 2 + 4 * rows * cols // gs + 4 * cols + 4 * rows
         nc = copies_for(nb)
         qbytes, ngroups = rows * cols // 2, rows * cols // gs
@@ -91,6 +102,8 @@ def bench_w4(iters):
 def bench_rowops(iters):
     rng = np.random.default_rng(2)
     for rows, n in [(4096, 768), (4096, 3200), (4096, 4096), (16384, 4096)]:
+        if not want((rows, n)):
+            continue
         nb = 4 * (2 * rows * n + n)
         nc = copies_for(nb)
         xs = [sg.DeviceBuffer.from_numpy(rng.standard_normal(rows * n).astype(np.float32)) for _ in range(min(nc, 8))]
@@ -114,6 +127,8 @@ def bench_gemm_i8(iters):
     cases = [(1024, 1024, 1024), (2048, 2048, 2048), (4096, 4096, 4096), (8192, 8192, 8192), (16384, 16384, 16384),
              (512, 3200, 9600), (512, 3200, 8640), (512, 8640, 3200)]
     for M, K, N in cases:
+        if not want((M, K, N)):
+            continue
         A = sg.DeviceBuffer.from_numpy(rng.integers(0, 256, (M, K), dtype=np.uint8))
         for b_t in (False, True):
             B = sg.DeviceBuffer.from_numpy(rng.integers(-128, 128, (K, N), dtype=np.int8))
@@ -163,7 +178,11 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--iters", type=int, default=50)
     ap.add_argument("--only", default="gemv_f32,w4,rowops,gemm_i8")
+    ap.add_argument("--shape", default=None, help="run only the case with this shape, e.g. 32000x3200")
     args = ap.parse_args()
+    global SHAPE_FILTER
+    if args.shape:
+        SHAPE_FILTER = [int(v) for v in args.shape.lower().split("x")]
     sg.init(int(os.environ.get("LOCAL_RANK", "0")))
     which = set(args.only.split(","))
     if "gemv_f32" in which:
