@@ -216,6 +216,18 @@ int simp_dist_allreduce_f32(float* buf_dev, size_t count);
 int simp_dist_matmul_i8_nsharded(const void* A_dev, const int8_t* B_local_dev, int32_t* C_blocks_dev,
                                  int64_t M, int64_t K, int64_t N_local, int a_unsigned,
                                  int b_transposed);
+/* The same GEMM with the exchange fused into the tensor-core kernel: every C tile is staged once in shared
+ * memory and TMA-stored into every rank's copy of the full row-major C[M, N_local*world] (own HBM and, over
+ * NVLink, the peers'), so the all-gather overlaps the main loop tile by tile and C arrives in the layout
+ * tensor_matmul defines.  C_symm_dev must come from simp_dist_symm_alloc (a collective that allocates
+ * `bytes` on every rank and maps all ranks' buffers through CUDA IPC); the call ends with simp_dist_barrier,
+ * which orders every rank's stores before later work on the stream. */
+int simp_dist_symm_alloc(size_t bytes, void** local_ptr);
+int simp_dist_symm_free(void* local_ptr);
+int simp_dist_barrier(void);
+int simp_dist_matmul_i8_nsharded_fused(const void* A_dev, const int8_t* B_local_dev, int32_t* C_symm_dev,
+                                       int64_t M, int64_t K, int64_t N_local, int a_unsigned,
+                                       int b_transposed);
 
 /* ---- memref-ABI shims ----------------------------------------------------------------------
  * What a GPU lowering pattern calls from compiled .sl code.  Arguments follow MLIR 14's std->LLVM

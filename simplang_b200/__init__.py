@@ -75,6 +75,10 @@ _SIGNATURES = {
     "simp_dist_allgather": [vp, vp, C.c_size_t],
     "simp_dist_allreduce_f32": [vp, C.c_size_t],
     "simp_dist_matmul_i8_nsharded": [vp, vp, vp, i64, i64, i64, C.c_int, C.c_int],
+    "simp_dist_symm_alloc": [C.c_size_t, C.POINTER(vp)],
+    "simp_dist_symm_free": [vp],
+    "simp_dist_barrier": [],
+    "simp_dist_matmul_i8_nsharded_fused": [vp, vp, vp, i64, i64, i64, C.c_int, C.c_int],
 }
 
 

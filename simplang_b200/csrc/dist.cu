@@ -14,6 +14,7 @@
 
 #include <cstring>
 #include <mutex>
+#include <vector>
 
 #include "common.cuh"
 
@@ -63,9 +64,102 @@ static int load_nccl() {
       return set_error(SIMP_ERR_COMM, "%s failed: %s", #call, g_nccl.GetErrorString(r__));           \
   } while (0)
 
+// Symmetric buffers: one cudaMalloc per rank, made addressable from every rank of the node through CUDA IPC.
+struct SymmBuf {
+  void* local = nullptr;
+  size_t bytes = 0;
+  void* peer[8] = {};  // peer[r] = rank r's buffer as seen from this process (peer[rank] == local)
+};
+static std::vector<SymmBuf> g_symm;
+
+int gemm_i8_run(const void* A, const int8_t* B, int32_t* C, int64_t M, int64_t K, int64_t N, int a_unsigned,
+                int b_transposed, int32_t* const* peer_c, int n_peers, int64_t ldc, int64_t col_offset);
+
 }  // namespace simp
 
 using namespace simp;
+
+// Collective: every rank allocates `bytes` and learns the addresses of all ranks' buffers (cudaIpc handles
+// travel through one NCCL all-gather).  Stores from a kernel to a peer address go over NVLink.
+SIMP_API int simp_dist_symm_alloc(size_t bytes, void** local_ptr) {
+  SIMP_REQUIRE(local_ptr != nullptr && bytes > 0, SIMP_ERR_ARG, "dist_symm_alloc: null pointer or empty buffer");
+  if (int rc = ensure_ready()) return rc;
+  SIMP_REQUIRE(g_world <= 8, SIMP_ERR_UNSUPPORTED, "dist_symm_alloc: at most 8 ranks");
+  SymmBuf b;
+  b.bytes = bytes;
+  SIMP_CUDA(cudaMalloc(&b.local, bytes));
+  b.peer[g_rank] = b.local;
+  if (g_world > 1) {
+    SIMP_REQUIRE(g_comm != nullptr, SIMP_ERR_STATE, "dist_symm_alloc: call simp_dist_init first");
+    cudaIpcMemHandle_t mine;
+    SIMP_CUDA(cudaIpcGetMemHandle(&mine, b.local));
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "unexpected IPC handle size");
+    uint8_t* dev = nullptr;
+    SIMP_CUDA(cudaMalloc(&dev, 64 * size_t(g_world)));
+    cudaStream_t st = ctx().stream;
+    SIMP_CUDA(cudaMemcpyAsync(dev + 64 * g_rank, &mine, 64, cudaMemcpyHostToDevice, st));
+    SIMP_NCCL(g_nccl.AllGather(dev + 64 * g_rank, dev, 64, ncclInt8, g_comm, st));
+    std::vector<cudaIpcMemHandle_t> all(g_world);
+    SIMP_CUDA(cudaMemcpyAsync(all.data(), dev, 64 * size_t(g_world), cudaMemcpyDeviceToHost, st));
+    SIMP_CUDA(cudaStreamSynchronize(st));
+    SIMP_CUDA(cudaFree(dev));
+    for (int r = 0; r < g_world; ++r) {
+      if (r == g_rank) continue;
+      SIMP_CUDA(cudaIpcOpenMemHandle(&b.peer[r], all[r], cudaIpcMemLazyEnablePeerAccess));
+    }
+  }
+  g_symm.push_back(b);
+  *local_ptr = b.local;
+  return SIMP_OK;
+}
+
+SIMP_API int simp_dist_symm_free(void* local_ptr) {
+  for (size_t i = 0; i < g_symm.size(); ++i) {
+    if (g_symm[i].local != local_ptr) continue;
+    cudaStreamSynchronize(ctx().stream);
+    for (int r = 0; r < g_world; ++r)
+      if (r != g_rank && g_symm[i].peer[r]) cudaIpcCloseMemHandle(g_symm[i].peer[r]);
+    cudaFree(g_symm[i].local);
+    g_symm.erase(g_symm.begin() + i);
+    return SIMP_OK;
+  }
+  return set_error(SIMP_ERR_ARG, "dist_symm_free: pointer was not returned by simp_dist_symm_alloc");
+}
+
+// Rendezvous on the library stream: returns (in stream order) only after every rank's earlier work on its own
+// stream has completed -- one 4-byte all-reduce.
+SIMP_API int simp_dist_barrier(void) {
+  if (int rc = ensure_ready()) return rc;
+  if (g_world == 1) return SIMP_OK;
+  SIMP_REQUIRE(g_comm != nullptr, SIMP_ERR_STATE, "dist_barrier: call simp_dist_init first");
+  float* word = static_cast<float*>(scratch(256, 7));
+  SIMP_REQUIRE(word != nullptr, SIMP_ERR_CUDA, "dist_barrier: out of device memory");
+  SIMP_NCCL(g_nccl.AllReduce(word, word, 1, ncclFloat, ncclSum, g_comm, ctx().stream));
+  return SIMP_OK;
+}
+
+// N-sharded tensor_matmul on i8 with the all-gather fused into the GEMM epilogue: each C tile is staged once
+// in shared memory and TMA-stored into every rank's copy of the full row-major C[M, N_local*world] -- the
+// exchange overlaps the tensor-core main loop tile by tile instead of following it.  C_symm must come from
+// simp_dist_symm_alloc (M * N_local * world * 4 bytes).  A trailing simp_dist_barrier orders the peers'
+// stores before later work on this stream.
+SIMP_API int simp_dist_matmul_i8_nsharded_fused(const void* A_dev, const int8_t* B_local_dev, int32_t* C_symm,
+                                                int64_t M, int64_t K, int64_t N_local, int a_unsigned,
+                                                int b_transposed) {
+  if (int rc = ensure_ready()) return rc;
+  const SymmBuf* sb = nullptr;
+  for (const auto& b : g_symm)
+    if (b.local == C_symm) sb = &b;
+  SIMP_REQUIRE(sb != nullptr, SIMP_ERR_ARG, "dist_matmul_i8_nsharded_fused: C must come from simp_dist_symm_alloc");
+  const int64_t ldc = N_local * g_world;
+  SIMP_REQUIRE(size_t(M) * size_t(ldc) * 4 <= sb->bytes, SIMP_ERR_SHAPE, "dist_matmul_i8_nsharded_fused: C buffer too small");
+  int32_t* peers[8];
+  for (int r = 0; r < g_world; ++r) peers[r] = static_cast<int32_t*>(sb->peer[r]);
+  if (int rc = gemm_i8_run(A_dev, B_local_dev, nullptr, M, K, N_local, a_unsigned, b_transposed, peers, g_world, ldc,
+                           int64_t(g_rank) * N_local))
+    return rc;
+  return simp_dist_barrier();
+}
 
 SIMP_API int simp_dist_unique_id(void* id_out, size_t bytes) {
   SIMP_REQUIRE(id_out != nullptr && bytes >= sizeof(ncclUniqueId), SIMP_ERR_ARG,

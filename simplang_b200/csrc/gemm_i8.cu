@@ -40,6 +40,11 @@ constexpr int TMEM_COLS = 512;
 constexpr int EPI_BYTES = 4 * 2 * 4096;      // per epilogue warp: two 32x32 i32 staging tiles for TMA stores
 constexpr size_t GEMM_SMEM = size_t(STAGES) * STAGE_BYTES + EPI_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 
+// Tensor maps of the C buffers a tile is stored to when the all-gather is fused into the epilogue.
+struct PeerMaps {
+  CUtensorMap m[8];
+};
+
 struct GemmParams {
   int M, N, K;
   int tiles_m, tiles_n, num_kb;
@@ -48,6 +53,8 @@ struct GemmParams {
   int32_t* C;
   int* status;
   int tma_store;    // 1: epilogue goes through shared memory + TMA stores (needs N % 4 == 0)
+  int n_peers;      // > 0: every C tile is TMA-stored into n_peers buffers (own + peer GPUs) at column col_offset
+  int col_offset;
   int bn;           // tile width in columns (multiple of 32, <= 256); the 2-CTA kernel always uses 256
   uint32_t stage_tx;  // bytes one stage's TMA loads deliver (1-CTA kernel)
 };
@@ -69,7 +76,8 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
 // (a) 128-byte-swizzled shared-memory tile -> TMA store of full 128-byte lines, two tiles in flight, or
 // (b) direct global stores when C's row pitch is not a 16-byte multiple.
 // Returns after the last tcgen05.ld has completed (the accumulator may then be reused).
-__device__ __forceinline__ void epilogue_rows(const CUtensorMap* tmap_c, const GemmParams& p, uint32_t tmem_acc,
+__device__ __forceinline__ void epilogue_rows(const CUtensorMap* tmap_c, const PeerMaps* peers, const GemmParams& p,
+                                              uint32_t tmem_acc,
                                               int q, int lane, int row0, int n0, uint32_t stage_smem,
                                               uint32_t& nstore) {
   const int row = row0 + lane;
@@ -100,7 +108,13 @@ __device__ __forceinline__ void epilogue_rows(const CUtensorMap* tmap_c, const G
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
-          tma_store_2d(tmap_c, buf, c0, row0);
+          if (p.n_peers > 0) {
+            // fused all-gather: the same staged tile goes to every rank's copy of C (own memory and, over
+            // NVLink, the peers'); plain TMA stores, no multicast
+            for (int r = 0; r < p.n_peers; ++r) tma_store_2d(&peers->m[r], buf, c0 + p.col_offset, row0);
+          } else {
+            tma_store_2d(tmap_c, buf, c0, row0);
+          }
           tma_store_commit();
         }
       }
@@ -121,7 +135,8 @@ __device__ __forceinline__ void epilogue_rows(const CUtensorMap* tmap_c, const G
 
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
     gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                           const __grid_constant__ CUtensorMap tmap_c, const GemmParams p) {
+                           const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ PeerMaps peers,
+                           const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t epi_base = smem_base + STAGES * STAGE_BYTES;
@@ -238,7 +253,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
       tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
       if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, 4)) break;
       tc_fence_after_sync();
-      epilogue_rows(&tmap_c, p, tmem_base + uint32_t(acc * BN), q, lane, tm * BM + q * 32, tn * p.bn, my_stage, nstore);
+      epilogue_rows(&tmap_c, &peers, p, tmem_base + uint32_t(acc * BN), q, lane, tm * BM + q * 32, tn * p.bn, my_stage,
+                    nstore);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty_bar(acc));
@@ -270,7 +286,8 @@ constexpr size_t GEMM2_SMEM = size_t(P_STAGES) * P_STAGE_BYTES + EPI_BYTES + 102
 
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
     gemm_i8_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                                const __grid_constant__ CUtensorMap tmap_c, const GemmParams p) {
+                                const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ PeerMaps peers,
+                           const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t epi_base = smem_base + P_STAGES * P_STAGE_BYTES;
@@ -381,8 +398,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
       tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
       if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, 14)) break;
       tc_fence_after_sync();
-      epilogue_rows(&tmap_c, p, tmem_base + uint32_t(acc * BN), q, lane, tm * 256 + int(cta_rank) * 128 + q * 32, tn * BN,
-                    my_stage, nstore);
+      epilogue_rows(&tmap_c, &peers, p, tmem_base + uint32_t(acc * BN), q, lane,
+                    tm * 256 + int(cta_rank) * 128 + q * 32, tn * BN, my_stage, nstore);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_even_cta(tempty_bar(acc));
@@ -512,25 +529,33 @@ static int make_map_u8(CUtensorMap* map, const void* base, int64_t inner, int64_
 
 }  // namespace simp
 
-using namespace simp;
-
-SIMP_API int simp_gpu_matmul_i8(const void* A, const int8_t* B, int32_t* C, int64_t M, int64_t K, int64_t N,
-                                int a_unsigned, int b_transposed) {
+namespace simp {
+// Shared by simp_gpu_matmul_i8 (n_peers == 0: C is [M,N] in this GPU's memory) and the fused N-sharded GEMM
+// (n_peers > 0: peer_c[r] are the row-major [M, ldc] copies of the full result on every rank, this rank's
+// column block starts at col_offset).
+int gemm_i8_run(const void* A, const int8_t* B, int32_t* C, int64_t M, int64_t K, int64_t N, int a_unsigned,
+                int b_transposed, int32_t* const* peer_c, int n_peers, int64_t ldc, int64_t col_offset) {
   if (int rc = ensure_ready()) return rc;
   SIMP_REQUIRE(M >= 0 && K >= 0 && N >= 0, SIMP_ERR_ARG, "matmul_i8: negative size");
   if (M == 0 || N == 0) return SIMP_OK;
-  SIMP_REQUIRE(A && B && C, SIMP_ERR_ARG, "matmul_i8: null pointer");
+  SIMP_REQUIRE(A && B && (C || n_peers > 0), SIMP_ERR_ARG, "matmul_i8: null pointer");
+  SIMP_REQUIRE(n_peers >= 0 && n_peers <= 8, SIMP_ERR_ARG, "matmul_i8: at most 8 peers");
   SIMP_REQUIRE(M <= 0x7fffffff && N <= 0x7fffffff && K <= 0x7fffffff, SIMP_ERR_SHAPE, "matmul_i8: dimension too large");
   cudaStream_t st = ctx().stream;
   if (K == 0) {
+    SIMP_REQUIRE(n_peers == 0, SIMP_ERR_SHAPE, "matmul_i8: K == 0 is not supported by the fused all-gather form");
     SIMP_CUDA(cudaMemsetAsync(C, 0, size_t(M) * size_t(N) * sizeof(int32_t), st));
     return SIMP_OK;
   }
   const bool a16 = (reinterpret_cast<uintptr_t>(A) & 15u) == 0, b16 = (reinterpret_cast<uintptr_t>(B) & 15u) == 0;
   const bool tma_ok = a16 && b16 && (K % 16 == 0) && (b_transposed ? true : (N % 16 == 0)) &&
                       ((reinterpret_cast<uintptr_t>(C) & 15u) == 0);
+  if (n_peers > 0)
+    SIMP_REQUIRE(tma_ok && N % 4 == 0 && ldc % 4 == 0 && col_offset % 4 == 0 && col_offset + N <= ldc, SIMP_ERR_SHAPE,
+                 "matmul_i8: the fused all-gather form needs 16-byte aligned operands, K %% 16 == 0 and column "
+                 "blocks that are multiples of 16");
   // The tensor-core kernel pays a fixed pipeline fill per tile; tiny problems stay on dp4a.
-  const bool tiny = M * N * K < int64_t(64) * 64 * 64;
+  const bool tiny = n_peers == 0 && M * N * K < int64_t(64) * 64 * 64;
   if (tma_ok && !tiny) {
     // Kernel choice: the 2-CTA kernel for problems with at least one full wave of 256x256 tiles on the
     // 74 CTA pairs; the 1-CTA kernel otherwise.  SIMP_GEMM_I8_KERNEL=1cta|2cta overrides (testing).
@@ -556,11 +581,20 @@ SIMP_API int simp_gpu_matmul_i8(const void* A, const int8_t* B, int32_t* C, int6
     p.tma_store = (N % 4 == 0) ? 1 : 0;
     if (const char* env = getenv("SIMP_GEMM_I8_EPILOGUE"))
       if (!strcmp(env, "direct")) p.tma_store = 0;
-    CUtensorMap mc;
-    if (p.tma_store) {
+    CUtensorMap mc = ma;  // placeholder when unused
+    PeerMaps peers;
+    for (auto& pm : peers.m) pm = ma;
+    p.n_peers = n_peers;
+    p.col_offset = int(col_offset);
+    if (n_peers > 0) {
+      p.tma_store = 1;
+      for (int r = 0; r < n_peers; ++r) {
+        SIMP_REQUIRE(peer_c[r] != nullptr && (reinterpret_cast<uintptr_t>(peer_c[r]) & 15u) == 0, SIMP_ERR_ARG,
+                     "matmul_i8: peer C pointer %d is null or misaligned", r);
+        if (int rc = make_map_c_i32(&peers.m[r], peer_c[r], ldc, M)) return rc;
+      }
+    } else if (p.tma_store) {
       if (int rc = make_map_c_i32(&mc, C, N, M)) return rc;
-    } else {
-      mc = ma;  // unused by the kernel
     }
     if (use_pair) {
       p.bn = BN;
@@ -589,7 +623,7 @@ SIMP_API int simp_gpu_matmul_i8(const void* A, const int8_t* B, int32_t* C, int6
       at[0].val.clusterDim.z = 1;
       cfg.attrs = at;
       cfg.numAttrs = 1;
-      SIMP_CUDA(cudaLaunchKernelEx(&cfg, gemm_i8_tcgen05_2cta_kernel, ma, mb, mc, p));
+      SIMP_CUDA(cudaLaunchKernelEx(&cfg, gemm_i8_tcgen05_2cta_kernel, ma, mb, mc, peers, p));
       return SIMP_OK;
     }
     // Tile width.  Measured on B200: a kind::i8 MMA of M = 128 takes the same ~128 clocks for every N <= 256
@@ -619,7 +653,7 @@ SIMP_API int simp_gpu_matmul_i8(const void* A, const int8_t* B, int32_t* C, int6
     const int64_t tiles = int64_t(p.tiles_m) * p.tiles_n;
     SIMP_REQUIRE(tiles <= 0x7fffffff, SIMP_ERR_SHAPE, "matmul_i8: too many tiles");
     const int grid = int(tiles < ctx().sm_count ? tiles : ctx().sm_count);
-    gemm_i8_tcgen05_kernel<<<grid, GEMM_THREADS, GEMM_SMEM, st>>>(ma, mb, mc, p);
+    gemm_i8_tcgen05_kernel<<<grid, GEMM_THREADS, GEMM_SMEM, st>>>(ma, mb, mc, peers, p);
   } else {
     const int64_t gx = cdiv(N, 64), gy = cdiv(M, 64);
     SIMP_REQUIRE(gy <= 65535, SIMP_ERR_SHAPE, "matmul_i8: M too large for the dp4a kernel");
@@ -631,4 +665,10 @@ SIMP_API int simp_gpu_matmul_i8(const void* A, const int8_t* B, int32_t* C, int6
   }
   SIMP_LAUNCH_CHECK();
   return SIMP_OK;
+}
+}  // namespace simp
+
+SIMP_API int simp_gpu_matmul_i8(const void* A, const int8_t* B, int32_t* C, int64_t M, int64_t K, int64_t N,
+                                int a_unsigned, int b_transposed) {
+  return simp::gemm_i8_run(A, B, C, M, K, N, a_unsigned, b_transposed, nullptr, 0, N, 0);
 }

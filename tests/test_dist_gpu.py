@@ -44,6 +44,26 @@ def _worker(rank, world, port, out_dir):
         sg.check(sg.lib().simp_dist_matmul_i8_nsharded(dA.ptr, dB.ptr, dC.ptr, M, K, hi - lo, 1, 0))
         full = sd.assemble_column_blocks(dC.to_numpy(np.int32, (world, M, hi - lo)))
         assert np.array_equal(full, oracle.tensor_matmul_i8(A, B))
+        # fused form: TMA stores from the epilogue into every rank's row-major C (CUDA IPC peers)
+        import ctypes as C
+        for (M2, K2, N2) in ((256, 512, 1024), (1024, 2048, 4096), (300, 256, 96 * world)):
+            A2 = rng.integers(0, 256, (M2, K2), dtype=np.uint8)
+            B2 = rng.integers(-128, 128, (K2, N2), dtype=np.int8)
+            lo2, hi2 = sd.column_shard(N2, world, rank)
+            dA2 = sg.DeviceBuffer.from_numpy(A2)
+            dB2 = sg.DeviceBuffer.from_numpy(np.ascontiguousarray(B2[:, lo2:hi2]))
+            cptr = C.c_void_p()
+            sg.check(sg.lib().simp_dist_symm_alloc(M2 * N2 * 4, C.byref(cptr)))
+            sg.check(sg.lib().simp_gpu_memset(cptr, 0xff, M2 * N2 * 4))
+            sg.check(sg.lib().simp_dist_barrier())
+            sg.check(sg.lib().simp_dist_matmul_i8_nsharded_fused(dA2.ptr, dB2.ptr, cptr, M2, K2, hi2 - lo2, 1, 0))
+            full2 = np.empty((M2, N2), np.int32)
+            sg.check(sg.lib().simp_gpu_download(full2.ctypes.data, cptr, full2.nbytes))
+            assert np.array_equal(full2, oracle.tensor_matmul_i8(A2, B2)), (M2, K2, N2)
+            sg.check(sg.lib().simp_dist_barrier())
+            sg.sync()
+            dist.barrier()
+            sg.check(sg.lib().simp_dist_symm_free(cptr))
         np.save(os.path.join(out_dir, f"ok{rank}.npy"), np.array([1]))
         sg.check(sg.lib().simp_dist_shutdown())
     finally:
