@@ -19,6 +19,8 @@ import numpy as np
 import simplang_b200 as sg
 
 L2_BYTES = 126 << 20
+WORLD = int(os.environ.get("WORLD_SIZE", "1"))
+RANK = int(os.environ.get("RANK", "0"))
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
@@ -155,8 +157,8 @@ def bench_decode(which, n_new=128):
         name = "llama 110M f32 decode"
     else:
         cfg = synth.LLAMA_3B_W4
-        t, off = synth.llama_w4_tensors(cfg, 0, threads=16)
-        m = sg.Llama(cfg, t, w4=True, offsets=off)
+        t, off = synth.llama_w4_tensors(cfg, 0, threads=max(2, 16 // WORLD))
+        m = sg.Llama(cfg, t, w4=True, offsets=off, tp_size=WORLD)  # tensor-parallel under torchrun
         d, h, L, V, gs = cfg["dim"], cfg["hidden_dim"], cfg["n_layers"], cfg["vocab_size"], cfg["group_size"]
         nw = L * (4 * d * d + 3 * d * h)
         wbytes = nw // 2 + 4 * nw // gs + 4 * V * d
@@ -167,6 +169,12 @@ def bench_decode(which, n_new=128):
     steps = 16 + n_new - 1
     us = ms * 1e3 / steps
     kv = 2 * cfg["n_layers"] * cfg["dim"] * 4 * (steps / 2)
+    if WORLD > 1:
+        name += f" (tensor-parallel x{WORLD}, rank {RANK})"
+        wbytes //= WORLD
+    if RANK != 0:
+        m.close()
+        return
     print(json.dumps({"op": name, "tokens": steps, "us_per_token": round(us, 1), "tok_s": round(1e6 / us, 1),
                       "weight_bytes_per_token": int(wbytes), "avg_kv_bytes_per_token": int(kv),
                       "gb_s": round((wbytes + kv) / us / 1e3, 1), "frac_of_hbm_peak": round((wbytes + kv) / us / 1e3 / peak, 4),
@@ -184,6 +192,13 @@ def main():
     if args.shape:
         SHAPE_FILTER = [int(v) for v in args.shape.lower().split("x")]
     sg.init(int(os.environ.get("LOCAL_RANK", "0")))
+    if WORLD > 1:  # torchrun: tensor-parallel decode
+        import torch
+        import torch.distributed as dist
+        from simplang_b200 import dist as sd
+        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+        dist.init_process_group("nccl", device_id=torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0"))))
+        sd.init_from_env(sg)
     which = set(args.only.split(","))
     if "gemv_f32" in which:
         bench_gemv_f32(args.iters)
