@@ -55,6 +55,8 @@ struct GemmParams {
   int tma_store;    // 1: epilogue goes through shared memory + TMA stores (needs N % 4 == 0)
   int n_peers;      // > 0: every C tile is TMA-stored into n_peers buffers (own + peer GPUs) at column col_offset
   int col_offset;
+  int streamk;      // 1: the tiles x K-blocks work units are split evenly over the CTAs; partial tiles are
+                    //    added into a zeroed C with TMA reduce-add (integer adds: exact in any order)
   int bn;           // tile width in columns (multiple of 32, <= 256); the 2-CTA kernel always uses 256
   uint32_t stage_tx;  // bytes one stage's TMA loads deliver (1-CTA kernel)
 };
@@ -71,6 +73,37 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
   tn = in_group / gsz;
 }
 
+
+// Work of one CTA of the 1-CTA kernel.  Classic mode: whole tiles, tile = blockIdx.x + i*gridDim.x.
+// Stream-K mode: the num_tiles*num_kb (tile, K-block) units are cut into gridDim.x equal contiguous ranges,
+// so every SM gets the same amount of math even when the tile count is not a multiple of the SM count.
+struct WorkIter {
+  int i = 0;       // classic: iteration count
+  int u = 0, u1 = 0;  // stream-K: next unit, end of this CTA's range
+};
+__device__ __forceinline__ void work_init(const GemmParams& p, int num_tiles, WorkIter& w) {
+  if (p.streamk) {
+    const long long total = (long long)num_tiles * p.num_kb;
+    w.u = int(total * blockIdx.x / gridDim.x);
+    w.u1 = int(total * (blockIdx.x + 1) / gridDim.x);
+  }
+}
+__device__ __forceinline__ bool work_next(const GemmParams& p, int num_tiles, WorkIter& w, int& tile, int& kb0, int& kb1) {
+  if (!p.streamk) {
+    tile = blockIdx.x + w.i * gridDim.x;
+    if (tile >= num_tiles) return false;
+    ++w.i;
+    kb0 = 0;
+    kb1 = p.num_kb;
+    return true;
+  }
+  if (w.u >= w.u1) return false;
+  tile = w.u / p.num_kb;
+  kb0 = w.u - tile * p.num_kb;
+  kb1 = min(p.num_kb, kb0 + (w.u1 - w.u));
+  w.u += kb1 - kb0;
+  return true;
+}
 
 // Epilogue of one 128 x 256 accumulator for the 32 rows owned by this warp: TMEM -> registers ->
 // (a) 128-byte-swizzled shared-memory tile -> TMA store of full 128-byte lines, two tiles in flight, or
@@ -112,6 +145,8 @@ __device__ __forceinline__ void epilogue_rows(const CUtensorMap* tmap_c, const P
             // fused all-gather: the same staged tile goes to every rank's copy of C (own memory and, over
             // NVLink, the peers'); plain TMA stores, no multicast
             for (int r = 0; r < p.n_peers; ++r) tma_store_2d(&peers->m[r], buf, c0 + p.col_offset, row0);
+          } else if (p.streamk) {
+            tma_reduce_add_2d(tmap_c, buf, c0, row0);
           } else {
             tma_store_2d(tmap_c, buf, c0, row0);
           }
@@ -182,11 +217,14 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      WorkIter wk;
+      work_init(p, num_tiles, wk);
+      int tile, kb0, kb1;
+      while (ok && work_next(p, num_tiles, wk, tile, kb0, kb1)) {
         int tm, tn;
         tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
         const int m0 = tm * BM, n0 = tn * p.bn;
-        for (int kb = 0; kb < p.num_kb; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, 1)) { ok = false; break; }
           const uint32_t sa = smem_base + stage * STAGE_BYTES;
           const uint32_t sb = sa + A_BYTES;
@@ -216,11 +254,14 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
       bool ok = true;
       const uint32_t b_lbo = p.b_mn_major ? uint32_t(B_BYTES / 2) : 16u;
       const uint32_t b_kstep = p.b_mn_major ? (32u * 128u) >> 4 : 32u >> 4;  // descriptor units of 16 B
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      WorkIter wk;
+      work_init(p, num_tiles, wk);
+      int tile, kb0, kb1;
+      while (ok && work_next(p, num_tiles, wk, tile, kb0, kb1)) {
         if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, 2)) { ok = false; break; }
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + uint32_t(acc * BN);
-        for (int kb = 0; kb < p.num_kb; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, 3)) { ok = false; break; }
           tc_fence_after_sync();
           const uint32_t sa = smem_base + stage * STAGE_BYTES;
@@ -230,7 +271,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
 #pragma unroll
           for (int j = 0; j < BK / 32; ++j) {
             mma_i8_ss(d_tmem, a_desc + uint64_t(j * 2), b_desc + uint64_t(j) * b_kstep, p.idesc,
-                      (kb | j) != 0 ? 1u : 0u);
+                      (kb != kb0 || j != 0) ? 1u : 0u);
           }
           mma_commit(empty_bar(stage));
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -248,7 +289,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     uint32_t acc_phase = 0;
     const uint32_t my_stage = epi_base + uint32_t(warp - 2) * 8192u;
     uint32_t nstore = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+    WorkIter wk;
+    work_init(p, num_tiles, wk);
+    int tile, kb0, kb1;
+    while (work_next(p, num_tiles, wk, tile, kb0, kb1)) {
       int tm, tn;
       tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
       if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, 4)) break;
@@ -599,6 +643,7 @@ int gemm_i8_run(const void* A, const int8_t* B, int32_t* C, int64_t M, int64_t K
     if (use_pair) {
       p.bn = BN;
       p.stage_tx = 0;
+      p.streamk = 0;
       p.tiles_m = int(cdiv(M, 256)); p.tiles_n = int(cdiv(N, BN));
       p.idesc = make_idesc_i8(256, BN, /*a_signed=*/!a_unsigned, /*b_signed=*/true, false, !b_transposed);
       static bool attr2_set = false;
@@ -652,7 +697,22 @@ int gemm_i8_run(const void* A, const int8_t* B, int32_t* C, int64_t M, int64_t K
     }
     const int64_t tiles = int64_t(p.tiles_m) * p.tiles_n;
     SIMP_REQUIRE(tiles <= 0x7fffffff, SIMP_ERR_SHAPE, "matmul_i8: too many tiles");
-    const int grid = int(tiles < ctx().sm_count ? tiles : ctx().sm_count);
+    int grid = int(tiles < ctx().sm_count ? tiles : ctx().sm_count);
+    // Stream-K when whole tiles would leave a large part of the last wave idle (e.g. 152 or 52 tiles on 148
+    // SMs): every CTA then gets the same number of K-blocks; C is zeroed and partial tiles are reduce-added.
+    p.streamk = 0;
+    {
+      const int sms = ctx().sm_count;
+      const int64_t waves = cdiv(tiles, sms);
+      const double eff = double(tiles) / double(waves * sms);
+      bool want = p.tma_store && n_peers == 0 && eff < 0.85 && tiles * p.num_kb >= int64_t(sms) * 4 && waves <= 8;
+      if (const char* env = getenv("SIMP_GEMM_I8_STREAMK")) want = p.tma_store && n_peers == 0 && atoi(env) != 0;
+      if (want) {
+        p.streamk = 1;
+        grid = sms;
+        SIMP_CUDA(cudaMemsetAsync(C, 0, size_t(M) * size_t(N) * sizeof(int32_t), st));
+      }
+    }
     gemm_i8_tcgen05_kernel<<<grid, GEMM_THREADS, GEMM_SMEM, st>>>(ma, mb, mc, peers, p);
   } else {
     const int64_t gx = cdiv(N, 64), gy = cdiv(M, 64);

@@ -93,6 +93,12 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, uint32_t src_
                ::"l"(m), "r"(src_smem), "r"(x), "r"(y)
                : "memory");
 }
+// 2-D tiled reduction shared -> global: global[tile] += shared tile (integer add, exact in any order).
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* m, uint32_t src_smem, int x, int y) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(m), "r"(src_smem), "r"(x), "r"(y)
+               : "memory");
+}
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void tma_store_wait_read() {
