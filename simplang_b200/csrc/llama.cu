@@ -19,34 +19,10 @@
 #include "common.cuh"
 #include "gemv_f32_core.cuh"
 #include "w4_core.cuh"
+#include "llama_model.hpp"
 
 namespace simp {
 
-struct LlamaModel {
-  simp_llama_config cfg;
-  int64_t kv_dim, head_size;
-  // weights (device)
-  float *tok_emb = nullptr, *rms_att = nullptr, *rms_ffn = nullptr, *rms_final = nullptr, *wcls = nullptr;
-  float *wq = nullptr, *wk = nullptr, *wv = nullptr, *wo = nullptr, *w1 = nullptr, *w2 = nullptr, *w3 = nullptr;
-  uint8_t* qweights = nullptr;
-  float *scales = nullptr, *zeros = nullptr;
-  int64_t off[7] = {0, 0, 0, 0, 0, 0, 0};   // wq wk wv wo w1 w2 w3 element offsets in the caller's arrays (W4)
-  int64_t loff[7] = {0, 0, 0, 0, 0, 0, 0};  // the same for the device copy (differs under tensor parallelism)
-  bool offsets_set = false;
-  int tp = 1, rank = 0;                      // tensor-parallel degree and this rank
-  // state (device)
-  float *x = nullptr, *xb = nullptr, *hb = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *logits = nullptr;
-  float *kc = nullptr, *vc = nullptr, *attn_part = nullptr;
-  int* attn_cnt = nullptr;  // per-head arrival counters of the attention kernel (zero between launches)
-  uint8_t *xpA = nullptr, *xpB = nullptr;  // packed activations for the W4 kernels (ping-pong)
-  float* ss = nullptr;                      // per-tile partial sums of squares (deferred rmsnorm)
-  int* ctl = nullptr;     // [0] token, [1] pos, [2] n_prompt, [3] step, [4] next (argmax)
-  int32_t *prompt = nullptr, *out_tokens = nullptr;
-  int64_t prompt_cap = 0, out_cap = 0;
-  int nsplit = 1;
-  cudaGraphExec_t graph = nullptr;
-  bool loaded_any = false;
-};
 
 // ---------------------------------------------------------------------------------------------
 // x = embedding row of the current token.  For the W4 path one warp per 32-element chunk also emits the
@@ -321,9 +297,18 @@ static int dev_alloc(void** p, size_t bytes) {
 // requests its first weights, then waits for its predecessor before touching activations.
 static int enqueue_token_tp(LlamaModel& m, cudaStream_t st);
 
+// f32 decode form: SIMP_DECODE_MODE=persistent selects the single cooperative kernel per token, =graph the
+// per-op kernels; unset picks the persistent kernel whenever the model fits its shared-memory plan.
+static bool use_persistent(const LlamaModel& m) {
+  const char* e = getenv("SIMP_DECODE_MODE");
+  if (e && !strcmp(e, "graph")) return false;
+  return persistent_f32_supported(m);
+}
+
 static int enqueue_token(LlamaModel& m, cudaStream_t st) {
   const simp_llama_config& c = m.cfg;
   if (c.w4) return enqueue_token_tp(m, st);  // the W4 model shares one path for 1 and R ranks
+  if (use_persistent(m)) return enqueue_token_persistent_f32(m, st);
   const int dim = int(c.dim), hd = int(c.hidden_dim), kv = int(m.kv_dim), hs = int(m.head_size);
   const int sms = ctx().sm_count;
   const bool pdl = true;
@@ -534,7 +519,7 @@ SIMP_API int simp_llama_create(const simp_llama_config* cfg, void** model) {
   const size_t kv_bytes = size_t(c.n_layers) * c.seq_len * (m->kv_dim / tp) * 4;  // this rank's heads only
   A((void**)&m->kc, kv_bytes);
   A((void**)&m->vc, kv_bytes);
-  A((void**)&m->attn_part, size_t(c.n_heads) * m->nsplit * (hs + 2) * 4);
+  A((void**)&m->attn_part, size_t(c.n_heads) * (m->nsplit > 4 ? m->nsplit : 4) * (hs + 2) * 4);
   A((void**)&m->attn_cnt, size_t(c.n_heads) * 4);
   A((void**)&m->xpA, w4_packed_bytes(int64_t(mx) + 32));
   A((void**)&m->xpB, w4_packed_bytes(int64_t(mx) + 32));

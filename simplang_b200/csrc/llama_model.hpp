@@ -1,0 +1,41 @@
+// llama_model.hpp -- device-resident state of one LLaMA decoder (shared by the per-op graph path in
+// llama.cu and the persistent per-token kernel in llama_persistent.cu).
+#pragma once
+#include <cuda_runtime.h>
+#include <cstdint>
+
+#include "simp_gpu.h"
+
+namespace simp {
+
+struct LlamaModel {
+  simp_llama_config cfg;
+  int64_t kv_dim, head_size;
+  // weights (device)
+  float *tok_emb = nullptr, *rms_att = nullptr, *rms_ffn = nullptr, *rms_final = nullptr, *wcls = nullptr;
+  float *wq = nullptr, *wk = nullptr, *wv = nullptr, *wo = nullptr, *w1 = nullptr, *w2 = nullptr, *w3 = nullptr;
+  uint8_t* qweights = nullptr;
+  float *scales = nullptr, *zeros = nullptr;
+  int64_t off[7] = {0, 0, 0, 0, 0, 0, 0};   // wq wk wv wo w1 w2 w3 element offsets in the caller's arrays (W4)
+  int64_t loff[7] = {0, 0, 0, 0, 0, 0, 0};  // the same for the device copy (differs under tensor parallelism)
+  bool offsets_set = false;
+  int tp = 1, rank = 0;                      // tensor-parallel degree and this rank
+  // state (device)
+  float *x = nullptr, *xb = nullptr, *hb = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *logits = nullptr;
+  float *kc = nullptr, *vc = nullptr, *attn_part = nullptr;
+  int* attn_cnt = nullptr;  // per-head arrival counters of the attention kernel (zero between launches)
+  uint8_t *xpA = nullptr, *xpB = nullptr;  // packed activations for the W4 kernels (ping-pong)
+  float* ss = nullptr;                      // per-tile partial sums of squares (deferred rmsnorm)
+  int* ctl = nullptr;     // [0] token, [1] pos, [2] n_prompt, [3] step, [4] next (argmax)
+  int32_t *prompt = nullptr, *out_tokens = nullptr;
+  int64_t prompt_cap = 0, out_cap = 0;
+  int nsplit = 1;
+  cudaGraphExec_t graph = nullptr;
+  bool loaded_any = false;
+};
+
+// One token of the f32 model as a single persistent cooperative kernel (llama_persistent.cu).
+int enqueue_token_persistent_f32(LlamaModel& m, cudaStream_t st);
+bool persistent_f32_supported(const LlamaModel& m);
+
+}  // namespace simp

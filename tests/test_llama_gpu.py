@@ -43,9 +43,25 @@ def run_pair(gpu, oracle, cfg, tensors, w4, offsets, n_prompt, n_new, seed=1234)
 TINY = dict(dim=128, hidden_dim=256, n_layers=3, n_heads=4, n_kv_heads=4, vocab_size=300, seq_len=64)
 
 
-def test_tiny_f32(gpu, oracle):
+@pytest.fixture(params=["persistent", "graph"])
+def decode_mode(request, monkeypatch):
+    """The f32 model has two device forms: one cooperative kernel per token, or a graph of per-op kernels.
+    The library reads SIMP_DECODE_MODE when a model builds its token graph."""
+    monkeypatch.setenv("SIMP_DECODE_MODE", request.param)
+    return request.param
+
+
+def test_tiny_f32(gpu, oracle, decode_mode):
     from simplang_b200 import synth
     run_pair(gpu, oracle, TINY, synth.llama_f32_tensors(TINY, 3), False, None, 5, 40)
+
+
+def test_small_f32_gqa_long(gpu, oracle, decode_mode):
+    """Grouped-query heads (kv_mul 2), rows not divisible by the SM count, context long enough for every
+    sequence split of the attention phase to hold several timesteps."""
+    from simplang_b200 import synth
+    cfg = dict(dim=256, hidden_dim=688, n_layers=2, n_heads=8, n_kv_heads=4, vocab_size=515, seq_len=320)
+    run_pair(gpu, oracle, cfg, synth.llama_f32_tensors(cfg, 11), False, None, 6, 300)
 
 
 def test_tiny_f32_gqa_odd_head(gpu, oracle):
@@ -79,12 +95,12 @@ def test_tiny_w4_asymmetric(gpu, oracle):
     run_pair(gpu, oracle, cfg, t, True, offsets, 4, 20)
 
 
-def test_stories110m_f32(gpu, oracle):
+def test_stories110m_f32(gpu, oracle, decode_mode):
     """BASELINE config: dim 768, 12 layers, 12 heads, FFN 2048, vocab 32000, seq 1024; 16-token prompt, 64 greedy tokens."""
     from simplang_b200 import synth
     cfg = synth.STORIES_110M
     worst, ms = run_pair(gpu, oracle, cfg, synth.llama_f32_tensors(cfg, 0), False, None, 16, 64)
-    print(f"110M f32: worst logit rel err {worst:.2e}, {79 / ms * 1e3:.0f} tok/s")
+    print(f"110M f32 ({decode_mode}): worst logit rel err {worst:.2e}, {79 / ms * 1e3:.0f} tok/s")
 
 
 def test_llama3b_w4(gpu, oracle):
