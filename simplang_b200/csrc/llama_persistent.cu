@@ -495,30 +495,63 @@ __global__ void __launch_bounds__(PK_BLOCK, 1) llama_f32_token_kernel(const Pers
     const float4* xv = reinterpret_cast<const float4*>(xs);
     float best = -INFINITY;
     int best_i = 0x7fffffff;
-    for (int row = b * PK_WARPS + warp; row < a.vocab; row += G * PK_WARPS) {
-      const float4* wr = reinterpret_cast<const float4*>(a.wcls) + size_t(row) * k4;
-      float acc = 0.0f;
-      int i = lane;
-      for (; i + 7 * 32 < k4; i += 8 * 32) {
-        float4 v[8];
-#pragma unroll
-        for (int u = 0; u < 8; ++u) v[u] = ld_stream_f4(wr + i + u * 32);
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-          const float4 x4 = xv[i + u * 32];
-          acc = fmaf(v[u].x, x4.x, acc); acc = fmaf(v[u].y, x4.y, acc);
-          acc = fmaf(v[u].z, x4.z, acc); acc = fmaf(v[u].w, x4.w, acc);
-        }
-      }
-      for (; i < k4; i += 32) {
-        const float4 v = ld_stream_f4(wr + i), x4 = xv[i];
-        acc = fmaf(v.x, x4.x, acc); acc = fmaf(v.y, x4.y, acc);
-        acc = fmaf(v.z, x4.z, acc); acc = fmaf(v.w, x4.w, acc);
-      }
+    auto finish_row = [&](int row, float acc) {
       acc = warp_sum(acc);
       if (lane == 0) {
         a.logits[row] = acc;
         if (acc > best || (acc == best && row < best_i)) { best = acc; best_i = row; }
+      }
+    };
+    const int row_step = G * PK_WARPS;
+    if (k4 <= 8 * 32) {
+      // Rows of up to 1024 elements: a lane holds a whole row slice in registers, and the next row's loads are
+      // issued before the current row is reduced, so every warp always has a row in flight.
+      float4 cur[8], nxt[8];
+      auto load_row = [&](int row, float4 (&v)[8]) {
+        const float4* wr = reinterpret_cast<const float4*>(a.wcls) + size_t(row) * k4;
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          v[u] = (row < a.vocab && lane + 32 * u < k4) ? ld_stream_f4(wr + lane + 32 * u) : make_float4(0.f, 0.f, 0.f, 0.f);
+      };
+      float4 xr[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) xr[u] = lane + 32 * u < k4 ? xv[lane + 32 * u] : make_float4(0.f, 0.f, 0.f, 0.f);
+      int row = b * PK_WARPS + warp;
+      load_row(row, cur);
+      for (; row < a.vocab; row += row_step) {
+        load_row(row + row_step, nxt);
+        float acc = 0.0f;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          acc = fmaf(cur[u].x, xr[u].x, acc); acc = fmaf(cur[u].y, xr[u].y, acc);
+          acc = fmaf(cur[u].z, xr[u].z, acc); acc = fmaf(cur[u].w, xr[u].w, acc);
+        }
+        finish_row(row, acc);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) cur[u] = nxt[u];
+      }
+    } else {
+      for (int row = b * PK_WARPS + warp; row < a.vocab; row += row_step) {
+        const float4* wr = reinterpret_cast<const float4*>(a.wcls) + size_t(row) * k4;
+        float acc = 0.0f;
+        int i = lane;
+        for (; i + 7 * 32 < k4; i += 8 * 32) {
+          float4 v[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) v[u] = ld_stream_f4(wr + i + u * 32);
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const float4 x4 = xv[i + u * 32];
+            acc = fmaf(v[u].x, x4.x, acc); acc = fmaf(v[u].y, x4.y, acc);
+            acc = fmaf(v[u].z, x4.z, acc); acc = fmaf(v[u].w, x4.w, acc);
+          }
+        }
+        for (; i < k4; i += 32) {
+          const float4 v = ld_stream_f4(wr + i), x4 = xv[i];
+          acc = fmaf(v.x, x4.x, acc); acc = fmaf(v.y, x4.y, acc);
+          acc = fmaf(v.z, x4.z, acc); acc = fmaf(v.w, x4.w, acc);
+        }
+        finish_row(row, acc);
       }
     }
     // block-level argmax (lane 0 of each warp holds a candidate)
@@ -538,14 +571,21 @@ __global__ void __launch_bounds__(PK_BLOCK, 1) llama_f32_token_kernel(const Pers
     }
   }
   if (!grid_sync(a.bar, epoch, &sh_abort, a.status, 0)) { drain(); return; }
-  if (b == 0 && threadIdx.x == 0) {
+  if (b == 0 && warp == 0) {
     float bv = -INFINITY;
     int bi = 0x7fffffff;
-    for (int g = 0; g < G; ++g) {
+    for (int g = lane; g < G; g += 32) {
       const float v = __ldcg(a.best_val + g);
       const int i = __ldcg(a.best_idx + g);
       if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
     }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    if (lane != 0) return;
     if (bi == 0x7fffffff) bi = 0;
     const int npos = pos + 1, n_prompt = a.ctl[2];
     a.ctl[4] = bi;
