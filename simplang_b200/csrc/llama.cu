@@ -297,18 +297,21 @@ static int dev_alloc(void** p, size_t bytes) {
 // requests its first weights, then waits for its predecessor before touching activations.
 static int enqueue_token_tp(LlamaModel& m, cudaStream_t st);
 
-// f32 decode form: SIMP_DECODE_MODE=persistent selects the single cooperative kernel per token, =graph the
-// per-op kernels; unset picks the persistent kernel whenever the model fits its shared-memory plan.
+// Decode form on one GPU.  f32 model: the single cooperative kernel per token whenever the model fits its
+// shared-memory plan, unless SIMP_DECODE_MODE=graph asks for the per-op kernels.  W4 model: the per-op
+// kernels (faster today), unless SIMP_DECODE_MODE=persistent asks for the cooperative kernel.
+// Tensor-parallel models always use per-op kernels.
 static bool use_persistent(const LlamaModel& m) {
   const char* e = getenv("SIMP_DECODE_MODE");
   if (e && !strcmp(e, "graph")) return false;
+  if (m.cfg.w4) return e && !strcmp(e, "persistent") && persistent_w4_supported(m);
   return persistent_f32_supported(m);
 }
 
 static int enqueue_token(LlamaModel& m, cudaStream_t st) {
   const simp_llama_config& c = m.cfg;
-  if (c.w4) return enqueue_token_tp(m, st);  // the W4 model shares one path for 1 and R ranks
-  if (use_persistent(m)) return enqueue_token_persistent_f32(m, st);
+  if (use_persistent(m)) return c.w4 ? enqueue_token_persistent_w4(m, st) : enqueue_token_persistent_f32(m, st);
+  if (c.w4) return enqueue_token_tp(m, st);  // the per-op W4 path is shared by 1 and R ranks
   const int dim = int(c.dim), hd = int(c.hidden_dim), kv = int(m.kv_dim), hs = int(m.head_size);
   const int sms = ctx().sm_count;
   const bool pdl = true;

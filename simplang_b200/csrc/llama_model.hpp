@@ -37,5 +37,8 @@ struct LlamaModel {
 // One token of the f32 model as a single persistent cooperative kernel (llama_persistent.cu).
 int enqueue_token_persistent_f32(LlamaModel& m, cudaStream_t st);
 bool persistent_f32_supported(const LlamaModel& m);
+// The same for the W4 model on one GPU (llama_persistent_w4.cu).
+int enqueue_token_persistent_w4(LlamaModel& m, cudaStream_t st);
+bool persistent_w4_supported(const LlamaModel& m);
 
 }  // namespace simp
