@@ -287,6 +287,26 @@ def run_ours(args):
         t_e2e = float(t.item())
     e2e_tops = ops / t_e2e / 1e12
 
+    # ---- int8 MMA issue ceiling of the same tiling (single GPU only): the GEMM kernel with its TMA loads and
+    # epilogue traffic switched off, run last so that it cannot disturb the timed region or the result check
+    mma_ceiling = None
+    if world == 1 and (M // 256) * (N // 256) >= 74:
+        os.environ["SIMP_GEMM_I8_ABLATE"] = "mma"
+        try:
+            dScratch = sg.DeviceBuffer(M * N * 4)
+            for _ in range(3):
+                sg.matmul_i8(dA, dB, dScratch, M, K, N, a_unsigned=True, b_transposed=False)
+            sg.sync()
+            f0, f1 = sg.Event(), sg.Event()
+            f0.record()
+            for _ in range(10):
+                sg.matmul_i8(dA, dB, dScratch, M, K, N, a_unsigned=True, b_transposed=False)
+            f1.record()
+            sg.sync()
+            mma_ceiling = ops / (f0.elapsed_ms(f1) / 10 * 1e-3) / 1e12
+        finally:
+            os.environ.pop("SIMP_GEMM_I8_ABLATE", None)
+
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
@@ -312,6 +332,10 @@ def run_ours(args):
                      "peak_basis": f"2 x cuBLAS bf16 burst ({peaks['bf16_tflops']} TFLOP/s, {peaks['source']}); "
                                    "int8 MMA issues at twice the bf16 rate",
                      "frac_of_nominal_4500": tops / world / NOMINAL_INT8_TOPS,
+                     "mma_issue_ceiling": mma_ceiling,
+                     "mma_issue_ceiling_note": "same kernel and tiling without TMA loads and epilogue traffic, 10 launches "
+                                               "at burst clocks (the timed region is power-capped): measured int8 pipe ceiling",
+                     "frac_of_mma_issue_ceiling": (tops / mma_ceiling) if mma_ceiling else None,
                      "traffic": NCU_TRAFFIC_BYTES.get(S), "algorithmic_bytes": int(M * K + K * N + 4 * M * N),
                      "kernel": "gemm_i8_tcgen05_2cta_kernel" if (M // 256) * (N // world // 256) >= 74 else "gemm_i8_tcgen05_kernel"},
     }

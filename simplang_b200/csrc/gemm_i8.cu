@@ -59,6 +59,8 @@ struct GemmParams {
                     //    added into a zeroed C with TMA reduce-add (integer adds: exact in any order)
   int bn;           // tile width in columns (multiple of 32, <= 256); the 2-CTA kernel always uses 256
   uint32_t stage_tx;  // bytes one stage's TMA loads deliver (1-CTA kernel)
+  int mma_only;     // measurement aid (2-CTA kernel): no TMA loads, no epilogue traffic -- the MMA issuer runs
+                    // over whatever the stages hold, which times the tensor pipe's issue ceiling for this tiling
 };
 
 __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
@@ -375,7 +377,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer (both CTAs)
-    if (lane == 0) {
+    if (lane == 0 && !p.mma_only) {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -411,7 +413,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + uint32_t(acc * BN);
         for (int kb = 0; kb < p.num_kb; ++kb) {
-          if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, 13)) { ok = false; break; }
+          if (!p.mma_only && !mbar_wait(full_bar(stage), phase, abort_flag, p.status, 13)) { ok = false; break; }
           tc_fence_after_sync();
           const uint32_t sa = smem_base + stage * P_STAGE_BYTES;
           const uint32_t sb = sa + P_A_BYTES;
@@ -442,8 +444,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
       tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
       if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, 14)) break;
       tc_fence_after_sync();
-      epilogue_rows(&tmap_c, &peers, p, tmem_base + uint32_t(acc * BN), q, lane,
-                    tm * 256 + int(cta_rank) * 128 + q * 32, tn * BN, my_stage, nstore);
+      if (!p.mma_only)
+        epilogue_rows(&tmap_c, &peers, p, tmem_base + uint32_t(acc * BN), q, lane,
+                      tm * 256 + int(cta_rank) * 128 + q * 32, tn * BN, my_stage, nstore);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_even_cta(tempty_bar(acc));
@@ -630,6 +633,10 @@ int gemm_i8_run(const void* A, const int8_t* B, int32_t* C, int64_t M, int64_t K
     for (auto& pm : peers.m) pm = ma;
     p.n_peers = n_peers;
     p.col_offset = int(col_offset);
+    // SIMP_GEMM_I8_ABLATE=mma: timing aid, the result is NOT computed (see GemmParams::mma_only).
+    p.mma_only = 0;
+    if (const char* env = getenv("SIMP_GEMM_I8_ABLATE"))
+      if (!strcmp(env, "mma") && n_peers == 0) p.mma_only = 1;
     if (n_peers > 0) {
       p.tma_store = 1;
       for (int r = 0; r < n_peers; ++r) {

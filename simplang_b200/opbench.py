@@ -2,7 +2,7 @@
 int8 GEMM at the configured shapes.  Prints one JSON line per case with the achieved GB/s (or TOPS), the
 algorithmic bytes used, and the fraction of the measured roofline.
 
-    python -m simplang_b200.opbench [--iters 50] [--only gemv_f32,w4,...]
+    python -m simplang_b200.opbench [--iters 50] [--only gemv_f32,w4,rowops,gemm_i8,mma_peak,decode110m,decode3b]
 
 Each case rotates over enough independent operand copies that the working set exceeds twice the
 126 MB L2, so every iteration streams from HBM the way consecutive layers of a decode step do.
@@ -144,6 +144,28 @@ def bench_gemm_i8(iters):
             del B, Cd
 
 
+def bench_mma_peak(iters):
+    """Issue ceiling of the int8 tensor pipe for the 2-CTA tiling: the GEMM kernel run with its TMA loads and
+    its epilogue traffic switched off (SIMP_GEMM_I8_ABLATE=mma; the result buffer is not written).  This is
+    the measured int8 figure next to the calibrated 2 x bf16 one."""
+    rng = np.random.default_rng(3)
+    M = K = N = 8192
+    A = sg.DeviceBuffer.from_numpy(rng.integers(0, 256, (M, K), dtype=np.uint8))
+    B = sg.DeviceBuffer.from_numpy(rng.integers(-128, 128, (K, N), dtype=np.int8))
+    Cd = sg.DeviceBuffer(M * N * 4)
+    out = {}
+    for mode in ("mma", None):
+        if mode:
+            os.environ["SIMP_GEMM_I8_ABLATE"] = mode
+        else:
+            os.environ.pop("SIMP_GEMM_I8_ABLATE", None)
+        ms = timed(lambda i: sg.matmul_i8(A, B, Cd, M, K, N, a_unsigned=True, b_transposed=False), 1, min(iters, 20))
+        out[mode or "full"] = 2.0 * M * N * K / (ms * 1e-3) / 1e12
+    print(json.dumps({"op": "int8 MMA issue ceiling (2-CTA tiling, 8192^3, no loads / no epilogue)",
+                      "tops_mma_only": round(out["mma"], 1), "tops_full_kernel": round(out["full"], 1),
+                      "full_over_mma_only": round(out["full"] / out["mma"], 4)}), flush=True)
+
+
 def bench_decode(which, n_new=128):
     """Greedy decode tokens/s of the two model configurations (random init), device-timed over the
     whole generation (prompt of 16 teacher-forced tokens + n_new generated)."""
@@ -208,6 +230,8 @@ def main():
         bench_rowops(args.iters)
     if "gemm_i8" in which:
         bench_gemm_i8(args.iters)
+    if "mma_peak" in which:
+        bench_mma_peak(args.iters)
     if "decode110m" in which:
         bench_decode("110m")
     if "decode3b" in which:
