@@ -528,6 +528,9 @@ SIMP_API int simp_llama_create(const simp_llama_config* cfg, void** model) {
   A((void**)&m->xpB, w4_packed_bytes(int64_t(mx) + 32));
   A((void**)&m->ss, (mx / 32 + 1) * 4);
   A((void**)&m->ctl, 64);
+  A((void**)&m->pk_bar, 64);
+  A((void**)&m->pk_best_val, size_t(ctx().sm_count) * 4);
+  A((void**)&m->pk_best_idx, size_t(ctx().sm_count) * 4);
   if (rc != SIMP_OK) { simp_llama_destroy(m); return rc; }
   cudaMemsetAsync(m->ctl, 0, 64, ctx().stream);
   cudaMemsetAsync(m->attn_cnt, 0, size_t(c.n_heads) * 4, ctx().stream);
@@ -720,7 +723,8 @@ SIMP_API int simp_llama_destroy(void* model) {
   if (m->graph) cudaGraphExecDestroy(m->graph);
   void* ptrs[] = {m->tok_emb, m->rms_att, m->rms_ffn, m->rms_final, m->wcls, m->wq, m->wk, m->wv, m->wo, m->w1, m->w2,
                   m->w3, m->qweights, m->scales, m->zeros, m->x, m->xb, m->hb, m->q, m->k, m->v, m->logits, m->kc,
-                  m->vc, m->attn_part, m->attn_cnt, m->xpA, m->xpB, m->ss, m->ctl, m->prompt, m->out_tokens};
+                  m->vc, m->attn_part, m->attn_cnt, m->xpA, m->xpB, m->ss, m->ctl, m->prompt, m->out_tokens,
+                  m->pk_bar, m->pk_best_val, m->pk_best_idx};
   for (void* p : ptrs)
     if (p) cudaFree(p);
   delete m;

@@ -30,6 +30,11 @@ struct LlamaModel {
   int32_t *prompt = nullptr, *out_tokens = nullptr;
   int64_t prompt_cap = 0, out_cap = 0;
   int nsplit = 1;
+  // scratch of the persistent per-token kernels: grid-barrier words, per-block argmax candidates
+  unsigned* pk_bar = nullptr;
+  float* pk_best_val = nullptr;
+  int* pk_best_idx = nullptr;
+  bool pk_attr_done = false;   // the kernel's shared-memory attribute was set on this model's device
   cudaGraphExec_t graph = nullptr;
   bool loaded_any = false;
 };

@@ -286,20 +286,9 @@ bool persistent_f32_supported(const LlamaModel& m) {
   return !m.cfg.w4 && pk_device_ok(m) && persist_smem_bytes(m, ctx().sm_count) <= PK_MAX_DYN_SMEM;
 }
 
-struct PersistScratch {
-  unsigned* bar = nullptr;
-  float* best_val = nullptr;
-  int* best_idx = nullptr;
-};
-static PersistScratch g_ps;
-
 int pk_fill_common(LlamaModel& m, PkCommon& a) {
   const int G = ctx().sm_count;
-  if (!g_ps.bar) {
-    SIMP_CUDA(cudaMalloc(&g_ps.bar, 64));
-    SIMP_CUDA(cudaMalloc(&g_ps.best_val, size_t(G) * 4));
-    SIMP_CUDA(cudaMalloc(&g_ps.best_idx, size_t(G) * 4));
-  }
+  SIMP_REQUIRE(m.pk_bar && m.pk_best_val && m.pk_best_idx, SIMP_ERR_STATE, "persistent decode: model scratch missing");
   const simp_llama_config& c = m.cfg;
   a.dim = int(c.dim); a.hd = int(c.hidden_dim); a.kv = int(m.kv_dim); a.hs = int(m.head_size);
   a.n_heads = int(c.n_heads); a.kv_mul = int(c.n_heads / c.n_kv_heads); a.n_layers = int(c.n_layers);
@@ -310,14 +299,14 @@ int pk_fill_common(LlamaModel& m, PkCommon& a) {
   a.x = m.x; a.hb = m.hb; a.q = m.q; a.k = m.k; a.v = m.v; a.logits = m.logits; a.kc = m.kc; a.vc = m.vc;
   a.part = m.attn_part;
   a.ctl = m.ctl; a.prompt = m.prompt; a.out_tokens = m.out_tokens;
-  a.bar = g_ps.bar; a.best_val = g_ps.best_val; a.best_idx = g_ps.best_idx;
+  a.bar = m.pk_bar; a.best_val = m.pk_best_val; a.best_idx = m.pk_best_idx;
   a.status = ctx().dev_status;
   return SIMP_OK;
 }
 
 // Zeroes the barrier words and launches `kernel` cooperatively: one block per SM, all co-resident.
-int pk_launch(const void* kernel, void* args_struct, size_t smem, cudaStream_t st) {
-  SIMP_CUDA(cudaMemsetAsync(g_ps.bar, 0, 8, st));
+int pk_launch(const void* kernel, void* args_struct, unsigned* bar, size_t smem, cudaStream_t st) {
+  SIMP_CUDA(cudaMemsetAsync(bar, 0, 8, st));
   void* params[1] = {args_struct};
   SIMP_CUDA(cudaLaunchCooperativeKernel(kernel, dim3(unsigned(ctx().sm_count)), dim3(PK_BLOCK), params, smem, st));
   return SIMP_OK;
@@ -338,12 +327,11 @@ int enqueue_token_persistent_f32(LlamaModel& m, cudaStream_t st) {
   const PersistPlan plan = persist_plan(m, ctx().sm_count);
   for (int k = 0; k < 5; ++k) a.koff[k] = plan.koff[k];
   a.xs_off = plan.xs_off;
-  static bool attr_set = false;
-  if (!attr_set) {
+  if (!m.pk_attr_done) {   // first (eager) pass of this model, outside any stream capture
     SIMP_CUDA(cudaFuncSetAttribute(llama_f32_token_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(PK_MAX_DYN_SMEM)));
-    attr_set = true;
+    m.pk_attr_done = true;
   }
-  return pk_launch(reinterpret_cast<const void*>(llama_f32_token_kernel), &a, plan.total, st);
+  return pk_launch(reinterpret_cast<const void*>(llama_f32_token_kernel), &a, a.c.bar, plan.total, st);
 }
 
 }  // namespace simp

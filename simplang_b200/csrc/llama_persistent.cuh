@@ -400,6 +400,6 @@ __device__ __forceinline__ void pk_advance(const PkCommon& c, int pos) {
 struct LlamaModel;
 int pk_fill_common(LlamaModel& m, PkCommon& c);
 bool pk_device_ok(const LlamaModel& m);
-int pk_launch(const void* kernel, void* args_struct, size_t smem, cudaStream_t st);
+int pk_launch(const void* kernel, void* args_struct, unsigned* bar, size_t smem, cudaStream_t st);
 
 }  // namespace simp

@@ -487,13 +487,11 @@ int enqueue_token_persistent_w4(LlamaModel& m, cudaStream_t st) {
   a.ka = p.ka; a.kg = p.kg; a.kd = p.kd;
   for (int s = 0; s < PW_SLOTS; ++s) a.slot_off[s] = p.slot_off[s];
   a.xp_off = p.xp_off; a.vec_off = p.vec_off; a.part_off = p.part_off;
-  static bool attr_set = false;
-  if (!attr_set) {
-    SIMP_CUDA(cudaFuncSetAttribute(llama_w4_token_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   int(PK_SMEM_LIMIT - PW_STATIC_SMEM)));
-    attr_set = true;
+  if (!m.pk_attr_done) {   // first (eager) pass of this model, outside any stream capture
+    SIMP_CUDA(cudaFuncSetAttribute(llama_w4_token_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(PK_SMEM_LIMIT - PW_STATIC_SMEM)));
+    m.pk_attr_done = true;
   }
-  return pk_launch(reinterpret_cast<const void*>(llama_w4_token_kernel), &a, p.total, st);
+  return pk_launch(reinterpret_cast<const void*>(llama_w4_token_kernel), &a, a.c.bar, p.total, st);
 }
 
 }  // namespace simp
