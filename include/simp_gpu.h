@@ -197,6 +197,31 @@ int simp_llama_generate(void* model, const int32_t* prompt, int64_t n_prompt, in
                         int32_t* tokens_out, float* logits_trace, float* ms_out);
 int simp_llama_destroy(void* model);
 
+/* ---- int8 LLaMA-3.2-1B-style token forward ---------------------------------------------------
+ * Replaces: the exported function `llama32_forward` of examples/llama2/llama32_1b_int8_tensor.sl:16-305
+ * as the host examples/llama2/bench_llama32_1b_int8.cpp:200-318 drives it: an int8 input vector, a position,
+ * f32 logits out; f32 residual stream and norms, int8 activations, int8 weights pre-transposed [N, K]
+ * (tensor_matmul_nt, i32 accumulation), int8 KV cache (acc / 256), grouped-query attention, f32 classifier.
+ * The .sl text applies no RoPE and divides scores by the literal 8.0; both are kept.
+ * Tensors (simp_llama_i8_load names): rms_att_w, rms_ffn_w [n_layers, dim], rms_final_w [dim], wcls
+ * [vocab, dim] (f32); wq_t, wo_t [n_layers, dim, dim], wk_t, wv_t [n_layers, kv_dim, dim], w1_t, w3_t
+ * [n_layers, hidden, dim], w2_t [n_layers, dim, hidden] (int8).  dim and hidden_dim must be multiples of 16,
+ * head_dim even and <= 128.  The KV cache lives on the device and is zeroed at creation. */
+typedef struct simp_llama_i8_config {
+  int64_t dim, hidden_dim, n_layers, n_heads, n_kv_heads, vocab_size, max_seq_len, head_dim;
+} simp_llama_i8_config;
+int simp_llama_i8_create(const simp_llama_i8_config* cfg, void** model);
+int simp_llama_i8_load(void* model, const char* name, const void* host, size_t bytes);
+/* One token: x_i8_host holds dim int8 values; logits_host (vocab floats) may be NULL. */
+int simp_llama_i8_forward(void* model, const int8_t* x_i8_host, int64_t pos, float* logits_host);
+/* The host's decode loop (bench_llama32_1b_int8.cpp:283-318): n_tokens forwards of the same input at
+ * positions start_pos, start_pos + 1, ...; ms_out receives the device time of the whole loop.  The position
+ * lives in device memory, so the loop runs without host synchronisation. */
+int simp_llama_i8_decode_loop(void* model, const int8_t* x_i8_host, int64_t start_pos, int64_t n_tokens,
+                              float* logits_host, float* ms_out);
+int simp_llama_i8_reset_cache(void* model);
+int simp_llama_i8_destroy(void* model);
+
 /* ---- multi-GPU (one process per GPU, NCCL over NVLink / NVSwitch) ---------------------------
  * Replaces: the reference's only parallel schemes, OpenMP row tiles (src/mlir/mlir_pipeline.cpp:265-364)
  * and host-side row chunks sharing B (simptensor/benchmarks/bench_int8_parallel_runner.cpp:70-91).

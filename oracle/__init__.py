@@ -207,6 +207,50 @@ class Llama:
         return self.logits
 
 
+I8_TENSORS = ("rms_att_w", "rms_ffn_w", "rms_final_w", "wcls", "wq_t", "wk_t", "wv_t", "wo_t", "w1_t", "w2_t", "w3_t")
+
+
+class LlamaI8Struct(C.Structure):
+    _fields_ = [(n, i64) for n in ("dim", "hidden_dim", "n_layers", "n_heads", "n_kv_heads", "vocab_size",
+                                   "max_seq_len", "head_dim")] + \
+               [(n, C.c_void_p) for n in I8_TENSORS] + \
+               [(n, C.c_void_p) for n in ("k_cache", "v_cache")]
+
+
+class LlamaI8:
+    """Whole-token forward of the int8 LLaMA-3.2-1B-style model (llama32_1b_int8_tensor.sl) on the CPU.
+
+    ``cfg``: dict with dim, hidden_dim, n_layers, n_heads, n_kv_heads, vocab_size, max_seq_len, head_dim.
+    ``tensors``: dict of numpy arrays named as in ``I8_TENSORS`` (int8 weights pre-transposed [N, K]).
+    The int8 KV cache lives in the object; ``forward(x_i8, pos)`` returns the logits.
+    """
+
+    def __init__(self, cfg, tensors, threads=0):
+        self.cfg = dict(cfg)
+        self._keep = {k: np.ascontiguousarray(v) for k, v in tensors.items()}
+        kv_dim = cfg["n_kv_heads"] * cfg["head_dim"]
+        self.k_cache = np.zeros(cfg["n_layers"] * cfg["max_seq_len"] * kv_dim, np.int8)
+        self.v_cache = np.zeros_like(self.k_cache)
+        self.logits = np.zeros(cfg["vocab_size"], np.float32)
+        s = LlamaI8Struct()
+        for n in ("dim", "hidden_dim", "n_layers", "n_heads", "n_kv_heads", "vocab_size", "max_seq_len", "head_dim"):
+            setattr(s, n, cfg[n])
+        for n in I8_TENSORS:
+            setattr(s, n, _ptr(self._keep[n]))
+        s.k_cache, s.v_cache = _ptr(self.k_cache), _ptr(self.v_cache)
+        self._s = s
+        self.threads = threads if threads > 0 else lib().simp_oracle_max_threads()
+
+    def forward(self, x_i8, pos):
+        x_i8 = np.ascontiguousarray(x_i8, np.int8)
+        assert x_i8.size == self.cfg["dim"] and 0 <= pos < self.cfg["max_seq_len"]
+        f = lib().simp_oracle_llama_i8_forward
+        f.argtypes = [C.c_void_p, C.c_void_p, i64, C.c_void_p, C.c_int32]
+        f.restype = None
+        f(C.byref(self._s), _ptr(x_i8), pos, _ptr(self.logits), self.threads)
+        return self.logits
+
+
 # --------------------------------------------------------------------------- reference's own kernels
 def cpu_has_vnni() -> bool:
     try:

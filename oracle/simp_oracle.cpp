@@ -446,3 +446,116 @@ ORACLE_API int64_t simp_oracle_argmax(const float* v, int64_t n) {
     if (v[i] > v[best]) best = i;
   return best;
 }
+
+// ---------------------------------------------------------------------------
+// Whole-token forward of the int8 LLaMA-3.2-1B-style model
+// (examples/llama2/llama32_1b_int8_tensor.sl:16-305): f32 residual stream and norms, int8
+// activations and weights ([N,K] pre-transposed), i32 accumulation (tensor_matmul_nt), int8 KV
+// cache, grouped-query attention, f32 classifier.  Restated literally, including what the .sl
+// text leaves out or hard-codes:
+//   * no RoPE is applied (the loop at :124-140 computes the angles and discards them);
+//   * the score divisor is the literal 8.0 (:178), whatever head_dim is;
+//   * K and V enter the cache as (i8)(acc / 256) -- integer division truncating toward zero, then
+//     a narrowing that keeps the low 8 bits (:146-149);
+//   * attn_out = (i32) trunc(weighted sum) (:196); the next input is clamp(attn_out / 256.0) (:207-213);
+//   * the FFN activation (i8)(silu(gate/65536) * (up/65536) * 127) has no clamp (:258-265): the f32->i8
+//     cast is taken as truncation to i32 followed by narrowing modulo 256 (what the x86 code does);
+//   * residual updates x += (f32)acc / 65536.0 (:227, :275).
+// f32 sums run sequentially in index order, as the scalar loops of the lowering do.
+// Parity unpinned: the reference holds no known-answer test for this model (its host,
+// bench_llama32_1b_int8.cpp, only times it).
+// ---------------------------------------------------------------------------
+struct SimpOracleLlamaI8 {
+  int64_t dim, hidden_dim, n_layers, n_heads, n_kv_heads, vocab_size, max_seq_len, head_dim;
+  const float *rms_att_w, *rms_ffn_w, *rms_final_w, *wcls;
+  const int8_t *wq_t, *wk_t, *wv_t, *wo_t, *w1_t, *w2_t, *w3_t;
+  int8_t *k_cache, *v_cache;  // [n_layers, max_seq_len, kv_dim], caller-owned
+};
+
+namespace {
+// tensor_matmul_nt with M = 1: out[j] = sum_p (i32)x[p] * (i32)Wt[j*K + p]
+void matvec_nt_i8(const int8_t* x, const int8_t* Wt, int32_t* out, int64_t N, int64_t K, int nt) {
+#pragma omp parallel for num_threads(nt) schedule(static) if (nt > 1)
+  for (int64_t j = 0; j < N; ++j) {
+    int32_t acc = 0;
+    const int8_t* w = Wt + j * K;
+    for (int64_t p = 0; p < K; ++p) acc += int32_t(x[p]) * int32_t(w[p]);
+    out[j] = acc;
+  }
+}
+inline int8_t quant_clamped(float v) {
+  if (v > 127.0f) v = 127.0f;
+  if (v < -128.0f) v = -128.0f;
+  return int8_t(int32_t(v));
+}
+}  // namespace
+
+ORACLE_API void simp_oracle_llama_i8_forward(const SimpOracleLlamaI8* mp, const int8_t* x_i8, int64_t pos,
+                                             float* logits, int threads) {
+  const SimpOracleLlamaI8& m = *mp;
+  const int nt = clamp_threads(threads);
+  const int64_t dim = m.dim, hd = m.hidden_dim, hs = m.head_dim;
+  const int64_t kv_dim = m.n_kv_heads * hs, n_rep = m.n_heads / m.n_kv_heads, seq_len = pos + 1;
+  std::vector<float> x(dim), xb(dim), att_scores(m.n_heads * m.max_seq_len), att_probs(m.n_heads * m.max_seq_len);
+  std::vector<int8_t> xb_i8(dim), ffn_hb(hd);
+  std::vector<int32_t> Q(dim), K(kv_dim), V(kv_dim), attn_out(dim), Wo(dim), Gate(hd), Up(hd), Down(dim);
+  for (int64_t i = 0; i < dim; ++i) x[i] = float(x_i8[i]) * 1.0f;
+  for (int64_t layer = 0; layer < m.n_layers; ++layer) {
+    simp_oracle_rmsnorm(x.data(), m.rms_att_w, xb.data(), dim, 0.00001f, layer * dim);
+    for (int64_t i = 0; i < dim; ++i) xb_i8[i] = quant_clamped(xb[i] * 127.0f);
+    matvec_nt_i8(xb_i8.data(), m.wq_t + layer * dim * dim, Q.data(), dim, dim, nt);
+    matvec_nt_i8(xb_i8.data(), m.wk_t + layer * kv_dim * dim, K.data(), kv_dim, dim, nt);
+    matvec_nt_i8(xb_i8.data(), m.wv_t + layer * kv_dim * dim, V.data(), kv_dim, dim, nt);
+    const int64_t cache_offset = layer * m.max_seq_len * kv_dim + pos * kv_dim;
+    for (int64_t i = 0; i < kv_dim; ++i) {
+      m.k_cache[cache_offset + i] = int8_t(uint8_t(uint32_t(K[i] / 256) & 0xffu));
+      m.v_cache[cache_offset + i] = int8_t(uint8_t(uint32_t(V[i] / 256) & 0xffu));
+    }
+    for (int64_t i = 0; i < dim; ++i) attn_out[i] = 0;
+#pragma omp parallel for num_threads(nt) schedule(static) if (nt > 1)
+    for (int64_t h = 0; h < m.n_heads; ++h) {
+      const int64_t q_offset = h * hs, kv_head_offset = (h / n_rep) * hs, att_offset = h * m.max_seq_len;
+      for (int64_t t = 0; t < seq_len; ++t) {
+        float score = 0.0f;
+        const int64_t k_pos = layer * m.max_seq_len * kv_dim + t * kv_dim + kv_head_offset;
+        for (int64_t d = 0; d < hs; ++d) score = score + float(Q[q_offset + d]) * float(m.k_cache[k_pos + d]);
+        att_scores[att_offset + t] = score / 8.0f;
+      }
+      simp_oracle_softmax(att_scores.data(), att_probs.data(), seq_len, att_offset, att_offset);
+      for (int64_t d = 0; d < hs; ++d) {
+        float val = 0.0f;
+        for (int64_t t = 0; t < seq_len; ++t) {
+          const int64_t v_pos = layer * m.max_seq_len * kv_dim + t * kv_dim + kv_head_offset;
+          val = val + att_probs[att_offset + t] * float(m.v_cache[v_pos + d]);
+        }
+        attn_out[q_offset + d] = int32_t(val);
+      }
+    }
+    for (int64_t i = 0; i < dim; ++i) xb_i8[i] = quant_clamped(float(attn_out[i]) / 256.0f);
+    matvec_nt_i8(xb_i8.data(), m.wo_t + layer * dim * dim, Wo.data(), dim, dim, nt);
+    for (int64_t i = 0; i < dim; ++i) x[i] = x[i] + float(Wo[i]) / 65536.0f;
+    simp_oracle_rmsnorm(x.data(), m.rms_ffn_w, xb.data(), dim, 0.00001f, layer * dim);
+    for (int64_t i = 0; i < dim; ++i) xb_i8[i] = quant_clamped(xb[i] * 127.0f);
+    matvec_nt_i8(xb_i8.data(), m.w1_t + layer * hd * dim, Gate.data(), hd, dim, nt);
+    matvec_nt_i8(xb_i8.data(), m.w3_t + layer * hd * dim, Up.data(), hd, dim, nt);
+    for (int64_t i = 0; i < hd; ++i) {
+      const float gate_f = float(Gate[i]) / 65536.0f;
+      const float silu = gate_f / (1.0f + std::exp(0.0f - gate_f));
+      const float up_f = float(Up[i]) / 65536.0f;
+      float hb_val = silu * up_f * 127.0f;
+      if (hb_val < -2147483648.0f) hb_val = -2147483648.0f;  // keep the conversion defined
+      if (hb_val > 2147483520.0f) hb_val = 2147483520.0f;
+      ffn_hb[i] = int8_t(uint8_t(uint32_t(int32_t(hb_val)) & 0xffu));
+    }
+    matvec_nt_i8(ffn_hb.data(), m.w2_t + layer * dim * hd, Down.data(), dim, hd, nt);
+    for (int64_t i = 0; i < dim; ++i) x[i] = x[i] + float(Down[i]) / 65536.0f;
+  }
+  simp_oracle_rmsnorm(x.data(), m.rms_final_w, xb.data(), dim, 0.00001f, 0);
+#pragma omp parallel for num_threads(nt) schedule(static) if (nt > 1)
+  for (int64_t i = 0; i < m.vocab_size; ++i) {
+    float sum = 0.0f;
+    const float* w = m.wcls + i * dim;
+    for (int64_t j = 0; j < dim; ++j) sum = sum + w[j] * xb[j];
+    logits[i] = sum;
+  }
+}

@@ -67,6 +67,12 @@ _SIGNATURES = {
     "simp_llama_forward": [vp, i64, i64, vp],
     "simp_llama_generate": [vp, vp, i64, i64, vp, vp, C.POINTER(C.c_float)],
     "simp_llama_destroy": [vp],
+    "simp_llama_i8_create": [vp, C.POINTER(vp)],
+    "simp_llama_i8_load": [vp, C.c_char_p, vp, C.c_size_t],
+    "simp_llama_i8_forward": [vp, vp, i64, vp],
+    "simp_llama_i8_decode_loop": [vp, vp, i64, i64, vp, C.POINTER(C.c_float)],
+    "simp_llama_i8_reset_cache": [vp],
+    "simp_llama_i8_destroy": [vp],
     "simp_dist_unique_id": [vp, C.c_size_t],
     "simp_dist_init": [C.c_int, C.c_int, vp, C.c_size_t],
     "simp_dist_shutdown": [],
@@ -323,6 +329,57 @@ class Llama:
     def close(self):
         if self.h:
             lib().simp_llama_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class LlamaI8Config(C.Structure):
+    _fields_ = [(n, i64) for n in ("dim", "hidden_dim", "n_layers", "n_heads", "n_kv_heads", "vocab_size",
+                                   "max_seq_len", "head_dim")]
+
+
+class LlamaI8:
+    """Device-resident int8 LLaMA-3.2-1B-style model (simp_llama_i8_*): int8 input vector and position in,
+    f32 logits out.  ``tensors`` maps the .sl argument names (rms_att_w, wq_t, ...) to numpy arrays."""
+
+    def __init__(self, cfg: dict, tensors: dict):
+        c = LlamaI8Config(**{k: cfg[k] for k in ("dim", "hidden_dim", "n_layers", "n_heads", "n_kv_heads", "vocab_size",
+                                                  "max_seq_len", "head_dim")})
+        h = vp()
+        check(lib().simp_llama_i8_create(C.byref(c), C.byref(h)))
+        self.h = h
+        self.dim, self.vocab = cfg["dim"], cfg["vocab_size"]
+        for name, arr in tensors.items():
+            arr = np.ascontiguousarray(arr)
+            check(lib().simp_llama_i8_load(self.h, name.encode(), arr.ctypes.data, arr.nbytes))
+
+    def forward(self, x_i8, pos: int) -> np.ndarray:
+        x_i8 = np.ascontiguousarray(x_i8, np.int8)
+        assert x_i8.size == self.dim
+        out = np.empty(self.vocab, np.float32)
+        check(lib().simp_llama_i8_forward(self.h, x_i8.ctypes.data, pos, out.ctypes.data))
+        return out
+
+    def decode_loop(self, x_i8, start_pos: int, n_tokens: int):
+        """n_tokens forwards at consecutive positions; returns (logits of the last one, device ms of the loop)."""
+        x_i8 = np.ascontiguousarray(x_i8, np.int8)
+        assert x_i8.size == self.dim
+        out = np.empty(self.vocab, np.float32)
+        ms = C.c_float()
+        check(lib().simp_llama_i8_decode_loop(self.h, x_i8.ctypes.data, start_pos, n_tokens, out.ctypes.data, C.byref(ms)))
+        return out, float(ms.value)
+
+    def reset_cache(self):
+        check(lib().simp_llama_i8_reset_cache(self.h))
+
+    def close(self):
+        if self.h:
+            lib().simp_llama_i8_destroy(self.h)
             self.h = None
 
     def __del__(self):

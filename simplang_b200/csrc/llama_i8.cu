@@ -1,0 +1,531 @@
+// llama_i8.cu -- token forward of the int8 LLaMA-3.2-1B-style model
+// (examples/llama2/llama32_1b_int8_tensor.sl:16-305): f32 residual stream and norms, int8 activations,
+// int8 weights pre-transposed [N, K] with i32 accumulation (tensor_matmul_nt at M = 1), int8 KV cache,
+// grouped-query attention, f32 classifier.  One CUDA graph per token, programmatic dependent launch
+// between the kernels; the position lives in device memory.
+//
+// Kernels per layer (5):
+//   gemv_i8_kernel<PRO_NORM, EPI_STORE>   rmsnorm + quantise folded into the prologue, q | k | v rows (i32)
+//   attn_i8_kernel                        KV store (acc / 256 -> i8), scores / 8.0, softmax, weighted sum,
+//                                         (i32) trunc, requantise clamp(v / 256.0) -> i8
+//   gemv_i8_kernel<PRO_I8, EPI_RESID>     wo: x += (f32)acc / 65536
+//   gemv_i8_kernel<PRO_NORM, EPI_GATEUP>  w1 | w3 pairs: (i8)(silu(g / 65536) * (u / 65536) * 127), no clamp
+//   gemv_i8_kernel<PRO_I8, EPI_RESID>     w2: x += (f32)acc / 65536
+// The GEMV is a streaming kernel (HBM-bound: every weight byte is read once per token): a warp owns RPW
+// rows, lanes read 16-byte pieces of the K-contiguous rows with no-allocate loads, four independent
+// pieces per row in flight, dp4a.s32.s32 against the int8 input vector staged in shared memory, one
+// shuffle reduction per row.  Integer accumulation is exact, so q, k, v, wo, gate, up and down match the CPU
+// reference bit for bit whenever their int8 inputs do; differences can only enter through the f32 sums of
+// the norms and of the attention (different summation order) at a quantisation boundary.
+#include <cstring>
+#include <string>
+
+#include "common.cuh"
+#include "gemv_f32_core.cuh"
+
+namespace simp {
+
+struct LlamaI8Model {
+  simp_llama_i8_config cfg;
+  int64_t kv_dim;
+  float *rms_att = nullptr, *rms_ffn = nullptr, *rms_final = nullptr, *wcls = nullptr;
+  int8_t *wq = nullptr, *wk = nullptr, *wv = nullptr, *wo = nullptr, *w1 = nullptr, *w2 = nullptr, *w3 = nullptr;
+  // state
+  int8_t *x_i8 = nullptr, *xb_i8 = nullptr, *ffn_hb = nullptr, *kc = nullptr, *vc = nullptr;
+  float *x = nullptr, *xb = nullptr, *logits = nullptr;
+  int32_t *q = nullptr, *k = nullptr, *v = nullptr;
+  int* ctl = nullptr;   // [0] pos
+  cudaGraphExec_t graph = nullptr;
+};
+
+enum { PRO_NORM = 0, PRO_I8 = 1 };
+enum { EPI_STORE = 0, EPI_RESID = 1, EPI_GATEUP = 2 };
+constexpr int GI8_WARPS = 8;
+
+struct GemvI8Seg {
+  const int8_t* w;   // [rows, K]
+  int32_t* out;      // EPI_STORE
+  int rows;
+};
+struct GemvI8Args {
+  GemvI8Seg seg[3];
+  int nseg, K;
+  const float* x_f32;     // PRO_NORM: vector to normalise; EPI_RESID: residual stream (updated in place)
+  const float* norm_w;    // PRO_NORM
+  const int8_t* x_i8;     // PRO_I8
+  float* resid;           // EPI_RESID: x[row] += acc / 65536
+  int8_t* hb;             // EPI_GATEUP: seg[0] = w1, seg[1] = w3
+  int total_rows;         // rows over all segments (EPI_GATEUP: rows of one matrix)
+};
+
+__device__ __forceinline__ int dp4a_ss(uint32_t a, uint32_t b, int c) {
+  int d;
+  asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+__device__ __forceinline__ uint4 ldg_stream_u4(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+// f32 -> i8 as the model text does it: clamp to [-128, 127], truncate toward zero.
+__device__ __forceinline__ int8_t quant_clamped(float v) {
+  v = fminf(v, 127.0f);
+  v = fmaxf(v, -128.0f);
+  return int8_t(__float2int_rz(v));
+}
+
+template <int PRO, int EPI, int RPW>
+__global__ void __launch_bounds__(GI8_WARPS * 32) gemv_i8_kernel(const GemvI8Args a) {
+  extern __shared__ __align__(16) uint8_t gi8_smem[];   // K int8 inputs
+  __shared__ float red[33];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int K = a.K, k16 = K >> 4;
+  constexpr int NM = EPI == EPI_GATEUP ? 2 : 1;
+  pdl_launch_dependents();
+  pdl_wait();
+  // ---- prologue: the int8 input vector in shared memory
+  if (PRO == PRO_NORM) {
+    // y = (x / r) * w, r = sqrt(mean(x^2) + 1e-5); v = y * 127 clamped, truncated (llama32_1b_int8_tensor.sl:93-103)
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < K; i += blockDim.x) {
+      const float t = a.x_f32[i];
+      ss += t * t;
+    }
+    ss = block_sum(ss, red);
+    const float r = sqrtf(ss / float(K) + 1e-5f);
+    for (int i = threadIdx.x; i < K; i += blockDim.x)
+      reinterpret_cast<int8_t*>(gi8_smem)[i] = quant_clamped(((a.x_f32[i] / r) * a.norm_w[i]) * 127.0f);
+  } else {
+    for (int i = threadIdx.x; i < k16; i += blockDim.x)
+      reinterpret_cast<uint4*>(gi8_smem)[i] = reinterpret_cast<const uint4*>(a.x_i8)[i];
+  }
+  __syncthreads();
+  const uint4* xs = reinterpret_cast<const uint4*>(gi8_smem);
+
+  const int row0 = (blockIdx.x * GI8_WARPS + warp) * RPW;
+  if (row0 >= a.total_rows) return;
+  // rows of this warp: (segment, row) pairs; a warp's RPW rows never straddle segments when every segment's
+  // row count is a multiple of RPW (checked on the host)
+  int s = 0, r_in = row0;
+  if (EPI != EPI_GATEUP)
+    while (s + 1 < a.nseg && r_in >= a.seg[s].rows) { r_in -= a.seg[s].rows; ++s; }
+  int acc[NM][RPW];
+#pragma unroll
+  for (int m = 0; m < NM; ++m)
+#pragma unroll
+    for (int r = 0; r < RPW; ++r) acc[m][r] = 0;
+  const uint4* wrow[NM][RPW];
+#pragma unroll
+  for (int m = 0; m < NM; ++m)
+#pragma unroll
+    for (int r = 0; r < RPW; ++r)
+      wrow[m][r] = reinterpret_cast<const uint4*>(a.seg[EPI == EPI_GATEUP ? m : s].w + size_t(r_in + r) * K);
+  constexpr int U = 4;   // 16-byte pieces per row in flight per lane
+  for (int j0 = lane; j0 < k16; j0 += 32 * U) {
+    uint4 w[NM][RPW][U];
+#pragma unroll
+    for (int m = 0; m < NM; ++m)
+#pragma unroll
+      for (int r = 0; r < RPW; ++r)
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int j = j0 + 32 * u;
+          w[m][r][u] = j < k16 ? ldg_stream_u4(wrow[m][r] + j) : make_uint4(0u, 0u, 0u, 0u);
+        }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int j = j0 + 32 * u;
+      const uint4 xv = j < k16 ? xs[j] : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+      for (int m = 0; m < NM; ++m)
+#pragma unroll
+        for (int r = 0; r < RPW; ++r) {
+          int t = acc[m][r];
+          t = dp4a_ss(w[m][r][u].x, xv.x, t);
+          t = dp4a_ss(w[m][r][u].y, xv.y, t);
+          t = dp4a_ss(w[m][r][u].z, xv.z, t);
+          t = dp4a_ss(w[m][r][u].w, xv.w, t);
+          acc[m][r] = t;
+        }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < RPW; ++r) {
+    int v0 = acc[0][r], v1 = NM == 2 ? acc[NM - 1][r] : 0;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      v0 += __shfl_xor_sync(0xffffffffu, v0, o);
+      if (NM == 2) v1 += __shfl_xor_sync(0xffffffffu, v1, o);
+    }
+    if (lane == 0) {
+      const int row = r_in + r;
+      if (EPI == EPI_STORE) a.seg[s].out[row] = v0;
+      if (EPI == EPI_RESID) a.resid[row] = a.resid[row] + float(v0) / 65536.0f;
+      if (EPI == EPI_GATEUP) {
+        const float gate_f = float(v0) / 65536.0f;
+        const float silu = gate_f / (1.0f + expf(0.0f - gate_f));
+        const float up_f = float(v1) / 65536.0f;
+        float hb = silu * up_f * 127.0f;
+        hb = fmaxf(fminf(hb, 2147483520.0f), -2147483648.0f);   // keeps the conversion defined
+        a.hb[row] = int8_t(uint8_t(uint32_t(__float2int_rz(hb)) & 0xffu));
+      }
+    }
+  }
+}
+
+// x_f32[i] = (f32) x_i8[i]  (llama32_1b_int8_tensor.sl:78-82)
+__global__ void i8_input_kernel(const int8_t* __restrict__ x_i8, float* __restrict__ x, int n) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) x[i] = float(x_i8[i]) * 1.0f;
+}
+
+// One block per query head (llama32_1b_int8_tensor.sl:142-215).  The new K/V row is derived by every block
+// from the i32 projections (so no block depends on another block's cache write); the first head of each KV
+// group stores it.  scores[t] = sum_d f32(q_d) * f32(k_td) / 8.0; softmax as the op (expf, division);
+// out_d = (i32) trunc(sum_t p_t * f32(v_td)); xb_i8 = clamp(out / 256.0) truncated.
+constexpr int AI8_WARPS = 8;
+__global__ void __launch_bounds__(AI8_WARPS * 32) attn_i8_kernel(const int32_t* __restrict__ Q, const int32_t* __restrict__ Kp,
+                                                                  const int32_t* __restrict__ Vp, int8_t* __restrict__ kc,
+                                                                  int8_t* __restrict__ vc, int8_t* __restrict__ xb_i8,
+                                                                  const int* __restrict__ ctl, int hs, int kv_dim, int n_rep,
+                                                                  int max_seq, int layer) {
+  extern __shared__ float scores[];   // max_seq floats
+  __shared__ float qf[128], knew[128], vnew[128], red[33];
+  __shared__ float part[AI8_WARPS][128];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int h = blockIdx.x, kvh = h / n_rep;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int pos = ctl[0], seq = pos + 1;
+  int8_t* kbase = kc + size_t(layer) * max_seq * kv_dim + kvh * hs;
+  int8_t* vbase = vc + size_t(layer) * max_seq * kv_dim + kvh * hs;
+  for (int d = threadIdx.x; d < hs; d += blockDim.x) {
+    qf[d] = float(Q[h * hs + d]);
+    const int8_t k8 = int8_t(uint8_t(uint32_t(Kp[kvh * hs + d] / 256) & 0xffu));
+    const int8_t v8 = int8_t(uint8_t(uint32_t(Vp[kvh * hs + d] / 256) & 0xffu));
+    knew[d] = float(k8);
+    vnew[d] = float(v8);
+    if (h % n_rep == 0) {
+      kbase[size_t(pos) * kv_dim + d] = k8;
+      vbase[size_t(pos) * kv_dim + d] = v8;
+    }
+  }
+  __syncthreads();
+  // ---- scores: a warp per timestep, four timesteps in flight; lanes own dims lane, lane + 32, ...
+  float q_r[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) q_r[e] = lane + 32 * e < hs ? qf[lane + 32 * e] : 0.0f;
+  constexpr int TU = 4;
+  for (int tb = warp; tb < seq; tb += AI8_WARPS * TU) {
+    float kf[TU][4];
+#pragma unroll
+    for (int u = 0; u < TU; ++u) {
+      const int t = tb + u * AI8_WARPS;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int d = lane + 32 * e;
+        kf[u][e] = 0.0f;
+        if (d < hs && t < seq) kf[u][e] = t == pos ? knew[d] : float(kbase[size_t(t) * kv_dim + d]);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < TU; ++u) {
+      const int t = tb + u * AI8_WARPS;
+      float sc = 0.0f;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) sc = fmaf(q_r[e], kf[u][e], sc);
+      sc = warp_sum(sc);
+      if (lane == 0 && t < seq) scores[t] = sc / 8.0f;
+    }
+  }
+  __syncthreads();
+  // ---- softmax over [0, seq)
+  float mx = -INFINITY;
+  for (int t = threadIdx.x; t < seq; t += blockDim.x) mx = fmaxf(mx, scores[t]);
+  mx = block_max(mx, red);
+  float sum = 0.0f;
+  for (int t = threadIdx.x; t < seq; t += blockDim.x) {
+    const float e = expf(scores[t] - mx);
+    scores[t] = e;
+    sum += e;
+  }
+  sum = block_sum(sum, red);
+  // ---- weighted sum of V: warps split the timesteps, lanes the dims
+  float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+  for (int t = warp; t < seq; t += AI8_WARPS) {
+    const float p = scores[t] / sum;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int d = lane + 32 * e;
+      if (d < hs) acc[e] = fmaf(p, t == pos ? vnew[d] : float(vbase[size_t(t) * kv_dim + d]), acc[e]);
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < 4; ++e)
+    if (lane + 32 * e < hs) part[warp][lane + 32 * e] = acc[e];
+  __syncthreads();
+  for (int d = threadIdx.x; d < hs; d += blockDim.x) {
+    float val = 0.0f;
+#pragma unroll
+    for (int w = 0; w < AI8_WARPS; ++w) val += part[w][d];
+    const int32_t out = __float2int_rz(val);                 // attn_out = val as i32
+    xb_i8[h * hs + d] = quant_clamped(float(out) / 256.0f);   // next projection's input
+  }
+}
+
+// xb = rmsnorm(x) * w for the classifier (one block).
+__global__ void __launch_bounds__(1024) i8_final_norm_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                                             float* __restrict__ y, int n) {
+  __shared__ float red[33];
+  pdl_launch_dependents();
+  pdl_wait();
+  float ss = 0.0f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) ss += x[i] * x[i];
+  ss = block_sum(ss, red);
+  const float r = sqrtf(ss / float(n) + 1e-5f);
+  for (int i = threadIdx.x; i < n; i += blockDim.x) y[i] = (x[i] / r) * w[i];
+}
+__global__ void i8_advance_kernel(int* ctl) { ctl[0] = ctl[0] + 1; }
+
+// ---------------------------------------------------------------------------------------------
+#define I8_LAUNCH(...)                                                                                  \
+  do {                                                                                                  \
+    cudaError_t e__ = launch_kernel(__VA_ARGS__);                                                       \
+    if (e__ != cudaSuccess)                                                                             \
+      return set_error(SIMP_ERR_CUDA, "int8 decode launch failed: %s (%s:%d)", cudaGetErrorString(e__), __FILE__, __LINE__); \
+  } while (0)
+
+template <int PRO, int EPI>
+static int gemv_i8_launch(GemvI8Args a, cudaStream_t st, int sms, bool pdl) {
+  // rows per warp: 4 when that still leaves two blocks per SM, else 2, else 1 (all segment row counts must
+  // divide; they are multiples of 16 here)
+  int rpw = 4;
+  bool div4 = true, div2 = true;
+  for (int s = 0; s < (EPI == EPI_GATEUP ? 1 : a.nseg); ++s) {
+    div4 = div4 && a.seg[s].rows % 4 == 0;
+    div2 = div2 && a.seg[s].rows % 2 == 0;
+  }
+  while (rpw > 1 && ((rpw == 4 && !div4) || (rpw == 2 && !div2) || a.total_rows / (GI8_WARPS * rpw) < 2 * sms)) rpw >>= 1;
+  if (EPI == EPI_GATEUP && rpw > 2) rpw = 2;   // two matrices per row: keep the loads in flight per lane bounded
+  const int grid = (a.total_rows + GI8_WARPS * rpw - 1) / (GI8_WARPS * rpw);
+  const size_t smem = size_t(a.K);
+  cudaError_t e;
+  if (rpw == 4) e = launch_kernel(gemv_i8_kernel<PRO, EPI, (EPI == EPI_GATEUP ? 2 : 4)>, dim3(grid), dim3(GI8_WARPS * 32), smem, st, pdl, a);
+  else if (rpw == 2) e = launch_kernel(gemv_i8_kernel<PRO, EPI, 2>, dim3(grid), dim3(GI8_WARPS * 32), smem, st, pdl, a);
+  else e = launch_kernel(gemv_i8_kernel<PRO, EPI, 1>, dim3(grid), dim3(GI8_WARPS * 32), smem, st, pdl, a);
+  if (e != cudaSuccess) return set_error(SIMP_ERR_CUDA, "gemv_i8 launch failed: %s", cudaGetErrorString(e));
+  return SIMP_OK;
+}
+
+static int i8_enqueue_token(LlamaI8Model& m, cudaStream_t st) {
+  const simp_llama_i8_config& c = m.cfg;
+  const int dim = int(c.dim), hd = int(c.hidden_dim), kv = int(m.kv_dim), hs = int(c.head_dim);
+  const int sms = ctx().sm_count;
+  I8_LAUNCH(i8_input_kernel, dim3((dim + 255) / 256), dim3(256), 0, st, false, (const int8_t*)m.x_i8, m.x, dim);
+  for (int64_t l = 0; l < c.n_layers; ++l) {
+    {
+      GemvI8Args a{};
+      a.seg[0] = GemvI8Seg{m.wq + l * dim * dim, m.q, dim};
+      a.seg[1] = GemvI8Seg{m.wk + l * int64_t(kv) * dim, m.k, kv};
+      a.seg[2] = GemvI8Seg{m.wv + l * int64_t(kv) * dim, m.v, kv};
+      a.nseg = 3; a.K = dim; a.x_f32 = m.x; a.norm_w = m.rms_att + l * dim; a.total_rows = dim + 2 * kv;
+      if (int rc = gemv_i8_launch<PRO_NORM, EPI_STORE>(a, st, sms, true)) return rc;
+    }
+    I8_LAUNCH(attn_i8_kernel, dim3(unsigned(c.n_heads)), dim3(AI8_WARPS * 32), size_t(c.max_seq_len) * 4, st, true,
+              (const int32_t*)m.q, (const int32_t*)m.k, (const int32_t*)m.v, m.kc, m.vc, m.xb_i8, (const int*)m.ctl, hs, kv,
+              int(c.n_heads / c.n_kv_heads), int(c.max_seq_len), int(l));
+    {
+      GemvI8Args a{};
+      a.seg[0] = GemvI8Seg{m.wo + l * dim * dim, nullptr, dim};
+      a.nseg = 1; a.K = dim; a.x_i8 = m.xb_i8; a.resid = m.x; a.total_rows = dim;
+      if (int rc = gemv_i8_launch<PRO_I8, EPI_RESID>(a, st, sms, true)) return rc;
+    }
+    {
+      GemvI8Args a{};
+      a.seg[0] = GemvI8Seg{m.w1 + l * int64_t(hd) * dim, nullptr, hd};
+      a.seg[1] = GemvI8Seg{m.w3 + l * int64_t(hd) * dim, nullptr, hd};
+      a.nseg = 2; a.K = dim; a.x_f32 = m.x; a.norm_w = m.rms_ffn + l * dim; a.hb = m.ffn_hb; a.total_rows = hd;
+      if (int rc = gemv_i8_launch<PRO_NORM, EPI_GATEUP>(a, st, sms, true)) return rc;
+    }
+    {
+      GemvI8Args a{};
+      a.seg[0] = GemvI8Seg{m.w2 + l * int64_t(dim) * hd, nullptr, dim};
+      a.nseg = 1; a.K = hd; a.x_i8 = m.ffn_hb; a.resid = m.x; a.total_rows = dim;
+      if (int rc = gemv_i8_launch<PRO_I8, EPI_RESID>(a, st, sms, true)) return rc;
+    }
+  }
+  I8_LAUNCH(i8_final_norm_kernel, dim3(1), dim3(1024), 0, st, true, (const float*)m.x, (const float*)m.rms_final, m.xb, dim);
+  {
+    GemvArgs g{};
+    g.seg[0] = GemvSeg{m.wcls, m.logits, int(c.vocab_size)};
+    g.nseg = 1; g.k4 = dim / 4; g.x = m.xb;
+    if (int rc = gemv_f32_launch<GEMV_STORE>(g, st, sms)) return rc;
+  }
+  I8_LAUNCH(i8_advance_kernel, dim3(1), dim3(1), 0, st, false, m.ctl);
+  return SIMP_OK;
+}
+
+static int i8_ensure_graph(LlamaI8Model& m) {
+  if (m.graph) return SIMP_OK;
+  cudaStream_t st = ctx().stream;
+  // one eager pass first (sets attributes, surfaces launch errors outside capture); it writes the cache row
+  // of the current position, which the replay writes again with the same values
+  int pos_save = 0;
+  SIMP_CUDA(cudaMemcpyAsync(&pos_save, m.ctl, 4, cudaMemcpyDeviceToHost, st));
+  SIMP_CUDA(cudaStreamSynchronize(st));
+  SIMP_CUDA(cudaFuncSetAttribute(attn_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(m.cfg.max_seq_len * 4)));
+  if (int rc = i8_enqueue_token(m, st)) return rc;
+  SIMP_CUDA(cudaStreamSynchronize(st));
+  SIMP_CUDA(cudaMemcpyAsync(m.ctl, &pos_save, 4, cudaMemcpyHostToDevice, st));
+  SIMP_CUDA(cudaStreamSynchronize(st));
+  cudaGraph_t g = nullptr;
+  SIMP_CUDA(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
+  const int rc = i8_enqueue_token(m, st);
+  cudaError_t e = cudaStreamEndCapture(st, &g);
+  if (rc != SIMP_OK) {
+    if (g) cudaGraphDestroy(g);
+    return rc;
+  }
+  SIMP_REQUIRE(e == cudaSuccess, SIMP_ERR_CUDA, "graph capture failed: %s", cudaGetErrorString(e));
+  e = cudaGraphInstantiate(&m.graph, g, 0);
+  cudaGraphDestroy(g);
+  SIMP_REQUIRE(e == cudaSuccess, SIMP_ERR_CUDA, "graph instantiate failed: %s", cudaGetErrorString(e));
+  return SIMP_OK;
+}
+
+}  // namespace simp
+
+using namespace simp;
+
+SIMP_API int simp_llama_i8_destroy(void* model) {
+  if (!model) return SIMP_OK;
+  LlamaI8Model* m = static_cast<LlamaI8Model*>(model);
+  if (ctx().ready) cudaStreamSynchronize(ctx().stream);
+  if (m->graph) cudaGraphExecDestroy(m->graph);
+  void* ptrs[] = {m->rms_att, m->rms_ffn, m->rms_final, m->wcls, m->wq, m->wk, m->wv, m->wo, m->w1, m->w2, m->w3,
+                  m->x_i8, m->xb_i8, m->ffn_hb, m->kc, m->vc, m->x, m->xb, m->logits, m->q, m->k, m->v, m->ctl};
+  for (void* p : ptrs)
+    if (p) cudaFree(p);
+  delete m;
+  return SIMP_OK;
+}
+
+SIMP_API int simp_llama_i8_create(const simp_llama_i8_config* cfg, void** model) {
+  SIMP_REQUIRE(cfg && model, SIMP_ERR_ARG, "llama_i8_create: null pointer");
+  if (int rc = ensure_ready()) return rc;
+  const simp_llama_i8_config& c = *cfg;
+  SIMP_REQUIRE(c.dim > 0 && c.hidden_dim > 0 && c.n_layers > 0 && c.n_heads > 0 && c.n_kv_heads > 0 && c.vocab_size > 0 &&
+                   c.max_seq_len > 0 && c.head_dim > 0,
+               SIMP_ERR_ARG, "llama_i8_create: non-positive dimension");
+  SIMP_REQUIRE(c.n_heads * c.head_dim == c.dim && c.n_heads % c.n_kv_heads == 0, SIMP_ERR_SHAPE,
+               "llama_i8_create: n_heads * head_dim must equal dim and n_kv_heads must divide n_heads");
+  SIMP_REQUIRE(c.dim % 16 == 0 && c.hidden_dim % 16 == 0 && c.dim <= 65536 && c.hidden_dim <= 65536, SIMP_ERR_SHAPE,
+               "llama_i8_create: dim and hidden_dim must be multiples of 16 and at most 65536");
+  SIMP_REQUIRE(c.head_dim <= 128 && c.max_seq_len <= 32768, SIMP_ERR_SHAPE,
+               "llama_i8_create: head_dim at most 128, max_seq_len at most 32768");
+  LlamaI8Model* m = new LlamaI8Model();
+  m->cfg = c;
+  m->kv_dim = c.n_kv_heads * c.head_dim;
+  int rc = SIMP_OK;
+  auto A = [&](void** p, size_t n) {
+    if (rc != SIMP_OK) return;
+    cudaError_t e = cudaMalloc(p, n ? n : 16);
+    if (e != cudaSuccess) rc = set_error(SIMP_ERR_CUDA, "llama_i8_create: cudaMalloc of %zu bytes failed: %s", n, cudaGetErrorString(e));
+  };
+  const size_t kv_bytes = size_t(c.n_layers) * c.max_seq_len * m->kv_dim;
+  A((void**)&m->x_i8, c.dim); A((void**)&m->xb_i8, c.dim); A((void**)&m->ffn_hb, c.hidden_dim);
+  A((void**)&m->kc, kv_bytes); A((void**)&m->vc, kv_bytes);
+  A((void**)&m->x, c.dim * 4); A((void**)&m->xb, c.dim * 4); A((void**)&m->logits, c.vocab_size * 4);
+  A((void**)&m->q, c.dim * 4); A((void**)&m->k, m->kv_dim * 4); A((void**)&m->v, m->kv_dim * 4);
+  A((void**)&m->ctl, 64);
+  if (rc != SIMP_OK) { simp_llama_i8_destroy(m); return rc; }
+  cudaMemsetAsync(m->ctl, 0, 64, ctx().stream);
+  cudaMemsetAsync(m->kc, 0, kv_bytes, ctx().stream);
+  cudaMemsetAsync(m->vc, 0, kv_bytes, ctx().stream);
+  *model = m;
+  return SIMP_OK;
+}
+
+SIMP_API int simp_llama_i8_load(void* model, const char* name, const void* host, size_t bytes) {
+  SIMP_REQUIRE(model && name && host, SIMP_ERR_ARG, "llama_i8_load: null pointer");
+  LlamaI8Model& m = *static_cast<LlamaI8Model*>(model);
+  const simp_llama_i8_config& c = m.cfg;
+  const std::string n(name);
+  const size_t d = c.dim, h = c.hidden_dim, L = c.n_layers, V = c.vocab_size, kv = m.kv_dim;
+  void** slot = nullptr;
+  size_t want = 0;
+  if (n == "rms_att_w") { slot = (void**)&m.rms_att; want = L * d * 4; }
+  else if (n == "rms_ffn_w") { slot = (void**)&m.rms_ffn; want = L * d * 4; }
+  else if (n == "rms_final_w") { slot = (void**)&m.rms_final; want = d * 4; }
+  else if (n == "wcls") { slot = (void**)&m.wcls; want = V * d * 4; }
+  else if (n == "wq_t") { slot = (void**)&m.wq; want = L * d * d; }
+  else if (n == "wk_t") { slot = (void**)&m.wk; want = L * kv * d; }
+  else if (n == "wv_t") { slot = (void**)&m.wv; want = L * kv * d; }
+  else if (n == "wo_t") { slot = (void**)&m.wo; want = L * d * d; }
+  else if (n == "w1_t") { slot = (void**)&m.w1; want = L * h * d; }
+  else if (n == "w2_t") { slot = (void**)&m.w2; want = L * d * h; }
+  else if (n == "w3_t") { slot = (void**)&m.w3; want = L * h * d; }
+  SIMP_REQUIRE(slot != nullptr, SIMP_ERR_ARG, "llama_i8_load: unknown tensor '%s'", name);
+  SIMP_REQUIRE(bytes == want, SIMP_ERR_SHAPE, "llama_i8_load: '%s' has %zu bytes, the configuration needs %zu", name, bytes, want);
+  if (!*slot) SIMP_CUDA(cudaMalloc(slot, want));
+  SIMP_CUDA(cudaMemcpyAsync(*slot, host, want, cudaMemcpyHostToDevice, ctx().stream));
+  SIMP_CUDA(cudaStreamSynchronize(ctx().stream));
+  return SIMP_OK;
+}
+
+static int i8_check_loaded(const LlamaI8Model& m) {
+  SIMP_REQUIRE(m.rms_att && m.rms_ffn && m.rms_final && m.wcls && m.wq && m.wk && m.wv && m.wo && m.w1 && m.w2 && m.w3,
+               SIMP_ERR_STATE, "llama_i8: not every tensor has been loaded");
+  return SIMP_OK;
+}
+
+SIMP_API int simp_llama_i8_reset_cache(void* model) {
+  SIMP_REQUIRE(model, SIMP_ERR_ARG, "llama_i8_reset_cache: null model");
+  LlamaI8Model& m = *static_cast<LlamaI8Model*>(model);
+  const size_t kv_bytes = size_t(m.cfg.n_layers) * m.cfg.max_seq_len * m.kv_dim;
+  SIMP_CUDA(cudaMemsetAsync(m.kc, 0, kv_bytes, ctx().stream));
+  SIMP_CUDA(cudaMemsetAsync(m.vc, 0, kv_bytes, ctx().stream));
+  return SIMP_OK;
+}
+
+SIMP_API int simp_llama_i8_decode_loop(void* model, const int8_t* x_i8_host, int64_t start_pos, int64_t n_tokens,
+                                       float* logits_host, float* ms_out) {
+  SIMP_REQUIRE(model && x_i8_host, SIMP_ERR_ARG, "llama_i8: null pointer");
+  LlamaI8Model& m = *static_cast<LlamaI8Model*>(model);
+  if (int rc = i8_check_loaded(m)) return rc;
+  SIMP_REQUIRE(n_tokens >= 1 && start_pos >= 0 && start_pos + n_tokens <= m.cfg.max_seq_len, SIMP_ERR_ARG,
+               "llama_i8: positions %lld .. %lld outside [0, %lld)", (long long)start_pos, (long long)(start_pos + n_tokens - 1),
+               (long long)m.cfg.max_seq_len);
+  cudaStream_t st = ctx().stream;
+  const int pos32 = int(start_pos);
+  SIMP_CUDA(cudaMemcpyAsync(m.x_i8, x_i8_host, size_t(m.cfg.dim), cudaMemcpyHostToDevice, st));
+  SIMP_CUDA(cudaMemcpyAsync(m.ctl, &pos32, 4, cudaMemcpyHostToDevice, st));
+  SIMP_CUDA(cudaStreamSynchronize(st));
+  if (int rc = i8_ensure_graph(m)) return rc;
+  cudaEvent_t e0 = nullptr, e1 = nullptr;
+  if (ms_out) {
+    SIMP_CUDA(cudaEventCreate(&e0));
+    SIMP_CUDA(cudaEventCreate(&e1));
+    SIMP_CUDA(cudaEventRecord(e0, st));
+  }
+  for (int64_t i = 0; i < n_tokens; ++i) SIMP_CUDA(cudaGraphLaunch(m.graph, st));
+  if (ms_out) SIMP_CUDA(cudaEventRecord(e1, st));
+  if (logits_host)
+    SIMP_CUDA(cudaMemcpyAsync(logits_host, m.logits, size_t(m.cfg.vocab_size) * 4, cudaMemcpyDeviceToHost, st));
+  SIMP_CUDA(cudaStreamSynchronize(st));
+  if (ms_out) {
+    SIMP_CUDA(cudaEventElapsedTime(ms_out, e0, e1));
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+  }
+  return simp_gpu_check_device_status();
+}
+
+SIMP_API int simp_llama_i8_forward(void* model, const int8_t* x_i8_host, int64_t pos, float* logits_host) {
+  return simp_llama_i8_decode_loop(model, x_i8_host, pos, 1, logits_host, nullptr);
+}

@@ -94,3 +94,38 @@ def llama_w4_tensors(cfg, seed=0, threads=16):
 
 def prompt_tokens(n, vocab, seed=1234):
     return np.random.default_rng(seed).integers(0, vocab, n).astype(np.int32)
+
+
+# --------------------------------------------------------------------------- int8 LLaMA-3.2-1B-style model
+# Shapes of examples/llama2/llama32_1b_int8_tensor.sl:5-13; the host bench_llama32_1b_int8.cpp:62-75, 184-195
+# fills int8 tensors with uniform integers in [-64, 63] and f32 tensors with uniform [-0.01, 0.01].
+LLAMA32_1B_INT8 = dict(dim=2048, hidden_dim=8192, n_layers=16, n_heads=32, n_kv_heads=8, vocab_size=128256,
+                       max_seq_len=4096, head_dim=64)
+
+
+def llama_i8_shapes(cfg):
+    d, h, L, V = cfg["dim"], cfg["hidden_dim"], cfg["n_layers"], cfg["vocab_size"]
+    kv = cfg["n_kv_heads"] * cfg["head_dim"]
+    return dict(rms_att_w=(L, d), rms_ffn_w=(L, d), rms_final_w=(d,), wcls=(V, d),
+                wq_t=(L, d, d), wk_t=(L, kv, d), wv_t=(L, kv, d), wo_t=(L, d, d),
+                w1_t=(L, h, d), w2_t=(L, d, h), w3_t=(L, h, d))
+
+
+def llama_i8_tensors(cfg, seed=0, style="bench"):
+    """Random-init tensors of the int8 model.  style "bench": the distributions of the reference's host
+    (int8 uniform [-64, 63]; f32 uniform [-0.01, 0.01]).  style "unit-norm": norm weights ~ N(1, 0.02),
+    which drives the quantised activations into their clamps and wrap-arounds (the harder parity case)."""
+    out = {}
+    for k, (name, shape) in enumerate(llama_i8_shapes(cfg).items()):
+        rng = np.random.default_rng([seed, k])
+        if name.endswith("_t"):
+            out[name] = rng.integers(-64, 64, size=shape, dtype=np.int8)
+        elif style == "unit-norm" and name.startswith("rms_"):
+            out[name] = (1.0 + 0.02 * rng.standard_normal(shape)).astype(np.float32)
+        else:
+            out[name] = rng.uniform(-0.01, 0.01, size=shape).astype(np.float32)
+    return out
+
+
+def llama_i8_input(cfg, seed=1):
+    return np.random.default_rng([seed, 99]).integers(-64, 64, size=cfg["dim"], dtype=np.int8)
