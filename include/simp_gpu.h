@@ -206,7 +206,7 @@ int simp_llama_destroy(void* model);
  * Tensors (simp_llama_i8_load names): rms_att_w, rms_ffn_w [n_layers, dim], rms_final_w [dim], wcls
  * [vocab, dim] (f32); wq_t, wo_t [n_layers, dim, dim], wk_t, wv_t [n_layers, kv_dim, dim], w1_t, w3_t
  * [n_layers, hidden, dim], w2_t [n_layers, dim, hidden] (int8).  dim and hidden_dim must be multiples of 16,
- * head_dim even and <= 128.  The KV cache lives on the device and is zeroed at creation. */
+ * head_dim 16, 32, 64 or 128.  The KV cache lives on the device and is zeroed at creation. */
 typedef struct simp_llama_i8_config {
   int64_t dim, hidden_dim, n_layers, n_heads, n_kv_heads, vocab_size, max_seq_len, head_dim;
 } simp_llama_i8_config;

@@ -17,6 +17,7 @@
 // shuffle reduction per row.  Integer accumulation is exact, so q, k, v, wo, gate, up and down match the CPU
 // reference bit for bit whenever their int8 inputs do; differences can only enter through the f32 sums of
 // the norms and of the attention (different summation order) at a quantisation boundary.
+#include <algorithm>
 #include <cstring>
 #include <string>
 
@@ -35,6 +36,9 @@ struct LlamaI8Model {
   float *x = nullptr, *xb = nullptr, *logits = nullptr;
   int32_t *q = nullptr, *k = nullptr, *v = nullptr;
   int* ctl = nullptr;   // [0] pos
+  float* attn_part = nullptr;   // [n_heads, nsplit, head_dim + 2] split partials of the attention
+  int* attn_cnt = nullptr;      // per-head arrival counters (zero between launches)
+  int nsplit = 1;
   cudaGraphExec_t graph = nullptr;
 };
 
@@ -184,24 +188,33 @@ __global__ void i8_input_kernel(const int8_t* __restrict__ x_i8, float* __restri
   if (i < n) x[i] = float(x_i8[i]) * 1.0f;
 }
 
-// One block per query head (llama32_1b_int8_tensor.sl:142-215).  The new K/V row is derived by every block
-// from the i32 projections (so no block depends on another block's cache write); the first head of each KV
-// group stores it.  scores[t] = sum_d f32(q_d) * f32(k_td) / 8.0; softmax as the op (expf, division);
-// out_d = (i32) trunc(sum_t p_t * f32(v_td)); xb_i8 = clamp(out / 256.0) truncated.
+// Attention of one layer (llama32_1b_int8_tensor.sl:142-215): grid (query heads, sequence splits).
+// The new K/V row is derived by every block from the i32 projections (so no block depends on another block's
+// cache write); split 0 of the first head of each KV group stores it.  A cache row of head_dim int8 values is
+// read as 16-byte pieces: a lane owns (timestep within a group of 32 / pieces, piece), converts to f32 and
+// multiplies as the model text does -- scores[t] = sum_d f32(q_d) * f32(k_td) / 8.0 -- then the split's
+// exp-weights and weighted V sums are formed; the block that arrives last for its head merges the splits
+// (online-softmax algebra), truncates to i32 (attn_out) and requantises clamp(out / 256.0) for the next
+// projection.  With one split the arithmetic is p = e / sum, out = sum_t p_t * v_t as in the text.
 constexpr int AI8_WARPS = 8;
+constexpr int AI8_MAX_SPLITS = 16;
 __global__ void __launch_bounds__(AI8_WARPS * 32) attn_i8_kernel(const int32_t* __restrict__ Q, const int32_t* __restrict__ Kp,
                                                                   const int32_t* __restrict__ Vp, int8_t* __restrict__ kc,
                                                                   int8_t* __restrict__ vc, int8_t* __restrict__ xb_i8,
+                                                                  float* __restrict__ part, int* __restrict__ counters,
                                                                   const int* __restrict__ ctl, int hs, int kv_dim, int n_rep,
-                                                                  int max_seq, int layer) {
-  extern __shared__ float scores[];   // max_seq floats
+                                                                  int max_seq, int layer, int nsplit) {
+  extern __shared__ float scores[];   // timesteps of this split
   __shared__ float qf[128], knew[128], vnew[128], red[33];
-  __shared__ float part[AI8_WARPS][128];
+  __shared__ float wpart[AI8_WARPS][128];
+  __shared__ bool is_last;
   pdl_launch_dependents();
   pdl_wait();
-  const int h = blockIdx.x, kvh = h / n_rep;
+  const int h = blockIdx.x, sp = blockIdx.y, kvh = h / n_rep;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int pos = ctl[0], seq = pos + 1;
+  const int per = (seq + nsplit - 1) / nsplit;
+  const int t0 = sp * per, t1 = min(seq, t0 + per), len = max(0, t1 - t0);
   int8_t* kbase = kc + size_t(layer) * max_seq * kv_dim + kvh * hs;
   int8_t* vbase = vc + size_t(layer) * max_seq * kv_dim + kvh * hs;
   for (int d = threadIdx.x; d < hs; d += blockDim.x) {
@@ -210,72 +223,119 @@ __global__ void __launch_bounds__(AI8_WARPS * 32) attn_i8_kernel(const int32_t* 
     const int8_t v8 = int8_t(uint8_t(uint32_t(Vp[kvh * hs + d] / 256) & 0xffu));
     knew[d] = float(k8);
     vnew[d] = float(v8);
-    if (h % n_rep == 0) {
+    if (sp == 0 && h % n_rep == 0) {
       kbase[size_t(pos) * kv_dim + d] = k8;
       vbase[size_t(pos) * kv_dim + d] = v8;
     }
   }
   __syncthreads();
-  // ---- scores: a warp per timestep, four timesteps in flight; lanes own dims lane, lane + 32, ...
-  float q_r[4];
+  const int pieces = hs >> 4;              // 16-byte pieces per cache row (1, 2, 4 or 8)
+  const int tpw = 32 / pieces;             // timesteps a warp covers per iteration
+  const int piece = lane % pieces, tsub = lane / pieces;
+  float q_r[16];
 #pragma unroll
-  for (int e = 0; e < 4; ++e) q_r[e] = lane + 32 * e < hs ? qf[lane + 32 * e] : 0.0f;
-  constexpr int TU = 4;
-  for (int tb = warp; tb < seq; tb += AI8_WARPS * TU) {
-    float kf[TU][4];
+  for (int i = 0; i < 16; ++i) q_r[i] = qf[piece * 16 + i];
+  auto load_row = [&](const int8_t* base, const float* fresh, int t, float (&f)[16]) {
+    if (t == pos) {
 #pragma unroll
-    for (int u = 0; u < TU; ++u) {
-      const int t = tb + u * AI8_WARPS;
+      for (int i = 0; i < 16; ++i) f[i] = fresh[piece * 16 + i];
+    } else {
+      const uint4 raw = *reinterpret_cast<const uint4*>(base + size_t(t) * kv_dim + piece * 16);
+      const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int d = lane + 32 * e;
-        kf[u][e] = 0.0f;
-        if (d < hs && t < seq) kf[u][e] = t == pos ? knew[d] : float(kbase[size_t(t) * kv_dim + d]);
-      }
+      for (int i = 0; i < 16; ++i) f[i] = float(int8_t(uint8_t(w[i >> 2] >> (8 * (i & 3)))));
     }
+  };
+  // ---- scores of this split
+  for (int tb = t0 + warp * tpw; tb < t1; tb += AI8_WARPS * tpw) {
+    const int t = tb + tsub;
+    float sc = 0.0f;
+    if (t < t1) {
+      float kf[16];
+      load_row(kbase, knew, t, kf);
 #pragma unroll
-    for (int u = 0; u < TU; ++u) {
-      const int t = tb + u * AI8_WARPS;
-      float sc = 0.0f;
-#pragma unroll
-      for (int e = 0; e < 4; ++e) sc = fmaf(q_r[e], kf[u][e], sc);
-      sc = warp_sum(sc);
-      if (lane == 0 && t < seq) scores[t] = sc / 8.0f;
+      for (int i = 0; i < 16; ++i) sc = fmaf(q_r[i], kf[i], sc);
     }
+    for (int o = 1; o < pieces; o <<= 1) sc += __shfl_xor_sync(0xffffffffu, sc, o);
+    if (piece == 0 && t < t1) scores[t - t0] = sc / 8.0f;
   }
   __syncthreads();
-  // ---- softmax over [0, seq)
+  // ---- exp-weights of the split
   float mx = -INFINITY;
-  for (int t = threadIdx.x; t < seq; t += blockDim.x) mx = fmaxf(mx, scores[t]);
+  for (int i = threadIdx.x; i < len; i += blockDim.x) mx = fmaxf(mx, scores[i]);
   mx = block_max(mx, red);
   float sum = 0.0f;
-  for (int t = threadIdx.x; t < seq; t += blockDim.x) {
-    const float e = expf(scores[t] - mx);
-    scores[t] = e;
+  for (int i = threadIdx.x; i < len; i += blockDim.x) {
+    const float e = expf(scores[i] - mx);
+    scores[i] = e;
     sum += e;
   }
   sum = block_sum(sum, red);
-  // ---- weighted sum of V: warps split the timesteps, lanes the dims
-  float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-  for (int t = warp; t < seq; t += AI8_WARPS) {
-    const float p = scores[t] / sum;
+  // ---- weighted sums of V (with one split the weights are the probabilities themselves, as in the text)
+  const bool single = nsplit == 1;
+  float acc[16];
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const int d = lane + 32 * e;
-      if (d < hs) acc[e] = fmaf(p, t == pos ? vnew[d] : float(vbase[size_t(t) * kv_dim + d]), acc[e]);
+  for (int i = 0; i < 16; ++i) acc[i] = 0.0f;
+  for (int tb = t0 + warp * tpw; tb < t1; tb += AI8_WARPS * tpw) {
+    const int t = tb + tsub;
+    if (t < t1) {
+      float vf[16];
+      load_row(vbase, vnew, t, vf);
+      const float p = single ? scores[t - t0] / sum : scores[t - t0];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) acc[i] = fmaf(p, vf[i], acc[i]);
     }
   }
 #pragma unroll
-  for (int e = 0; e < 4; ++e)
-    if (lane + 32 * e < hs) part[warp][lane + 32 * e] = acc[e];
+  for (int i = 0; i < 16; ++i) {
+    float v = acc[i];
+    for (int o = pieces; o < 32; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    acc[i] = v;
+  }
+  if (tsub == 0) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) wpart[warp][piece * 16 + i] = acc[i];
+  }
   __syncthreads();
+  float* mine = part + (size_t(h) * nsplit + sp) * (hs + 2);
   for (int d = threadIdx.x; d < hs; d += blockDim.x) {
     float val = 0.0f;
 #pragma unroll
-    for (int w = 0; w < AI8_WARPS; ++w) val += part[w][d];
-    const int32_t out = __float2int_rz(val);                 // attn_out = val as i32
-    xb_i8[h * hs + d] = quant_clamped(float(out) / 256.0f);   // next projection's input
+    for (int w = 0; w < AI8_WARPS; ++w) val += wpart[w][d];
+    if (single) {
+      const int32_t out = __float2int_rz(val);                 // attn_out = val as i32
+      xb_i8[h * hs + d] = quant_clamped(float(out) / 256.0f);   // next projection's input
+    } else {
+      mine[2 + d] = val;
+    }
   }
+  if (single) return;
+  if (threadIdx.x == 0) { mine[0] = len > 0 ? mx : -INFINITY; mine[1] = len > 0 ? sum : 0.0f; }
+  // last block of this head merges (writes above are published by the fence + atomic)
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) is_last = (atomicAdd(&counters[h], 1) == nsplit - 1);
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  const float* p0 = part + size_t(h) * nsplit * (hs + 2);
+  float M = -INFINITY;
+  for (int x = 0; x < nsplit; ++x) M = fmaxf(M, __ldcg(p0 + x * (hs + 2)));
+  float total = 0.0f;
+  for (int x = 0; x < nsplit; ++x) {
+    const float mm = __ldcg(p0 + x * (hs + 2));
+    if (mm != -INFINITY) total += __ldcg(p0 + x * (hs + 2) + 1) * expf(mm - M);
+  }
+  for (int d = threadIdx.x; d < hs; d += blockDim.x) {
+    float val = 0.0f;
+    for (int x = 0; x < nsplit; ++x) {
+      const float mm = __ldcg(p0 + x * (hs + 2));
+      if (mm != -INFINITY) val += __ldcg(p0 + x * (hs + 2) + 2 + d) * expf(mm - M);
+    }
+    const int32_t out = __float2int_rz(val / total);
+    xb_i8[h * hs + d] = quant_clamped(float(out) / 256.0f);
+  }
+  if (threadIdx.x == 0) counters[h] = 0;
 }
 
 // xb = rmsnorm(x) * w for the classifier (one block).
@@ -322,6 +382,11 @@ static int gemv_i8_launch(GemvI8Args a, cudaStream_t st, int sms, bool pdl) {
   return SIMP_OK;
 }
 
+// shared memory of the attention kernel: the scores of one sequence split
+static size_t i8_attn_smem(const LlamaI8Model& m) {
+  return size_t((m.cfg.max_seq_len + m.nsplit - 1) / m.nsplit + 1) * 4;
+}
+
 static int i8_enqueue_token(LlamaI8Model& m, cudaStream_t st) {
   const simp_llama_i8_config& c = m.cfg;
   const int dim = int(c.dim), hd = int(c.hidden_dim), kv = int(m.kv_dim), hs = int(c.head_dim);
@@ -336,9 +401,10 @@ static int i8_enqueue_token(LlamaI8Model& m, cudaStream_t st) {
       a.nseg = 3; a.K = dim; a.x_f32 = m.x; a.norm_w = m.rms_att + l * dim; a.total_rows = dim + 2 * kv;
       if (int rc = gemv_i8_launch<PRO_NORM, EPI_STORE>(a, st, sms, true)) return rc;
     }
-    I8_LAUNCH(attn_i8_kernel, dim3(unsigned(c.n_heads)), dim3(AI8_WARPS * 32), size_t(c.max_seq_len) * 4, st, true,
-              (const int32_t*)m.q, (const int32_t*)m.k, (const int32_t*)m.v, m.kc, m.vc, m.xb_i8, (const int*)m.ctl, hs, kv,
-              int(c.n_heads / c.n_kv_heads), int(c.max_seq_len), int(l));
+    I8_LAUNCH(attn_i8_kernel, dim3(unsigned(c.n_heads), unsigned(m.nsplit)), dim3(AI8_WARPS * 32),
+              i8_attn_smem(m), st, true, (const int32_t*)m.q, (const int32_t*)m.k, (const int32_t*)m.v, m.kc, m.vc, m.xb_i8,
+              m.attn_part, m.attn_cnt, (const int*)m.ctl, hs, kv, int(c.n_heads / c.n_kv_heads), int(c.max_seq_len), int(l),
+              m.nsplit);
     {
       GemvI8Args a{};
       a.seg[0] = GemvI8Seg{m.wo + l * dim * dim, nullptr, dim};
@@ -378,7 +444,7 @@ static int i8_ensure_graph(LlamaI8Model& m) {
   int pos_save = 0;
   SIMP_CUDA(cudaMemcpyAsync(&pos_save, m.ctl, 4, cudaMemcpyDeviceToHost, st));
   SIMP_CUDA(cudaStreamSynchronize(st));
-  SIMP_CUDA(cudaFuncSetAttribute(attn_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(m.cfg.max_seq_len * 4)));
+  SIMP_CUDA(cudaFuncSetAttribute(attn_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(i8_attn_smem(m))));
   if (int rc = i8_enqueue_token(m, st)) return rc;
   SIMP_CUDA(cudaStreamSynchronize(st));
   SIMP_CUDA(cudaMemcpyAsync(m.ctl, &pos_save, 4, cudaMemcpyHostToDevice, st));
@@ -408,7 +474,8 @@ SIMP_API int simp_llama_i8_destroy(void* model) {
   if (ctx().ready) cudaStreamSynchronize(ctx().stream);
   if (m->graph) cudaGraphExecDestroy(m->graph);
   void* ptrs[] = {m->rms_att, m->rms_ffn, m->rms_final, m->wcls, m->wq, m->wk, m->wv, m->wo, m->w1, m->w2, m->w3,
-                  m->x_i8, m->xb_i8, m->ffn_hb, m->kc, m->vc, m->x, m->xb, m->logits, m->q, m->k, m->v, m->ctl};
+                  m->x_i8, m->xb_i8, m->ffn_hb, m->kc, m->vc, m->x, m->xb, m->logits, m->q, m->k, m->v, m->ctl,
+                  m->attn_part, m->attn_cnt};
   for (void* p : ptrs)
     if (p) cudaFree(p);
   delete m;
@@ -426,8 +493,8 @@ SIMP_API int simp_llama_i8_create(const simp_llama_i8_config* cfg, void** model)
                "llama_i8_create: n_heads * head_dim must equal dim and n_kv_heads must divide n_heads");
   SIMP_REQUIRE(c.dim % 16 == 0 && c.hidden_dim % 16 == 0 && c.dim <= 65536 && c.hidden_dim <= 65536, SIMP_ERR_SHAPE,
                "llama_i8_create: dim and hidden_dim must be multiples of 16 and at most 65536");
-  SIMP_REQUIRE(c.head_dim <= 128 && c.max_seq_len <= 32768, SIMP_ERR_SHAPE,
-               "llama_i8_create: head_dim at most 128, max_seq_len at most 32768");
+  SIMP_REQUIRE((c.head_dim == 16 || c.head_dim == 32 || c.head_dim == 64 || c.head_dim == 128) && c.max_seq_len <= 131072,
+               SIMP_ERR_SHAPE, "llama_i8_create: head_dim must be 16, 32, 64 or 128; max_seq_len at most 131072");
   LlamaI8Model* m = new LlamaI8Model();
   m->cfg = c;
   m->kv_dim = c.n_kv_heads * c.head_dim;
@@ -443,8 +510,13 @@ SIMP_API int simp_llama_i8_create(const simp_llama_i8_config* cfg, void** model)
   A((void**)&m->x, c.dim * 4); A((void**)&m->xb, c.dim * 4); A((void**)&m->logits, c.vocab_size * 4);
   A((void**)&m->q, c.dim * 4); A((void**)&m->k, m->kv_dim * 4); A((void**)&m->v, m->kv_dim * 4);
   A((void**)&m->ctl, 64);
+  // one sequence split per 256 positions of context, at most 16: (heads x splits) blocks keep the SMs busy
+  m->nsplit = int(std::min<int64_t>(AI8_MAX_SPLITS, std::max<int64_t>(1, c.max_seq_len / 256)));
+  A((void**)&m->attn_part, size_t(c.n_heads) * m->nsplit * (c.head_dim + 2) * 4);
+  A((void**)&m->attn_cnt, size_t(c.n_heads) * 4);
   if (rc != SIMP_OK) { simp_llama_i8_destroy(m); return rc; }
   cudaMemsetAsync(m->ctl, 0, 64, ctx().stream);
+  cudaMemsetAsync(m->attn_cnt, 0, size_t(c.n_heads) * 4, ctx().stream);
   cudaMemsetAsync(m->kc, 0, kv_bytes, ctx().stream);
   cudaMemsetAsync(m->vc, 0, kv_bytes, ctx().stream);
   *model = m;

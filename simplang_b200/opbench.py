@@ -2,7 +2,7 @@
 int8 GEMM at the configured shapes.  Prints one JSON line per case with the achieved GB/s (or TOPS), the
 algorithmic bytes used, and the fraction of the measured roofline.
 
-    python -m simplang_b200.opbench [--iters 50] [--only gemv_f32,w4,rowops,gemm_i8,mma_peak,decode110m,decode3b]
+    python -m simplang_b200.opbench [--iters 50] [--only gemv_f32,w4,rowops,gemm_i8,mma_peak,decode110m,decode3b,decode_i8]
 
 Each case rotates over enough independent operand copies that the working set exceeds twice the
 126 MB L2, so every iteration streams from HBM the way consecutive layers of a decode step do.
@@ -204,6 +204,36 @@ def bench_decode(which, n_new=128):
     m.close()
 
 
+def bench_decode_i8():
+    """The int8 LLaMA-3.2-1B-style model as its host times it (bench_llama32_1b_int8.cpp): forwards of one
+    int8 input at positions 0 / 127 / 511 / 1023 / 2047 / 4095 (5 each) and a 64-token loop from position 128."""
+    from simplang_b200 import synth
+    peak, src = hbm_peak()
+    cfg = synth.LLAMA32_1B_INT8
+    t = synth.llama_i8_tensors(cfg, 0, "bench")
+    x = synth.llama_i8_input(cfg)
+    m = sg.LlamaI8(cfg, t)
+    d, h, L, V = cfg["dim"], cfg["hidden_dim"], cfg["n_layers"], cfg["vocab_size"]
+    kvd = cfg["n_kv_heads"] * cfg["head_dim"]
+    wbytes = L * (2 * d * d + 2 * kvd * d + 3 * h * d) + 4 * V * d
+    m.decode_loop(x, 0, 3)
+    for pos in (0, 127, 511, 1023, 2047, 4095):
+        ms = min(m.decode_loop(x, pos, 1)[1] for _ in range(5))
+        kvb = 2 * L * (pos + 1) * kvd
+        print(json.dumps({"op": "llama-3.2-1B int8 forward", "pos": pos, "us_per_token": round(ms * 1e3, 1),
+                          "tok_s": round(1e3 / ms, 1), "weight_bytes_per_token": int(wbytes), "kv_bytes": int(kvb),
+                          "frac_of_hbm_peak": round((wbytes + kvb) / (ms * 1e-3) / 1e9 / peak, 4), "peak": src}), flush=True)
+    m.reset_cache()
+    _, ms = m.decode_loop(x, 128, 64)
+    us = ms * 1e3 / 64
+    kvb = 2 * L * 160 * kvd
+    print(json.dumps({"op": "llama-3.2-1B int8 decode loop (64 tokens from pos 128)", "us_per_token": round(us, 1),
+                      "tok_s": round(1e6 / us, 1), "weight_bytes_per_token": int(wbytes),
+                      "gb_s": round((wbytes + kvb) / us / 1e3, 1),
+                      "frac_of_hbm_peak": round((wbytes + kvb) / us / 1e3 / peak, 4), "peak_gb_s": peak, "peak": src}), flush=True)
+    m.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--iters", type=int, default=50)
@@ -236,6 +266,8 @@ def main():
         bench_decode("110m")
     if "decode3b" in which:
         bench_decode("3b")
+    if "decode_i8" in which:
+        bench_decode_i8()
     sg.check(sg.lib().simp_gpu_check_device_status())
 
 

@@ -43,6 +43,15 @@ def test_mid_gqa(gpu, oracle, style):
     run_positions(gpu, oracle, MID, 5, style, range(0, 150))
 
 
+@pytest.mark.parametrize("style", ["bench", "unit-norm"])
+def test_long_context_sequence_splits(gpu, oracle, style):
+    """max_seq_len 1100 gives the attention kernel 4 sequence splits per head; positions are visited sparsely
+    (rows never visited stay zero in both caches), including split boundaries and the last position."""
+    cfg = dict(dim=256, hidden_dim=512, n_layers=2, n_heads=4, n_kv_heads=2, vocab_size=400, max_seq_len=1100, head_dim=64)
+    positions = list(range(0, 9)) + list(range(270, 280)) + list(range(548, 553)) + list(range(1090, 1100))
+    run_positions(gpu, oracle, cfg, 11, style, positions)
+
+
 def test_decode_loop_matches_single_forwards(gpu, oracle):
     from simplang_b200 import synth
     t = synth.llama_i8_tensors(SMALL, 7, "unit-norm")
