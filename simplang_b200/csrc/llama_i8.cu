@@ -88,48 +88,23 @@ __global__ void __launch_bounds__(GI8_WARPS * 32) gemv_i8_kernel(const GemvI8Arg
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int K = a.K, k16 = K >> 4;
   constexpr int NM = EPI == EPI_GATEUP ? 2 : 1;
+  constexpr int U = 4;   // 16-byte pieces per row in flight per lane
   pdl_launch_dependents();
-  pdl_wait();
-  // ---- prologue: the int8 input vector in shared memory
-  if (PRO == PRO_NORM) {
-    // y = (x / r) * w, r = sqrt(mean(x^2) + 1e-5); v = y * 127 clamped, truncated (llama32_1b_int8_tensor.sl:93-103)
-    float ss = 0.0f;
-    for (int i = threadIdx.x; i < K; i += blockDim.x) {
-      const float t = a.x_f32[i];
-      ss += t * t;
-    }
-    ss = block_sum(ss, red);
-    const float r = sqrtf(ss / float(K) + 1e-5f);
-    for (int i = threadIdx.x; i < K; i += blockDim.x)
-      reinterpret_cast<int8_t*>(gi8_smem)[i] = quant_clamped(((a.x_f32[i] / r) * a.norm_w[i]) * 127.0f);
-  } else {
-    for (int i = threadIdx.x; i < k16; i += blockDim.x)
-      reinterpret_cast<uint4*>(gi8_smem)[i] = reinterpret_cast<const uint4*>(a.x_i8)[i];
-  }
-  __syncthreads();
-  const uint4* xs = reinterpret_cast<const uint4*>(gi8_smem);
-
-  const int row0 = (blockIdx.x * GI8_WARPS + warp) * RPW;
-  if (row0 >= a.total_rows) return;
   // rows of this warp: (segment, row) pairs; a warp's RPW rows never straddle segments when every segment's
   // row count is a multiple of RPW (checked on the host)
+  const int row0 = (blockIdx.x * GI8_WARPS + warp) * RPW;
+  const bool active = row0 < a.total_rows;
   int s = 0, r_in = row0;
   if (EPI != EPI_GATEUP)
     while (s + 1 < a.nseg && r_in >= a.seg[s].rows) { r_in -= a.seg[s].rows; ++s; }
-  int acc[NM][RPW];
-#pragma unroll
-  for (int m = 0; m < NM; ++m)
-#pragma unroll
-    for (int r = 0; r < RPW; ++r) acc[m][r] = 0;
   const uint4* wrow[NM][RPW];
 #pragma unroll
   for (int m = 0; m < NM; ++m)
 #pragma unroll
     for (int r = 0; r < RPW; ++r)
-      wrow[m][r] = reinterpret_cast<const uint4*>(a.seg[EPI == EPI_GATEUP ? m : s].w + size_t(r_in + r) * K);
-  constexpr int U = 4;   // 16-byte pieces per row in flight per lane
-  for (int j0 = lane; j0 < k16; j0 += 32 * U) {
-    uint4 w[NM][RPW][U];
+      wrow[m][r] = reinterpret_cast<const uint4*>(a.seg[EPI == EPI_GATEUP ? m : s].w + size_t(active ? r_in + r : 0) * K);
+  uint4 w[NM][RPW][U];
+  auto load_batch = [&](int j0) {
 #pragma unroll
     for (int m = 0; m < NM; ++m)
 #pragma unroll
@@ -137,8 +112,60 @@ __global__ void __launch_bounds__(GI8_WARPS * 32) gemv_i8_kernel(const GemvI8Arg
 #pragma unroll
         for (int u = 0; u < U; ++u) {
           const int j = j0 + 32 * u;
-          w[m][r][u] = j < k16 ? ldg_stream_u4(wrow[m][r] + j) : make_uint4(0u, 0u, 0u, 0u);
+          w[m][r][u] = (active && j < k16) ? ldg_stream_u4(wrow[m][r] + j) : make_uint4(0u, 0u, 0u, 0u);
         }
+  };
+  // Weights never change: the first pieces of every row are requested before waiting for the producer of the
+  // input vector, so they stream in under the predecessor's tail and under the prologue below.
+  load_batch(lane);
+  // ... and so are the norm weights (first NW_REG per thread; longer vectors read the rest after the wait)
+  constexpr int NW_REG = 8;
+  float nw[NW_REG];
+  if (PRO == PRO_NORM) {
+#pragma unroll
+    for (int u = 0; u < NW_REG; ++u) {
+      const int i = threadIdx.x + u * (GI8_WARPS * 32);
+      nw[u] = i < K ? __ldg(a.norm_w + i) : 0.0f;
+    }
+  }
+  pdl_wait();
+  // ---- prologue: the int8 input vector in shared memory
+  if (PRO == PRO_NORM) {
+    // y = (x / r) * w, r = sqrt(mean(x^2) + 1e-5); v = y * 127 clamped, truncated (llama32_1b_int8_tensor.sl:93-103)
+    float xr[NW_REG];
+    float ss = 0.0f;
+#pragma unroll
+    for (int u = 0; u < NW_REG; ++u) {
+      const int i = threadIdx.x + u * (GI8_WARPS * 32);
+      xr[u] = i < K ? a.x_f32[i] : 0.0f;
+      ss += xr[u] * xr[u];
+    }
+    for (int i = threadIdx.x + NW_REG * (GI8_WARPS * 32); i < K; i += blockDim.x) {
+      const float t = a.x_f32[i];
+      ss += t * t;
+    }
+    ss = block_sum(ss, red);
+    const float r = sqrtf(ss / float(K) + 1e-5f);
+#pragma unroll
+    for (int u = 0; u < NW_REG; ++u) {
+      const int i = threadIdx.x + u * (GI8_WARPS * 32);
+      if (i < K) reinterpret_cast<int8_t*>(gi8_smem)[i] = quant_clamped(((xr[u] / r) * nw[u]) * 127.0f);
+    }
+    for (int i = threadIdx.x + NW_REG * (GI8_WARPS * 32); i < K; i += blockDim.x)
+      reinterpret_cast<int8_t*>(gi8_smem)[i] = quant_clamped(((a.x_f32[i] / r) * a.norm_w[i]) * 127.0f);
+  } else {
+    for (int i = threadIdx.x; i < k16; i += blockDim.x)
+      reinterpret_cast<uint4*>(gi8_smem)[i] = reinterpret_cast<const uint4*>(a.x_i8)[i];
+  }
+  __syncthreads();
+  if (!active) return;
+  const uint4* xs = reinterpret_cast<const uint4*>(gi8_smem);
+  int acc[NM][RPW];
+#pragma unroll
+  for (int m = 0; m < NM; ++m)
+#pragma unroll
+    for (int r = 0; r < RPW; ++r) acc[m][r] = 0;
+  for (int j0 = lane; j0 < k16; j0 += 32 * U) {
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int j = j0 + 32 * u;
@@ -155,6 +182,7 @@ __global__ void __launch_bounds__(GI8_WARPS * 32) gemv_i8_kernel(const GemvI8Arg
           acc[m][r] = t;
         }
     }
+    if (j0 + 32 * U < k16) load_batch(j0 + 32 * U);
   }
 #pragma unroll
   for (int r = 0; r < RPW; ++r) {
@@ -213,6 +241,10 @@ __global__ void __launch_bounds__(AI8_WARPS * 32) attn_i8_kernel(const int32_t* 
   const int h = blockIdx.x, sp = blockIdx.y, kvh = h / n_rep;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int pos = ctl[0], seq = pos + 1;
+  // splits actually used: one per 64 positions of the current context, so short contexts do not pay for the
+  // merge of up to 16 nearly empty splits; the blocks of unused splits leave at once
+  nsplit = min(nsplit, (seq + 63) / 64);
+  if (sp >= nsplit) return;
   const int per = (seq + nsplit - 1) / nsplit;
   const int t0 = sp * per, t1 = min(seq, t0 + per), len = max(0, t1 - t0);
   int8_t* kbase = kc + size_t(layer) * max_seq * kv_dim + kvh * hs;
@@ -246,6 +278,12 @@ __global__ void __launch_bounds__(AI8_WARPS * 32) attn_i8_kernel(const int32_t* 
       for (int i = 0; i < 16; ++i) f[i] = float(int8_t(uint8_t(w[i >> 2] >> (8 * (i & 3)))));
     }
   };
+  // The V piece of this lane's first timestep is requested together with its K piece, so the second pass does
+  // not start with a fresh round trip (short contexts have one timestep per lane).
+  const int t_first = t0 + warp * tpw + tsub;
+  uint4 v_first = make_uint4(0u, 0u, 0u, 0u);
+  if (t_first < t1 && t_first != pos)
+    v_first = *reinterpret_cast<const uint4*>(vbase + size_t(t_first) * kv_dim + piece * 16);
   // ---- scores of this split
   for (int tb = t0 + warp * tpw; tb < t1; tb += AI8_WARPS * tpw) {
     const int t = tb + tsub;
@@ -280,7 +318,13 @@ __global__ void __launch_bounds__(AI8_WARPS * 32) attn_i8_kernel(const int32_t* 
     const int t = tb + tsub;
     if (t < t1) {
       float vf[16];
-      load_row(vbase, vnew, t, vf);
+      if (t == t_first && t != pos) {
+        const uint32_t w[4] = {v_first.x, v_first.y, v_first.z, v_first.w};
+#pragma unroll
+        for (int i = 0; i < 16; ++i) vf[i] = float(int8_t(uint8_t(w[i >> 2] >> (8 * (i & 3)))));
+      } else {
+        load_row(vbase, vnew, t, vf);
+      }
       const float p = single ? scores[t - t0] / sum : scores[t - t0];
 #pragma unroll
       for (int i = 0; i < 16; ++i) acc[i] = fmaf(p, vf[i], acc[i]);

@@ -153,3 +153,69 @@ def test_llama_forward_runs_and_is_causal(oracle):
     assert np.allclose(m2.forward(3, 0), l0, rtol=1e-5, atol=1e-6)
     with pytest.raises(ValueError):
         m.forward(0, 16)
+
+
+def test_llama_i8_oracle_against_numpy_restatement():
+    """The int8 LLaMA-3.2-1B-style oracle (examples/llama2/llama32_1b_int8_tensor.sl:16-305) checked against an
+    independent, vectorised numpy restatement of the same text on a tiny configuration.  Integer steps must agree
+    exactly; the two differ only in the f32 summation order of the norms and the attention, so logits are
+    compared within 1e-4.  (The reference holds no known-answer test for this model: parity unpinned.)"""
+    import oracle
+    from simplang_b200 import synth
+    cfg = dict(dim=64, hidden_dim=96, n_layers=2, n_heads=4, n_kv_heads=2, vocab_size=50, max_seq_len=12, head_dim=16)
+    for style in ("bench", "unit-norm"):
+        t = synth.llama_i8_tensors(cfg, 21, style)
+        x_i8 = synth.llama_i8_input(cfg, 4)
+        om = oracle.LlamaI8(cfg, t, threads=1)
+        d, hd, hs, L = cfg["dim"], cfg["hidden_dim"], cfg["head_dim"], cfg["n_layers"]
+        kvd, n_rep = cfg["n_kv_heads"] * hs, cfg["n_heads"] // cfg["n_kv_heads"]
+        kc = np.zeros((L, cfg["max_seq_len"], kvd), np.int8)
+        vc = np.zeros_like(kc)
+        f32 = np.float32
+
+        def rms(v, w):
+            ss = f32(0)
+            for e in v:
+                ss = f32(ss + e * e)
+            r = np.sqrt(f32(ss / f32(len(v)) + f32(1e-5)))
+            return ((v / r) * w).astype(f32)
+
+        def quant(v):
+            return np.trunc(np.clip(v, -128.0, 127.0)).astype(np.int8)
+
+        def mv(x8, w):  # [N, K] int8 x [K] int8 -> i32, exact
+            return (w.astype(np.int64) @ x8.astype(np.int64)).astype(np.int32)
+
+        def wrap8(v):  # keep the low 8 bits of an integer array
+            return (v.astype(np.int64) & 0xff).astype(np.uint8).view(np.int8)
+
+        for pos in range(5):
+            ref = om.forward(x_i8, pos).copy()
+            x = x_i8.astype(f32)
+            for l in range(L):
+                xb8 = quant(rms(x, t["rms_att_w"][l]) * f32(127.0))
+                Q, K, V = mv(xb8, t["wq_t"][l]), mv(xb8, t["wk_t"][l]), mv(xb8, t["wv_t"][l])
+                kc[l, pos] = wrap8(np.trunc(K / 256.0))   # integer division truncating toward zero
+                vc[l, pos] = wrap8(np.trunc(V / 256.0))
+                attn = np.zeros(d, np.int32)
+                for h in range(cfg["n_heads"]):
+                    g = (h // n_rep) * hs
+                    q = Q[h * hs:(h + 1) * hs].astype(f32)
+                    sc = np.array([np.sum((q * kc[l, tt, g:g + hs].astype(f32)).astype(np.float64)) for tt in range(pos + 1)])
+                    sc = (sc / 8.0).astype(f32)
+                    e = np.exp(sc - sc.max()).astype(f32)
+                    p = (e / e.sum(dtype=f32)).astype(f32)
+                    val = (p[:, None].astype(np.float64) * vc[l, :pos + 1, g:g + hs].astype(np.float64)).sum(axis=0)
+                    attn[h * hs:(h + 1) * hs] = np.trunc(val.astype(f32)).astype(np.int32)
+                xb8 = quant(attn.astype(f32) / f32(256.0))
+                x = (x + mv(xb8, t["wo_t"][l]).astype(f32) / f32(65536.0)).astype(f32)
+                xb8 = quant(rms(x, t["rms_ffn_w"][l]) * f32(127.0))
+                gate = mv(xb8, t["w1_t"][l]).astype(f32) / f32(65536.0)
+                up = mv(xb8, t["w3_t"][l]).astype(f32) / f32(65536.0)
+                hb = ((gate / (f32(1.0) + np.exp(-gate))).astype(f32) * up * f32(127.0)).astype(f32)
+                hb8 = wrap8(np.trunc(hb))
+                x = (x + mv(hb8, t["w2_t"][l]).astype(f32) / f32(65536.0)).astype(f32)
+            logits = t["wcls"].astype(np.float64) @ rms(x, t["rms_final_w"]).astype(np.float64)
+            assert np.max(np.abs(logits - ref)) <= 1e-4 * np.max(np.abs(ref)) + 1e-12, (style, pos)
+            # the int8 caches of both restatements must be identical
+            assert np.array_equal(om.k_cache.reshape(kc.shape), kc) and np.array_equal(om.v_cache.reshape(vc.shape), vc)
