@@ -219,6 +219,14 @@ int simp_llama_i8_forward(void* model, const int8_t* x_i8_host, int64_t pos, flo
  * lives in device memory, so the loop runs without host synchronisation. */
 int simp_llama_i8_decode_loop(void* model, const int8_t* x_i8_host, int64_t start_pos, int64_t n_tokens,
                               float* logits_host, float* ms_out);
+/* Prefill of seq_len <= min(256, max_seq_len) tokens at once: the exported functions llama32_prefill_8 ... _256 of
+ * examples/llama2/llama32_1b_int8_prefill.sl:11-232 (host: bench_llama32_1b_int8_prefill.cpp:180-215).  The seven
+ * projections of a layer run as int8 GEMMs on the tensor cores.  x_i8_host is [seq_len, dim]; outputs (each may be
+ * NULL): the residual stream x_fp32 [seq_len, dim] and the K / V cache rows [n_layers, seq_len, kv_dim].  The rows
+ * also stay in the model's device cache (positions 0 .. seq_len-1), so decoding can continue at seq_len.  As in
+ * the .sl text there is no clamp in the quantisation steps, no final norm and no classifier. */
+int simp_llama_i8_prefill(void* model, const int8_t* x_i8_host, int64_t seq_len, float* x_fp32_host,
+                          int8_t* k_cache_host, int8_t* v_cache_host, float* ms_out);
 int simp_llama_i8_reset_cache(void* model);
 int simp_llama_i8_destroy(void* model);
 

@@ -251,6 +251,23 @@ class LlamaI8:
         return self.logits
 
 
+    def prefill(self, x_i8, seq_len):
+        """llama32_prefill_<seq_len>: x_i8 [seq_len, dim] -> (x_fp32 [seq_len, dim], k_cache, v_cache
+        [n_layers, seq_len, kv_dim]).  Does not touch the object's decode cache."""
+        c = self.cfg
+        x_i8 = np.ascontiguousarray(x_i8, np.int8)
+        assert x_i8.size == seq_len * c["dim"]
+        kv_dim = c["n_kv_heads"] * c["head_dim"]
+        x = np.zeros((seq_len, c["dim"]), np.float32)
+        kc = np.zeros((c["n_layers"], seq_len, kv_dim), np.int8)
+        vc = np.zeros_like(kc)
+        f = lib().simp_oracle_llama_i8_prefill
+        f.argtypes = [C.c_void_p, C.c_void_p, i64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32]
+        f.restype = None
+        f(C.byref(self._s), _ptr(x_i8), seq_len, _ptr(x), _ptr(kc), _ptr(vc), self.threads)
+        return x, kc, vc
+
+
 # --------------------------------------------------------------------------- reference's own kernels
 def cpu_has_vnni() -> bool:
     try:

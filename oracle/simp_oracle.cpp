@@ -559,3 +559,113 @@ ORACLE_API void simp_oracle_llama_i8_forward(const SimpOracleLlamaI8* mp, const 
     logits[i] = sum;
   }
 }
+
+// ---------------------------------------------------------------------------
+// Prefill of the same int8 model over seq_len tokens at once
+// (examples/llama2/llama32_1b_int8_prefill.sl:11-232; the six exported variants differ only in the
+// compile-time seq_len 8 ... 256).  Differences from the single-token text, all kept:
+//   * rmsnorm is x * (1 / sqrt(mean(x^2) + 1e-5)) * w (reciprocal, left to right), computed inline (:33-51);
+//   * no quantisation step clamps (:48, :148, :183, :209): f32 -> i8 is taken as truncation to i32 followed by
+//     narrowing modulo 256, as for the FFN activation of the single-token model;
+//   * causal attention with the softmax written out (:81-141); the cache of a layer is [seq_len, kv_dim] (:69);
+//   * there is no final norm or classifier: the result is the residual stream x_fp32 [seq_len, dim] (:231).
+// Parity unpinned (no known-answer test in the reference).
+// ---------------------------------------------------------------------------
+namespace {
+inline int8_t narrow_f32_to_i8(float v) {
+  if (v < -2147483648.0f) v = -2147483648.0f;  // keep the conversion defined
+  if (v > 2147483520.0f) v = 2147483520.0f;
+  return int8_t(uint8_t(uint32_t(int32_t(v)) & 0xffu));
+}
+// tensor_matmul_nt: C[t, j] = sum_p A[t, p] * Wt[j, p]
+void matmul_nt_i8(const int8_t* A, const int8_t* Wt, int32_t* C, int64_t M, int64_t N, int64_t K, int nt) {
+#pragma omp parallel for num_threads(nt) schedule(static) if (nt > 1)
+  for (int64_t j = 0; j < N; ++j) {
+    const int8_t* w = Wt + j * K;
+    for (int64_t t = 0; t < M; ++t) {
+      const int8_t* a = A + t * K;
+      int32_t acc = 0;
+      for (int64_t p = 0; p < K; ++p) acc += int32_t(a[p]) * int32_t(w[p]);
+      C[t * N + j] = acc;
+    }
+  }
+}
+}  // namespace
+
+ORACLE_API void simp_oracle_llama_i8_prefill(const SimpOracleLlamaI8* mp, const int8_t* x_i8, int64_t seq_len,
+                                             float* x_fp32, int8_t* k_cache, int8_t* v_cache, int threads) {
+  const SimpOracleLlamaI8& m = *mp;
+  const int nt = clamp_threads(threads);
+  const int64_t dim = m.dim, hd = m.hidden_dim, hs = m.head_dim, S = seq_len;
+  const int64_t kv_dim = m.n_kv_heads * hs, n_rep = m.n_heads / m.n_kv_heads;
+  std::vector<float> xb(S * dim), att_scores(m.n_heads * S * S), att_probs(m.n_heads * S * S);
+  std::vector<int8_t> xb_i8(S * dim), ffn_hb(S * hd);
+  std::vector<int32_t> Q(S * dim), K(S * kv_dim), V(S * kv_dim), attn_out(S * dim), Wo(S * dim), Gate(S * hd), Up(S * hd), Down(S * dim);
+  for (int64_t i = 0; i < S * dim; ++i) x_fp32[i] = float(x_i8[i]) * 1.0f;
+  auto norm_quant = [&](const float* w) {
+    for (int64_t t = 0; t < S; ++t) {
+      const int64_t o = t * dim;
+      float ss = 0.0f;
+      for (int64_t i = 0; i < dim; ++i) ss = ss + x_fp32[o + i] * x_fp32[o + i];
+      ss = 1.0f / std::sqrt(ss / (float(dim) * 1.0f) + 0.00001f);
+      for (int64_t i = 0; i < dim; ++i) {
+        xb[o + i] = x_fp32[o + i] * ss * w[i];
+        xb_i8[o + i] = narrow_f32_to_i8(xb[o + i] * 127.0f);
+      }
+    }
+  };
+  for (int64_t layer = 0; layer < m.n_layers; ++layer) {
+    norm_quant(m.rms_att_w + layer * dim);
+    matmul_nt_i8(xb_i8.data(), m.wq_t + layer * dim * dim, Q.data(), S, dim, dim, nt);
+    matmul_nt_i8(xb_i8.data(), m.wk_t + layer * kv_dim * dim, K.data(), S, kv_dim, dim, nt);
+    matmul_nt_i8(xb_i8.data(), m.wv_t + layer * kv_dim * dim, V.data(), S, kv_dim, dim, nt);
+    const int64_t cl = layer * S * kv_dim;
+    for (int64_t i = 0; i < S * kv_dim; ++i) {
+      k_cache[cl + i] = int8_t(uint8_t(uint32_t(K[i] / 256) & 0xffu));
+      v_cache[cl + i] = int8_t(uint8_t(uint32_t(V[i] / 256) & 0xffu));
+    }
+#pragma omp parallel for num_threads(nt) schedule(static) if (nt > 1)
+    for (int64_t h = 0; h < m.n_heads; ++h) {
+      const int64_t qo = h * hs, ko = (h / n_rep) * hs;
+      for (int64_t q_pos = 0; q_pos < S; ++q_pos) {
+        const int64_t ao = h * S * S + q_pos * S;
+        for (int64_t k_pos = 0; k_pos <= q_pos; ++k_pos) {
+          float score = 0.0f;
+          for (int64_t d = 0; d < hs; ++d)
+            score = score + float(Q[q_pos * dim + qo + d]) * 1.0f * float(k_cache[cl + k_pos * kv_dim + ko + d]) * 1.0f;
+          att_scores[ao + k_pos] = score / 8.0f;
+        }
+        float max_val = att_scores[ao];
+        for (int64_t ki = 1; ki <= q_pos; ++ki)
+          if (att_scores[ao + ki] > max_val) max_val = att_scores[ao + ki];
+        float sum_exp = 0.0f;
+        for (int64_t ki = 0; ki <= q_pos; ++ki) {
+          const float e = std::exp(att_scores[ao + ki] - max_val);
+          att_probs[ao + ki] = e;
+          sum_exp = sum_exp + e;
+        }
+        for (int64_t ki = 0; ki <= q_pos; ++ki) att_probs[ao + ki] = att_probs[ao + ki] / sum_exp;
+        for (int64_t d = 0; d < hs; ++d) {
+          float val = 0.0f;
+          for (int64_t vi = 0; vi <= q_pos; ++vi)
+            val = val + att_probs[ao + vi] * float(v_cache[cl + vi * kv_dim + ko + d]) * 1.0f;
+          attn_out[q_pos * dim + qo + d] = int32_t(val);
+        }
+      }
+    }
+    for (int64_t i = 0; i < S * dim; ++i) xb_i8[i] = narrow_f32_to_i8(float(attn_out[i]) * 1.0f / 256.0f);
+    matmul_nt_i8(xb_i8.data(), m.wo_t + layer * dim * dim, Wo.data(), S, dim, dim, nt);
+    for (int64_t i = 0; i < S * dim; ++i) x_fp32[i] = x_fp32[i] + float(Wo[i]) * 1.0f / 65536.0f;
+    norm_quant(m.rms_ffn_w + layer * dim);
+    matmul_nt_i8(xb_i8.data(), m.w1_t + layer * hd * dim, Gate.data(), S, hd, dim, nt);
+    matmul_nt_i8(xb_i8.data(), m.w3_t + layer * hd * dim, Up.data(), S, hd, dim, nt);
+    for (int64_t i = 0; i < S * hd; ++i) {
+      const float gate_f = float(Gate[i]) * 1.0f / 65536.0f;
+      const float silu = gate_f / (1.0f + std::exp(0.0f - gate_f));
+      const float up_f = float(Up[i]) * 1.0f / 65536.0f;
+      ffn_hb[i] = narrow_f32_to_i8(silu * up_f * 127.0f);
+    }
+    matmul_nt_i8(ffn_hb.data(), m.w2_t + layer * dim * hd, Down.data(), S, dim, hd, nt);
+    for (int64_t i = 0; i < S * dim; ++i) x_fp32[i] = x_fp32[i] + float(Down[i]) * 1.0f / 65536.0f;
+  }
+}

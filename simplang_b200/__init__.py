@@ -71,6 +71,7 @@ _SIGNATURES = {
     "simp_llama_i8_load": [vp, C.c_char_p, vp, C.c_size_t],
     "simp_llama_i8_forward": [vp, vp, i64, vp],
     "simp_llama_i8_decode_loop": [vp, vp, i64, i64, vp, C.POINTER(C.c_float)],
+    "simp_llama_i8_prefill": [vp, vp, i64, vp, vp, vp, C.POINTER(C.c_float)],
     "simp_llama_i8_reset_cache": [vp],
     "simp_llama_i8_destroy": [vp],
     "simp_dist_unique_id": [vp, C.c_size_t],
@@ -354,6 +355,7 @@ class LlamaI8:
         check(lib().simp_llama_i8_create(C.byref(c), C.byref(h)))
         self.h = h
         self.dim, self.vocab = cfg["dim"], cfg["vocab_size"]
+        self.n_layers, self.kv_dim = cfg["n_layers"], cfg["n_kv_heads"] * cfg["head_dim"]
         for name, arr in tensors.items():
             arr = np.ascontiguousarray(arr)
             check(lib().simp_llama_i8_load(self.h, name.encode(), arr.ctypes.data, arr.nbytes))
@@ -373,6 +375,18 @@ class LlamaI8:
         ms = C.c_float()
         check(lib().simp_llama_i8_decode_loop(self.h, x_i8.ctypes.data, start_pos, n_tokens, out.ctypes.data, C.byref(ms)))
         return out, float(ms.value)
+
+    def prefill(self, x_i8, seq_len: int):
+        """llama32_prefill_<seq_len>: returns (x_fp32 [seq_len, dim], k_cache, v_cache [n_layers, seq_len, kv_dim], ms)."""
+        x_i8 = np.ascontiguousarray(x_i8, np.int8)
+        assert x_i8.size == seq_len * self.dim
+        x = np.empty((seq_len, self.dim), np.float32)
+        kc = np.empty((self.n_layers, seq_len, self.kv_dim), np.int8)
+        vc = np.empty_like(kc)
+        ms = C.c_float()
+        check(lib().simp_llama_i8_prefill(self.h, x_i8.ctypes.data, seq_len, x.ctypes.data, kc.ctypes.data, vc.ctypes.data,
+                                          C.byref(ms)))
+        return x, kc, vc, float(ms.value)
 
     def reset_cache(self):
         check(lib().simp_llama_i8_reset_cache(self.h))

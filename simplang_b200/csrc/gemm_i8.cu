@@ -712,7 +712,11 @@ int gemm_i8_run(const void* A, const int8_t* B, int32_t* C, int64_t M, int64_t K
       const int sms = ctx().sm_count;
       const int64_t waves = cdiv(tiles, sms);
       const double eff = double(tiles) / double(waves * sms);
-      bool want = p.tma_store && n_peers == 0 && eff < 0.85 && tiles * p.num_kb >= int64_t(sms) * 4 && waves <= 8;
+      // Skinny problems (M <= 256: one or two row tiles, prefill of a few tokens) are weight-bandwidth bound and
+      // have few tiles; splitting K over all SMs is what lets every SM stream a share of B, and the partial
+      // tiles that are reduce-added hold only M rows.
+      const bool enough = tiles * p.num_kb >= int64_t(sms) * 4 || (M <= 256 && tiles * p.num_kb >= sms / 2);
+      bool want = p.tma_store && n_peers == 0 && eff < 0.85 && enough && waves <= 8;
       if (const char* env = getenv("SIMP_GEMM_I8_STREAMK")) want = p.tma_store && n_peers == 0 && atoi(env) != 0;
       if (want) {
         p.streamk = 1;

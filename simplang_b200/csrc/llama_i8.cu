@@ -20,6 +20,7 @@
 #include <algorithm>
 #include <cstring>
 #include <string>
+#include <vector>
 
 #include "common.cuh"
 #include "gemv_f32_core.cuh"
@@ -40,6 +41,15 @@ struct LlamaI8Model {
   int* attn_cnt = nullptr;      // per-head arrival counters (zero between launches)
   int nsplit = 1;
   cudaGraphExec_t graph = nullptr;
+  // prefill: scratch and one captured graph per sequence length that has been used
+  struct PrefillPlan {
+    int64_t M = 0;
+    float* x = nullptr;
+    int8_t *x_i8 = nullptr, *xb_i8 = nullptr, *hb = nullptr;
+    int32_t *acc0 = nullptr, *acc1 = nullptr;
+    cudaGraphExec_t graph = nullptr;
+  };
+  std::vector<PrefillPlan> plans;
 };
 
 enum { PRO_NORM = 0, PRO_I8 = 1 };
@@ -508,6 +518,135 @@ static int i8_ensure_graph(LlamaI8Model& m) {
   return SIMP_OK;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Prefill over M tokens at once (examples/llama2/llama32_1b_int8_prefill.sl:11-232).  The seven projections of
+// a layer are int8 GEMMs on the tensor cores (gemm_i8_run: tcgen05 kind::i8, A = activations [M, K] s8,
+// B = weights [N, K] s8 K-major); the steps between them are small row kernels that restate the text.
+int gemm_i8_run(const void* A, const int8_t* B, int32_t* C, int64_t M, int64_t K, int64_t N, int a_unsigned,
+                int b_transposed, int32_t* const* peer_c, int n_peers, int64_t ldc, int64_t col_offset);
+
+// f32 -> i8 without a clamp: truncate to i32, keep the low 8 bits (what the compiled reference does on x86).
+__device__ __forceinline__ int8_t narrow_f32_to_i8(float v) {
+  v = fmaxf(fminf(v, 2147483520.0f), -2147483648.0f);
+  return int8_t(uint8_t(uint32_t(__float2int_rz(v)) & 0xffu));
+}
+
+// x_f32 = (f32) x_i8 over M * dim elements (prefill.sl:23-27); rows = 1 block each for the norm below.
+__global__ void pf_input_kernel(const int8_t* __restrict__ x_i8, float* __restrict__ x, int64_t n) {
+  const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i < n) x[i] = float(x_i8[i]) * 1.0f;
+}
+// One block per token: ss = 1 / sqrt(mean(x^2) + 1e-5); xb = x * ss * w; xb_i8 = (i8)(xb * 127) unclamped (:33-51).
+__global__ void __launch_bounds__(256) pf_norm_quant_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                                            int8_t* __restrict__ xb_i8, int dim) {
+  __shared__ float red[33];
+  const float* xr = x + size_t(blockIdx.x) * dim;
+  float ss = 0.0f;
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) ss += xr[i] * xr[i];
+  ss = block_sum(ss, red);
+  ss = 1.0f / sqrtf(ss / (float(dim) * 1.0f) + 0.00001f);
+  for (int i = threadIdx.x; i < dim; i += blockDim.x)
+    xb_i8[size_t(blockIdx.x) * dim + i] = narrow_f32_to_i8((xr[i] * ss * w[i]) * 127.0f);
+}
+// cache[layer][t][i] = (i8)(acc / 256) for K and V (:69-79); the device cache keeps its [max_seq, kv_dim] layout.
+__global__ void pf_kv_store_kernel(const int32_t* __restrict__ K, const int32_t* __restrict__ V, int8_t* __restrict__ kc,
+                                   int8_t* __restrict__ vc, int64_t n) {
+  const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i < n) {
+    kc[i] = int8_t(uint8_t(uint32_t(K[i] / 256) & 0xffu));
+    vc[i] = int8_t(uint8_t(uint32_t(V[i] / 256) & 0xffu));
+  }
+}
+// Causal attention, one block per (head, query position) (:81-141): thread t scores key t, block softmax with
+// the division of the text, thread d sums dim d; attn_out = (i32) trunc, next input = (i8)(attn_out / 256.0).
+__global__ void __launch_bounds__(256) pf_attn_kernel(const int32_t* __restrict__ Q, const int8_t* __restrict__ kc,
+                                                      const int8_t* __restrict__ vc, int8_t* __restrict__ xb_i8, int dim,
+                                                      int hs, int kv_dim, int n_rep) {
+  __shared__ float qf[128], probs[256], red[33];
+  const int h = blockIdx.x, q_pos = blockIdx.y, ko = (h / n_rep) * hs;
+  for (int d = threadIdx.x; d < hs; d += blockDim.x) qf[d] = float(Q[size_t(q_pos) * dim + h * hs + d]);
+  __syncthreads();
+  const int t = threadIdx.x;
+  float score = -INFINITY;
+  if (t <= q_pos) {
+    const uint4* kr = reinterpret_cast<const uint4*>(kc + size_t(t) * kv_dim + ko);   // head_dim is a multiple of 16
+    float sc = 0.0f;
+    for (int d16 = 0; d16 < (hs >> 4); ++d16) {
+      const uint4 raw = kr[d16];
+      const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+      for (int i = 0; i < 16; ++i)
+        sc = sc + qf[d16 * 16 + i] * 1.0f * float(int8_t(uint8_t(w[i >> 2] >> (8 * (i & 3))))) * 1.0f;
+    }
+    score = sc / 8.0f;
+  }
+  const float mx = block_max(score, red);
+  const float e = t <= q_pos ? expf(score - mx) : 0.0f;
+  const float sum = block_sum(e, red);
+  probs[t] = t <= q_pos ? e / sum : 0.0f;
+  __syncthreads();
+  if (t < hs) {
+    float val = 0.0f;
+    int vi = 0;
+    for (; vi + 8 <= q_pos + 1; vi += 8) {   // eight rows requested together; the sum keeps its order
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = float(vc[size_t(vi + u) * kv_dim + ko + t]);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) val = val + probs[vi + u] * v[u] * 1.0f;
+    }
+    for (; vi <= q_pos; ++vi) val = val + probs[vi] * float(vc[size_t(vi) * kv_dim + ko + t]) * 1.0f;
+    const int32_t out = __float2int_rz(val);
+    xb_i8[size_t(q_pos) * dim + h * hs + t] = narrow_f32_to_i8(float(out) * 1.0f / 256.0f);
+  }
+}
+// x += (f32) acc / 65536 (:160-167, :220-227)
+__global__ void pf_resid_kernel(float* __restrict__ x, const int32_t* __restrict__ acc, int64_t n) {
+  const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i < n) x[i] = x[i] + float(acc[i]) * 1.0f / 65536.0f;
+}
+// ffn_hb = (i8)(silu(gate / 65536) * (up / 65536) * 127) unclamped (:203-213)
+__global__ void pf_swiglu_kernel(const int32_t* __restrict__ gate, const int32_t* __restrict__ up, int8_t* __restrict__ hb,
+                                 int64_t n) {
+  const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i < n) {
+    const float gate_f = float(gate[i]) * 1.0f / 65536.0f;
+    const float silu = gate_f / (1.0f + expf(0.0f - gate_f));
+    const float up_f = float(up[i]) * 1.0f / 65536.0f;
+    hb[i] = narrow_f32_to_i8(silu * up_f * 127.0f);
+  }
+}
+
+static int i8_prefill_run(LlamaI8Model& m, int64_t M, float* x, int8_t* x_i8, int8_t* xb_i8, int8_t* hb, int32_t* acc0,
+                          int32_t* acc1, cudaStream_t st) {
+  const simp_llama_i8_config& c = m.cfg;
+  const int64_t dim = c.dim, hd = c.hidden_dim, kv = m.kv_dim;
+  auto blocks = [](int64_t n) { return dim3(unsigned((n + 255) / 256)); };
+  pf_input_kernel<<<blocks(M * dim), 256, 0, st>>>(x_i8, x, M * dim);
+  for (int64_t l = 0; l < c.n_layers; ++l) {
+    pf_norm_quant_kernel<<<dim3(unsigned(M)), 256, 0, st>>>(x, m.rms_att + l * dim, xb_i8, int(dim));
+    int32_t *Q = acc0, *K = acc1, *V = acc1 + M * kv;
+    if (int rc = gemm_i8_run(xb_i8, m.wq + l * dim * dim, Q, M, dim, dim, 0, 1, nullptr, 0, dim, 0)) return rc;
+    if (int rc = gemm_i8_run(xb_i8, m.wk + l * kv * dim, K, M, dim, kv, 0, 1, nullptr, 0, kv, 0)) return rc;
+    if (int rc = gemm_i8_run(xb_i8, m.wv + l * kv * dim, V, M, dim, kv, 0, 1, nullptr, 0, kv, 0)) return rc;
+    int8_t* kc = m.kc + size_t(l) * c.max_seq_len * kv;
+    int8_t* vc = m.vc + size_t(l) * c.max_seq_len * kv;
+    pf_kv_store_kernel<<<blocks(M * kv), 256, 0, st>>>(K, V, kc, vc, M * kv);
+    pf_attn_kernel<<<dim3(unsigned(c.n_heads), unsigned(M)), 256, 0, st>>>(Q, kc, vc, xb_i8, int(dim), int(c.head_dim), int(kv),
+                                                                        int(c.n_heads / c.n_kv_heads));
+    if (int rc = gemm_i8_run(xb_i8, m.wo + l * dim * dim, acc0, M, dim, dim, 0, 1, nullptr, 0, dim, 0)) return rc;
+    pf_resid_kernel<<<blocks(M * dim), 256, 0, st>>>(x, acc0, M * dim);
+    pf_norm_quant_kernel<<<dim3(unsigned(M)), 256, 0, st>>>(x, m.rms_ffn + l * dim, xb_i8, int(dim));
+    if (int rc = gemm_i8_run(xb_i8, m.w1 + l * hd * dim, acc0, M, dim, hd, 0, 1, nullptr, 0, hd, 0)) return rc;
+    if (int rc = gemm_i8_run(xb_i8, m.w3 + l * hd * dim, acc1, M, dim, hd, 0, 1, nullptr, 0, hd, 0)) return rc;
+    pf_swiglu_kernel<<<blocks(M * hd), 256, 0, st>>>(acc0, acc1, hb, M * hd);
+    if (int rc = gemm_i8_run(hb, m.w2 + l * dim * hd, acc0, M, hd, dim, 0, 1, nullptr, 0, dim, 0)) return rc;
+    pf_resid_kernel<<<blocks(M * dim), 256, 0, st>>>(x, acc0, M * dim);
+  }
+  SIMP_LAUNCH_CHECK();
+  return SIMP_OK;
+}
+
 }  // namespace simp
 
 using namespace simp;
@@ -517,6 +656,12 @@ SIMP_API int simp_llama_i8_destroy(void* model) {
   LlamaI8Model* m = static_cast<LlamaI8Model*>(model);
   if (ctx().ready) cudaStreamSynchronize(ctx().stream);
   if (m->graph) cudaGraphExecDestroy(m->graph);
+  for (auto& pl : m->plans) {
+    if (pl.graph) cudaGraphExecDestroy(pl.graph);
+    void* pp[] = {pl.x, pl.x_i8, pl.xb_i8, pl.hb, pl.acc0, pl.acc1};
+    for (void* p : pp)
+      if (p) cudaFree(p);
+  }
   void* ptrs[] = {m->rms_att, m->rms_ffn, m->rms_final, m->wcls, m->wq, m->wk, m->wv, m->wo, m->w1, m->w2, m->w3,
                   m->x_i8, m->xb_i8, m->ffn_hb, m->kc, m->vc, m->x, m->xb, m->logits, m->q, m->k, m->v, m->ctl,
                   m->attn_part, m->attn_cnt};
@@ -644,4 +789,90 @@ SIMP_API int simp_llama_i8_decode_loop(void* model, const int8_t* x_i8_host, int
 
 SIMP_API int simp_llama_i8_forward(void* model, const int8_t* x_i8_host, int64_t pos, float* logits_host) {
   return simp_llama_i8_decode_loop(model, x_i8_host, pos, 1, logits_host, nullptr);
+}
+
+// Scratch and graph of a prefill length, created on first use: one eager pass (sets kernel attributes, surfaces
+// launch errors outside capture), then the same enqueue captured.  The host work of a prefill -- 112 GEMM calls
+// with three tensor-map encodes each -- would otherwise cost more than the device work at small seq_len.
+static int i8_prefill_plan(LlamaI8Model& m, int64_t M, LlamaI8Model::PrefillPlan** out) {
+  for (auto& pl : m.plans)
+    if (pl.M == M) { *out = &pl; return SIMP_OK; }
+  const simp_llama_i8_config& c = m.cfg;
+  const int64_t dim = c.dim, hd = c.hidden_dim, kv = m.kv_dim;
+  LlamaI8Model::PrefillPlan pl;
+  pl.M = M;
+  const size_t acc_elems = size_t(M) * size_t(std::max<int64_t>(hd, std::max<int64_t>(dim, 2 * kv)));
+  int rc = SIMP_OK;
+  auto A = [&](void** p, size_t n) {
+    if (rc != SIMP_OK) return;
+    cudaError_t e = cudaMalloc(p, n);
+    if (e != cudaSuccess) rc = set_error(SIMP_ERR_CUDA, "llama_i8_prefill: cudaMalloc of %zu bytes failed: %s", n, cudaGetErrorString(e));
+  };
+  A((void**)&pl.x, size_t(M) * dim * 4); A((void**)&pl.x_i8, size_t(M) * dim); A((void**)&pl.xb_i8, size_t(M) * dim);
+  A((void**)&pl.hb, size_t(M) * hd); A((void**)&pl.acc0, acc_elems * 4); A((void**)&pl.acc1, acc_elems * 4);
+  cudaStream_t st = ctx().stream;
+  if (rc == SIMP_OK) {
+    cudaMemsetAsync(pl.x_i8, 0, size_t(M) * dim, st);
+    rc = i8_prefill_run(m, M, pl.x, pl.x_i8, pl.xb_i8, pl.hb, pl.acc0, pl.acc1, st);
+    if (rc == SIMP_OK && cudaStreamSynchronize(st) != cudaSuccess) rc = set_error(SIMP_ERR_CUDA, "llama_i8_prefill: eager pass failed");
+  }
+  if (rc == SIMP_OK) {
+    cudaGraph_t g = nullptr;
+    if (cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal) != cudaSuccess)
+      rc = set_error(SIMP_ERR_CUDA, "llama_i8_prefill: begin capture failed");
+    if (rc == SIMP_OK) {
+      const int rr = i8_prefill_run(m, M, pl.x, pl.x_i8, pl.xb_i8, pl.hb, pl.acc0, pl.acc1, st);
+      cudaError_t e = cudaStreamEndCapture(st, &g);
+      if (rr != SIMP_OK) rc = rr;
+      else if (e != cudaSuccess) rc = set_error(SIMP_ERR_CUDA, "llama_i8_prefill: capture failed: %s", cudaGetErrorString(e));
+      else if ((e = cudaGraphInstantiate(&pl.graph, g, 0)) != cudaSuccess)
+        rc = set_error(SIMP_ERR_CUDA, "llama_i8_prefill: graph instantiate failed: %s", cudaGetErrorString(e));
+      if (g) cudaGraphDestroy(g);
+    }
+  }
+  if (rc != SIMP_OK) {
+    void* pp[] = {pl.x, pl.x_i8, pl.xb_i8, pl.hb, pl.acc0, pl.acc1};
+    for (void* p : pp)
+      if (p) cudaFree(p);
+    return rc;
+  }
+  m.plans.push_back(pl);
+  *out = &m.plans.back();
+  return SIMP_OK;
+}
+
+SIMP_API int simp_llama_i8_prefill(void* model, const int8_t* x_i8_host, int64_t seq_len, float* x_fp32_host,
+                                   int8_t* k_cache_host, int8_t* v_cache_host, float* ms_out) {
+  SIMP_REQUIRE(model && x_i8_host, SIMP_ERR_ARG, "llama_i8_prefill: null pointer");
+  LlamaI8Model& m = *static_cast<LlamaI8Model*>(model);
+  if (int rc = i8_check_loaded(m)) return rc;
+  const simp_llama_i8_config& c = m.cfg;
+  const int64_t M = seq_len, dim = c.dim, kv = m.kv_dim;
+  SIMP_REQUIRE(M >= 1 && M <= 256 && M <= c.max_seq_len, SIMP_ERR_ARG,
+               "llama_i8_prefill: seq_len %lld outside [1, min(256, max_seq_len)]", (long long)M);
+  LlamaI8Model::PrefillPlan* pl = nullptr;
+  if (int rc = i8_prefill_plan(m, M, &pl)) return rc;
+  cudaStream_t st = ctx().stream;
+  SIMP_CUDA(cudaMemcpyAsync(pl->x_i8, x_i8_host, size_t(M) * dim, cudaMemcpyHostToDevice, st));
+  cudaEvent_t e0 = nullptr, e1 = nullptr;
+  if (ms_out) {
+    SIMP_CUDA(cudaEventCreate(&e0));
+    SIMP_CUDA(cudaEventCreate(&e1));
+    SIMP_CUDA(cudaEventRecord(e0, st));
+  }
+  SIMP_CUDA(cudaGraphLaunch(pl->graph, st));
+  if (ms_out) SIMP_CUDA(cudaEventRecord(e1, st));
+  if (x_fp32_host) SIMP_CUDA(cudaMemcpyAsync(x_fp32_host, pl->x, size_t(M) * dim * 4, cudaMemcpyDeviceToHost, st));
+  for (int64_t l = 0; l < c.n_layers; ++l) {   // cache rows 0 .. M-1 of every layer, packed [n_layers, M, kv_dim]
+    const size_t src = size_t(l) * c.max_seq_len * kv, dst = size_t(l) * M * kv;
+    if (k_cache_host) SIMP_CUDA(cudaMemcpyAsync(k_cache_host + dst, m.kc + src, size_t(M) * kv, cudaMemcpyDeviceToHost, st));
+    if (v_cache_host) SIMP_CUDA(cudaMemcpyAsync(v_cache_host + dst, m.vc + src, size_t(M) * kv, cudaMemcpyDeviceToHost, st));
+  }
+  SIMP_CUDA(cudaStreamSynchronize(st));
+  if (ms_out) {
+    SIMP_CUDA(cudaEventElapsedTime(ms_out, e0, e1));
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+  }
+  return simp_gpu_check_device_status();
 }

@@ -2,7 +2,7 @@
 int8 GEMM at the configured shapes.  Prints one JSON line per case with the achieved GB/s (or TOPS), the
 algorithmic bytes used, and the fraction of the measured roofline.
 
-    python -m simplang_b200.opbench [--iters 50] [--only gemv_f32,w4,rowops,gemm_i8,mma_peak,decode110m,decode3b,decode_i8]
+    python -m simplang_b200.opbench [--iters 50] [--only gemv_f32,w4,rowops,gemm_i8,mma_peak,decode110m,decode3b,decode_i8,prefill_i8]
 
 Each case rotates over enough independent operand copies that the working set exceeds twice the
 126 MB L2, so every iteration streams from HBM the way consecutive layers of a decode step do.
@@ -234,6 +234,26 @@ def bench_decode_i8():
     m.close()
 
 
+def bench_prefill_i8():
+    """Prefill of the int8 LLaMA-3.2-1B-style model as its host times it (bench_llama32_1b_int8_prefill.cpp):
+    seq_len 8 ... 256, prompt tokens per second; the seven projections per layer are tcgen05 int8 GEMMs."""
+    from simplang_b200 import synth
+    cfg = dict(synth.LLAMA32_1B_INT8, max_seq_len=256)
+    t = synth.llama_i8_tensors(cfg, 0, "bench")
+    m = sg.LlamaI8(cfg, t)
+    d, h, L = cfg["dim"], cfg["hidden_dim"], cfg["n_layers"]
+    kvd = cfg["n_kv_heads"] * cfg["head_dim"]
+    w_params = L * (2 * d * d + 2 * kvd * d + 3 * h * d)
+    for M in (8, 16, 32, 64, 128, 256):
+        x = np.random.default_rng(M).integers(-64, 64, (M, d), dtype=np.int8)
+        m.prefill(x, M)
+        ms = min(m.prefill(x, M)[3] for _ in range(5))
+        print(json.dumps({"op": "llama-3.2-1B int8 prefill", "seq_len": M, "ms": round(ms, 3),
+                          "prompt_tok_s": round(M / ms * 1e3, 1), "gemm_tops": round(2.0 * M * w_params / (ms * 1e-3) / 1e12, 2),
+                          "weight_gb_s": round(w_params / (ms * 1e-3) / 1e9, 1)}), flush=True)
+    m.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--iters", type=int, default=50)
@@ -268,6 +288,8 @@ def main():
         bench_decode("3b")
     if "decode_i8" in which:
         bench_decode_i8()
+    if "prefill_i8" in which:
+        bench_prefill_i8()
     sg.check(sg.lib().simp_gpu_check_device_status())
 
 

@@ -95,3 +95,63 @@ def test_errors(gpu):
         check = gpu.check
         check(gpu.lib().simp_llama_i8_load(gm.h, b"wq_t", t["wq_t"].ctypes.data, 5))
     gm.close()
+
+
+# --------------------------------------------------------------------------- prefill (llama32_1b_int8_prefill.sl)
+def run_prefill(gpu, oracle, cfg, seed, style, M, x_seed=0):
+    from simplang_b200 import synth
+    t = synth.llama_i8_tensors(cfg, seed, style)
+    x = np.random.default_rng([x_seed, M]).integers(-64, 64, (M, cfg["dim"]), dtype=np.int8)
+    gm = gpu.LlamaI8(cfg, t)
+    om = oracle.LlamaI8(cfg, t)
+    xg, kg, vg, ms = gm.prefill(x, M)
+    xo, ko, vo = om.prefill(x, M)
+    err = float(np.max(np.abs(xg - xo)) / (np.max(np.abs(xo)) + 1e-30))
+    # the caches are integers: count mismatching entries (a flip needs an f32 difference at a truncation boundary)
+    bad = int(np.count_nonzero(kg != ko) + np.count_nonzero(vg != vo))
+    gm.close()
+    return err, bad, ko.size + vo.size, ms, (gm, om, t, x, ko, vo)
+
+
+@pytest.mark.parametrize("style", ["bench", "unit-norm"])
+@pytest.mark.parametrize("M", [1, 8, 13, 48])
+def test_prefill_small(gpu, oracle, style, M):
+    err, bad, total, _, _ = run_prefill(gpu, oracle, SMALL, 3, style, M)
+    assert err <= 1e-3, err
+    assert bad <= total // 1000, (bad, total)
+
+
+@pytest.mark.parametrize("M", [64, 150])
+def test_prefill_mid_gqa(gpu, oracle, M):
+    err, bad, total, _, _ = run_prefill(gpu, oracle, MID, 5, "bench", M)
+    assert err <= 1e-3, err
+    assert bad <= total // 1000, (bad, total)
+
+
+def test_prefill_then_decode_continues(gpu, oracle):
+    """The prefill leaves its K/V rows in the device cache; a decode step at position M must see them."""
+    from simplang_b200 import synth
+    cfg, M = SMALL, 16
+    t = synth.llama_i8_tensors(cfg, 9, "bench")
+    x = np.random.default_rng(5).integers(-64, 64, (M, cfg["dim"]), dtype=np.int8)
+    gm, om = gpu.LlamaI8(cfg, t), oracle.LlamaI8(cfg, t)
+    gm.prefill(x, M)
+    _, ko, vo = om.prefill(x, M)
+    kv = cfg["n_kv_heads"] * cfg["head_dim"]
+    om.k_cache.reshape(cfg["n_layers"], cfg["max_seq_len"], kv)[:, :M] = ko
+    om.v_cache.reshape(cfg["n_layers"], cfg["max_seq_len"], kv)[:, :M] = vo
+    xi = synth.llama_i8_input(cfg, 3)
+    a, b = gm.forward(xi, M), om.forward(xi, M)
+    assert np.max(np.abs(a - b)) <= 1e-3 * np.max(np.abs(b))
+    gm.close()
+
+
+@pytest.mark.parametrize("M", [8, 64])
+def test_prefill_llama32_1b_full_size(gpu, oracle, M):
+    """The reference's configuration and its host's distributions (bench_llama32_1b_int8_prefill.cpp)."""
+    from simplang_b200 import synth
+    cfg = dict(synth.LLAMA32_1B_INT8, max_seq_len=256)
+    err, bad, total, ms, _ = run_prefill(gpu, oracle, cfg, 0, "bench", M)
+    print(f"llama-3.2-1B int8 prefill M={M}: rel err {err:.2e}, cache mismatches {bad}/{total}, {ms:.2f} ms")
+    assert err <= 1e-3, err
+    assert bad <= total // 1000, (bad, total)
