@@ -24,33 +24,9 @@
 
 #include "common.cuh"
 #include "gemv_f32_core.cuh"
+#include "llama_i8_model.hpp"
 
 namespace simp {
-
-struct LlamaI8Model {
-  simp_llama_i8_config cfg;
-  int64_t kv_dim;
-  float *rms_att = nullptr, *rms_ffn = nullptr, *rms_final = nullptr, *wcls = nullptr;
-  int8_t *wq = nullptr, *wk = nullptr, *wv = nullptr, *wo = nullptr, *w1 = nullptr, *w2 = nullptr, *w3 = nullptr;
-  // state
-  int8_t *x_i8 = nullptr, *xb_i8 = nullptr, *ffn_hb = nullptr, *kc = nullptr, *vc = nullptr;
-  float *x = nullptr, *xb = nullptr, *logits = nullptr;
-  int32_t *q = nullptr, *k = nullptr, *v = nullptr;
-  int* ctl = nullptr;   // [0] pos
-  float* attn_part = nullptr;   // [n_heads, nsplit, head_dim + 2] split partials of the attention
-  int* attn_cnt = nullptr;      // per-head arrival counters (zero between launches)
-  int nsplit = 1;
-  cudaGraphExec_t graph = nullptr;
-  // prefill: scratch and one captured graph per sequence length that has been used
-  struct PrefillPlan {
-    int64_t M = 0;
-    float* x = nullptr;
-    int8_t *x_i8 = nullptr, *xb_i8 = nullptr, *hb = nullptr;
-    int32_t *acc0 = nullptr, *acc1 = nullptr;
-    cudaGraphExec_t graph = nullptr;
-  };
-  std::vector<PrefillPlan> plans;
-};
 
 enum { PRO_NORM = 0, PRO_I8 = 1 };
 enum { EPI_STORE = 0, EPI_RESID = 1, EPI_GATEUP = 2 };
@@ -443,6 +419,12 @@ static size_t i8_attn_smem(const LlamaI8Model& m) {
 
 static int i8_enqueue_token(LlamaI8Model& m, cudaStream_t st) {
   const simp_llama_i8_config& c = m.cfg;
+  // SIMP_DECODE_MODE=persistent selects the single cooperative kernel per token (llama_i8_persistent.cu; parity
+  // green, a few percent slower than the per-op kernels below today), anything else the per-op kernels
+  {
+    const char* e = getenv("SIMP_DECODE_MODE");
+    if (e && !strcmp(e, "persistent") && persistent_i8_supported(m)) return enqueue_token_persistent_i8(m, st);
+  }
   const int dim = int(c.dim), hd = int(c.hidden_dim), kv = int(m.kv_dim), hs = int(c.head_dim);
   const int sms = ctx().sm_count;
   I8_LAUNCH(i8_input_kernel, dim3((dim + 255) / 256), dim3(256), 0, st, false, (const int8_t*)m.x_i8, m.x, dim);
@@ -664,7 +646,7 @@ SIMP_API int simp_llama_i8_destroy(void* model) {
   }
   void* ptrs[] = {m->rms_att, m->rms_ffn, m->rms_final, m->wcls, m->wq, m->wk, m->wv, m->wo, m->w1, m->w2, m->w3,
                   m->x_i8, m->xb_i8, m->ffn_hb, m->kc, m->vc, m->x, m->xb, m->logits, m->q, m->k, m->v, m->ctl,
-                  m->attn_part, m->attn_cnt};
+                  m->attn_part, m->attn_cnt, m->pk_bar, m->pk_best_val, m->pk_best_idx, m->pk_part};
   for (void* p : ptrs)
     if (p) cudaFree(p);
   delete m;
@@ -703,6 +685,10 @@ SIMP_API int simp_llama_i8_create(const simp_llama_i8_config* cfg, void** model)
   m->nsplit = int(std::min<int64_t>(AI8_MAX_SPLITS, std::max<int64_t>(1, c.max_seq_len / 256)));
   A((void**)&m->attn_part, size_t(c.n_heads) * m->nsplit * (c.head_dim + 2) * 4);
   A((void**)&m->attn_cnt, size_t(c.n_heads) * 4);
+  A((void**)&m->pk_bar, 64);
+  A((void**)&m->pk_best_val, size_t(ctx().sm_count) * 4);
+  A((void**)&m->pk_best_idx, size_t(ctx().sm_count) * 4);
+  A((void**)&m->pk_part, size_t(c.n_heads) * 4 * (c.head_dim + 2) * 4);
   if (rc != SIMP_OK) { simp_llama_i8_destroy(m); return rc; }
   cudaMemsetAsync(m->ctl, 0, 64, ctx().stream);
   cudaMemsetAsync(m->attn_cnt, 0, size_t(c.n_heads) * 4, ctx().stream);

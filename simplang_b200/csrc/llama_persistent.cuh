@@ -36,6 +36,7 @@ struct PkStatic {
   int sh_abort, prod_done;
   float sm_m[PK_WARPS], sm_s[PK_WARPS];
   float qs[128], ks[128], vs[128];
+  int halves[2][4 * PK_WARPS];   // int8 kernel: partial row sums of two warps sharing a row (double-buffered by tile)
 };
 
 __device__ __forceinline__ int share_rows(int R, int G, int b) { return R / G + (b < R % G ? 1 : 0); }
