@@ -57,6 +57,7 @@ struct GemmParams {
   int col_offset;
   int streamk;      // 1: the tiles x K-blocks work units are split evenly over the CTAs; partial tiles are
                     //    added into a zeroed C with TMA reduce-add (integer adds: exact in any order)
+                    // 2: hybrid -- full waves as whole tiles, only the tiles of the last partial wave are split
   int bn;           // tile width in columns (multiple of 32, <= 256); the 2-CTA kernel always uses 256
   uint32_t stage_tx;  // bytes one stage's TMA loads deliver (1-CTA kernel)
   int mma_only;     // measurement aid (2-CTA kernel): no TMA loads, no epilogue traffic -- the MMA issuer runs
@@ -77,34 +78,57 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
 
 
 // Work of one CTA of the 1-CTA kernel.  Classic mode: whole tiles, tile = blockIdx.x + i*gridDim.x.
-// Stream-K mode: the num_tiles*num_kb (tile, K-block) units are cut into gridDim.x equal contiguous ranges,
-// so every SM gets the same amount of math even when the tile count is not a multiple of the SM count.
+// Stream-K mode (streamk = 1): the num_tiles*num_kb (tile, K-block) units are cut into gridDim.x equal contiguous
+// ranges, so every SM gets the same amount of math even when the tile count is not a multiple of the SM count.
+// Hybrid mode (streamk = 2, more than one wave): the full waves run as whole tiles with plain stores, and only
+// the tiles of the last, partial wave are cut into equal K ranges -- so only those few tiles pay for zeroing
+// and reduce-adds.
 struct WorkIter {
-  int i = 0;       // classic: iteration count
-  int u = 0, u1 = 0;  // stream-K: next unit, end of this CTA's range
+  int i = 0;          // whole tiles: iteration count
+  int u = 0, u1 = 0;  // split part: next unit, end of this CTA's range
 };
+__device__ __forceinline__ int work_full_tiles(const GemmParams& p, int num_tiles) {
+  return p.streamk == 2 ? (num_tiles / int(gridDim.x)) * int(gridDim.x) : (p.streamk == 1 ? 0 : num_tiles);
+}
 __device__ __forceinline__ void work_init(const GemmParams& p, int num_tiles, WorkIter& w) {
   if (p.streamk) {
-    const long long total = (long long)num_tiles * p.num_kb;
+    const long long total = (long long)(num_tiles - work_full_tiles(p, num_tiles)) * p.num_kb;
     w.u = int(total * blockIdx.x / gridDim.x);
     w.u1 = int(total * (blockIdx.x + 1) / gridDim.x);
   }
 }
-__device__ __forceinline__ bool work_next(const GemmParams& p, int num_tiles, WorkIter& w, int& tile, int& kb0, int& kb1) {
-  if (!p.streamk) {
-    tile = blockIdx.x + w.i * gridDim.x;
-    if (tile >= num_tiles) return false;
+// Next work item: tile, K-block range, and whether the result is a partial sum to be reduce-added.
+__device__ __forceinline__ bool work_next(const GemmParams& p, int num_tiles, WorkIter& w, int& tile, int& kb0, int& kb1,
+                                          bool& partial) {
+  const int full = work_full_tiles(p, num_tiles);
+  tile = blockIdx.x + w.i * gridDim.x;
+  if (tile < full) {
     ++w.i;
     kb0 = 0;
     kb1 = p.num_kb;
+    partial = false;
     return true;
   }
   if (w.u >= w.u1) return false;
-  tile = w.u / p.num_kb;
-  kb0 = w.u - tile * p.num_kb;
+  const int t = w.u / p.num_kb;
+  tile = full + t;
+  kb0 = w.u - t * p.num_kb;
   kb1 = min(p.num_kb, kb0 + (w.u1 - w.u));
   w.u += kb1 - kb0;
+  partial = true;
   return true;
+}
+
+// Zeroes the C region of the tiles [first, num_tiles) (the split tiles of the hybrid mode): one block per tile.
+__global__ void zero_tiles_kernel(int32_t* __restrict__ C, int M, int N, int tiles_m, int tiles_n, int bn, int first) {
+  int tm, tn;
+  tile_coords(first + blockIdx.x, tiles_m, tiles_n, tm, tn);
+  const int m0 = tm * 128, n0 = tn * bn;
+  for (int r = threadIdx.x >> 5; r < 128; r += blockDim.x >> 5) {
+    const int row = m0 + r;
+    if (row >= M) break;
+    for (int cidx = n0 + (threadIdx.x & 31); cidx < min(N, n0 + bn); cidx += 32) C[size_t(row) * N + cidx] = 0;
+  }
 }
 
 // Epilogue of one 128 x 256 accumulator for the 32 rows owned by this warp: TMEM -> registers ->
@@ -114,7 +138,7 @@ __device__ __forceinline__ bool work_next(const GemmParams& p, int num_tiles, Wo
 __device__ __forceinline__ void epilogue_rows(const CUtensorMap* tmap_c, const PeerMaps* peers, const GemmParams& p,
                                               uint32_t tmem_acc,
                                               int q, int lane, int row0, int n0, uint32_t stage_smem,
-                                              uint32_t& nstore) {
+                                              uint32_t& nstore, bool partial = false) {
   const int row = row0 + lane;
   int32_t* crow = p.C + int64_t(row) * p.N + n0;
   const bool vec_ok = (p.N % 4) == 0;
@@ -147,7 +171,7 @@ __device__ __forceinline__ void epilogue_rows(const CUtensorMap* tmap_c, const P
             // fused all-gather: the same staged tile goes to every rank's copy of C (own memory and, over
             // NVLink, the peers'); plain TMA stores, no multicast
             for (int r = 0; r < p.n_peers; ++r) tma_store_2d(&peers->m[r], buf, c0 + p.col_offset, row0);
-          } else if (p.streamk) {
+          } else if (partial) {
             tma_reduce_add_2d(tmap_c, buf, c0, row0);
           } else {
             tma_store_2d(tmap_c, buf, c0, row0);
@@ -222,7 +246,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
       WorkIter wk;
       work_init(p, num_tiles, wk);
       int tile, kb0, kb1;
-      while (ok && work_next(p, num_tiles, wk, tile, kb0, kb1)) {
+      bool partial;
+      while (ok && work_next(p, num_tiles, wk, tile, kb0, kb1, partial)) {
         int tm, tn;
         tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
         const int m0 = tm * BM, n0 = tn * p.bn;
@@ -259,7 +284,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
       WorkIter wk;
       work_init(p, num_tiles, wk);
       int tile, kb0, kb1;
-      while (ok && work_next(p, num_tiles, wk, tile, kb0, kb1)) {
+      bool partial;
+      while (ok && work_next(p, num_tiles, wk, tile, kb0, kb1, partial)) {
         if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, 2)) { ok = false; break; }
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + uint32_t(acc * BN);
@@ -294,13 +320,14 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     WorkIter wk;
     work_init(p, num_tiles, wk);
     int tile, kb0, kb1;
-    while (work_next(p, num_tiles, wk, tile, kb0, kb1)) {
+    bool partial;
+    while (work_next(p, num_tiles, wk, tile, kb0, kb1, partial)) {
       int tm, tn;
       tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
       if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, 4)) break;
       tc_fence_after_sync();
       epilogue_rows(&tmap_c, &peers, p, tmem_base + uint32_t(acc * BN), q, lane, tm * BM + q * 32, tn * p.bn, my_stage,
-                    nstore);
+                    nstore, partial);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty_bar(acc));
@@ -606,8 +633,13 @@ int gemm_i8_run(const void* A, const int8_t* B, int32_t* C, int64_t M, int64_t K
   if (tma_ok && !tiny) {
     // Kernel choice: the 2-CTA kernel for problems with at least one full wave of 256x256 tiles on the
     // 74 CTA pairs; the 1-CTA kernel otherwise.  SIMP_GEMM_I8_KERNEL=1cta|2cta overrides (testing).
+    // Kernel choice: the 2-CTA kernel when 256x256 tiles fill its waves well (at least one wave on the 74 CTA
+    // pairs and a last wave that is not nearly empty: 76 tiles would take two waves for 1.03 waves of work);
+    // otherwise the 1-CTA kernel, whose hybrid stream-K mode spreads a partial last wave over all SMs.
     const int64_t tiles2 = cdiv(M, 256) * cdiv(N, 256);
-    bool use_pair = tiles2 >= (ctx().sm_count / 2) && ctx().sm_count >= 2;
+    const int64_t pairs_all = ctx().sm_count / 2;
+    const double eff2 = pairs_all > 0 ? double(tiles2) / double(cdiv(tiles2, pairs_all) * pairs_all) : 0.0;
+    bool use_pair = tiles2 >= pairs_all && ctx().sm_count >= 2 && eff2 >= 0.8;
     if (const char* env = getenv("SIMP_GEMM_I8_KERNEL")) {
       if (!strcmp(env, "1cta")) use_pair = false;
       if (!strcmp(env, "2cta")) use_pair = true;
@@ -718,10 +750,17 @@ int gemm_i8_run(const void* A, const int8_t* B, int32_t* C, int64_t M, int64_t K
       const bool enough = tiles * p.num_kb >= int64_t(sms) * 4 || (M <= 256 && tiles * p.num_kb >= sms / 2);
       bool want = p.tma_store && n_peers == 0 && eff < 0.85 && enough && waves <= 8;
       if (const char* env = getenv("SIMP_GEMM_I8_STREAMK")) want = p.tma_store && n_peers == 0 && atoi(env) != 0;
+      // (waves <= 8 above: with many waves the last one matters little; SIMP_GEMM_I8_STREAMK=1 forces the split anyway)
       if (want) {
-        p.streamk = 1;
         grid = sms;
-        SIMP_CUDA(cudaMemsetAsync(C, 0, size_t(M) * size_t(N) * sizeof(int32_t), st));
+        if (tiles > sms) {   // more than one wave: only the last, partial wave is split and needs zeroing
+          p.streamk = 2;
+          const int full = int(tiles / sms) * sms;
+          zero_tiles_kernel<<<int(tiles) - full, 256, 0, st>>>(C, int(M), int(N), p.tiles_m, p.tiles_n, bn, full);
+        } else {
+          p.streamk = 1;
+          SIMP_CUDA(cudaMemsetAsync(C, 0, size_t(M) * size_t(N) * sizeof(int32_t), st));
+        }
       }
     }
     gemm_i8_tcgen05_kernel<<<grid, GEMM_THREADS, GEMM_SMEM, st>>>(ma, mb, mc, peers, p);

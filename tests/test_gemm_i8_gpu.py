@@ -35,6 +35,21 @@ def test_matmul_i8(gpu, oracle, M, K, N, a_unsigned, b_t):
     assert bad.size == 0, f"{len(bad)} mismatches, first at {bad[:5].tolist()}"
 
 
+@pytest.mark.parametrize("M,K,N,b_t", [(650, 384, 7952, False), (650, 384, 7952, True), (1280, 256, 4864, False)])
+def test_hybrid_stream_k_ragged(gpu, oracle, monkeypatch, M, K, N, b_t):
+    """More tiles than SMs with a partial last wave and ragged edges, split forced on: the full waves are stored
+    as whole tiles, the tiles of the last wave are zeroed and reduce-added from K ranges."""
+    monkeypatch.setenv("SIMP_GEMM_I8_STREAMK", "1")
+    monkeypatch.setenv("SIMP_GEMM_I8_KERNEL", "1cta")
+    rng = np.random.default_rng(M + N)
+    A = rand(rng, (M, K), True)
+    B = rand(rng, (N, K) if b_t else (K, N), False)
+    out = gpu.np_matmul_i8(A, B, b_transposed=b_t)
+    ref = oracle.tensor_matmul_i8(A, B, b_transposed=b_t)
+    bad = np.argwhere(out != ref)
+    assert bad.size == 0, f"{len(bad)} mismatches, first at {bad[:5].tolist()}"
+
+
 def test_extremes_and_wraparound(gpu, oracle):
     # 255*127 and 255*-128 products (test_vnni_correctness.cpp:118-160) and i32 wrap (:248-277):
     # K = 131072 of 255 * -128 overflows int32 and must wrap, not saturate.
