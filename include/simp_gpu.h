@@ -143,6 +143,17 @@ int simp_gpu_event_record(void* event);                      /* on the library s
 int simp_gpu_event_elapsed_ms(void* start, void* stop, float* ms);
 int simp_gpu_event_destroy(void* event);
 
+/* Record-and-replay of a sequence of device-pointer calls (no counterpart in the reference: its hosts call a
+ * compiled CPU function in a loop, e.g. simptensor/benchmarks/bench_int8_matmul_omp_runner.cpp:150-175; on a GPU a
+ * call of a few microseconds is dominated by its launch unless the sequence is replayed as one unit).
+ * Between record_begin and record_end the calls are recorded, not executed; only the simp_gpu_* compute entry
+ * points with device pointers may be called (no alloc / upload / download / sync, no first call of an op
+ * family -- run the sequence once before recording it).  Pointers and shapes are frozen into the recording. */
+int simp_gpu_record_begin(void);
+int simp_gpu_record_end(void** recording);
+int simp_gpu_replay(void* recording, int64_t times);       /* enqueued on the library stream */
+int simp_gpu_recording_destroy(void* recording);
+
 /* ---- the same ops on HOST pointers ---------------------------------------------------------
  * What a compiled .sl kernel's host sees today: plain host arrays in, results in host arrays on
  * return (hosts: simptensor/benchmarks/bench_prefill_matmul_runner.cpp:18-23, 77-120;

@@ -61,6 +61,10 @@ _SIGNATURES = {
     "simp_host_rmsnorm_f32": [vp, vp, vp, i64, i64, C.c_float, i64],
     "simp_host_softmax_f32": [vp, vp, i64, i64, i64, i64, i64],
     "simp_host_silu_f32": [vp, vp, vp, i64],
+    "simp_gpu_record_begin": [],
+    "simp_gpu_record_end": [C.POINTER(vp)],
+    "simp_gpu_replay": [vp, i64],
+    "simp_gpu_recording_destroy": [vp],
     "simp_llama_create": [vp, C.POINTER(vp)],
     "simp_llama_load": [vp, C.c_char_p, vp, C.c_size_t],
     "simp_llama_set_w4_offsets": [vp, C.POINTER(i64)],
@@ -285,6 +289,33 @@ def host_tensor_matmul_i8(A: np.ndarray, B: np.ndarray, out: np.ndarray = None, 
 
 
 # ------------------------------------------------------------------------- LLaMA decode driver
+class Recording:
+    """``with Recording() as r: <device-pointer calls>`` records the calls; ``r.replay(n)`` enqueues them n times."""
+
+    def __init__(self):
+        self.h = None
+
+    def __enter__(self):
+        check(lib().simp_gpu_record_begin())
+        return self
+
+    def __exit__(self, et, ev, tb):
+        h = vp()
+        rc = lib().simp_gpu_record_end(C.byref(h))
+        if et is None:
+            check(rc)
+            self.h = h
+        return False
+
+    def replay(self, times=1):
+        check(lib().simp_gpu_replay(self.h, times))
+
+    def close(self):
+        if self.h:
+            lib().simp_gpu_recording_destroy(self.h)
+            self.h = None
+
+
 class LlamaConfig(C.Structure):
     _fields_ = [(n, i64) for n in ("dim", "hidden_dim", "n_layers", "n_heads", "n_kv_heads", "vocab_size", "seq_len",
                                    "w4", "group_size", "tp_size")]

@@ -112,6 +112,37 @@ SIMP_API int simp_gpu_event_destroy(void* ev) {
   return SIMP_OK;
 }
 
+// ---- replaying a sequence of calls ----------------------------------------------------------
+// A host that repeats the same sequence of device-pointer calls (a benchmark loop, a layer applied to resident
+// buffers) can record it once and replay it: the replay costs one launch instead of one per call, which is
+// what a microsecond-scale kernel needs to be measured (or used) at its device speed.
+SIMP_API int simp_gpu_record_begin(void) {
+  if (int rc = ensure_ready()) return rc;
+  SIMP_CUDA(cudaStreamBeginCapture(ctx().stream, cudaStreamCaptureModeThreadLocal));
+  return SIMP_OK;
+}
+SIMP_API int simp_gpu_record_end(void** recording) {
+  SIMP_REQUIRE(recording != nullptr, SIMP_ERR_ARG, "record_end: null pointer");
+  cudaGraph_t g = nullptr;
+  cudaError_t e = cudaStreamEndCapture(ctx().stream, &g);
+  SIMP_REQUIRE(e == cudaSuccess && g != nullptr, SIMP_ERR_CUDA, "record_end: capture failed: %s", cudaGetErrorString(e));
+  cudaGraphExec_t ex = nullptr;
+  e = cudaGraphInstantiate(&ex, g, 0);
+  cudaGraphDestroy(g);
+  SIMP_REQUIRE(e == cudaSuccess, SIMP_ERR_CUDA, "record_end: instantiate failed: %s", cudaGetErrorString(e));
+  *recording = ex;
+  return SIMP_OK;
+}
+SIMP_API int simp_gpu_replay(void* recording, int64_t times) {
+  SIMP_REQUIRE(recording != nullptr && times >= 0, SIMP_ERR_ARG, "replay: null recording or negative count");
+  for (int64_t i = 0; i < times; ++i) SIMP_CUDA(cudaGraphLaunch(static_cast<cudaGraphExec_t>(recording), ctx().stream));
+  return SIMP_OK;
+}
+SIMP_API int simp_gpu_recording_destroy(void* recording) {
+  if (recording) SIMP_CUDA(cudaGraphExecDestroy(static_cast<cudaGraphExec_t>(recording)));
+  return SIMP_OK;
+}
+
 // ---- host-pointer ops -------------------------------------------------------------------------
 // tensor_matmul on i8 with host operands.  Rows of A are processed in chunks so that the upload of
 // chunk c+1, the GEMM of chunk c and the download of chunk c-1 overlap on three streams.

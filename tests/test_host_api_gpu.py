@@ -125,3 +125,32 @@ def test_cpp_host_driver(gpu):
     assert "verification passed" in r.stdout and "GIOP/s" in r.stdout
     r = subprocess.run([exe, os.path.join(os.path.dirname(gpu.LIB_PATH), "missing.so")], capture_output=True, text=True)
     assert r.returncode == 1 and "Failed to load library" in r.stderr
+
+
+def test_record_and_replay(gpu, oracle):
+    """A recorded sequence of device-pointer calls replays with the results of the direct calls."""
+    rng = np.random.default_rng(5)
+    M, K, N = 96, 256, 160
+    A = rng.integers(0, 256, (M, K), dtype=np.uint8)
+    B = rng.integers(-128, 128, (K, N), dtype=np.int8)
+    dA, dB = gpu.DeviceBuffer.from_numpy(A), gpu.DeviceBuffer.from_numpy(B)
+    dC = gpu.DeviceBuffer(M * N * 4)
+    x = rng.standard_normal(4096).astype(np.float32)
+    dx, dy = gpu.DeviceBuffer.from_numpy(x), gpu.DeviceBuffer(x.nbytes)
+    # run once first (first calls of an op family set kernel attributes, which a recording may not do)
+    gpu.matmul_i8(dA, dB, dC, M, K, N, a_unsigned=True, b_transposed=False)
+    gpu.silu_f32(dx, None, dy, x.size)
+    gpu.check(gpu.lib().simp_gpu_memset(dC.ptr, 0, dC.nbytes))
+    gpu.check(gpu.lib().simp_gpu_memset(dy.ptr, 0, dy.nbytes))
+    gpu.sync()
+    with gpu.Recording() as rec:
+        gpu.matmul_i8(dA, dB, dC, M, K, N, a_unsigned=True, b_transposed=False)
+        gpu.silu_f32(dx, None, dy, x.size)
+    gpu.sync()
+    assert not dC.to_numpy(np.int32, (M, N)).any()      # recording does not execute
+    rec.replay(3)
+    gpu.sync()
+    assert np.array_equal(dC.to_numpy(np.int32, (M, N)), oracle.tensor_matmul_i8(A, B))
+    ref = oracle.silu(x)
+    assert np.max(np.abs(dy.to_numpy(np.float32, x.shape) - ref)) <= 1e-4 * np.max(np.abs(ref))
+    rec.close()
