@@ -716,6 +716,12 @@ int gemm_i8_run(const void* A, const int8_t* B, int32_t* C, int64_t M, int64_t K
     int bn = BN;
     {
       if (N < BN) bn = int(cdiv(N, 32) * 32);
+      // Small problems (too little work for the K split to pay: measured 11.4 us split vs 8.2 whole at 1024^3) that
+      // fill less than half of the SMs with 256-wide tiles: narrower tiles put more SMs to work and halve the
+      // epilogue per CTA (1024^3: 8.2 us at 256, 6.9 at 128, 6.4 at 64).
+      const int64_t tm1 = cdiv(M, BM);
+      if (n_peers == 0 && M > 256 && tm1 * cdiv(N, BN) * cdiv(K, BK) < int64_t(ctx().sm_count) * 4)
+        while (bn > 64 && tm1 * cdiv(N, bn) * 2 <= ctx().sm_count) bn >>= 1;
       if (const char* env = getenv("SIMP_GEMM_I8_BN")) {
         const int v = atoi(env);
         if (v >= 32 && v <= 256 && v % 32 == 0) bn = v;

@@ -60,11 +60,13 @@ static __global__ void __launch_bounds__(256) w4_pack_x_kernel(const float* __re
                                                                int nchunks, const float* __restrict__ mul,
                                                                float* __restrict__ ss_out) {
   pdl_launch_dependents();
-  pdl_wait();
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  // the norm weights never change: requested before waiting for the producer of x (they miss in L2 once per layer)
+  const float mw = (mul && warp < nchunks) ? __ldg(mul + warp * 32 + lane) : 1.0f;
+  pdl_wait();
   if (warp >= nchunks) return;
   const float v = x[warp * 32 + lane];
-  w4_pack_chunk(mul ? v * mul[warp * 32 + lane] : v, lane, xp + size_t(warp) * (W4_CHUNK_U4 * 16));
+  w4_pack_chunk(mul ? v * mw : v, lane, xp + size_t(warp) * (W4_CHUNK_U4 * 16));
   if (ss_out) {
     const float q = warp_sum(v * v);
     if (lane == 0) ss_out[warp] = q;
