@@ -253,6 +253,11 @@ int simp_dist_shutdown(void);
 int simp_dist_rank(void);
 int simp_dist_world(void);
 int simp_dist_allgather(const void* send_dev, void* recv_dev, size_t bytes_per_rank);
+/* In-place all-gather inside a buffer from simp_dist_symm_alloc, without NCCL: every rank stores its slice
+ * (already at offset + rank * slice) straight into the peers' copies over NVLink and waits, bounded, for theirs.
+ * For kilobyte-sized exchanges (tensor-parallel decode) this costs a launch and one NVLink round trip.
+ * Collective and ordered like the NCCL calls; the first call allocates its flag words (not inside a capture). */
+int simp_dist_allgather_peer(void* symm_local, size_t offset, size_t slice);
 int simp_dist_allreduce_f32(float* buf_dev, size_t count);
 /* N-sharded tensor_matmul on i8: A[M,K] replicated, this rank's column block of B ([K,N_local], or
  * [N_local,K] when b_transposed); C_blocks_dev receives world blocks of M x N_local i32, block r being

@@ -17,6 +17,7 @@
 #include <vector>
 
 #include "common.cuh"
+#include "sm100_ptx.cuh"
 
 namespace simp {
 
@@ -74,6 +75,60 @@ static std::vector<SymmBuf> g_symm;
 
 int gemm_i8_run(const void* A, const int8_t* B, int32_t* C, int64_t M, int64_t K, int64_t N, int a_unsigned,
                 int b_transposed, int32_t* const* peer_c, int n_peers, int64_t ldc, int64_t col_offset);
+
+// ---- peer-store all-gather ---------------------------------------------------------------------
+// In-place all-gather of a small vector that lives in a symmetric buffer: every rank stores its slice straight
+// into the other ranks' copies (plain stores through the CUDA IPC mappings, i.e. over NVLink), publishes a
+// per-source epoch word in each peer's flag array, and waits for the epochs of the other sources.  One block,
+// no NCCL call: for the kilobyte-sized slices of batch-1 decode the cost is a launch plus one NVLink round trip.
+// The wait is bounded (1 s); on expiry the library status word is set and the kernel returns.
+struct LlPeers {
+  uint8_t* buf[8];
+  unsigned* flags[8];
+};
+static unsigned* g_ll_flags = nullptr;   // symmetric: [8] epoch words, written by the peers
+static unsigned* g_ll_seq = nullptr;     // local: epochs issued so far
+
+__device__ __forceinline__ void st_release_sys_u32(unsigned* p, unsigned v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned ld_acquire_sys_u32(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__global__ void __launch_bounds__(256) ll_allgather_kernel(LlPeers peers, unsigned* seq, int rank, int world, size_t offset,
+                                                           size_t slice, int* status) {
+  const unsigned epoch = *seq + 1u;
+  const uint8_t* mine = peers.buf[rank] + offset + size_t(rank) * slice;
+  const bool vec = ((reinterpret_cast<uintptr_t>(mine) | slice) & 15u) == 0;
+  for (int r = 0; r < world; ++r) {
+    if (r == rank) continue;
+    uint8_t* dst = peers.buf[r] + offset + size_t(rank) * slice;
+    if (vec) {
+      for (size_t i = threadIdx.x; i < (slice >> 4); i += blockDim.x)
+        reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(mine)[i];
+    } else {
+      for (size_t i = threadIdx.x; i < slice; i += blockDim.x) dst[i] = mine[i];
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  const int t = threadIdx.x;
+  if (t < world && t != rank) {
+    st_release_sys_u32(peers.flags[t] + rank, epoch);   // "rank's slice of this epoch has landed in t's buffer"
+    const unsigned long long t0 = ptx::globaltimer_ns();
+    for (unsigned spin = 1;; ++spin) {
+      if (int(ld_acquire_sys_u32(peers.flags[rank] + t) - epoch) >= 0) break;
+      if ((spin & 63u) == 0 && ptx::globaltimer_ns() - t0 > 1000000000ull) {
+        if (atomicCAS(status, 0, 1) == 0) status[1] = 90 + t;
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  if (t == 0) *seq = epoch;
+}
 
 }  // namespace simp
 
@@ -188,6 +243,14 @@ SIMP_API int simp_dist_init(int rank, int world, const void* id, size_t bytes) {
 }
 
 SIMP_API int simp_dist_shutdown(void) {
+  if (g_ll_flags) {
+    simp_dist_symm_free(g_ll_flags);
+    g_ll_flags = nullptr;
+  }
+  if (g_ll_seq) {
+    cudaFree(g_ll_seq);
+    g_ll_seq = nullptr;
+  }
   std::lock_guard<std::mutex> lk(g_dist_mu);
   if (g_comm) {
     cudaStreamSynchronize(ctx().stream);
@@ -213,6 +276,44 @@ SIMP_API int simp_dist_allgather(const void* send_dev, void* recv_dev, size_t by
   }
   SIMP_REQUIRE(g_comm != nullptr, SIMP_ERR_STATE, "dist_allgather: call simp_dist_init first");
   SIMP_NCCL(g_nccl.AllGather(send_dev, recv_dev, bytes_per_rank, ncclInt8, g_comm, ctx().stream));
+  return SIMP_OK;
+}
+
+// In-place all-gather inside a symmetric buffer without NCCL: on return (in stream order) the bytes
+// [offset, offset + world * slice) of `symm_local` hold every rank's slice; this rank's slice must already be at
+// offset + rank * slice.  Every rank calls it in the same order.  The first call allocates the flag words
+// (a collective): make it outside stream capture.
+SIMP_API int simp_dist_allgather_peer(void* symm_local, size_t offset, size_t slice) {
+  if (int rc = ensure_ready()) return rc;
+  if (g_world == 1 || slice == 0) return SIMP_OK;
+  const SymmBuf* sb = nullptr;
+  for (const auto& b : g_symm)
+    if (b.local == symm_local) sb = &b;
+  SIMP_REQUIRE(sb != nullptr, SIMP_ERR_ARG, "dist_allgather_peer: buffer must come from simp_dist_symm_alloc");
+  SIMP_REQUIRE(offset + slice * size_t(g_world) <= sb->bytes, SIMP_ERR_SHAPE, "dist_allgather_peer: range outside the buffer");
+  if (!g_ll_flags) {
+    void* f = nullptr;
+    if (int rc = simp_dist_symm_alloc(256, &f)) return rc;
+    SIMP_CUDA(cudaMemsetAsync(f, 0, 256, ctx().stream));
+    SIMP_CUDA(cudaMalloc(&g_ll_seq, 64));
+    SIMP_CUDA(cudaMemsetAsync(g_ll_seq, 0, 64, ctx().stream));
+    g_ll_flags = static_cast<unsigned*>(f);
+    if (int rc = simp_dist_barrier()) return rc;   // every rank's flags are zero before anyone publishes
+    SIMP_CUDA(cudaStreamSynchronize(ctx().stream));
+    for (const auto& b : g_symm)   // g_symm may have been reallocated by the push: look the buffer up again
+      if (b.local == symm_local) sb = &b;
+  }
+  const SymmBuf* fb = nullptr;
+  for (const auto& b : g_symm)
+    if (b.local == g_ll_flags) fb = &b;
+  SIMP_REQUIRE(fb != nullptr, SIMP_ERR_STATE, "dist_allgather_peer: flag buffer missing");
+  LlPeers peers{};
+  for (int r = 0; r < g_world; ++r) {
+    peers.buf[r] = static_cast<uint8_t*>(sb->peer[r]);
+    peers.flags[r] = static_cast<unsigned*>(fb->peer[r]);
+  }
+  ll_allgather_kernel<<<1, 256, 0, ctx().stream>>>(peers, g_ll_seq, g_rank, g_world, offset, slice, ctx().dev_status);
+  SIMP_LAUNCH_CHECK();
   return SIMP_OK;
 }
 

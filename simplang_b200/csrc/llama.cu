@@ -387,6 +387,15 @@ static int enqueue_token_tp(LlamaModel& m, cudaStream_t st) {
   auto pack = [&](const float* x, uint8_t* xp, int n, const float* mul, float* ss, bool pdl) {
     return launch_kernel(w4_pack_x_kernel, dim3((n / 32 + 7) / 8), dim3(256), 0, st, pdl, x, xp, n / 32, mul, ss);
   };
+  // exchange of this rank's slice [rk * n, (rk + 1) * n) of an activation vector: peer stores inside the model's
+  // symmetric arena (default) or an in-place NCCL all-gather (SIMP_TP_ALLGATHER=nccl, or no arena)
+  auto gather = [&](float* vec, int64_t n_per_rank) -> int {
+    if (R == 1) return SIMP_OK;
+    if (m.tp_arena && !m.tp_nccl)
+      return simp_dist_allgather_peer(m.tp_arena, size_t(reinterpret_cast<uint8_t*>(vec) - reinterpret_cast<uint8_t*>(m.tp_arena)),
+                                      size_t(n_per_rank) * 4);
+    return simp_dist_allgather(vec + rk * n_per_rank, vec, size_t(n_per_rank) * 4);
+  };
 #define TP_CUDA(e) do { cudaError_t e__ = (e); if (e__ != cudaSuccess) return set_error(SIMP_ERR_CUDA, "tp decode launch failed: %s", cudaGetErrorString(e__)); } while (0)
   for (int64_t l = 0; l < c.n_layers; ++l) {
     {
@@ -401,7 +410,7 @@ static int enqueue_token_tp(LlamaModel& m, cudaStream_t st) {
                    (const float*)m.q, (const float*)m.k, (const float*)m.v, m.kc, m.vc, m.attn_part, m.attn_cnt,
                    m.xb + rk * dim_l, (const int*)m.ctl, hs, kv_l, int(c.n_heads / c.n_kv_heads), int(c.seq_len), int(l),
                    m.nsplit);
-    if (int rc = simp_dist_allgather(m.xb + rk * dim_l, m.xb, size_t(dim_l) * 4)) return rc;
+    if (int rc = gather(m.xb, dim_l)) return rc;
     TP_CUDA(pack(m.xb, m.xpB, dim, nullptr, nullptr, chain));
     {
       W4Args a = w4args(dim, m.xpB);
@@ -409,7 +418,7 @@ static int enqueue_token_tp(LlamaModel& m, cudaStream_t st) {
       a.nseg = 1; a.res = m.x + rk * dim_l;
       if (int rc = w4_launch<W4_ADD>(a, st, sms, true)) return rc;
     }
-    if (int rc = simp_dist_allgather(m.x + rk * dim_l, m.x, size_t(dim_l) * 4)) return rc;
+    if (int rc = gather(m.x, dim_l)) return rc;
     TP_CUDA(pack(m.x, m.xpA, dim, m.rms_ffn + l * dim, m.ss, chain));
     {
       W4Args g = w4args(dim, m.xpA);
@@ -418,7 +427,7 @@ static int enqueue_token_tp(LlamaModel& m, cudaStream_t st) {
       g.nseg = 2; g.ss_part = m.ss; g.n_ss = n_ss;
       if (int rc = w4_launch<W4_GATE_UP>(g, st, sms, true)) return rc;
     }
-    if (int rc = simp_dist_allgather(m.hb + rk * hd_l, m.hb, size_t(hd_l) * 4)) return rc;
+    if (int rc = gather(m.hb, hd_l)) return rc;
     TP_CUDA(pack(m.hb, m.xpB, hd, nullptr, nullptr, chain));
     {
       W4Args d = w4args(hd, m.xpB);
@@ -426,7 +435,7 @@ static int enqueue_token_tp(LlamaModel& m, cudaStream_t st) {
       d.nseg = 1; d.res = m.x + rk * dim_l;
       if (int rc = w4_launch<W4_ADD>(d, st, sms, true)) return rc;
     }
-    if (int rc = simp_dist_allgather(m.x + rk * dim_l, m.x, size_t(dim_l) * 4)) return rc;
+    if (int rc = gather(m.x, dim_l)) return rc;
     if (l + 1 < c.n_layers) TP_CUDA(pack(m.x, m.xpA, dim, m.rms_att + (l + 1) * dim, m.ss, chain));
   }
   LAUNCH_OR_FAIL(dec_rmsnorm_kernel, dim3(1), dim3(1024), 0, st, chain, (const float*)m.x, (const float*)m.rms_final,
@@ -437,7 +446,7 @@ static int enqueue_token_tp(LlamaModel& m, cudaStream_t st) {
     g.nseg = 1; g.k4 = dim / 4; g.x = m.xb;
     if (int rc = gemv_f32_launch<GEMV_STORE>(g, st, sms)) return rc;
   }
-  if (int rc = simp_dist_allgather(m.logits + int64_t(rk) * V_l, m.logits, size_t(V_l) * 4)) return rc;
+  if (int rc = gather(m.logits, V_l)) return rc;
   LAUNCH_OR_FAIL(argmax_advance_kernel, dim3(1), dim3(1024), 0, st, false, (const float*)m.logits, int(c.vocab_size),
                  m.ctl, (const int32_t*)m.prompt, m.out_tokens);
 #undef TP_CUDA
@@ -516,9 +525,29 @@ SIMP_API int simp_llama_create(const simp_llama_config* cfg, void** model) {
   int rc = SIMP_OK;
   auto A = [&](void** p, size_t n) { if (rc == SIMP_OK) rc = dev_alloc(p, n); };
   const size_t mx = size_t(c.dim > c.hidden_dim ? c.dim : c.hidden_dim);
-  A((void**)&m->x, c.dim * 4); A((void**)&m->xb, mx * 4); A((void**)&m->hb, c.hidden_dim * 4);
+  if (tp > 1) {
+    // the exchanged vectors (x, xb, hb, logits) live in one symmetric arena so that ranks can store their slices
+    // straight into each other's copies
+    auto al = [](size_t v) { return (v + 255) & ~size_t(255); };
+    const size_t o_xb = al(size_t(c.dim) * 4), o_hb = o_xb + al(mx * 4), o_lg = o_hb + al(size_t(c.hidden_dim) * 4);
+    const size_t total = o_lg + al(size_t(c.vocab_size) * 4);
+    const char* e = getenv("SIMP_TP_ALLGATHER");
+    m->tp_nccl = e && !strcmp(e, "nccl");
+    if (rc == SIMP_OK) rc = simp_dist_symm_alloc(total, &m->tp_arena);
+    if (rc == SIMP_OK) {
+      uint8_t* base = static_cast<uint8_t*>(m->tp_arena);
+      m->x = reinterpret_cast<float*>(base);
+      m->xb = reinterpret_cast<float*>(base + o_xb);
+      m->hb = reinterpret_cast<float*>(base + o_hb);
+      m->logits = reinterpret_cast<float*>(base + o_lg);
+      // first use of the peer exchange allocates its flag words (a collective): do it here, outside any capture
+      if (!m->tp_nccl) rc = simp_dist_allgather_peer(m->tp_arena, 0, 16);
+    }
+  } else {
+    A((void**)&m->x, c.dim * 4); A((void**)&m->xb, mx * 4); A((void**)&m->hb, c.hidden_dim * 4);
+  }
   A((void**)&m->q, c.dim * 4); A((void**)&m->k, m->kv_dim * 4); A((void**)&m->v, m->kv_dim * 4);
-  A((void**)&m->logits, c.vocab_size * 4);
+  if (tp == 1) A((void**)&m->logits, c.vocab_size * 4);
   const size_t kv_bytes = size_t(c.n_layers) * c.seq_len * (m->kv_dim / tp) * 4;  // this rank's heads only
   A((void**)&m->kc, kv_bytes);
   A((void**)&m->vc, kv_bytes);
@@ -721,6 +750,10 @@ SIMP_API int simp_llama_destroy(void* model) {
   LlamaModel* m = static_cast<LlamaModel*>(model);
   if (ctx().ready) cudaStreamSynchronize(ctx().stream);
   if (m->graph) cudaGraphExecDestroy(m->graph);
+  if (m->tp_arena) {   // x, xb, hb and logits live inside the symmetric arena
+    simp_dist_symm_free(m->tp_arena);
+    m->x = m->xb = m->hb = m->logits = nullptr;
+  }
   void* ptrs[] = {m->tok_emb, m->rms_att, m->rms_ffn, m->rms_final, m->wcls, m->wq, m->wk, m->wv, m->wo, m->w1, m->w2,
                   m->w3, m->qweights, m->scales, m->zeros, m->x, m->xb, m->hb, m->q, m->k, m->v, m->logits, m->kc,
                   m->vc, m->attn_part, m->attn_cnt, m->xpA, m->xpB, m->ss, m->ctl, m->prompt, m->out_tokens,

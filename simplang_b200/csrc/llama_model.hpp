@@ -20,6 +20,8 @@ struct LlamaModel {
   int64_t loff[7] = {0, 0, 0, 0, 0, 0, 0};  // the same for the device copy (differs under tensor parallelism)
   bool offsets_set = false;
   int tp = 1, rank = 0;                      // tensor-parallel degree and this rank
+  void* tp_arena = nullptr;                  // tp > 1: symmetric buffer holding x | xb | hb | logits (peer-store exchange)
+  bool tp_nccl = false;                      // tp > 1: exchange with NCCL all-gathers instead
   // state (device)
   float *x = nullptr, *xb = nullptr, *hb = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *logits = nullptr;
   float *kc = nullptr, *vc = nullptr, *attn_part = nullptr;
