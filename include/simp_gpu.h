@@ -76,6 +76,13 @@ int simp_gpu_matmul_f32(const float* A_dev, int64_t aoff, const float* B_dev, in
 int simp_gpu_matmul_i8(const void* A_dev, const int8_t* B_dev, int32_t* C_dev, int64_t M,
                        int64_t K, int64_t N, int a_unsigned, int b_transposed);
 
+/* tensor_matmul on packed signed i4 operands, fresh i16 result.
+ * Replaces: TensorMatMulOpLowering, packed-i4 branch (src/mlir/lowering/ConvertSimpToMemRef.cpp:2953-3133;
+ * timed by simptensor/benchmarks/bench_int4_matmul.sl:16-47).  Two 4-bit two's-complement values per byte along
+ * the LAST dimension of each operand, low nibble = even index: A is [M, ceil(K/2)] bytes, B is [K, ceil(N/2)]
+ * bytes; C[i,j] = low 16 bits of sum_k a[i,k] * b[k,j] (the i32 sum is exact), row-major [M, N]. */
+int simp_gpu_matmul_i4(const uint8_t* A_packed, const uint8_t* B_packed, int16_t* C, int64_t M, int64_t K, int64_t N);
+
 /* ---- matmul_quant / dequant_w4 (W4) --------------------------------------------------------
  * out[rows] = W4[rows,cols] . x[cols]; nibbles packed two per byte, low nibble = even flat index,
  * w = q*scale + zero (MatMulQuantOpLowering, ConvertSimpToMemRef.cpp:3853-4013;

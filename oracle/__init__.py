@@ -158,6 +158,39 @@ def dequantize_i32(acc, divisor=65536.0):
     return y
 
 
+def pack_i4(values):
+    """[rows, cols] integers in [-8, 7] -> [rows, ceil(cols / 2)] bytes, low nibble = even column."""
+    v = np.asarray(values)
+    rows, cols = v.shape
+    n = (v.astype(np.int64) & 15).astype(np.uint8)
+    if cols & 1:
+        n = np.concatenate([n, np.zeros((rows, 1), np.uint8)], axis=1)
+    return np.ascontiguousarray(n[:, 0::2] | (n[:, 1::2] << 4))
+
+
+def tensor_matmul_i4(A_packed, B_packed, M, K, N, threads=0):
+    """Packed signed i4 x i4 -> i16 (wrapping): A [M, ceil(K/2)] bytes, B [K, ceil(N/2)] bytes."""
+    A_packed = np.ascontiguousarray(A_packed, np.uint8)
+    B_packed = np.ascontiguousarray(B_packed, np.uint8)
+    out = np.empty((M, N), np.int16)
+    f = lib().simp_oracle_tensor_matmul_i4
+    f.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, i64, i64, i64, C.c_int32]
+    f.restype = None
+    f(_ptr(A_packed), _ptr(B_packed), _ptr(out), M, K, N, threads if threads > 0 else lib().simp_oracle_max_threads())
+    return out
+
+
+def ref_int4_checksums(N):
+    """(scalar, packed) checksums of the reference's own i4 runner code, or None when oracle/_ref is absent."""
+    L = ref("int4runner")
+    if L is None:
+        return None
+    a, b = C.c_int32(), C.c_int32()
+    if L.simp_ref_int4_checksums(N, C.byref(a), C.byref(b)) != 0:
+        raise ValueError(f"size {N} not instantiated")
+    return int(a.value), int(b.value)
+
+
 def argmax(v):
     return int(lib().simp_oracle_argmax(v, v.size))
 

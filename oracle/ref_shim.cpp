@@ -15,6 +15,8 @@
 //                        -> scalar_vpdpbusd_reference / vnni_vpdpbusd (:28-59) and its 9 tests
 //   REF_UNIT_OMPRUNNER : simptensor/benchmarks/bench_int8_matmul_omp_runner.cpp
 //                        -> scalar_matmul_checksum() (:36-64)
+//   REF_UNIT_INT4RUNNER: simptensor/benchmarks/bench_int4_matmul_runner.cpp
+//                        -> scalar_matmul_int4<N>() (:34-68), packed_matmul_int4<N>() (:74-148)
 #include <cstdint>
 #define REF_API extern "C" __attribute__((visibility("default")))
 
@@ -83,4 +85,20 @@ REF_API int simp_ref_vnni_selftest() { return simp_ref_vnnitest_main(); }
 #undef main
 // Checksum of the scalar s8 x s8 product on the ((i*N+j)%127)-64 fill, N = 1024.
 REF_API int32_t simp_ref_scalar_checksum_1024() { return scalar_matmul_checksum(); }
+#endif
+
+#if defined(REF_UNIT_INT4RUNNER)
+#define main simp_ref_int4runner_main
+#include "simptensor/benchmarks/bench_int4_matmul_runner.cpp"
+#undef main
+// Checksums of the i4 x i4 -> i16 product on the ((i*N+j)%15)-7 fill (B[j,i] = A[i,j]): the scalar reference and
+// the packed-storage reference of the runner.  Returns 0 and writes both, or -1 for a size it does not instantiate.
+REF_API int simp_ref_int4_checksums(int N, int32_t* scalar, int32_t* packed) {
+#define REF_CASE(n) case n: *scalar = scalar_matmul_int4<n>(); *packed = packed_matmul_int4<n>(); return 0;
+  switch (N) {
+    REF_CASE(32) REF_CASE(64) REF_CASE(128) REF_CASE(256) REF_CASE(384) REF_CASE(512) REF_CASE(768) REF_CASE(1024)
+    default: return -1;
+  }
+#undef REF_CASE
+}
 #endif

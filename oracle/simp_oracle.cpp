@@ -669,3 +669,31 @@ ORACLE_API void simp_oracle_llama_i8_prefill(const SimpOracleLlamaI8* mp, const 
     for (int64_t i = 0; i < S * dim; ++i) x_fp32[i] = x_fp32[i] + float(Down[i]) * 1.0f / 65536.0f;
   }
 }
+
+// ---------------------------------------------------------------------------
+// tensor_matmul on packed i4 (TensorMatMulOpLowering, packed-i4 branch,
+// src/mlir/lowering/ConvertSimpToMemRef.cpp:2953-3133): operands hold two signed 4-bit values per byte along
+// their LAST dimension (low nibble = even index; A is [M, K/2] bytes, B is [K, N/2] bytes); both are unpacked
+// with sign extension, C[i, j] = (i16) trunc( sum_k (i32) a[i,k] * b[k,j] ), a fresh [M, N] i16 result.
+// Pinned by the reference's runner: scalar_matmul_int4<N> / packed_matmul_int4<N> checksums on the
+// ((i*N+j)%15)-7 fill (simptensor/benchmarks/bench_int4_matmul_runner.cpp:34-148; the .sl kernels being timed are
+// simptensor/benchmarks/bench_int4_matmul.sl:16-47).
+// ---------------------------------------------------------------------------
+namespace {
+inline int32_t nibble_s4(uint8_t byte, int64_t idx) {
+  const int32_t n = (idx & 1) ? (byte >> 4) & 15 : byte & 15;
+  return n >= 8 ? n - 16 : n;
+}
+}  // namespace
+ORACLE_API void simp_oracle_tensor_matmul_i4(const uint8_t* A, const uint8_t* B, int16_t* C, int64_t M,
+                                             int64_t K, int64_t N, int threads) {
+  const int nt = clamp_threads(threads);
+  const int64_t ak = (K + 1) / 2, bn = (N + 1) / 2;
+#pragma omp parallel for num_threads(nt) schedule(static) if (nt > 1)
+  for (int64_t i = 0; i < M; ++i)
+    for (int64_t j = 0; j < N; ++j) {
+      int32_t acc = 0;
+      for (int64_t k = 0; k < K; ++k) acc += nibble_s4(A[i * ak + (k >> 1)], k) * nibble_s4(B[k * bn + (j >> 1)], j);
+      C[i * N + j] = int16_t(uint16_t(uint32_t(acc) & 0xffffu));
+    }
+}

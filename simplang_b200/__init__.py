@@ -61,6 +61,7 @@ _SIGNATURES = {
     "simp_host_rmsnorm_f32": [vp, vp, vp, i64, i64, C.c_float, i64],
     "simp_host_softmax_f32": [vp, vp, i64, i64, i64, i64, i64],
     "simp_host_silu_f32": [vp, vp, vp, i64],
+    "simp_gpu_matmul_i4": [vp, vp, vp, i64, i64, i64],
     "simp_gpu_record_begin": [],
     "simp_gpu_record_end": [C.POINTER(vp)],
     "simp_gpu_replay": [vp, i64],
@@ -289,6 +290,15 @@ def host_tensor_matmul_i8(A: np.ndarray, B: np.ndarray, out: np.ndarray = None, 
 
 
 # ------------------------------------------------------------------------- LLaMA decode driver
+def np_matmul_i4(A_packed: np.ndarray, B_packed: np.ndarray, M: int, K: int, N: int) -> np.ndarray:
+    """Packed signed i4 x i4 -> i16 (numpy in / out): A [M, ceil(K/2)] bytes, B [K, ceil(N/2)] bytes."""
+    dA = DeviceBuffer.from_numpy(np.ascontiguousarray(A_packed, np.uint8))
+    dB = DeviceBuffer.from_numpy(np.ascontiguousarray(B_packed, np.uint8))
+    dC = DeviceBuffer(max(M * N * 2, 16))
+    check(lib().simp_gpu_matmul_i4(dA.ptr, dB.ptr, dC.ptr, M, K, N))
+    return dC.to_numpy(np.int16, (M, N))
+
+
 class Recording:
     """``with Recording() as r: <device-pointer calls>`` records the calls; ``r.replay(n)`` enqueues them n times."""
 

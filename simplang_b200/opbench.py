@@ -2,7 +2,7 @@
 int8 GEMM at the configured shapes.  Prints one JSON line per case with the achieved GB/s (or TOPS), the
 algorithmic bytes used, and the fraction of the measured roofline.
 
-    python -m simplang_b200.opbench [--iters 50] [--only gemv_f32,w4,rowops,gemm_i8,mma_peak,decode110m,decode3b,decode_i8,prefill_i8]
+    python -m simplang_b200.opbench [--iters 50] [--only gemv_f32,w4,rowops,gemm_i8,gemm_i4,mma_peak,decode110m,decode3b,decode_i8,prefill_i8]
 
 Each case rotates over enough independent operand copies that the working set exceeds twice the
 126 MB L2, so every iteration streams from HBM the way consecutive layers of a decode step do.
@@ -183,6 +183,31 @@ def bench_mma_peak(iters):
                       "full_over_mma_only": round(out["full"] / out["mma"], 4)}), flush=True)
 
 
+def bench_gemm_i4(iters):
+    """Packed i4 x i4 -> i16 tensor_matmul at the sizes of the reference's benchmark (bench_int4_matmul.sl: 32 ... 1024)."""
+    rng = np.random.default_rng(4)
+    for n in (32, 64, 128, 256, 384, 512, 768, 1024, 4096):
+        A = sg.DeviceBuffer.from_numpy(rng.integers(0, 256, (n, n // 2), dtype=np.uint8))
+        B = sg.DeviceBuffer.from_numpy(rng.integers(0, 256, (n, n // 2), dtype=np.uint8))
+        Cd = sg.DeviceBuffer(n * n * 2)
+        call = lambda i: sg.check(sg.lib().simp_gpu_matmul_i4(A.ptr, B.ptr, Cd.ptr, n, n, n))
+        ms = timed(call, 1, iters)
+        with sg.Recording() as rec:
+            for _ in range(10):
+                call(0)
+        rec.replay(1)
+        sg.sync()
+        e0, e1 = sg.Event(), sg.Event()
+        e0.record()
+        rec.replay(5)
+        e1.record()
+        sg.sync()
+        ms_r = e0.elapsed_ms(e1) / 50
+        rec.close()
+        print(json.dumps({"op": "gemm_i4", "n": n, "us": round(ms * 1e3, 2), "us_replayed": round(ms_r * 1e3, 2),
+                          "giops_replayed": round(2.0 * n ** 3 / (ms_r * 1e-3) / 1e9, 1)}), flush=True)
+
+
 def bench_decode(which, n_new=128):
     """Greedy decode tokens/s of the two model configurations (random init), device-timed over the
     whole generation (prompt of 16 teacher-forced tokens + n_new generated)."""
@@ -297,6 +322,8 @@ def main():
         bench_rowops(args.iters)
     if "gemm_i8" in which:
         bench_gemm_i8(args.iters)
+    if "gemm_i4" in which:
+        bench_gemm_i4(args.iters)
     if "mma_peak" in which:
         bench_mma_peak(args.iters)
     if "decode110m" in which:

@@ -70,6 +70,13 @@ def main():
         C = oracle.ref_vnni_mnk(A, Bt, threads=1)
         g["ref_int8"].append({"kernel": "vnni_matmul_i8 (bench_qkv_only_runner.cpp:43-70)", "M": M, "N": N, "K": K,
                               "seed": M * 1000 + K, "sha256": digest(C), "checksum": oracle.checksum_i32(C)})
+    # reference's own i4 x i4 -> i16 references on the ((i*N+j)%15)-7 fill (bench_int4_matmul_runner.cpp:34-148)
+    g["int4_fill_checksums"] = {"src": "simptensor/benchmarks/bench_int4_matmul_runner.cpp:34-148 "
+                                       "(scalar_matmul_int4<N>, packed_matmul_int4<N>)", "values": {}}
+    for n in (32, 64, 128, 256, 384, 512, 768, 1024):
+        sc, pk = oracle.ref_int4_checksums(n)
+        assert sc == pk
+        g["int4_fill_checksums"]["values"][str(n)] = sc
     with open(os.path.join(HERE, "golden.json"), "w") as f:
         json.dump(g, f, indent=1)
     print("wrote golden.json")

@@ -219,3 +219,35 @@ def test_llama_i8_oracle_against_numpy_restatement():
             assert np.max(np.abs(logits - ref)) <= 1e-4 * np.max(np.abs(ref)) + 1e-12, (style, pos)
             # the int8 caches of both restatements must be identical
             assert np.array_equal(om.k_cache.reshape(kc.shape), kc) and np.array_equal(om.v_cache.reshape(vc.shape), vc)
+
+
+def test_tensor_matmul_i4_fill_checksums():
+    """Packed-i4 tensor_matmul oracle against the checksums of the reference's own scalar and packed i4
+    references on its deterministic fill (bench_int4_matmul_runner.cpp:34-148), stored in golden.json, and
+    against the compiled reference itself when oracle/_ref is present."""
+    import json
+    import os
+    import oracle
+    g = json.load(open(os.path.join(os.path.dirname(__file__), "golden", "golden.json")))["int4_fill_checksums"]["values"]
+    for n_s, expect in g.items():
+        n = int(n_s)
+        if n > 512:
+            continue   # the plain-loop oracle is O(n^3); larger sizes are covered on the GPU
+        i, j = np.meshgrid(np.arange(n), np.arange(n), indexing="ij")
+        A = ((i * n + j) % 15) - 7
+        Cm = oracle.tensor_matmul_i4(oracle.pack_i4(A), oracle.pack_i4(A.T.copy()), n, n, n)
+        assert int(np.sum(Cm.astype(np.int64))) == expect, n
+        live = oracle.ref_int4_checksums(n)
+        if live is not None:
+            assert live == (expect, expect)
+
+
+def test_tensor_matmul_i4_against_numpy():
+    import oracle
+    rng = np.random.default_rng(4)
+    for (M, K, N) in ((1, 1, 1), (3, 5, 7), (16, 33, 18), (40, 64, 24)):
+        A = rng.integers(-8, 8, (M, K))
+        B = rng.integers(-8, 8, (K, N))
+        ref = (A @ B).astype(np.int64)
+        out = oracle.tensor_matmul_i4(oracle.pack_i4(A), oracle.pack_i4(B), M, K, N)
+        assert np.array_equal(out, ref.astype(np.int16))
