@@ -83,6 +83,15 @@ int simp_gpu_matmul_i8(const void* A_dev, const int8_t* B_dev, int32_t* C_dev, i
  * bytes; C[i,j] = low 16 bits of sum_k a[i,k] * b[k,j] (the i32 sum is exact), row-major [M, N]. */
 int simp_gpu_matmul_i4(const uint8_t* A_packed, const uint8_t* B_packed, int16_t* C, int64_t M, int64_t K, int64_t N);
 
+/* tensor_gather: result[..., n, ...] = source[..., indices[n], ...] along one axis.
+ * Replaces: TensorGatherOpLowering (src/mlir/lowering/ConvertSimpToMemRef.cpp:2625-2776).  The source is passed as
+ * its [outer, axis_dim, inner] view (outer = product of the dimensions before the axis, inner = product of those
+ * after it), elements are opaque (elem_size bytes), indices are i64 on the device.  An index outside
+ * [0, axis_dim) is undefined in the reference; here that row is skipped and simp_gpu_check_device_status()
+ * reports it. */
+int simp_gpu_tensor_gather(const void* src_dev, const int64_t* indices_dev, void* dst_dev, int64_t outer,
+                           int64_t axis_dim, int64_t inner, int64_t n_idx, int64_t elem_size);
+
 /* ---- matmul_quant / dequant_w4 (W4) --------------------------------------------------------
  * out[rows] = W4[rows,cols] . x[cols]; nibbles packed two per byte, low nibble = even flat index,
  * w = q*scale + zero (MatMulQuantOpLowering, ConvertSimpToMemRef.cpp:3853-4013;

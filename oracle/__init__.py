@@ -191,6 +191,23 @@ def ref_int4_checksums(N):
     return int(a.value), int(b.value)
 
 
+def tensor_gather(source, indices, axis=0):
+    """tensor_gather on a numpy array of any rank and dtype; indices are int64."""
+    source = np.ascontiguousarray(source)
+    indices = np.ascontiguousarray(indices, np.int64)
+    axis = axis + source.ndim if axis < 0 else axis
+    shape = source.shape
+    outer = int(np.prod(shape[:axis], dtype=np.int64))
+    inner = int(np.prod(shape[axis + 1:], dtype=np.int64))
+    out = np.empty(shape[:axis] + (indices.size,) + shape[axis + 1:], source.dtype)
+    f = lib().simp_oracle_tensor_gather
+    f.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, i64, i64, i64, i64, i64]
+    f.restype = C.c_int
+    if f(_ptr(source), _ptr(indices), _ptr(out), outer, shape[axis], inner, indices.size, source.dtype.itemsize) != 0:
+        raise IndexError("gather index out of range")
+    return out
+
+
 def argmax(v):
     return int(lib().simp_oracle_argmax(v, v.size))
 

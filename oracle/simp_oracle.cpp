@@ -697,3 +697,22 @@ ORACLE_API void simp_oracle_tensor_matmul_i4(const uint8_t* A, const uint8_t* B,
       C[i * N + j] = int16_t(uint16_t(uint32_t(acc) & 0xffffu));
     }
 }
+
+// ---------------------------------------------------------------------------
+// tensor_gather (TensorGatherOpLowering, src/mlir/lowering/ConvertSimpToMemRef.cpp:2625-2776):
+//   result[..., n, ...] = source[..., indices[n], ...] along `axis`; indices are i64; every other dimension is
+//   copied whole.  With the source viewed as [outer, axis_dim, inner] this is dst[o, n, :] = src[o, indices[n], :].
+// Elements are opaque (elem_size bytes).  Pinned by simptensor/tests/test_scatter_gather.sl:8-147 (eight known
+// answers, expected values in test_scatter_gather_host.cpp:61-68).
+// ---------------------------------------------------------------------------
+ORACLE_API int simp_oracle_tensor_gather(const uint8_t* src, const int64_t* indices, uint8_t* dst, int64_t outer,
+                                         int64_t axis_dim, int64_t inner, int64_t n_idx, int64_t elem_size) {
+  const int64_t row = inner * elem_size;
+  for (int64_t o = 0; o < outer; ++o)
+    for (int64_t n = 0; n < n_idx; ++n) {
+      const int64_t s = indices[n];
+      if (s < 0 || s >= axis_dim) return -1;   // the reference leaves this undefined
+      std::memcpy(dst + (o * n_idx + n) * row, src + (o * axis_dim + s) * row, size_t(row));
+    }
+  return 0;
+}

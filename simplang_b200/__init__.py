@@ -62,6 +62,7 @@ _SIGNATURES = {
     "simp_host_softmax_f32": [vp, vp, i64, i64, i64, i64, i64],
     "simp_host_silu_f32": [vp, vp, vp, i64],
     "simp_gpu_matmul_i4": [vp, vp, vp, i64, i64, i64],
+    "simp_gpu_tensor_gather": [vp, vp, vp, i64, i64, i64, i64, i64],
     "simp_gpu_record_begin": [],
     "simp_gpu_record_end": [C.POINTER(vp)],
     "simp_gpu_replay": [vp, i64],
@@ -297,6 +298,23 @@ def np_matmul_i4(A_packed: np.ndarray, B_packed: np.ndarray, M: int, K: int, N: 
     dC = DeviceBuffer(max(M * N * 2, 16))
     check(lib().simp_gpu_matmul_i4(dA.ptr, dB.ptr, dC.ptr, M, K, N))
     return dC.to_numpy(np.int16, (M, N))
+
+
+def np_tensor_gather(source: np.ndarray, indices, axis: int = 0) -> np.ndarray:
+    """tensor_gather on a numpy array of any rank and dtype (numpy in / out)."""
+    source = np.ascontiguousarray(source)
+    indices = np.ascontiguousarray(indices, np.int64)
+    axis = axis + source.ndim if axis < 0 else axis
+    shape = source.shape
+    outer = int(np.prod(shape[:axis], dtype=np.int64))
+    inner = int(np.prod(shape[axis + 1:], dtype=np.int64))
+    out_shape = shape[:axis] + (indices.size,) + shape[axis + 1:]
+    dS, dI = DeviceBuffer.from_numpy(source), DeviceBuffer.from_numpy(indices)
+    nbytes = int(np.prod(out_shape, dtype=np.int64)) * source.dtype.itemsize
+    dD = DeviceBuffer(max(nbytes, 16))
+    check(lib().simp_gpu_tensor_gather(dS.ptr, dI.ptr, dD.ptr, outer, shape[axis], inner, indices.size, source.dtype.itemsize))
+    check(lib().simp_gpu_check_device_status())
+    return dD.to_numpy(source.dtype, out_shape)
 
 
 class Recording:

@@ -361,3 +361,44 @@ SIMP_API int simp_gpu_dequant_w4(const uint8_t* qw, const float* sc, const float
   SIMP_LAUNCH_CHECK();
   return SIMP_OK;
 }
+
+// ---- tensor_gather ------------------------------------------------------------------------------
+// dst[o, n, :] = src[o, indices[n], :] over rows of `row_bytes` bytes (TensorGatherOpLowering,
+// ConvertSimpToMemRef.cpp:2625-2776, with the source viewed as [outer, axis_dim, inner]).  One block per
+// (o, n) row, 16-byte pieces when both rows are 16-byte aligned.  An index outside [0, axis_dim) -- undefined in
+// the reference -- copies nothing and raises the device status word.
+namespace simp {
+__global__ void __launch_bounds__(256) gather_rows_kernel(const uint8_t* __restrict__ src, const int64_t* __restrict__ indices,
+                                                          uint8_t* __restrict__ dst, int64_t axis_dim, int64_t n_idx,
+                                                          int64_t row_bytes, int* status) {
+  const int64_t o = blockIdx.y, n = blockIdx.x;
+  const int64_t s = indices[n];
+  if (s < 0 || s >= axis_dim) {
+    if (threadIdx.x == 0 && atomicCAS(status, 0, 2) == 0) status[1] = int(n);
+    return;
+  }
+  const uint8_t* from = src + (o * axis_dim + s) * row_bytes;
+  uint8_t* to = dst + (o * n_idx + n) * row_bytes;
+  if ((((reinterpret_cast<uintptr_t>(from) | reinterpret_cast<uintptr_t>(to)) | uintptr_t(row_bytes)) & 15u) == 0) {
+    for (int64_t i = threadIdx.x; i < (row_bytes >> 4); i += blockDim.x)
+      reinterpret_cast<uint4*>(to)[i] = reinterpret_cast<const uint4*>(from)[i];
+  } else {
+    for (int64_t i = threadIdx.x; i < row_bytes; i += blockDim.x) to[i] = from[i];
+  }
+}
+}  // namespace simp
+
+SIMP_API int simp_gpu_tensor_gather(const void* src_dev, const int64_t* indices_dev, void* dst_dev, int64_t outer,
+                                    int64_t axis_dim, int64_t inner, int64_t n_idx, int64_t elem_size) {
+  if (int rc = simp::ensure_ready()) return rc;
+  SIMP_REQUIRE(outer >= 0 && axis_dim >= 0 && inner >= 0 && n_idx >= 0 && elem_size > 0, SIMP_ERR_ARG,
+               "tensor_gather: negative size");
+  if (outer == 0 || n_idx == 0 || inner == 0) return SIMP_OK;
+  SIMP_REQUIRE(src_dev && indices_dev && dst_dev, SIMP_ERR_ARG, "tensor_gather: null pointer");
+  SIMP_REQUIRE(outer <= 65535 && n_idx <= 0x7fffffff, SIMP_ERR_SHAPE, "tensor_gather: outer extent above 65535");
+  simp::gather_rows_kernel<<<dim3(unsigned(n_idx), unsigned(outer)), 256, 0, simp::ctx().stream>>>(
+      static_cast<const uint8_t*>(src_dev), indices_dev, static_cast<uint8_t*>(dst_dev), axis_dim, n_idx, inner * elem_size,
+      simp::ctx().dev_status);
+  SIMP_LAUNCH_CHECK();
+  return SIMP_OK;
+}

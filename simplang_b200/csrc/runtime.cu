@@ -175,6 +175,8 @@ SIMP_API int simp_gpu_check_device_status(void) {
   if (g_ctx.host_status[0] != 0) {
     const int code = g_ctx.host_status[0], where = g_ctx.host_status[1];
     cudaMemsetAsync(g_ctx.dev_status, 0, 16, g_ctx.stream);
+    if (code == 2)   // raised by tensor_gather: an index outside the gathered axis
+      return set_error(SIMP_ERR_ARG, "tensor_gather: index %d is outside the gathered axis (row skipped)", where);
     return set_error(SIMP_ERR_TIMEOUT, "a bounded device-side wait gave up (code %d, site %d)", code,
                      where);
   }

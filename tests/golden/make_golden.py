@@ -70,6 +70,28 @@ def main():
         C = oracle.ref_vnni_mnk(A, Bt, threads=1)
         g["ref_int8"].append({"kernel": "vnni_matmul_i8 (bench_qkv_only_runner.cpp:43-70)", "M": M, "N": N, "K": K,
                               "seed": M * 1000 + K, "sha256": digest(C), "checksum": oracle.checksum_i32(C)})
+    # tensor_gather known answers (simptensor/tests/test_scatter_gather.sl:8-147; expected values in
+    # simptensor/tests/test_scatter_gather_host.cpp:61-68): source = 1..n in row-major order unless given
+    def seq(*shape):
+        return (np.arange(int(np.prod(shape))) + 1.0).reshape(shape).tolist()
+    g["gather_known_answers"] = [
+        {"src": "test_scatter_gather.sl:9-15", "source": [float(v) for v in range(10)], "indices": [0, 3, 7, 2], "axis": 0,
+         "sum_at": [[0], [1], [2], [3]], "expect": 12.0},
+        {"src": "test_scatter_gather.sl:18-24", "source": [10.0 * (v + 1) for v in range(8)], "indices": [7, 2, 0], "axis": 0,
+         "sum_at": [[0], [1], [2]], "expect": 120.0},
+        {"src": "test_scatter_gather.sl:27-42", "source": seq(5, 3), "indices": [4, 1, 0], "axis": 0,
+         "sum_at": [[0, 0], [1, 1], [2, 2]], "expect": 21.0},
+        {"src": "test_scatter_gather.sl:45-58", "source": seq(3, 5), "indices": [4, 1], "axis": 1,
+         "sum_at": [[0, 0], [1, 1], [2, 0]], "expect": 27.0},
+        {"src": "test_scatter_gather.sl:61-80", "source": seq(4, 2, 3), "indices": [3, 0], "axis": 0,
+         "sum_at": [[0, 0, 0], [1, 1, 2]], "expect": 25.0},
+        {"src": "test_scatter_gather.sl:83-100", "source": seq(2, 4, 3), "indices": [3, 0], "axis": 1,
+         "sum_at": [[0, 0, 0], [1, 1, 2]], "expect": 25.0},
+        {"src": "test_scatter_gather.sl:103-118", "source": seq(2, 3, 5), "indices": [4, 1, 0], "axis": 2,
+         "sum_at": [[0, 0, 0], [1, 2, 1]], "expect": 32.0},
+        {"src": "test_scatter_gather.sl:121-147", "source": seq(2, 2, 3, 4), "indices": [2, 0], "axis": 2,
+         "sum_at": [[0, 0, 0, 0], [1, 1, 1, 3]], "expect": 49.0},
+    ]
     # reference's own i4 x i4 -> i16 references on the ((i*N+j)%15)-7 fill (bench_int4_matmul_runner.cpp:34-148)
     g["int4_fill_checksums"] = {"src": "simptensor/benchmarks/bench_int4_matmul_runner.cpp:34-148 "
                                        "(scalar_matmul_int4<N>, packed_matmul_int4<N>)", "values": {}}

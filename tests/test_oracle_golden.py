@@ -251,3 +251,25 @@ def test_tensor_matmul_i4_against_numpy():
         ref = (A @ B).astype(np.int64)
         out = oracle.tensor_matmul_i4(oracle.pack_i4(A), oracle.pack_i4(B), M, K, N)
         assert np.array_equal(out, ref.astype(np.int16))
+
+
+def _gather_cases():
+    import json
+    import os
+    return json.load(open(os.path.join(os.path.dirname(__file__), "golden", "golden.json")))["gather_known_answers"]
+
+
+def test_tensor_gather_known_answers():
+    """tensor_gather oracle against the reference's eight known answers (test_scatter_gather.sl / _host.cpp)
+    and against numpy.take on random shapes, dtypes and axes."""
+    import oracle
+    for case in _gather_cases():
+        out = oracle.tensor_gather(np.array(case["source"], np.float32), case["indices"], case["axis"])
+        assert sum(float(out[tuple(ix)]) for ix in case["sum_at"]) == case["expect"], case["src"]
+    rng = np.random.default_rng(8)
+    for shape, axis, dt in (((7,), 0, np.float32), ((5, 9), 1, np.int8), ((3, 4, 6), -2, np.float64), ((2, 3, 4, 5), 3, np.int32)):
+        src = rng.integers(-100, 100, shape).astype(dt)
+        idx = rng.integers(0, shape[axis], 11)
+        assert np.array_equal(oracle.tensor_gather(src, idx, axis), np.take(src, idx, axis=axis))
+    with pytest.raises(IndexError):
+        oracle.tensor_gather(np.zeros(4, np.float32), [4], 0)
