@@ -92,6 +92,15 @@ int simp_gpu_matmul_i4(const uint8_t* A_packed, const uint8_t* B_packed, int16_t
 int simp_gpu_tensor_gather(const void* src_dev, const int64_t* indices_dev, void* dst_dev, int64_t outer,
                            int64_t axis_dim, int64_t inner, int64_t n_idx, int64_t elem_size);
 
+/* conv2d on f32: NHWC input, weights [OC, KH, KW, IC], bias [OC], NHWC output (caller-allocated,
+ * out_h = (in_h + 2*pad_h - kernel_h) / stride_h + 1, same for w), zero padding.
+ * Replaces: Conv2DOpLowering (src/mlir/lowering/ConvertSimpToMemRef.cpp:1924-2150); argument order as the op's
+ * operands (:1934-1948).  Taps accumulate in (kh, kw, ic) order starting from the bias, multiply and add
+ * separately, so results equal the CPU loop bit for bit. */
+int simp_gpu_conv2d_f32(const float* input_dev, const float* weights_dev, const float* bias_dev, float* output_dev,
+                        int64_t batch, int64_t in_h, int64_t in_w, int64_t in_c, int64_t out_c, int64_t kernel_h,
+                        int64_t kernel_w, int64_t stride_h, int64_t stride_w, int64_t pad_h, int64_t pad_w);
+
 /* ---- matmul_quant / dequant_w4 (W4) --------------------------------------------------------
  * out[rows] = W4[rows,cols] . x[cols]; nibbles packed two per byte, low nibble = even flat index,
  * w = q*scale + zero (MatMulQuantOpLowering, ConvertSimpToMemRef.cpp:3853-4013;

@@ -208,6 +208,24 @@ def tensor_gather(source, indices, axis=0):
     return out
 
 
+def conv2d_f32(x, w, bias, stride=(1, 1), pad=(0, 0), threads=0):
+    """conv2d: x [N, H, W, IC] f32, w [OC, KH, KW, IC], bias [OC] -> [N, OH, OW, OC]."""
+    x = np.ascontiguousarray(x, np.float32)
+    w = np.ascontiguousarray(w, np.float32)
+    bias = np.ascontiguousarray(bias, np.float32)
+    n, h, wd, ic = x.shape
+    oc, kh, kw, ic2 = w.shape
+    assert ic == ic2 and bias.size == oc
+    oh, ow = (h + 2 * pad[0] - kh) // stride[0] + 1, (wd + 2 * pad[1] - kw) // stride[1] + 1
+    out = np.empty((n, oh, ow, oc), np.float32)
+    f = lib().simp_oracle_conv2d_f32
+    f.argtypes = [C.c_void_p] * 4 + [i64] * 11 + [C.c_int32]
+    f.restype = None
+    f(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), n, h, wd, ic, oc, kh, kw, stride[0], stride[1], pad[0], pad[1],
+      threads if threads > 0 else lib().simp_oracle_max_threads())
+    return out
+
+
 def argmax(v):
     return int(lib().simp_oracle_argmax(v, v.size))
 

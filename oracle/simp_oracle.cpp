@@ -716,3 +716,36 @@ ORACLE_API int simp_oracle_tensor_gather(const uint8_t* src, const int64_t* indi
     }
   return 0;
 }
+
+// ---------------------------------------------------------------------------
+// conv2d (Conv2DOpLowering, src/mlir/lowering/ConvertSimpToMemRef.cpp:1924-2150): NHWC input, weights
+// [OC, KH, KW, IC], bias [OC], NHWC output; out_h = (in_h + 2*pad_h - kh) / stride_h + 1 (same for w);
+// acc = bias[oc]; for kh, kw, ic in that order: taps outside the input are skipped (zero padding);
+// acc = acc + input * weight (separate multiply and add).
+// Pinned by tests/mlir/integration/test_conv2d_host.cpp:28-44: a 4x4 ramp 0..15 under a 3x3 kernel of ones, bias 0 --
+// the top-left unpadded window sums to 45.0 (with the pad 1 of test_conv2d_fp32_only.sl:17-18 the same window is
+// the output at (1, 1)).
+// ---------------------------------------------------------------------------
+ORACLE_API void simp_oracle_conv2d_f32(const float* input, const float* weights, const float* bias, float* output,
+                                       int64_t batch, int64_t in_h, int64_t in_w, int64_t in_c, int64_t out_c,
+                                       int64_t kh, int64_t kw, int64_t stride_h, int64_t stride_w, int64_t pad_h,
+                                       int64_t pad_w, int threads) {
+  const int nt = clamp_threads(threads);
+  const int64_t out_h = (in_h + 2 * pad_h - kh) / stride_h + 1, out_w = (in_w + 2 * pad_w - kw) / stride_w + 1;
+#pragma omp parallel for num_threads(nt) schedule(static) collapse(2) if (nt > 1)
+  for (int64_t b = 0; b < batch; ++b)
+    for (int64_t oh = 0; oh < out_h; ++oh)
+      for (int64_t ow = 0; ow < out_w; ++ow)
+        for (int64_t oc = 0; oc < out_c; ++oc) {
+          volatile float acc = bias[oc];   // volatile: keeps the multiply and the add separate (no contraction)
+          for (int64_t y = 0; y < kh; ++y)
+            for (int64_t x = 0; x < kw; ++x)
+              for (int64_t ic = 0; ic < in_c; ++ic) {
+                const int64_t ih = oh * stride_h + y - pad_h, iw = ow * stride_w + x - pad_w;
+                if (ih < 0 || ih >= in_h || iw < 0 || iw >= in_w) continue;
+                volatile float prod = input[((b * in_h + ih) * in_w + iw) * in_c + ic] * weights[((oc * kh + y) * kw + x) * in_c + ic];
+                acc = acc + prod;
+              }
+          output[((b * out_h + oh) * out_w + ow) * out_c + oc] = acc;
+        }
+}

@@ -63,6 +63,7 @@ _SIGNATURES = {
     "simp_host_silu_f32": [vp, vp, vp, i64],
     "simp_gpu_matmul_i4": [vp, vp, vp, i64, i64, i64],
     "simp_gpu_tensor_gather": [vp, vp, vp, i64, i64, i64, i64, i64],
+    "simp_gpu_conv2d_f32": [vp, vp, vp, vp] + [i64] * 11,
     "simp_gpu_record_begin": [],
     "simp_gpu_record_end": [C.POINTER(vp)],
     "simp_gpu_replay": [vp, i64],
@@ -315,6 +316,20 @@ def np_tensor_gather(source: np.ndarray, indices, axis: int = 0) -> np.ndarray:
     check(lib().simp_gpu_tensor_gather(dS.ptr, dI.ptr, dD.ptr, outer, shape[axis], inner, indices.size, source.dtype.itemsize))
     check(lib().simp_gpu_check_device_status())
     return dD.to_numpy(source.dtype, out_shape)
+
+
+def np_conv2d_f32(x: np.ndarray, w: np.ndarray, bias: np.ndarray, stride=(1, 1), pad=(0, 0)) -> np.ndarray:
+    """conv2d (numpy in / out): x [N, H, W, IC], w [OC, KH, KW, IC], bias [OC] -> [N, OH, OW, OC]."""
+    x = np.ascontiguousarray(x, np.float32)
+    w = np.ascontiguousarray(w, np.float32)
+    bias = np.ascontiguousarray(bias, np.float32)
+    n, h, wd, ic = x.shape
+    oc, kh, kw, _ = w.shape
+    oh, ow = (h + 2 * pad[0] - kh) // stride[0] + 1, (wd + 2 * pad[1] - kw) // stride[1] + 1
+    dX, dW, dB = DeviceBuffer.from_numpy(x), DeviceBuffer.from_numpy(w), DeviceBuffer.from_numpy(bias)
+    dY = DeviceBuffer(max(n * oh * ow * oc * 4, 16))
+    check(lib().simp_gpu_conv2d_f32(dX.ptr, dW.ptr, dB.ptr, dY.ptr, n, h, wd, ic, oc, kh, kw, stride[0], stride[1], pad[0], pad[1]))
+    return dY.to_numpy(np.float32, (n, oh, ow, oc))
 
 
 class Recording:

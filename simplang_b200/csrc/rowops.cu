@@ -402,3 +402,69 @@ SIMP_API int simp_gpu_tensor_gather(const void* src_dev, const int64_t* indices_
   SIMP_LAUNCH_CHECK();
   return SIMP_OK;
 }
+
+// ---- conv2d ---------------------------------------------------------------------------------------
+// Direct convolution as Conv2DOpLowering writes it (ConvertSimpToMemRef.cpp:1924-2150): NHWC input, weights
+// [OC, KH, KW, IC], acc = bias[oc], taps in (kh, kw, ic) order, taps outside the input skipped, multiply and add
+// kept separate (__fmul_rn / __fadd_rn, no contraction), so every output equals the CPU loop bit for bit.
+// One thread per output element with oc fastest: neighbouring threads read the same input value (broadcast) and,
+// through a [KH, KW, IC, OC] copy of the weights made per call, neighbouring weight values (coalesced).
+namespace simp {
+__global__ void conv2d_weights_to_hwio_kernel(const float* __restrict__ w, float* __restrict__ wt, int64_t oc, int64_t taps) {
+  const int64_t idx = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;   // over [OC, taps]
+  if (idx >= oc * taps) return;
+  const int64_t o = idx / taps, t = idx - o * taps;
+  wt[t * oc + o] = w[idx];
+}
+__global__ void __launch_bounds__(256) conv2d_f32_kernel(const float* __restrict__ in, const float* __restrict__ wt,
+                                                         const float* __restrict__ bias, float* __restrict__ out, int64_t total,
+                                                         int in_h, int in_w, int in_c, int out_h, int out_w, int out_c, int kh,
+                                                         int kw, int stride_h, int stride_w, int pad_h, int pad_w) {
+  const int64_t idx = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const int oc = int(idx % out_c);
+  int64_t r = idx / out_c;
+  const int ow = int(r % out_w);
+  r /= out_w;
+  const int oh = int(r % out_h);
+  const int64_t b = r / out_h;
+  float acc = bias[oc];
+  for (int y = 0; y < kh; ++y) {
+    const int ih = oh * stride_h + y - pad_h;
+    for (int x = 0; x < kw; ++x) {
+      const int iw = ow * stride_w + x - pad_w;
+      if (ih < 0 || ih >= in_h || iw < 0 || iw >= in_w) continue;
+      const float* ip = in + ((b * in_h + ih) * in_w + iw) * int64_t(in_c);
+      const float* wp = wt + (int64_t(y) * kw + x) * in_c * int64_t(out_c) + oc;
+      for (int ic = 0; ic < in_c; ++ic) acc = __fadd_rn(acc, __fmul_rn(ip[ic], wp[int64_t(ic) * out_c]));
+    }
+  }
+  out[idx] = acc;
+}
+}  // namespace simp
+
+SIMP_API int simp_gpu_conv2d_f32(const float* input_dev, const float* weights_dev, const float* bias_dev, float* output_dev,
+                                 int64_t batch, int64_t in_h, int64_t in_w, int64_t in_c, int64_t out_c, int64_t kernel_h,
+                                 int64_t kernel_w, int64_t stride_h, int64_t stride_w, int64_t pad_h, int64_t pad_w) {
+  if (int rc = simp::ensure_ready()) return rc;
+  SIMP_REQUIRE(batch >= 0 && in_h > 0 && in_w > 0 && in_c > 0 && out_c > 0 && kernel_h > 0 && kernel_w > 0 && stride_h > 0 &&
+                   stride_w > 0 && pad_h >= 0 && pad_w >= 0,
+               SIMP_ERR_ARG, "conv2d: non-positive dimension, stride or negative padding");
+  SIMP_REQUIRE(in_h + 2 * pad_h >= kernel_h && in_w + 2 * pad_w >= kernel_w, SIMP_ERR_SHAPE, "conv2d: kernel larger than the padded input");
+  if (batch == 0) return SIMP_OK;
+  SIMP_REQUIRE(input_dev && weights_dev && bias_dev && output_dev, SIMP_ERR_ARG, "conv2d: null pointer");
+  const int64_t out_h = (in_h + 2 * pad_h - kernel_h) / stride_h + 1, out_w = (in_w + 2 * pad_w - kernel_w) / stride_w + 1;
+  const int64_t taps = kernel_h * kernel_w * in_c, total = batch * out_h * out_w * out_c;
+  SIMP_REQUIRE(in_h < (1 << 30) && in_w < (1 << 30) && in_c < (1 << 30) && out_c < (1 << 30) && total / 256 < 0x7fffffff,
+               SIMP_ERR_SHAPE, "conv2d: dimension too large");
+  float* wt = static_cast<float*>(simp::scratch(size_t(taps) * out_c * 4, 11));
+  SIMP_REQUIRE(wt != nullptr, SIMP_ERR_CUDA, "conv2d: out of device memory for the weight copy");
+  cudaStream_t st = simp::ctx().stream;
+  simp::conv2d_weights_to_hwio_kernel<<<unsigned((taps * out_c + 255) / 256), 256, 0, st>>>(weights_dev, wt, out_c, taps);
+  simp::conv2d_f32_kernel<<<unsigned((total + 255) / 256), 256, 0, st>>>(input_dev, wt, bias_dev, output_dev, total, int(in_h),
+                                                                         int(in_w), int(in_c), int(out_h), int(out_w), int(out_c),
+                                                                         int(kernel_h), int(kernel_w), int(stride_h), int(stride_w),
+                                                                         int(pad_h), int(pad_w));
+  SIMP_LAUNCH_CHECK();
+  return SIMP_OK;
+}

@@ -273,3 +273,29 @@ def test_tensor_gather_known_answers():
         assert np.array_equal(oracle.tensor_gather(src, idx, axis), np.take(src, idx, axis=axis))
     with pytest.raises(IndexError):
         oracle.tensor_gather(np.zeros(4, np.float32), [4], 0)
+
+
+def test_conv2d_known_answer_and_numpy():
+    """conv2d oracle: the reference's known answer (tests/mlir/integration/test_conv2d_host.cpp:31-36: 4x4 ramp,
+    3x3 ones, bias 0, first unpadded window = 45.0) and a vectorised numpy restatement on random shapes."""
+    import oracle
+    x = np.arange(16, dtype=np.float32).reshape(1, 4, 4, 1)
+    w = np.ones((1, 3, 3, 1), np.float32)
+    b = np.zeros(1, np.float32)
+    assert oracle.conv2d_f32(x, w, b, (1, 1), (0, 0))[0, 0, 0, 0] == 45.0
+    assert oracle.conv2d_f32(x, w, b, (1, 1), (1, 1))[0, 1, 1, 0] == 45.0
+    rng = np.random.default_rng(2)
+    for (n, h, wd, ic, oc, kh, kw, st, pd) in ((1, 5, 6, 3, 4, 3, 3, (1, 1), (1, 1)), (2, 9, 7, 2, 5, 3, 2, (2, 1), (0, 1)),
+                                               (1, 8, 8, 4, 3, 1, 1, (1, 1), (0, 0)), (1, 7, 7, 1, 2, 5, 5, (2, 2), (2, 2))):
+        x = rng.standard_normal((n, h, wd, ic)).astype(np.float32)
+        w = rng.standard_normal((oc, kh, kw, ic)).astype(np.float32)
+        b = rng.standard_normal(oc).astype(np.float32)
+        out = oracle.conv2d_f32(x, w, b, st, pd)
+        xp = np.pad(x.astype(np.float64), ((0, 0), (pd[0], pd[0]), (pd[1], pd[1]), (0, 0)))
+        oh, ow = out.shape[1], out.shape[2]
+        ref = np.zeros(out.shape)
+        for y in range(oh):
+            for xx in range(ow):
+                win = xp[:, y * st[0]:y * st[0] + kh, xx * st[1]:xx * st[1] + kw, :]
+                ref[:, y, xx, :] = np.einsum("nhwc,ohwc->no", win, w.astype(np.float64)) + b
+        assert np.max(np.abs(out - ref)) <= 1e-4 * np.max(np.abs(ref))
