@@ -11,10 +11,11 @@
 // barriers only gate the compute, never the weight stream, so HBM keeps streaming while a phase waits for
 // its input vector and the ring is full when the phase starts.
 //
-// Compute: the activation vector is packed to 16-bit block floating point in shared memory (w4_pack_chunk),
-// warps are arranged as rg row groups x ks column slices, a warp owns rw rows of the tile and the chunks of
-// its column slice (dp4a, exact integer accumulation per 32-weight chunk, see w4_core.cuh), partial sums of
-// the column slices are added in slice order.  The next rmsnorm is deferred exactly as in the per-op path:
+// Compute: the activation vector is packed to 16-bit block floating point in shared memory (the layout of
+// w4_pack_chunk, four threads per chunk), a tile is cut into slabs of 16 rows and the 16 warps are arranged as
+// slabs x matrices x interleaved sets of 128-weight spans; each warp runs the tensor-core integer dot products of
+// w4_mma_spans (exact integer accumulation per 32-weight chunk, see w4_core.cuh), partial sums of the span sets
+// are added in set order.  The next rmsnorm is deferred exactly as in the per-op path:
 // the packed vector holds x*w_norm and every dot product is scaled by 1/sqrt(mean(x^2)+eps).
 // Per layer: q/k/v | attention | wo + residual | gate/up + silu*mul | down + residual; then the f32
 // classifier streamed from HBM + greedy argmax.  Reduction orders are fixed: results are run-to-run identical.
@@ -26,16 +27,15 @@ namespace simp {
 
 constexpr int PW_SLOTS = 3;
 constexpr int PW_MAX_TR = 32;   // rows per tile (per matrix) never exceed this
-constexpr int PW_MAX_KS = 8;    // column slices never exceed this
+constexpr int PW_MAX_KS = 16;   // span sets per row never exceed this
 constexpr size_t PW_STATIC_SMEM = 3072;
 
 // Tile geometry of one phase kind.
 struct PwKind {
   int cols, nchunks, row_bytes, gpr, log2_cpg;
-  int rg, ks, rw;   // warps = rg row groups x ks column slices; rw rows per warp
-  int tr;           // rows per tile and matrix = rg * rw
+  int sl, ms, kp;   // warps = sl slabs of 16 rows x ms matrices x kp interleaved span sets
+  int tr;           // rows per tile and matrix (at most 16 * sl)
   int unit;         // row slices and tiles are multiples of `unit` rows (keeps every scale row block 16-byte aligned)
-  int cps;          // chunks per column slice
 };
 
 struct PersistW4Args {
@@ -78,123 +78,113 @@ __device__ __forceinline__ void pw_tile_range(int nu, int nt, int i, int& first,
   count = base + (i < rem ? 1 : 0);
 }
 
-// Partial dot products of one tile: this warp's rows x the chunks of its column slice.
-template <int RW, int NM>
+// Partial dot products of one tile: this warp's slab (and matrix) x its set of spans.
+template <int NM>
 __device__ __forceinline__ void pw_tile_partials(const uint8_t* slot, int tr_i, const PwKind& K, bool has_z,
                                                  const uint4* __restrict__ xp, float* __restrict__ partial) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int rg = warp % K.rg, ks = warp / K.rg;
-  const int wr0 = rg * RW;
-  if (wr0 >= tr_i) return;
-  const size_t mat_w = size_t(tr_i) * K.row_bytes, mat_s = size_t(tr_i) * K.gpr * 4;
-  const size_t mat_bytes = mat_w + mat_s * (has_z ? 2 : 1);
-  const int c0 = ks * K.cps, c1 = min(K.nchunks, c0 + K.cps);
-  float acc[NM][RW];
+  const int slab = warp % K.sl, rest = warp / K.sl;
+  const int msel = rest % K.ms, kpart = rest / K.ms;
+  if (slab * 16 >= tr_i) return;
+  W4Tile tl;
+  tl.mat_w = size_t(tr_i) * K.row_bytes;
+  tl.mat_s = size_t(tr_i) * K.gpr * 4;
+  tl.mat_bytes = tl.mat_w + tl.mat_s * (has_z ? 2 : 1);
+  tl.row_bytes = K.row_bytes;
+  tl.sc_row = K.gpr;
+  tl.has_z = has_z;
+  tl.base = slot + (NM == 1 ? msel : 0) * tl.mat_bytes;
+  float acc[NM][2];
+#pragma unroll
+  for (int m = 0; m < NM; ++m) acc[m][0] = acc[m][1] = 0.0f;
+  w4_mma_spans<NM, false>(tl, slab * 16, tr_i, xp, K.nchunks, K.log2_cpg, kpart, K.kp, lane, acc);
 #pragma unroll
   for (int m = 0; m < NM; ++m)
 #pragma unroll
-    for (int r = 0; r < RW; ++r) acc[m][r] = 0.0f;
-  for (int ch = c0 + lane; ch < c1; ch += 32) {
-    uint4 xq[4];
-#pragma unroll
-    for (int t = 0; t < 4; ++t) xq[t] = xp[ch * W4_CHUNK_U4 + t];
-    const uint4 meta = xp[ch * W4_CHUNK_U4 + 4];
-    const float sx = __uint_as_float(meta.x), sumx = __uint_as_float(meta.y);
-    const int sum16 = int(meta.z);
-    const int g = ch >> K.log2_cpg;
-#pragma unroll
-    for (int m = 0; m < NM; ++m) {
-      const uint8_t* base = slot + m * mat_bytes;
-#pragma unroll
-      for (int r = 0; r < RW; ++r) {
-        if (wr0 + r < tr_i) {
-          const uint4 w = *reinterpret_cast<const uint4*>(base + size_t(wr0 + r) * K.row_bytes + size_t(ch) * 16);
-          const int tot = w4_chunk_dot(w, xq);
-          const float scale = reinterpret_cast<const float*>(base + mat_w)[(wr0 + r) * K.gpr + g];
-          if (!has_z) {
-            acc[m][r] = fmaf(float(tot - 8 * sum16) * sx, scale, acc[m][r]);
-          } else {
-            const float z = reinterpret_cast<const float*>(base + mat_w + mat_s)[(wr0 + r) * K.gpr + g];
-            acc[m][r] = fmaf(float(tot) * sx, scale, fmaf(z, sumx, acc[m][r]));
-          }
-        }
-      }
-    }
-  }
-#pragma unroll
-  for (int m = 0; m < NM; ++m)
-#pragma unroll
-    for (int r = 0; r < RW; ++r) {
-      const float v = warp_sum(acc[m][r]);
-      if (lane == 0 && wr0 + r < tr_i) partial[(m * PW_MAX_TR + wr0 + r) * PW_MAX_KS + ks] = v;
+    for (int h = 0; h < 2; ++h) {
+      float v = acc[m][h];
+      v += __shfl_xor_sync(0xffffffffu, v, 1);
+      v += __shfl_xor_sync(0xffffffffu, v, 2);
+      const int mm = NM == 1 ? msel : m;
+      if ((lane & 3) == 0) partial[(mm * PW_MAX_TR + slab * 16 + (lane >> 2) + 8 * h) * PW_MAX_KS + kpart] = v;
     }
 }
 
-// One chunk of 32 inputs packed by ONE thread (the layout and arithmetic of w4_pack_chunk, without its 15
-// warp shuffles: every block packs the whole vector for itself, so the pack must be cheap in instructions).
-__device__ __forceinline__ void pw_pack_chunk_serial(const float (&v)[32], uint4* chunk) {
-  float amax = 0.0f;
+// Eight inputs of a chunk packed by one thread, the four threads of a chunk (adjacent lanes, j = lane & 3) sharing
+// the maximum and the sums by two shuffles each: thread j produces word j of both byte planes (the layout and
+// arithmetic of w4_pack_chunk).  Every block packs the whole vector for itself, so the pack must be short.
+// All 32 lanes of a warp must call this together; `active` = this thread's chunk exists.
+__device__ __forceinline__ void pw_pack_quarter(const float (&v)[8], bool active, int j, uint8_t* chunk) {
+  float amax = 0.0f, sumx = 0.0f;
 #pragma unroll
-  for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(v[i]));
-  const float inv = amax > 0.0f ? 32767.0f / amax : 0.0f;
+  for (int i = 0; i < 8; ++i) {
+    amax = fmaxf(amax, fabsf(v[i]));
+    sumx += v[i];
+  }
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+  const float inv = amax > 0.0f ? 32512.0f / amax : 0.0f;
   int sum16 = 0;
-  float sumx = 0.0f;
+  uint32_t xh[2] = {0u, 0u}, xl[2] = {0u, 0u};
 #pragma unroll
-  for (int wd = 0; wd < 4; ++wd) {
-    uint32_t xh[2] = {0u, 0u}, xl[2] = {0u, 0u};
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const float f = v[wd * 8 + j];
-      int x16 = __float2int_rn(f * inv);
-      x16 = max(-32767, min(32767, x16));
-      sum16 += x16;
-      sumx += f;
-      xh[j & 1] |= uint32_t((x16 >> 8) & 255) << (8 * (j >> 1));   // signed high byte, floor
-      xl[j & 1] |= uint32_t(x16 & 255) << (8 * (j >> 1));          // unsigned low byte
-    }
-    chunk[wd] = make_uint4(xh[0], xh[1], xl[0], xl[1]);
+  for (int e = 0; e < 8; ++e) {
+    int x16 = __float2int_rn(v[e] * inv);
+    x16 = max(-32512, min(32512, x16));
+    sum16 += x16;
+    const int h = (x16 + 128) >> 8;
+    const int l = x16 - (h << 8);
+    xh[e & 1] |= uint32_t(h & 255) << (8 * (e >> 1));
+    xl[e & 1] |= uint32_t(l & 255) << (8 * (e >> 1));
   }
-  chunk[4] = make_uint4(__float_as_uint(amax > 0.0f ? amax / 32767.0f : 0.0f), __float_as_uint(sumx), uint32_t(sum16), 0u);
+  sumx += __shfl_xor_sync(0xffffffffu, sumx, 1);
+  sumx += __shfl_xor_sync(0xffffffffu, sumx, 2);
+  sum16 += __shfl_xor_sync(0xffffffffu, sum16, 1);
+  sum16 += __shfl_xor_sync(0xffffffffu, sum16, 2);
+  if (active) {
+    *reinterpret_cast<uint2*>(chunk + j * 8) = make_uint2(xh[0], xh[1]);
+    *reinterpret_cast<uint2*>(chunk + 32 + j * 8) = make_uint2(xl[0], xl[1]);
+    if (j == 0)
+      *reinterpret_cast<uint4*>(chunk + 64) =
+          make_uint4(__float_as_uint(amax > 0.0f ? amax / 32512.0f : 0.0f), __float_as_uint(sumx), uint32_t(sum16), 0u);
+  }
 }
 
-// Packs n32 chunks of a global vector (optionally times mul) into xp, one thread per chunk: eight 16-byte
-// loads through L2 per thread, all in flight together.  Returns this thread's share of sum(x^2) of the
-// unscaled input.
+// Packs n32 chunks of a global vector (optionally times mul) into xp, four threads per chunk: two 16-byte loads
+// through L2 per thread and operand.  Returns this thread's share of sum(x^2) of the unscaled input.
 __device__ __forceinline__ float pw_pack_global(const float* __restrict__ x, const float* __restrict__ mul, uint8_t* xp,
                                                 int n32) {
   float ss = 0.0f;
-  for (int ch = threadIdx.x; ch < n32; ch += PK_THREADS) {
-    float v[32];
-    const float4* src = reinterpret_cast<const float4*>(x + size_t(ch) * 32);
+  for (int base = 0; base < n32 * 4; base += PK_THREADS) {
+    const int q = base + int(threadIdx.x);
+    const bool active = q < n32 * 4;
+    float v[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+    if (active) {
+      const float4* src = reinterpret_cast<const float4*>(x + size_t(q) * 8);
+      const float4 t0 = __ldcg(src), t1 = __ldcg(src + 1);
+      v[0] = t0.x; v[1] = t0.y; v[2] = t0.z; v[3] = t0.w; v[4] = t1.x; v[5] = t1.y; v[6] = t1.z; v[7] = t1.w;
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      const float4 t = __ldcg(src + k);
-      v[4 * k] = t.x; v[4 * k + 1] = t.y; v[4 * k + 2] = t.z; v[4 * k + 3] = t.w;
-    }
-#pragma unroll
-    for (int i = 0; i < 32; ++i) ss = fmaf(v[i], v[i], ss);
-    if (mul) {
-      const float4* ms = reinterpret_cast<const float4*>(mul + size_t(ch) * 32);
-#pragma unroll
-      for (int k = 0; k < 8; ++k) {
-        const float4 t = __ldg(ms + k);
-        v[4 * k] *= t.x; v[4 * k + 1] *= t.y; v[4 * k + 2] *= t.z; v[4 * k + 3] *= t.w;
+      for (int i = 0; i < 8; ++i) ss = fmaf(v[i], v[i], ss);
+      if (mul) {
+        const float4* ms = reinterpret_cast<const float4*>(mul + size_t(q) * 8);
+        const float4 m0 = __ldg(ms), m1 = __ldg(ms + 1);
+        v[0] *= m0.x; v[1] *= m0.y; v[2] *= m0.z; v[3] *= m0.w; v[4] *= m1.x; v[5] *= m1.y; v[6] *= m1.z; v[7] *= m1.w;
       }
     }
-    pw_pack_chunk_serial(v, reinterpret_cast<uint4*>(xp) + size_t(ch) * W4_CHUNK_U4);
+    pw_pack_quarter(v, active, q & 3, xp + size_t(q >> 2) * (W4_CHUNK_U4 * 16));
   }
   return ss;
 }
 __device__ __forceinline__ void pw_pack_shared(const float* vec, uint8_t* xp, int n32) {
-  for (int ch = threadIdx.x; ch < n32; ch += PK_THREADS) {
-    float v[32];
-    const float4* src = reinterpret_cast<const float4*>(vec + size_t(ch) * 32);
-#pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      const float4 t = src[k];
-      v[4 * k] = t.x; v[4 * k + 1] = t.y; v[4 * k + 2] = t.z; v[4 * k + 3] = t.w;
+  for (int base = 0; base < n32 * 4; base += PK_THREADS) {
+    const int q = base + int(threadIdx.x);
+    const bool active = q < n32 * 4;
+    float v[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+    if (active) {
+      const float4* src = reinterpret_cast<const float4*>(vec + size_t(q) * 8);
+      const float4 t0 = src[0], t1 = src[1];
+      v[0] = t0.x; v[1] = t0.y; v[2] = t0.z; v[3] = t0.w; v[4] = t1.x; v[5] = t1.y; v[6] = t1.z; v[7] = t1.w;
     }
-    pw_pack_chunk_serial(v, reinterpret_cast<uint4*>(xp) + size_t(ch) * W4_CHUNK_U4);
+    pw_pack_quarter(v, active, q & 3, xp + size_t(q >> 2) * (W4_CHUNK_U4 * 16));
   }
 }
 
@@ -319,15 +309,8 @@ __global__ void __launch_bounds__(PK_BLOCK, 1) llama_w4_token_kernel(const Persi
       const uint8_t* sl = smem + a.slot_off[slot];
       float* pbuf = part + (tcount & 1u) * (2 * PW_MAX_TR * PW_MAX_KS);
       const uint4* xq = reinterpret_cast<const uint4*>(xp);
-      if (mode == 2) {
-        if (K.rw == 4) pw_tile_partials<4, 2>(sl, tr_i, K, has_z, xq, pbuf);
-        else if (K.rw == 3) pw_tile_partials<3, 2>(sl, tr_i, K, has_z, xq, pbuf);
-        else pw_tile_partials<2, 2>(sl, tr_i, K, has_z, xq, pbuf);
-      } else {
-        if (K.rw == 4) pw_tile_partials<4, 1>(sl, tr_i, K, has_z, xq, pbuf);
-        else if (K.rw == 3) pw_tile_partials<3, 1>(sl, tr_i, K, has_z, xq, pbuf);
-        else pw_tile_partials<2, 1>(sl, tr_i, K, has_z, xq, pbuf);
-      }
+      if (mode == 2 && K.ms == 1) pw_tile_partials<2>(sl, tr_i, K, has_z, xq, pbuf);
+      else pw_tile_partials<1>(sl, tr_i, K, has_z, xq, pbuf);
       // residual rows are requested before the block-wide sync so their latency overlaps it
       const int r = threadIdx.x;
       const float resid = (mode == 1 && r < tr_i) ? __ldcg(c.x + row0 + r) : 0.0f;
@@ -335,9 +318,9 @@ __global__ void __launch_bounds__(PK_BLOCK, 1) llama_w4_token_kernel(const Persi
       if (threadIdx.x == 0) ptx::mbar_arrive(ptx::smem_u32(&empty[slot]));   // every warp has read the slot
       if (r < tr_i) {
         float v0 = 0.0f, v1 = 0.0f;
-        for (int k = 0; k < K.ks; ++k) v0 += pbuf[r * PW_MAX_KS + k];
+        for (int k = 0; k < K.kp; ++k) v0 += pbuf[r * PW_MAX_KS + k];
         if (mode == 2)
-          for (int k = 0; k < K.ks; ++k) v1 += pbuf[(PW_MAX_TR + r) * PW_MAX_KS + k];
+          for (int k = 0; k < K.kp; ++k) v1 += pbuf[(PW_MAX_TR + r) * PW_MAX_KS + k];
         if (mode == 0) out[row0 + r] = v0 * inv_r;
         if (mode == 1) c.x[row0 + r] = resid + v0;
         if (mode == 2) {
@@ -416,7 +399,8 @@ struct PersistW4Plan {
 
 static int gcd_i(int a, int b) { return b ? gcd_i(b, a % b) : a; }
 
-// Warp arrangement for tiles of `nm` matrices with rows of `cols` weights: the largest tile that fits a slot.
+// Tile size and warp arrangement for tiles of `nm` matrices with rows of `cols` weights: the largest tile of at
+// most 32 rows (a multiple of the unit) that fits a slot; 16 warps = slabs x matrices x span sets.
 static bool pw_pick(int cols, int gs, int nm, bool zeros, size_t slot_bytes, PwKind& K) {
   K = PwKind{};
   K.cols = cols;
@@ -426,16 +410,14 @@ static bool pw_pick(int cols, int gs, int nm, bool zeros, size_t slot_bytes, PwK
   K.log2_cpg = __builtin_ctz(unsigned(gs / 32));
   K.unit = 4 / gcd_i(4, K.gpr);
   const size_t row_b = size_t(K.row_bytes) + size_t(K.gpr) * 4 * (zeros ? 2 : 1);
-  static const int cand[][3] = {{8, 2, 4}, {4, 4, 4}, {4, 4, 3}, {4, 4, 2}, {2, 8, 4}, {2, 8, 3}, {2, 8, 2}};
-  for (const auto& cd : cand) {
-    const int rg = cd[0], ks = cd[1], rw = cd[2], tr = rg * rw;
-    if (tr % K.unit || tr > PW_MAX_TR || ks > PW_MAX_KS || ks > K.nchunks) continue;
-    if (size_t(nm) * tr * row_b > slot_bytes) continue;
-    K.rg = rg; K.ks = ks; K.rw = rw; K.tr = tr;
-    K.cps = (K.nchunks + ks - 1) / ks;
-    return true;
-  }
-  return false;
+  int tr = int(std::min<size_t>(PW_MAX_TR, slot_bytes / (size_t(nm) * row_b)));
+  tr -= tr % K.unit;
+  if (tr < K.unit || tr < 4) return false;
+  K.tr = tr;
+  K.sl = (tr + 15) / 16;
+  K.ms = (nm == 2 && K.sl == 1) ? 2 : 1;
+  K.kp = PK_WARPS / (K.sl * K.ms);
+  return K.kp >= 1 && K.kp <= PW_MAX_KS;
 }
 
 static PersistW4Plan persist_w4_plan(const LlamaModel& m) {

@@ -4,19 +4,22 @@
 // w = q*scale + zero per group of gs consecutive weights (MatMulQuantOpLowering,
 // src/mlir/lowering/ConvertSimpToMemRef.cpp:3906-4005).
 //
-// The kernel is HBM-bound only if the per-weight instruction count stays near one, so the
-// activations are first packed (w4_pack_x_kernel) into 16-bit block floating point: per chunk of
-// 32 inputs a scale sx = max|x|/32767 and x16 = rint(x/sx) split into a signed high byte and an
-// unsigned low byte, laid out so that one masked weight word (4 nibbles as 4 bytes) meets 4 input
-// bytes in one dp4a.  Per 8 weights: 3 logic ops + 4 dp4a, exact integer accumulation; per chunk
-// one int->float conversion and one FMA with scale*sx.  Rounding x to 16 bits inside each chunk
-// bounds the error of a term by 1.5e-5 * max|x_chunk| * |w| -- two orders below the 1e-3
-// tolerance of the W4 path, and independent of outliers elsewhere in x.
+// The kernel is HBM-bound only if the per-weight instruction count stays well below one: lop3, shf, dp4a and
+// the integer multiply-add share a pipe that issues 64 lane-operations per clock and SM, while HBM delivers ~50
+// weights per clock and SM.  So the activations are first packed (w4_pack_x_kernel) into 16-bit block floating
+// point -- per chunk of 32 inputs a scale sx = max|x|/32512 and x16 = rint(x/sx) split into two signed bytes
+// x16 = 256*xh + xl -- and the integer dot products run on the tensor cores as warp-level
+// mma.sync.m16n8k32 (u8 nibbles x s8 input bytes -> s32): a GEMV has one column, so the eight columns of the
+// B operand carry the high and low byte planes of four different 32-input chunks, each zero outside its own
+// chunk.  One group of four MMAs then yields, for 16 rows, the exact integer dot product of four chunks, every
+// lane holding one (row pair, chunk) result to scale by its group's scale.  Per 8 weights of a row: 3 logic ops
+// (shared by 16 rows' worth of tensor work) instead of 3 logic ops + 4 dp4a.  Rounding x to 16 bits inside each
+// chunk bounds the error of a term by 1.6e-5 * max|x_chunk| * |w| -- two orders below the 1e-3 tolerance of
+// the W4 path, and independent of outliers elsewhere in x.
 //
-// Packed layout, per chunk c (80 bytes, 5 x uint4): words wd = 0..3 cover inputs 32c+8wd .. +7:
-//   uint4 wd = { XH_even, XH_odd, XL_even, XL_odd }  (even/odd = the inputs paired with the low /
-//   high nibbles of the weight word), then uint4 meta = { sx, sum(x) f32, sum(x16) i32, 0 }.
-// The 80-byte stride makes the 128-bit shared-memory reads of 8 neighbouring lanes conflict-free.
+// Packed layout, per chunk c (80 bytes, 5 x uint4): bytes 0..31 the high plane, 32..63 the low plane, each as
+// words j = 0..3 (inputs 32c+8j .. +7) of { 4 even inputs, 4 odd inputs } -- the inputs that meet the low / high
+// nibbles of weight word j -- then uint4 meta = { sx, sum(x) f32, sum(x16) i32, 0 }.
 #pragma once
 #include "common.cuh"
 #include "sm100_ptx.cuh"
@@ -31,22 +34,22 @@ inline size_t w4_packed_bytes(int64_t cols) { return size_t(cols / 32) * W4_CHUN
 // One warp per 32-input chunk.  `x` may be produced by a fused prologue: see w4_pack_value().
 __device__ __forceinline__ void w4_pack_chunk(float xv, int lane, uint8_t* chunk_bytes) {
   const float amax = warp_max(fabsf(xv));
-  const float inv = amax > 0.0f ? 32767.0f / amax : 0.0f;
+  const float inv = amax > 0.0f ? 32512.0f / amax : 0.0f;
   int x16 = __float2int_rn(xv * inv);
-  x16 = max(-32767, min(32767, x16));
-  const int xh = x16 >> 8;    // signed high byte, floor
-  const int xl = x16 & 255;   // unsigned low byte: x16 == xh*256 + xl
-  const int wd = lane >> 3, j = lane & 7;
-  const int pos = wd * 16 + (j & 1) * 4 + (j >> 1);
+  x16 = max(-32512, min(32512, x16));
+  const int xh = (x16 + 128) >> 8;   // nearest multiple of 256, in [-127, 127]
+  const int xl = x16 - (xh << 8);    // signed low byte, in [-128, 127]
+  const int j = lane >> 3, e = lane & 7;
+  const int pos = j * 8 + (e & 1) * 4 + (e >> 1);
   chunk_bytes[pos] = uint8_t(xh);
-  chunk_bytes[pos + 8] = uint8_t(xl);
+  chunk_bytes[pos + 32] = uint8_t(xl);
   const float sumx = warp_sum(xv);
   int sum16 = x16;
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) sum16 += __shfl_xor_sync(0xffffffffu, sum16, o);
   if (lane == 0) {
     uint4 meta;
-    meta.x = __float_as_uint(amax > 0.0f ? amax / 32767.0f : 0.0f);
+    meta.x = __float_as_uint(amax > 0.0f ? amax / 32512.0f : 0.0f);
     meta.y = __float_as_uint(sumx);
     meta.z = uint32_t(sum16);
     meta.w = 0;
@@ -134,32 +137,111 @@ struct W4Args {
   int seg_tile_start[4];
 };
 
-// Shared-memory footprint of one pipeline stage: 8*RW rows of every streamed matrix with their scales (+zeros).
-inline size_t w4_stage_bytes(int cols, int groups_per_row, int nm, bool zeros, int rw) {
-  return size_t(nm) * size_t(8 * rw) * (size_t(cols / 2) + size_t(groups_per_row) * 4 * (zeros ? 2 : 1));
+// Shared-memory footprint of one pipeline stage: TR rows of every streamed matrix with their scales (+zeros).
+inline size_t w4_stage_bytes(int cols, int groups_per_row, int nm, bool zeros, int tr) {
+  return size_t(nm) * size_t(tr) * (size_t(cols / 2) + size_t(groups_per_row) * 4 * (zeros ? 2 : 1));
 }
 
-// Streaming kernel.  A block owns tiles of 8*RW consecutive rows; a tile is fetched by ONE bulk async copy
+// D (16 x 8, s32) += A (16 x 32 unsigned bytes, row-major fragments) * B (32 x 8 signed bytes, column fragments).
+__device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Shared-memory view of one tile for w4_mma_spans: matrix m starts at base + m * mat_bytes and holds its rows
+// (row_bytes each), then the rows' scales at +mat_w and, when has_z, the zeros at +mat_w+mat_s.
+struct W4Tile {
+  const uint8_t* base;
+  size_t mat_bytes, mat_w, mat_s;
+  int row_bytes, sc_row;
+  bool has_z;
+};
+
+// One warp, 16 rows (HALF: 8 rows) starting at tile row `r0`, spans s0, s0+sstep, ... of 128 weights.
+// In the warp's MMA lane (g, t) = (lane / 4, lane % 4) reads 16 bytes -- chunk 4s+t -- of rows g and g+8; MMA j
+// multiplies word j of every lane's piece (low nibbles as the first 16 k-slots, high nibbles as the second) with a
+// B operand whose column n is the byte plane (n & 1) of chunk 4s + n/2 and zero in the other chunks' k-slots:
+// lanes with t == g/2 load those 32 bytes from the packed input, the others pass zeros.  After the four MMAs
+// lane (g, t) holds the integer dot products of chunk 4s+t with rows g and g+8 (high plane in c0/c2, low plane
+// in c1/c3), which it scales and adds to acc[m][0] (row g) and acc[m][1] (row g+8).
+template <int NM, bool HALF>
+__device__ __forceinline__ void w4_mma_spans(const W4Tile& tl, int r0, int vrows, const uint4* __restrict__ xs, int nchunks,
+                                             int log2_cpg, int s0, int sstep, int lane, float (&acc)[NM][2]) {
+  const int g = lane >> 2, t = lane & 3;
+  const bool va = r0 + g < vrows, vb = !HALF && r0 + g + 8 < vrows;   // rows past the tile's last row read nothing
+  const bool bsel = t == (g >> 1);
+  const int plane = g & 1;
+  const int nspans = (nchunks + 3) >> 2;
+  for (int s = s0; s < nspans; s += sstep) {
+    const int c = 4 * s + t;
+    const bool valid = c < nchunks;
+    uint4 xb0 = make_uint4(0, 0, 0, 0), xb1 = xb0, meta = xb0;
+    if (valid) {
+      meta = xs[c * W4_CHUNK_U4 + 4];
+      if (bsel) {
+        xb0 = xs[c * W4_CHUNK_U4 + plane * 2];
+        xb1 = xs[c * W4_CHUNK_U4 + plane * 2 + 1];
+      }
+    }
+    const float sx = __uint_as_float(meta.x), sumx = __uint_as_float(meta.y);
+    const int m8 = -8 * int(meta.z);
+    const int grp = c >> log2_cpg;
+#pragma unroll
+    for (int m = 0; m < NM; ++m) {
+      const uint8_t* mb = tl.base + m * tl.mat_bytes;
+      const uint8_t* wp = mb + size_t(r0 + g) * tl.row_bytes + size_t(c) * 16;
+      uint4 wa = make_uint4(0, 0, 0, 0), wb = wa;
+      if (valid && va) wa = *reinterpret_cast<const uint4*>(wp);
+      if (valid && vb) wb = *reinterpret_cast<const uint4*>(wp + size_t(8) * tl.row_bytes);
+      int cc[4] = {0, 0, 0, 0};
+      constexpr uint32_t MK = 0x0F0F0F0Fu;
+      mma_u8s8(cc, wa.x & MK, wb.x & MK, (wa.x >> 4) & MK, (wb.x >> 4) & MK, xb0.x, xb0.y);
+      mma_u8s8(cc, wa.y & MK, wb.y & MK, (wa.y >> 4) & MK, (wb.y >> 4) & MK, xb0.z, xb0.w);
+      mma_u8s8(cc, wa.z & MK, wb.z & MK, (wa.z >> 4) & MK, (wb.z >> 4) & MK, xb1.x, xb1.y);
+      mma_u8s8(cc, wa.w & MK, wb.w & MK, (wa.w >> 4) & MK, (wb.w >> 4) & MK, xb1.z, xb1.w);
+      const float* scp = reinterpret_cast<const float*>(mb + tl.mat_w) + (r0 + g) * tl.sc_row + grp;
+      const float* zp = reinterpret_cast<const float*>(mb + tl.mat_w + tl.mat_s) + (r0 + g) * tl.sc_row + grp;
+      if (valid && va) {
+        const int tot = cc[0] * 256 + cc[1];
+        if (!tl.has_z) acc[m][0] = fmaf(float(tot + m8) * sx, scp[0], acc[m][0]);
+        else acc[m][0] = fmaf(float(tot) * sx, scp[0], fmaf(zp[0], sumx, acc[m][0]));
+      }
+      if (valid && vb) {
+        const int tot = cc[2] * 256 + cc[3];
+        if (!tl.has_z) acc[m][1] = fmaf(float(tot + m8) * sx, scp[8 * tl.sc_row], acc[m][1]);
+        else acc[m][1] = fmaf(float(tot) * sx, scp[8 * tl.sc_row], fmaf(zp[8 * tl.sc_row], sumx, acc[m][1]));
+      }
+    }
+  }
+}
+
+// Streaming kernel.  A block owns tiles of TR consecutive rows; a tile is fetched by ONE bulk async copy
 // per matrix (cp.async.bulk global -> shared, completion on an mbarrier; rows of a row-major matrix are
 // contiguous) plus one for its scales, two tiles in flight.  The copies of the first two tiles are issued
 // before the kernel waits for the producer of its input vector, so under programmatic dependent launch
 // the weights of the next projection are already streaming while the previous kernel finishes.
-// Warps then read weights, scales and the packed input from shared memory only; warp w owns rows
-// w*RW .. w*RW+RW-1 of the tile, lanes split the 32-weight chunks, one shuffle reduction per row.
-template <int MODE, int RW>
+// Warps then read weights, scales and the packed input from shared memory only: a tile is TR/16 slabs of 16
+// rows (TR == 8: one half-used slab), the eight warps split slabs x interleaved 128-weight spans, and the
+// per-warp partial sums of a row meet in a small shared array.
+template <int MODE, int TR>
 __global__ void __launch_bounds__(W4_WARPS * 32, 3) w4_gemv_kernel(const W4Args a) {
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ float sh_inv_r;
   __shared__ __align__(8) uint64_t bars[2];
   __shared__ int abort_flag;
   constexpr int NM = MODE == W4_GATE_UP ? 2 : 1;
-  constexpr int S_ROWS = 8 * RW;
+  constexpr int S_ROWS = TR;
+  constexpr int SL = TR == 32 ? 2 : 1;      // slabs per tile
+  constexpr int KP = W4_WARPS / SL;         // warps that split the spans of one slab
+  constexpr bool HALF = TR == 8;
+  __shared__ float red[2][NM][KP][S_ROWS];
   const int nchunks = a.cols >> 5;
   const int row_bytes = a.cols >> 1;
   const int sc_row = a.groups_per_row;  // floats of scale per row
   const bool has_z = a.seg[0].zr != nullptr;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n_it = (nchunks + 31) >> 5;
   const size_t xs_bytes = size_t(nchunks) * (W4_CHUNK_U4 * 16);
   const size_t mat_w = size_t(S_ROWS) * row_bytes, mat_s = size_t(S_ROWS) * sc_row * 4;
   const size_t mat_bytes = mat_w + mat_s * (has_z ? 2 : 1);
@@ -240,63 +322,52 @@ __global__ void __launch_bounds__(W4_WARPS * 32, 3) w4_gemv_kernel(const W4Args 
   }
   __syncthreads();
   const float inv_r = sh_inv_r;
+  const int slab = warp % SL, kpart = warp / SL;
 
   for (int q = 0; q < my_steps; ++q) {
     int s, row0, rows;
     locate(q, s, row0, rows);
     const int st = q & 1;
     if (!ptx::mbar_wait(ptx::smem_u32(&bars[st]), uint32_t(q >> 1) & 1u, &abort_flag, a.status, 10)) break;
-    float acc[NM][RW];
+    float acc[NM][2];
+#pragma unroll
+    for (int m = 0; m < NM; ++m) acc[m][0] = acc[m][1] = 0.0f;
+    W4Tile tl;
+    tl.base = stage_ptr(st, 0);
+    tl.mat_bytes = mat_bytes;
+    tl.mat_w = mat_w;
+    tl.mat_s = mat_s;
+    tl.row_bytes = row_bytes;
+    tl.sc_row = sc_row;
+    tl.has_z = has_z;
+    if (row0 + slab * 16 < rows) w4_mma_spans<NM, HALF>(tl, slab * 16, S_ROWS, xs, nchunks, a.log2_cpg, kpart, KP, lane, acc);
 #pragma unroll
     for (int m = 0; m < NM; ++m)
 #pragma unroll
-      for (int r = 0; r < RW; ++r) acc[m][r] = 0.0f;
-    const int wr0 = warp * RW;  // first row of this warp inside the tile
-    if (row0 + wr0 < rows) {
-      for (int it = 0; it < n_it; ++it) {
-        const int c = lane + (it << 5);
-        if (c < nchunks) {
-          uint4 xq[4];
-#pragma unroll
-          for (int t = 0; t < 4; ++t) xq[t] = xs[c * W4_CHUNK_U4 + t];
-          const uint4 meta = xs[c * W4_CHUNK_U4 + 4];
-          const float sx = __uint_as_float(meta.x), sumx = __uint_as_float(meta.y);
-          const int sum16 = int(meta.z);
-          const int g = c >> a.log2_cpg;
-#pragma unroll
-          for (int m = 0; m < NM; ++m) {
-            const uint8_t* base = stage_ptr(st, m);
-#pragma unroll
-            for (int r = 0; r < RW; ++r) {
-              if (row0 + wr0 + r < rows) {
-                const uint4 w = *reinterpret_cast<const uint4*>(base + size_t(wr0 + r) * row_bytes + size_t(c) * 16);
-                const int tot = w4_chunk_dot(w, xq);
-                const float scale = reinterpret_cast<const float*>(base + mat_w)[(wr0 + r) * sc_row + g];
-                if (!has_z) {
-                  acc[m][r] = fmaf(float(tot - 8 * sum16) * sx, scale, acc[m][r]);
-                } else {
-                  const float z = reinterpret_cast<const float*>(base + mat_w + mat_s)[(wr0 + r) * sc_row + g];
-                  acc[m][r] = fmaf(float(tot) * sx, scale, fmaf(z, sumx, acc[m][r]));
-                }
-              }
-            }
-          }
-        }
+      for (int h = 0; h < (HALF ? 1 : 2); ++h) {
+        float v = acc[m][h];
+        v += __shfl_xor_sync(0xffffffffu, v, 1);
+        v += __shfl_xor_sync(0xffffffffu, v, 2);
+        if ((lane & 3) == 0) red[st][m][kpart][slab * 16 + (lane >> 2) + 8 * h] = v;
       }
-    }
+    __syncthreads();  // partial sums published; every warp is done with stage st before it is refilled
+    issue(q + 2);
+    if (threadIdx.x < S_ROWS) {
+      const int row = row0 + int(threadIdx.x);
+      float v0 = 0.0f, v1 = 0.0f;
 #pragma unroll
-    for (int r = 0; r < RW; ++r) {
-      const float v0 = warp_sum(acc[0][r]) * inv_r;
-      const float v1 = NM == 2 ? warp_sum(acc[NM - 1][r]) * inv_r : 0.0f;
-      const int row = row0 + wr0 + r;
-      if (lane == 0 && row < rows) {
+      for (int k = 0; k < KP; ++k) {
+        v0 += red[st][0][k][threadIdx.x];
+        if (NM == 2) v1 += red[st][NM - 1][k][threadIdx.x];
+      }
+      v0 *= inv_r;
+      v1 *= inv_r;
+      if (row < rows) {
         if (MODE == W4_STORE) a.seg[s].out[row] = v0;
         if (MODE == W4_ADD) a.seg[s].out[row] = a.res[row] + v0;
         if (MODE == W4_GATE_UP) a.seg[0].out[row] = (v0 / (1.0f + expf(-v0))) * v1;
       }
     }
-    __syncthreads();  // every warp is done with stage st before it is refilled
-    issue(q + 2);
   }
 }
 
@@ -315,41 +386,42 @@ inline int w4_launch(W4Args a, cudaStream_t st, int sm_count, bool pdl = false) 
     if (s < nseg_tiles) total_rows += a.seg[s].rows;
   }
   if (total_rows == 0) return SIMP_OK;
-  // Rows per warp (tile = 8*RW rows).  More rows per tile reuse the packed input better (less shared-memory
-  // traffic per weight); fewer keep every SM busy on the short matrices of batch-1 decode.  Two tiles must
-  // fit in shared memory next to the packed input, with room for 2-3 blocks per SM.
+  // Rows per tile.  Larger tiles mean fewer barriers per weight; smaller ones keep every SM busy on the short
+  // matrices of batch-1 decode.  Two tiles must fit in shared memory next to the packed input, with room for
+  // 2-3 blocks per SM.
   const size_t xs_bytes = w4_packed_bytes(a.cols);
-  int rw = 4;
-  while (rw > 1 && xs_bytes + 2 * w4_stage_bytes(a.cols, a.groups_per_row, NM, zeros, rw) > 74 * 1024) rw >>= 1;
-  if (rw == 1 && xs_bytes + 2 * w4_stage_bytes(a.cols, a.groups_per_row, NM, zeros, 2) <= 112 * 1024) rw = 2;
-  while (rw > 1 && total_rows / (8 * rw) < 2 * int64_t(sm_count)) rw >>= 1;
-  const size_t smem = xs_bytes + 2 * w4_stage_bytes(a.cols, a.groups_per_row, NM, zeros, rw);
+  auto need = [&](int tr) { return xs_bytes + 2 * w4_stage_bytes(a.cols, a.groups_per_row, NM, zeros, tr); };
+  int tr = 32;
+  while (tr > 8 && need(tr) > 74 * 1024) tr >>= 1;
+  if (tr == 8 && need(16) <= 112 * 1024) tr = 16;
+  while (tr > 8 && total_rows / tr < 2 * int64_t(sm_count)) tr >>= 1;
+  const size_t smem = need(tr);
   if (smem > 220 * 1024) return set_error(SIMP_ERR_SHAPE, "w4_gemv: row too long for the shared-memory pipeline");
   int g = 0;
   for (int s = 0; s < nseg_tiles; ++s) {
     a.seg_tile_start[s] = g;
-    g += (a.seg[s].rows + 8 * rw - 1) / (8 * rw);
+    g += (a.seg[s].rows + tr - 1) / tr;
   }
   a.seg_tile_start[nseg_tiles] = g;
   a.total_tiles = g;
-  int per_sm = int((227 * 1024) / (smem + 1024));
+  int per_sm = int((227 * 1024) / (smem + 4096));
   per_sm = per_sm < 1 ? 1 : (per_sm > 3 ? 3 : per_sm);
   const int cap = sm_count * per_sm;
   const int grid = g < cap ? g : cap;
   cudaError_t e;
-#define W4_LAUNCH_RW(RWV)                                                                                   \
+#define W4_LAUNCH_TR(TRV)                                                                                   \
   do {                                                                                                      \
     static bool attr_set = false;                                                                           \
     if (!attr_set) {                                                                                        \
-      cudaFuncSetAttribute(w4_gemv_kernel<MODE, RWV>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024); \
+      cudaFuncSetAttribute(w4_gemv_kernel<MODE, TRV>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024); \
       attr_set = true;                                                                                      \
     }                                                                                                       \
-    e = launch_kernel(w4_gemv_kernel<MODE, RWV>, dim3(grid), dim3(W4_WARPS * 32), smem, st, pdl, a);        \
+    e = launch_kernel(w4_gemv_kernel<MODE, TRV>, dim3(grid), dim3(W4_WARPS * 32), smem, st, pdl, a);        \
   } while (0)
-  if (rw == 4) W4_LAUNCH_RW(4);
-  else if (rw == 2) W4_LAUNCH_RW(2);
-  else W4_LAUNCH_RW(1);
-#undef W4_LAUNCH_RW
+  if (tr == 32) W4_LAUNCH_TR(32);
+  else if (tr == 16) W4_LAUNCH_TR(16);
+  else W4_LAUNCH_TR(8);
+#undef W4_LAUNCH_TR
   if (e != cudaSuccess) return set_error(SIMP_ERR_CUDA, "w4_gemv launch failed: %s", cudaGetErrorString(e));
   return SIMP_OK;
 }
