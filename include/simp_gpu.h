@@ -118,14 +118,13 @@ int simp_gpu_dequant_w4(const uint8_t* qweights_dev, const float* scales_dev,
                         int64_t group_size, float* out_dev);
 /* Same result as simp_gpu_matmul_w4, for callers that must not allocate device memory (a host that gave its
  * whole memory budget to its own pool at start-up, or code running where the runtime forbids allocation).
- * This entry point has no counterpart in the reference.  The packed copy of x that the streaming kernel
- * needs lives in a fixed 40 KB device array inside the library instead of the growable arena, so:
+ * This entry point has no counterpart in the reference.  The streaming kernel packs x in shared memory, so the
+ * call needs no scratch in global memory; it differs from simp_gpu_matmul_w4 in what it refuses:
  *   - cols may not exceed SIMP_W4_NOALLOC_MAX_COLS (larger shapes are rejected with SIMP_ERR_SHAPE);
  *   - the library must already be initialised (simp_gpu_init allocates; this call returns SIMP_ERR_STATE
  *     rather than initialising on demand);
- *   - the first call on a device looks the array's address up (cudaGetSymbolAddress): make that first
- *     call before starting any stream capture;
- *   - all calls share the array: calls whose kernels overlap on the GPU race, keep them on one stream. */
+ *   - the first call with a given tile shape sets a kernel attribute: make that first call before starting
+ *     any stream capture. */
 #define SIMP_W4_NOALLOC_MAX_COLS 16384
 int simp_gpu_matmul_w4_noalloc(const uint8_t* qweights_dev, const float* scales_dev,
                                const float* zeros_dev, const float* x_dev, float* out_dev, int64_t rows,

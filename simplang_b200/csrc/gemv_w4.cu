@@ -67,14 +67,9 @@ SIMP_API int simp_gpu_matmul_w4(const uint8_t* qw, const float* sc, const float*
   const bool sc_aligned = ((reinterpret_cast<uintptr_t>(sc + soff_chk) & 15u) == 0) &&
                           (!zr || (reinterpret_cast<uintptr_t>(zr + soff_chk) & 15u) == 0);
   const bool fast = sc_aligned && log2_cpg >= 0 && mode_ok && cols > 0 && cols % gs == 0 && cols <= 16384 && offset % 32 == 0 &&
-                    ((reinterpret_cast<uintptr_t>(base) & 15u) == 0) && rows <= 0x7fffffff;
+                    ((reinterpret_cast<uintptr_t>(base) & 15u) == 0) && ((reinterpret_cast<uintptr_t>(x) & 15u) == 0) &&
+                    rows <= 0x7fffffff;
   if (fast) {
-    // scratch: the packed form of x (80 bytes per 32 inputs), produced by one small kernel
-    uint8_t* xp = static_cast<uint8_t*>(scratch(w4_packed_bytes(cols), 5));
-    SIMP_REQUIRE(xp != nullptr, SIMP_ERR_CUDA, "matmul_w4: out of device memory for the packed input");
-    const int nchunks = int(cols / 32);
-    w4_pack_x_kernel<<<int(cdiv(nchunks, 8)), 256, 0, st>>>(x, xp, nchunks, nullptr, nullptr);
-    SIMP_LAUNCH_CHECK();
     const int64_t soff = scale_mode == 1 ? offset / gs : 0;
     W4Args a{};
     a.seg[0] = W4Seg{base, sc + soff, zr ? zr + soff : nullptr, out, int(rows)};
@@ -82,7 +77,7 @@ SIMP_API int simp_gpu_matmul_w4(const uint8_t* qw, const float* sc, const float*
     a.cols = int(cols);
     a.log2_cpg = log2_cpg;
     a.groups_per_row = int(cols / gs);
-    a.xp = xp;
+    a.x = x;
     a.res = nullptr;
     return w4_launch<W4_STORE>(a, st, ctx().sm_count);
   }
@@ -102,33 +97,11 @@ SIMP_API int simp_gpu_matmul_w4(const uint8_t* qw, const float* sc, const float*
 //
 // Some hosts may not allocate device memory when they call into this library: a serving process
 // that hands its whole memory budget to its own pool at start-up (a later cudaMalloc then fails or
-// fragments the pool), or code running where the CUDA runtime forbids allocation altogether.  The
-// regular entry point keeps the packed copy of x in a library arena that is created on first use
-// and grows on demand; this one keeps it in a fixed device array that is part of the library image.
-//
-// The array holds the packed form of at most SIMP_W4_NOALLOC_MAX_COLS inputs (80 bytes per 32
-// inputs = 40 KB).  Every GPU that loads the library carries it until the process exits.  All calls
-// share it: the pack kernel rewrites the part a call uses before the GEMV reads it, so nothing has
-// to be cleared, but two calls whose kernels overlap on the GPU (different streams or threads) race
-// on it -- keep calls on one stream.
+// fragments the pool), or code running where the CUDA runtime forbids allocation altogether.
+// The streaming kernel packs the input vector in every block's shared memory, so this entry point
+// needs no scratch in global memory at all: it only refuses to initialise the library (which
+// allocates) and shapes beyond SIMP_W4_NOALLOC_MAX_COLS columns.
 constexpr int64_t W4_NOALLOC_MAX_COLS = 16384;
-static __device__ __align__(256) uint8_t w4_noalloc_scratch[(W4_NOALLOC_MAX_COLS / 32) * (simp::W4_CHUNK_U4 * 16)];
-
-// Device address of the array for the current device.  The symbol's name is only a host-side handle;
-// kernels need the address cudaGetSymbolAddress reports, looked up once per device.
-static int w4_noalloc_scratch_ptr(uint8_t** out) {
-  static uint8_t* cached[64] = {};
-  int dev = -1;
-  SIMP_CUDA(cudaGetDevice(&dev));
-  SIMP_REQUIRE(dev >= 0 && dev < 64, SIMP_ERR_STATE, "matmul_w4_noalloc: unexpected device index %d", dev);
-  if (!cached[dev]) {
-    void* p = nullptr;
-    SIMP_CUDA(cudaGetSymbolAddress(&p, w4_noalloc_scratch));
-    cached[dev] = static_cast<uint8_t*>(p);
-  }
-  *out = cached[dev];
-  return SIMP_OK;
-}
 
 SIMP_API int simp_gpu_matmul_w4_noalloc(const uint8_t* qw, const float* sc, const float* zr, const float* x,
                                         float* out, int64_t rows, int64_t cols, int64_t gs, int64_t offset,
@@ -155,20 +128,16 @@ SIMP_API int simp_gpu_matmul_w4_noalloc(const uint8_t* qw, const float* sc, cons
   const bool sc_aligned = ((reinterpret_cast<uintptr_t>(sc + soff) & 15u) == 0) &&
                           (!zr || (reinterpret_cast<uintptr_t>(zr + soff) & 15u) == 0);
   const bool fast = sc_aligned && log2_cpg >= 0 && mode_ok && cols > 0 && cols % gs == 0 && offset % 32 == 0 &&
-                    ((reinterpret_cast<uintptr_t>(base) & 15u) == 0) && rows <= 0x7fffffff;
+                    ((reinterpret_cast<uintptr_t>(base) & 15u) == 0) && ((reinterpret_cast<uintptr_t>(x) & 15u) == 0) &&
+                    rows <= 0x7fffffff;
   if (fast) {
-    uint8_t* xp = nullptr;
-    if (int rc = w4_noalloc_scratch_ptr(&xp)) return rc;
-    const int nchunks = int(cols / 32);
-    w4_pack_x_kernel<<<int(cdiv(nchunks, 8)), 256, 0, st>>>(x, xp, nchunks, nullptr, nullptr);
-    SIMP_LAUNCH_CHECK();
     W4Args a{};
     a.seg[0] = W4Seg{base, sc + soff, zr ? zr + soff : nullptr, out, int(rows)};
     a.nseg = 1;
     a.cols = int(cols);
     a.log2_cpg = log2_cpg;
     a.groups_per_row = int(cols / gs);
-    a.xp = xp;
+    a.x = x;
     return w4_launch<W4_STORE>(a, st, ctx().sm_count);
   }
   // shapes outside the streaming kernel's domain use the general kernel, which needs no scratch at all

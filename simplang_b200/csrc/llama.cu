@@ -25,23 +25,14 @@ namespace simp {
 
 
 // ---------------------------------------------------------------------------------------------
-// x = embedding row of the current token.  For the W4 path one warp per 32-element chunk also emits the
-// packed form of x * norm_w (input of the first q/k/v GEMV) and the chunk's sum of squares.
+// x = embedding row of the current token.
 __global__ void __launch_bounds__(256) embed_kernel(float* __restrict__ x, const float* __restrict__ table,
-                                                    const int* __restrict__ ctl, int dim, const float* __restrict__ norm_w,
-                                                    uint8_t* __restrict__ xp, float* __restrict__ ss) {
+                                                    const int* __restrict__ ctl, int dim) {
   pdl_launch_dependents();
   pdl_wait();
   const int64_t token = ctl[0];
-  const int lane = threadIdx.x & 31;
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  const float v = i < dim ? table[token * dim + i] : 0.0f;
-  if (i < dim) x[i] = v;
-  if (xp && (i - lane) < dim) {
-    w4_pack_chunk(i < dim ? v * norm_w[i] : 0.0f, lane, xp + size_t(i >> 5) * (W4_CHUNK_U4 * 16));
-    const float q = warp_sum(v * v);
-    if (lane == 0) ss[i >> 5] = q;
-  }
+  if (i < dim) x[i] = table[token * dim + i];
 }
 
 // rmsnorm of one row before the classifier: y = (x / sqrt(ss/n + eps)) * w (the arithmetic of rmsnorm_any_kernel).
@@ -315,8 +306,7 @@ static int enqueue_token(LlamaModel& m, cudaStream_t st) {
   const int dim = int(c.dim), hd = int(c.hidden_dim), kv = int(m.kv_dim), hs = int(m.head_size);
   const int sms = ctx().sm_count;
   const bool pdl = true;
-  LAUNCH_OR_FAIL(embed_kernel, dim3((dim + 255) / 256), dim3(256), 0, st, false, m.x, m.tok_emb, m.ctl, dim,
-                 (const float*)nullptr, (uint8_t*)nullptr, m.ss);
+  LAUNCH_OR_FAIL(embed_kernel, dim3((dim + 255) / 256), dim3(256), 0, st, false, m.x, m.tok_emb, m.ctl, dim);
   for (int64_t l = 0; l < c.n_layers; ++l) {
     {
       GemvDecArgs g{};
@@ -359,9 +349,9 @@ static int enqueue_token(LlamaModel& m, cudaStream_t st) {
 }
 
 // W4 token, single GPU (R = 1) or tensor-parallel: every projection computes this rank's output rows from the full,
-// replicated input vector, and the row slices are exchanged with in-place all-gathers.  Packing of a
-// gathered vector (and the partial sums of the following rmsnorm) is done by the small pack kernel on
-// every rank, so each output element keeps the single-GPU arithmetic.
+// replicated input vector, and the row slices are exchanged with in-place all-gathers.  Every projection kernel
+// packs its (gathered) input vector itself and folds the preceding rmsnorm in, so each output element keeps the
+// single-GPU arithmetic.
 static int enqueue_token_tp(LlamaModel& m, cudaStream_t st) {
   const simp_llama_config& c = m.cfg;
   const int R = m.tp, rk = m.rank;
@@ -369,23 +359,20 @@ static int enqueue_token_tp(LlamaModel& m, cudaStream_t st) {
   const int dim_l = dim / R, kv_l = kv / R, hd_l = hd / R, V_l = int(c.vocab_size) / R, heads_l = int(c.n_heads) / R;
   const int sms = ctx().sm_count;
   const int log2_cpg = __builtin_ctzll(uint64_t(c.group_size / 32));
-  const int n_ss = dim / 32;
-  const bool chain = R == 1;  // no NCCL kernels in between: every launch can be a programmatic dependent
-  LAUNCH_OR_FAIL(embed_kernel, dim3((dim + 255) / 256), dim3(256), 0, st, false, m.x, m.tok_emb, m.ctl, dim, m.rms_att,
-                 m.xpA, m.ss);
+  const bool chain = R == 1;  // no exchange kernels in between: every launch can be a programmatic dependent
+  LAUNCH_OR_FAIL(embed_kernel, dim3((dim + 255) / 256), dim3(256), 0, st, false, m.x, m.tok_emb, m.ctl, dim);
   auto w4seg = [&](int fam, int64_t layer, int64_t rows_l, int64_t cols, float* out) {
     const int64_t o = m.loff[fam] + layer * rows_l * cols;
     return W4Seg{m.qweights + o / 2, m.scales + o / c.group_size, m.zeros ? m.zeros + o / c.group_size : nullptr, out,
                  int(rows_l)};
   };
-  auto w4args = [&](int cols, const uint8_t* xp) {
+  // input vector x; norm_w != nullptr folds rmsnorm(x, norm_w) into the projection
+  auto w4args = [&](int cols, const float* x, const float* norm_w) {
     W4Args a{};
-    a.cols = cols; a.log2_cpg = log2_cpg; a.groups_per_row = int(cols / c.group_size); a.xp = xp;
+    a.cols = cols; a.log2_cpg = log2_cpg; a.groups_per_row = int(cols / c.group_size);
+    a.x = x; a.mul = norm_w; a.norm = norm_w != nullptr;
     a.eps = 1e-5f; a.ss_div = float(dim);
     return a;
-  };
-  auto pack = [&](const float* x, uint8_t* xp, int n, const float* mul, float* ss, bool pdl) {
-    return launch_kernel(w4_pack_x_kernel, dim3((n / 32 + 7) / 8), dim3(256), 0, st, pdl, x, xp, n / 32, mul, ss);
   };
   // exchange of this rank's slice [rk * n, (rk + 1) * n) of an activation vector: peer stores inside the model's
   // symmetric arena (default) or an in-place NCCL all-gather (SIMP_TP_ALLGATHER=nccl, or no arena)
@@ -399,44 +386,40 @@ static int enqueue_token_tp(LlamaModel& m, cudaStream_t st) {
 #define TP_CUDA(e) do { cudaError_t e__ = (e); if (e__ != cudaSuccess) return set_error(SIMP_ERR_CUDA, "tp decode launch failed: %s", cudaGetErrorString(e__)); } while (0)
   for (int64_t l = 0; l < c.n_layers; ++l) {
     {
-      W4Args a = w4args(dim, m.xpA);
+      W4Args a = w4args(dim, m.x, m.rms_att + l * dim);
       a.seg[0] = w4seg(0, l, dim_l, dim, m.q);
       a.seg[1] = w4seg(1, l, kv_l, dim, m.k);
       a.seg[2] = w4seg(2, l, kv_l, dim, m.v);
-      a.nseg = 3; a.ss_part = m.ss; a.n_ss = n_ss;
-      if (int rc = w4_launch<W4_STORE>(a, st, sms, true)) return rc;
+      a.nseg = 3;
+      if (int rc = w4_launch<W4_STORE>(a, st, sms, chain)) return rc;
     }
     LAUNCH_OR_FAIL(attn_fused_kernel, dim3(unsigned(heads_l), unsigned(m.nsplit)), dim3(ATT_WARPS * 32), 0, st, true,
                    (const float*)m.q, (const float*)m.k, (const float*)m.v, m.kc, m.vc, m.attn_part, m.attn_cnt,
                    m.xb + rk * dim_l, (const int*)m.ctl, hs, kv_l, int(c.n_heads / c.n_kv_heads), int(c.seq_len), int(l),
                    m.nsplit);
     if (int rc = gather(m.xb, dim_l)) return rc;
-    TP_CUDA(pack(m.xb, m.xpB, dim, nullptr, nullptr, chain));
     {
-      W4Args a = w4args(dim, m.xpB);
+      W4Args a = w4args(dim, m.xb, nullptr);
       a.seg[0] = w4seg(3, l, dim_l, dim, m.x + rk * dim_l);
       a.nseg = 1; a.res = m.x + rk * dim_l;
-      if (int rc = w4_launch<W4_ADD>(a, st, sms, true)) return rc;
+      if (int rc = w4_launch<W4_ADD>(a, st, sms, chain)) return rc;
     }
     if (int rc = gather(m.x, dim_l)) return rc;
-    TP_CUDA(pack(m.x, m.xpA, dim, m.rms_ffn + l * dim, m.ss, chain));
     {
-      W4Args g = w4args(dim, m.xpA);
+      W4Args g = w4args(dim, m.x, m.rms_ffn + l * dim);
       g.seg[0] = w4seg(4, l, hd_l, dim, m.hb + rk * hd_l);
       g.seg[1] = w4seg(6, l, hd_l, dim, nullptr);
-      g.nseg = 2; g.ss_part = m.ss; g.n_ss = n_ss;
-      if (int rc = w4_launch<W4_GATE_UP>(g, st, sms, true)) return rc;
+      g.nseg = 2;
+      if (int rc = w4_launch<W4_GATE_UP>(g, st, sms, chain)) return rc;
     }
     if (int rc = gather(m.hb, hd_l)) return rc;
-    TP_CUDA(pack(m.hb, m.xpB, hd, nullptr, nullptr, chain));
     {
-      W4Args d = w4args(hd, m.xpB);
+      W4Args d = w4args(hd, m.hb, nullptr);
       d.seg[0] = w4seg(5, l, dim_l, hd, m.x + rk * dim_l);
       d.nseg = 1; d.res = m.x + rk * dim_l;
-      if (int rc = w4_launch<W4_ADD>(d, st, sms, true)) return rc;
+      if (int rc = w4_launch<W4_ADD>(d, st, sms, chain)) return rc;
     }
     if (int rc = gather(m.x, dim_l)) return rc;
-    if (l + 1 < c.n_layers) TP_CUDA(pack(m.x, m.xpA, dim, m.rms_att + (l + 1) * dim, m.ss, chain));
   }
   LAUNCH_OR_FAIL(dec_rmsnorm_kernel, dim3(1), dim3(1024), 0, st, chain, (const float*)m.x, (const float*)m.rms_final,
                  m.xb, dim, 1e-5f);
@@ -553,9 +536,6 @@ SIMP_API int simp_llama_create(const simp_llama_config* cfg, void** model) {
   A((void**)&m->vc, kv_bytes);
   A((void**)&m->attn_part, size_t(c.n_heads) * (m->nsplit > 4 ? m->nsplit : 4) * (hs + 2) * 4);
   A((void**)&m->attn_cnt, size_t(c.n_heads) * 4);
-  A((void**)&m->xpA, w4_packed_bytes(int64_t(mx) + 32));
-  A((void**)&m->xpB, w4_packed_bytes(int64_t(mx) + 32));
-  A((void**)&m->ss, (mx / 32 + 1) * 4);
   A((void**)&m->ctl, 64);
   A((void**)&m->pk_bar, 64);
   A((void**)&m->pk_best_val, size_t(ctx().sm_count) * 4);
@@ -756,7 +736,7 @@ SIMP_API int simp_llama_destroy(void* model) {
   }
   void* ptrs[] = {m->tok_emb, m->rms_att, m->rms_ffn, m->rms_final, m->wcls, m->wq, m->wk, m->wv, m->wo, m->w1, m->w2,
                   m->w3, m->qweights, m->scales, m->zeros, m->x, m->xb, m->hb, m->q, m->k, m->v, m->logits, m->kc,
-                  m->vc, m->attn_part, m->attn_cnt, m->xpA, m->xpB, m->ss, m->ctl, m->prompt, m->out_tokens,
+                  m->vc, m->attn_part, m->attn_cnt, m->ctl, m->prompt, m->out_tokens,
                   m->pk_bar, m->pk_best_val, m->pk_best_idx};
   for (void* p : ptrs)
     if (p) cudaFree(p);

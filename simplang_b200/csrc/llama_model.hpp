@@ -26,8 +26,6 @@ struct LlamaModel {
   float *x = nullptr, *xb = nullptr, *hb = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *logits = nullptr;
   float *kc = nullptr, *vc = nullptr, *attn_part = nullptr;
   int* attn_cnt = nullptr;  // per-head arrival counters of the attention kernel (zero between launches)
-  uint8_t *xpA = nullptr, *xpB = nullptr;  // packed activations for the W4 kernels (ping-pong)
-  float* ss = nullptr;                      // per-tile partial sums of squares (deferred rmsnorm)
   int* ctl = nullptr;     // [0] token, [1] pos, [2] n_prompt, [3] step, [4] next (argmax)
   int32_t *prompt = nullptr, *out_tokens = nullptr;
   int64_t prompt_cap = 0, out_cap = 0;

@@ -11,8 +11,8 @@
 // barriers only gate the compute, never the weight stream, so HBM keeps streaming while a phase waits for
 // its input vector and the ring is full when the phase starts.
 //
-// Compute: the activation vector is packed to 16-bit block floating point in shared memory (the layout of
-// w4_pack_chunk, four threads per chunk), a tile is cut into slabs of 16 rows and the 16 warps are arranged as
+// Compute: the activation vector is packed to 16-bit block floating point in shared memory (w4_pack_quarter,
+// four threads per chunk), a tile is cut into slabs of 16 rows and the 16 warps are arranged as
 // slabs x matrices x interleaved sets of 128-weight spans; each warp runs the tensor-core integer dot products of
 // w4_mma_spans (exact integer accumulation per 32-weight chunk, see w4_core.cuh), partial sums of the span sets
 // are added in set order.  The next rmsnorm is deferred exactly as in the per-op path:
@@ -110,45 +110,6 @@ __device__ __forceinline__ void pw_tile_partials(const uint8_t* slot, int tr_i, 
     }
 }
 
-// Eight inputs of a chunk packed by one thread, the four threads of a chunk (adjacent lanes, j = lane & 3) sharing
-// the maximum and the sums by two shuffles each: thread j produces word j of both byte planes (the layout and
-// arithmetic of w4_pack_chunk).  Every block packs the whole vector for itself, so the pack must be short.
-// All 32 lanes of a warp must call this together; `active` = this thread's chunk exists.
-__device__ __forceinline__ void pw_pack_quarter(const float (&v)[8], bool active, int j, uint8_t* chunk) {
-  float amax = 0.0f, sumx = 0.0f;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    amax = fmaxf(amax, fabsf(v[i]));
-    sumx += v[i];
-  }
-  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-  const float inv = amax > 0.0f ? 32512.0f / amax : 0.0f;
-  int sum16 = 0;
-  uint32_t xh[2] = {0u, 0u}, xl[2] = {0u, 0u};
-#pragma unroll
-  for (int e = 0; e < 8; ++e) {
-    int x16 = __float2int_rn(v[e] * inv);
-    x16 = max(-32512, min(32512, x16));
-    sum16 += x16;
-    const int h = (x16 + 128) >> 8;
-    const int l = x16 - (h << 8);
-    xh[e & 1] |= uint32_t(h & 255) << (8 * (e >> 1));
-    xl[e & 1] |= uint32_t(l & 255) << (8 * (e >> 1));
-  }
-  sumx += __shfl_xor_sync(0xffffffffu, sumx, 1);
-  sumx += __shfl_xor_sync(0xffffffffu, sumx, 2);
-  sum16 += __shfl_xor_sync(0xffffffffu, sum16, 1);
-  sum16 += __shfl_xor_sync(0xffffffffu, sum16, 2);
-  if (active) {
-    *reinterpret_cast<uint2*>(chunk + j * 8) = make_uint2(xh[0], xh[1]);
-    *reinterpret_cast<uint2*>(chunk + 32 + j * 8) = make_uint2(xl[0], xl[1]);
-    if (j == 0)
-      *reinterpret_cast<uint4*>(chunk + 64) =
-          make_uint4(__float_as_uint(amax > 0.0f ? amax / 32512.0f : 0.0f), __float_as_uint(sumx), uint32_t(sum16), 0u);
-  }
-}
-
 // Packs n32 chunks of a global vector (optionally times mul) into xp, four threads per chunk: two 16-byte loads
 // through L2 per thread and operand.  Returns this thread's share of sum(x^2) of the unscaled input.
 __device__ __forceinline__ float pw_pack_global(const float* __restrict__ x, const float* __restrict__ mul, uint8_t* xp,
@@ -170,7 +131,7 @@ __device__ __forceinline__ float pw_pack_global(const float* __restrict__ x, con
         v[0] *= m0.x; v[1] *= m0.y; v[2] *= m0.z; v[3] *= m0.w; v[4] *= m1.x; v[5] *= m1.y; v[6] *= m1.z; v[7] *= m1.w;
       }
     }
-    pw_pack_quarter(v, active, q & 3, xp + size_t(q >> 2) * (W4_CHUNK_U4 * 16));
+    w4_pack_quarter(v, active, q & 3, xp + size_t(q >> 2) * (W4_CHUNK_U4 * 16));
   }
   return ss;
 }
@@ -184,7 +145,7 @@ __device__ __forceinline__ void pw_pack_shared(const float* vec, uint8_t* xp, in
       const float4 t0 = src[0], t1 = src[1];
       v[0] = t0.x; v[1] = t0.y; v[2] = t0.z; v[3] = t0.w; v[4] = t1.x; v[5] = t1.y; v[6] = t1.z; v[7] = t1.w;
     }
-    pw_pack_quarter(v, active, q & 3, xp + size_t(q >> 2) * (W4_CHUNK_U4 * 16));
+    w4_pack_quarter(v, active, q & 3, xp + size_t(q >> 2) * (W4_CHUNK_U4 * 16));
   }
 }
 

@@ -6,7 +6,7 @@
 //
 // The kernel is HBM-bound only if the per-weight instruction count stays well below one: lop3, shf, dp4a and
 // the integer multiply-add share a pipe that issues 64 lane-operations per clock and SM, while HBM delivers ~50
-// weights per clock and SM.  So the activations are first packed (w4_pack_x_kernel) into 16-bit block floating
+// weights per clock and SM.  So every block first packs the activations (w4_pack_quarter) into 16-bit block floating
 // point -- per chunk of 32 inputs a scale sx = max|x|/32512 and x16 = rint(x/sx) split into two signed bytes
 // x16 = 256*xh + xl -- and the integer dot products run on the tensor cores as warp-level
 // mma.sync.m16n8k32 (u8 nibbles x s8 input bytes -> s32): a GEMV has one column, so the eight columns of the
@@ -28,88 +28,47 @@ namespace simp {
 
 constexpr int W4_WARPS = 8;
 constexpr int W4_CHUNK_U4 = 5;  // uint4 per packed chunk
+constexpr int W4_PACK_ROUNDS = 3;   // rounds of input loads a thread keeps in flight while packing
 
 inline size_t w4_packed_bytes(int64_t cols) { return size_t(cols / 32) * W4_CHUNK_U4 * 16; }
 
-// One warp per 32-input chunk.  `x` may be produced by a fused prologue: see w4_pack_value().
-__device__ __forceinline__ void w4_pack_chunk(float xv, int lane, uint8_t* chunk_bytes) {
-  const float amax = warp_max(fabsf(xv));
+// Eight inputs of a chunk packed by one thread, the four threads of a chunk (adjacent lanes, j = lane & 3) sharing
+// the maximum and the sums by two shuffles each: thread j produces word j of both byte planes.  Every block packs
+// the whole vector for itself, so the pack must be short.  All 32 lanes of a warp must call this together;
+// `active` = this thread's chunk exists.
+__device__ __forceinline__ void w4_pack_quarter(const float (&v)[8], bool active, int j, uint8_t* chunk) {
+  float amax = 0.0f, sumx = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    amax = fmaxf(amax, fabsf(v[i]));
+    sumx += v[i];
+  }
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
   const float inv = amax > 0.0f ? 32512.0f / amax : 0.0f;
-  int x16 = __float2int_rn(xv * inv);
-  x16 = max(-32512, min(32512, x16));
-  const int xh = (x16 + 128) >> 8;   // nearest multiple of 256, in [-127, 127]
-  const int xl = x16 - (xh << 8);    // signed low byte, in [-128, 127]
-  const int j = lane >> 3, e = lane & 7;
-  const int pos = j * 8 + (e & 1) * 4 + (e >> 1);
-  chunk_bytes[pos] = uint8_t(xh);
-  chunk_bytes[pos + 32] = uint8_t(xl);
-  const float sumx = warp_sum(xv);
-  int sum16 = x16;
+  int sum16 = 0;
+  uint32_t xh[2] = {0u, 0u}, xl[2] = {0u, 0u};
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) sum16 += __shfl_xor_sync(0xffffffffu, sum16, o);
-  if (lane == 0) {
-    uint4 meta;
-    meta.x = __float_as_uint(amax > 0.0f ? amax / 32512.0f : 0.0f);
-    meta.y = __float_as_uint(sumx);
-    meta.z = uint32_t(sum16);
-    meta.w = 0;
-    *reinterpret_cast<uint4*>(chunk_bytes + 64) = meta;
+  for (int e = 0; e < 8; ++e) {
+    int x16 = __float2int_rn(v[e] * inv);
+    x16 = max(-32512, min(32512, x16));
+    sum16 += x16;
+    const int h = (x16 + 128) >> 8;   // nearest multiple of 256, in [-127, 127]
+    const int l = x16 - (h << 8);     // signed low byte, in [-128, 127]
+    xh[e & 1] |= uint32_t(h & 255) << (8 * (e >> 1));
+    xl[e & 1] |= uint32_t(l & 255) << (8 * (e >> 1));
   }
-}
-
-// Packs x (optionally x[i]*mul[i], the next rmsnorm's weight) chunk by chunk; ss_out (optional) receives the
-// sum of squares of the unscaled x per chunk -- the deterministic partials of that rmsnorm.
-static __global__ void __launch_bounds__(256) w4_pack_x_kernel(const float* __restrict__ x, uint8_t* __restrict__ xp,
-                                                               int nchunks, const float* __restrict__ mul,
-                                                               float* __restrict__ ss_out) {
-  pdl_launch_dependents();
-  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-  // the norm weights never change: requested before waiting for the producer of x (they miss in L2 once per layer)
-  const float mw = (mul && warp < nchunks) ? __ldg(mul + warp * 32 + lane) : 1.0f;
-  pdl_wait();
-  if (warp >= nchunks) return;
-  const float v = x[warp * 32 + lane];
-  w4_pack_chunk(mul ? v * mw : v, lane, xp + size_t(warp) * (W4_CHUNK_U4 * 16));
-  if (ss_out) {
-    const float q = warp_sum(v * v);
-    if (lane == 0) ss_out[warp] = q;
+  sumx += __shfl_xor_sync(0xffffffffu, sumx, 1);
+  sumx += __shfl_xor_sync(0xffffffffu, sumx, 2);
+  sum16 += __shfl_xor_sync(0xffffffffu, sum16, 1);
+  sum16 += __shfl_xor_sync(0xffffffffu, sum16, 2);
+  if (active) {
+    *reinterpret_cast<uint2*>(chunk + j * 8) = make_uint2(xh[0], xh[1]);
+    *reinterpret_cast<uint2*>(chunk + 32 + j * 8) = make_uint2(xl[0], xl[1]);
+    if (j == 0)
+      *reinterpret_cast<uint4*>(chunk + 64) =
+          make_uint4(__float_as_uint(amax > 0.0f ? amax / 32512.0f : 0.0f), __float_as_uint(sumx), uint32_t(sum16), 0u);
   }
-}
-
-__device__ __forceinline__ uint4 ldg_nc_u4(const uint4* p) {
-  uint4 v;
-  asm("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-      : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-      : "l"(p));
-  return v;
-}
-__device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c) {  // unsigned a bytes x signed b bytes
-  int d;
-  asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-  return d;
-}
-__device__ __forceinline__ uint32_t dp4a_uu(uint32_t a, uint32_t b, uint32_t c) {
-  uint32_t d;
-  asm("dp4a.u32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-  return d;
-}
-
-// sum_j q_j * x16_j over one 32-weight chunk: weights `w` (4 words), packed inputs `xq` (4 uint4).
-__device__ __forceinline__ int w4_chunk_dot(const uint4& w, const uint4* xq) {
-  // four independent accumulation chains (high/low byte x low/high nibble) keep the dp4a pipe fed
-  int ah0 = 0, ah1 = 0;
-  uint32_t al0 = 0, al1 = 0;
-  const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
-#pragma unroll
-  for (int wd = 0; wd < 4; ++wd) {
-    const uint32_t lo = ws[wd] & 0x0F0F0F0Fu;
-    const uint32_t hi = (ws[wd] >> 4) & 0x0F0F0F0Fu;
-    ah0 = dp4a_us(lo, xq[wd].x, ah0);
-    ah1 = dp4a_us(hi, xq[wd].y, ah1);
-    al0 = dp4a_uu(lo, xq[wd].z, al0);
-    al1 = dp4a_uu(hi, xq[wd].w, al1);
-  }
-  return (ah0 + ah1) * 256 + int(al0 + al1);
 }
 
 // One matrix segment of a launch.  All segments share cols / group size / the packed input.
@@ -125,11 +84,11 @@ struct W4Args {
   W4Seg seg[3];
   int nseg;
   int cols, log2_cpg, groups_per_row;
-  const uint8_t* xp;       // packed input
-  // Deferred rmsnorm of the input: when ss_part != nullptr the packed input holds x[i]*w_norm[i] and every
-  // dot product is multiplied by 1/sqrt(sum(ss_part[0..n_ss)) / ss_div + eps).
-  const float* ss_part;
-  int n_ss;
+  const float* x;          // input vector (cols floats, 32-byte aligned)
+  // Fused rmsnorm of the input: with mul != nullptr the packed input holds x[i]*mul[i], and with norm != 0 every
+  // dot product is multiplied by 1/sqrt(sum(x^2) / ss_div + eps).
+  const float* mul;
+  int norm;
   float ss_div, eps;
   const float* res;        // W4_ADD: out[i] = res[i] + dot (segment 0 only)
   int total_tiles;         // row tiles over all segments (W4_GATE_UP: over segment 0)
@@ -221,14 +180,15 @@ __device__ __forceinline__ void w4_mma_spans(const W4Tile& tl, int r0, int vrows
 // per matrix (cp.async.bulk global -> shared, completion on an mbarrier; rows of a row-major matrix are
 // contiguous) plus one for its scales, two tiles in flight.  The copies of the first two tiles are issued
 // before the kernel waits for the producer of its input vector, so under programmatic dependent launch
-// the weights of the next projection are already streaming while the previous kernel finishes.
+// the weights of the next projection are already streaming while the previous kernel finishes.  The input
+// vector is then packed by every block for itself (no separate pack launch, no packed copy in global memory).
 // Warps then read weights, scales and the packed input from shared memory only: a tile is TR/16 slabs of 16
 // rows (TR == 8: one half-used slab), the eight warps split slabs x interleaved 128-weight spans, and the
 // per-warp partial sums of a row meet in a small shared array.
 template <int MODE, int TR>
 __global__ void __launch_bounds__(W4_WARPS * 32, 3) w4_gemv_kernel(const W4Args a) {
   extern __shared__ __align__(128) uint8_t smem[];
-  __shared__ float sh_inv_r;
+  __shared__ float sh_ss[W4_WARPS];
   __shared__ __align__(8) uint64_t bars[2];
   __shared__ int abort_flag;
   constexpr int NM = MODE == W4_GATE_UP ? 2 : 1;
@@ -306,22 +266,63 @@ __global__ void __launch_bounds__(W4_WARPS * 32, 3) w4_gemv_kernel(const W4Args 
   // Weights never change: the first two tiles are requested before waiting for the producer of the input.
   issue(0);
   issue(1);
+  // Pack the input vector into this block's shared memory, four threads per chunk, W4_PACK_ROUNDS rounds of
+  // loads in flight together.  The norm weights never change: the first batch is requested before waiting for
+  // the producer of x (they miss in L2 once per layer).
   pdl_launch_dependents();
-  pdl_wait();
-  for (int i = threadIdx.x; i < nchunks * W4_CHUNK_U4; i += blockDim.x)
-    xs[i] = __ldg(reinterpret_cast<const uint4*>(a.xp) + i);
-  if (warp == 0) {
-    float inv_r = 1.0f;
-    if (a.ss_part) {
-      float ss = 0.0f;
-      for (int i = lane; i < a.n_ss; i += 32) ss += a.ss_part[i];
-      ss = warp_sum(ss);
-      inv_r = 1.0f / sqrtf(ss / a.ss_div + a.eps);
+  const int ntask = nchunks * 4;
+  float ssl = 0.0f;
+  float4 mv[W4_PACK_ROUNDS][2];
+#pragma unroll
+  for (int r = 0; r < W4_PACK_ROUNDS; ++r) {
+    const int q = r * int(blockDim.x) + int(threadIdx.x);
+    mv[r][0] = mv[r][1] = make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+    if (a.mul && q < ntask) {
+      mv[r][0] = __ldg(reinterpret_cast<const float4*>(a.mul) + 2 * q);
+      mv[r][1] = __ldg(reinterpret_cast<const float4*>(a.mul) + 2 * q + 1);
     }
-    if (lane == 0) sh_inv_r = inv_r;
+  }
+  pdl_wait();
+  for (int b0 = 0; b0 < ntask; b0 += W4_PACK_ROUNDS * int(blockDim.x)) {
+    float4 xv[W4_PACK_ROUNDS][2];
+#pragma unroll
+    for (int r = 0; r < W4_PACK_ROUNDS; ++r) {
+      const int q = b0 + r * int(blockDim.x) + int(threadIdx.x);
+      xv[r][0] = xv[r][1] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      if (q < ntask) {
+        xv[r][0] = __ldcg(reinterpret_cast<const float4*>(a.x) + 2 * q);
+        xv[r][1] = __ldcg(reinterpret_cast<const float4*>(a.x) + 2 * q + 1);
+        if (b0 > 0 && a.mul) {
+          mv[r][0] = __ldg(reinterpret_cast<const float4*>(a.mul) + 2 * q);
+          mv[r][1] = __ldg(reinterpret_cast<const float4*>(a.mul) + 2 * q + 1);
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < W4_PACK_ROUNDS; ++r) {
+      const int q = b0 + r * int(blockDim.x) + int(threadIdx.x);
+      if (b0 + r * int(blockDim.x) < ntask) {   // uniform over the block: whole warps take part in the shuffles
+        float v[8] = {xv[r][0].x, xv[r][0].y, xv[r][0].z, xv[r][0].w, xv[r][1].x, xv[r][1].y, xv[r][1].z, xv[r][1].w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ssl = fmaf(v[i], v[i], ssl);
+        v[0] *= mv[r][0].x; v[1] *= mv[r][0].y; v[2] *= mv[r][0].z; v[3] *= mv[r][0].w;
+        v[4] *= mv[r][1].x; v[5] *= mv[r][1].y; v[6] *= mv[r][1].z; v[7] *= mv[r][1].w;
+        w4_pack_quarter(v, q < ntask, q & 3, smem + size_t(q >> 2) * (W4_CHUNK_U4 * 16));
+      }
+    }
+  }
+  if (a.norm) {
+    ssl = warp_sum(ssl);
+    if (lane == 0) sh_ss[warp] = ssl;
   }
   __syncthreads();
-  const float inv_r = sh_inv_r;
+  float inv_r = 1.0f;
+  if (a.norm) {
+    float ss = 0.0f;
+#pragma unroll
+    for (int w = 0; w < W4_WARPS; ++w) ss += sh_ss[w];
+    inv_r = 1.0f / sqrtf(ss / a.ss_div + a.eps);
+  }
   const int slab = warp % SL, kpart = warp / SL;
 
   for (int q = 0; q < my_steps; ++q) {
@@ -386,6 +387,8 @@ inline int w4_launch(W4Args a, cudaStream_t st, int sm_count, bool pdl = false) 
     if (s < nseg_tiles) total_rows += a.seg[s].rows;
   }
   if (total_rows == 0) return SIMP_OK;
+  if ((reinterpret_cast<uintptr_t>(a.x) & 15u) || (reinterpret_cast<uintptr_t>(a.mul) & 15u))
+    return set_error(SIMP_ERR_SHAPE, "w4_gemv: the input vector and the norm weights must be 16-byte aligned");
   // Rows per tile.  Larger tiles mean fewer barriers per weight; smaller ones keep every SM busy on the short
   // matrices of batch-1 decode.  Two tiles must fit in shared memory next to the packed input, with room for
   // 2-3 blocks per SM.
