@@ -99,6 +99,9 @@ __device__ __forceinline__ unsigned ld_acquire_sys_u32(const unsigned* p) {
 }
 __global__ void __launch_bounds__(256) ll_allgather_kernel(LlPeers peers, unsigned* seq, int rank, int world, size_t offset,
                                                            size_t slice, int* status) {
+  // a consumer launched as a programmatic dependent may start its prologue (weight requests) now; its
+  // griddepcontrol.wait still returns only when this exchange has completed
+  pdl_launch_dependents();
   const unsigned epoch = *seq + 1u;
   const uint8_t* mine = peers.buf[rank] + offset + size_t(rank) * slice;
   const bool vec = ((reinterpret_cast<uintptr_t>(mine) | slice) & 15u) == 0;

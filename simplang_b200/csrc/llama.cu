@@ -360,6 +360,8 @@ static int enqueue_token_tp(LlamaModel& m, cudaStream_t st) {
   const int sms = ctx().sm_count;
   const int log2_cpg = __builtin_ctzll(uint64_t(c.group_size / 32));
   const bool chain = R == 1;  // no exchange kernels in between: every launch can be a programmatic dependent
+  // projections that follow an exchange: programmatic dependents of the peer-store kernel, plain launches after NCCL
+  const bool chain_x = chain || (m.tp_arena && !m.tp_nccl);
   LAUNCH_OR_FAIL(embed_kernel, dim3((dim + 255) / 256), dim3(256), 0, st, false, m.x, m.tok_emb, m.ctl, dim);
   auto w4seg = [&](int fam, int64_t layer, int64_t rows_l, int64_t cols, float* out) {
     const int64_t o = m.loff[fam] + layer * rows_l * cols;
@@ -391,7 +393,7 @@ static int enqueue_token_tp(LlamaModel& m, cudaStream_t st) {
       a.seg[1] = w4seg(1, l, kv_l, dim, m.k);
       a.seg[2] = w4seg(2, l, kv_l, dim, m.v);
       a.nseg = 3;
-      if (int rc = w4_launch<W4_STORE>(a, st, sms, chain)) return rc;
+      if (int rc = w4_launch<W4_STORE>(a, st, sms, chain_x)) return rc;
     }
     LAUNCH_OR_FAIL(attn_fused_kernel, dim3(unsigned(heads_l), unsigned(m.nsplit)), dim3(ATT_WARPS * 32), 0, st, true,
                    (const float*)m.q, (const float*)m.k, (const float*)m.v, m.kc, m.vc, m.attn_part, m.attn_cnt,
@@ -402,7 +404,7 @@ static int enqueue_token_tp(LlamaModel& m, cudaStream_t st) {
       W4Args a = w4args(dim, m.xb, nullptr);
       a.seg[0] = w4seg(3, l, dim_l, dim, m.x + rk * dim_l);
       a.nseg = 1; a.res = m.x + rk * dim_l;
-      if (int rc = w4_launch<W4_ADD>(a, st, sms, chain)) return rc;
+      if (int rc = w4_launch<W4_ADD>(a, st, sms, chain_x)) return rc;
     }
     if (int rc = gather(m.x, dim_l)) return rc;
     {
@@ -410,14 +412,14 @@ static int enqueue_token_tp(LlamaModel& m, cudaStream_t st) {
       g.seg[0] = w4seg(4, l, hd_l, dim, m.hb + rk * hd_l);
       g.seg[1] = w4seg(6, l, hd_l, dim, nullptr);
       g.nseg = 2;
-      if (int rc = w4_launch<W4_GATE_UP>(g, st, sms, chain)) return rc;
+      if (int rc = w4_launch<W4_GATE_UP>(g, st, sms, chain_x)) return rc;
     }
     if (int rc = gather(m.hb, hd_l)) return rc;
     {
       W4Args d = w4args(hd, m.hb, nullptr);
       d.seg[0] = w4seg(5, l, dim_l, hd, m.x + rk * dim_l);
       d.nseg = 1; d.res = m.x + rk * dim_l;
-      if (int rc = w4_launch<W4_ADD>(d, st, sms, chain)) return rc;
+      if (int rc = w4_launch<W4_ADD>(d, st, sms, chain_x)) return rc;
     }
     if (int rc = gather(m.x, dim_l)) return rc;
   }
