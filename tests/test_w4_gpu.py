@@ -29,7 +29,9 @@ def row_scale(oracle, qw, sc, zr, x, rows, cols, gs, offset):
 
 
 @pytest.mark.parametrize("rows,cols,gs", [(3200, 3200, 64), (8640, 3200, 64), (3200, 8640, 64), (1536, 1536, 128),
-                                          (100, 256, 32), (7, 128, 128), (33, 1024, 256), (9600, 3200, 32)])
+                                          (100, 256, 32), (7, 128, 128), (33, 1024, 256), (9600, 3200, 32),
+                                          # chunk counts that leave a partial 128-weight span; enough rows for 32-row tiles
+                                          (50, 160, 32), (40, 224, 32), (12000, 512, 64), (20001, 1024, 128)])
 @pytest.mark.parametrize("symmetric", [True, False])
 def test_matmul_w4_per_matrix(gpu, oracle, rows, cols, gs, symmetric):
     rng = np.random.default_rng(rows + cols + gs)
