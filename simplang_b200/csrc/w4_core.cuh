@@ -183,18 +183,19 @@ __device__ __forceinline__ void w4_mma_spans(const W4Tile& tl, int r0, int vrows
 // the weights of the next projection are already streaming while the previous kernel finishes.  The input
 // vector is then packed by every block for itself (no separate pack launch, no packed copy in global memory).
 // Warps then read weights, scales and the packed input from shared memory only: a tile is TR/16 slabs of 16
-// rows (TR == 8: one half-used slab), the eight warps split slabs x interleaved 128-weight spans, and the
-// per-warp partial sums of a row meet in a small shared array.
-template <int MODE, int TR>
-__global__ void __launch_bounds__(W4_WARPS * 32, 3) w4_gemv_kernel(const W4Args a) {
+// rows (TR == 8: one half-used slab), the NW warps split slabs x interleaved 128-weight spans, and the
+// per-warp partial sums of a row meet in a small shared array.  NW = 8 with up to three blocks per SM; for rows so
+// long that only 8-row tiles would fit that way, NW = 16 with 16-row tiles and one block per SM.
+template <int MODE, int TR, int NW>
+__global__ void __launch_bounds__(NW * 32, NW == 8 ? 3 : 1) w4_gemv_kernel(const W4Args a) {
   extern __shared__ __align__(128) uint8_t smem[];
-  __shared__ float sh_ss[W4_WARPS];
+  __shared__ float sh_ss[NW];
   __shared__ __align__(8) uint64_t bars[2];
   __shared__ int abort_flag;
   constexpr int NM = MODE == W4_GATE_UP ? 2 : 1;
   constexpr int S_ROWS = TR;
   constexpr int SL = TR == 32 ? 2 : 1;      // slabs per tile
-  constexpr int KP = W4_WARPS / SL;         // warps that split the spans of one slab
+  constexpr int KP = NW / SL;               // warps that split the spans of one slab
   constexpr bool HALF = TR == 8;
   __shared__ float red[2][NM][KP][S_ROWS];
   const int nchunks = a.cols >> 5;
@@ -320,7 +321,7 @@ __global__ void __launch_bounds__(W4_WARPS * 32, 3) w4_gemv_kernel(const W4Args 
   if (a.norm) {
     float ss = 0.0f;
 #pragma unroll
-    for (int w = 0; w < W4_WARPS; ++w) ss += sh_ss[w];
+    for (int w = 0; w < NW; ++w) ss += sh_ss[w];
     inv_r = 1.0f / sqrtf(ss / a.ss_div + a.eps);
   }
   const int slab = warp % SL, kpart = warp / SL;
@@ -398,6 +399,10 @@ inline int w4_launch(W4Args a, cudaStream_t st, int sm_count, bool pdl = false) 
   while (tr > 8 && need(tr) > 74 * 1024) tr >>= 1;
   if (tr == 8 && need(16) <= 112 * 1024) tr = 16;
   while (tr > 8 && total_rows / tr < 2 * int64_t(sm_count)) tr >>= 1;
+  // long rows: 8-row tiles would use half of every MMA; 16-row tiles with 16 warps in one block per SM instead
+  const bool wide = !getenv("SIMP_W4_NO_WIDE") && tr == 8 && need(16) > 112 * 1024 && need(16) <= 220 * 1024 && total_rows / 16 >= int64_t(sm_count);
+  if (wide) tr = 16;
+  const int nw = wide ? 16 : W4_WARPS;
   const size_t smem = need(tr);
   if (smem > 220 * 1024) return set_error(SIMP_ERR_SHAPE, "w4_gemv: row too long for the shared-memory pipeline");
   int g = 0;
@@ -408,22 +413,23 @@ inline int w4_launch(W4Args a, cudaStream_t st, int sm_count, bool pdl = false) 
   a.seg_tile_start[nseg_tiles] = g;
   a.total_tiles = g;
   int per_sm = int((227 * 1024) / (smem + 4096));
-  per_sm = per_sm < 1 ? 1 : (per_sm > 3 ? 3 : per_sm);
+  per_sm = wide || per_sm < 1 ? 1 : (per_sm > 3 ? 3 : per_sm);
   const int cap = sm_count * per_sm;
   const int grid = g < cap ? g : cap;
   cudaError_t e;
-#define W4_LAUNCH_TR(TRV)                                                                                   \
+#define W4_LAUNCH_TR(TRV, NWV)                                                                              \
   do {                                                                                                      \
     static bool attr_set = false;                                                                           \
     if (!attr_set) {                                                                                        \
-      cudaFuncSetAttribute(w4_gemv_kernel<MODE, TRV>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024); \
+      cudaFuncSetAttribute(w4_gemv_kernel<MODE, TRV, NWV>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024); \
       attr_set = true;                                                                                      \
     }                                                                                                       \
-    e = launch_kernel(w4_gemv_kernel<MODE, TRV>, dim3(grid), dim3(W4_WARPS * 32), smem, st, pdl, a);        \
+    e = launch_kernel(w4_gemv_kernel<MODE, TRV, NWV>, dim3(grid), dim3(NWV * 32), smem, st, pdl, a);        \
   } while (0)
-  if (tr == 32) W4_LAUNCH_TR(32);
-  else if (tr == 16) W4_LAUNCH_TR(16);
-  else W4_LAUNCH_TR(8);
+  if (nw == 16) W4_LAUNCH_TR(16, 16);
+  else if (tr == 32) W4_LAUNCH_TR(32, 8);
+  else if (tr == 16) W4_LAUNCH_TR(16, 8);
+  else W4_LAUNCH_TR(8, 8);
 #undef W4_LAUNCH_TR
   if (e != cudaSuccess) return set_error(SIMP_ERR_CUDA, "w4_gemv launch failed: %s", cudaGetErrorString(e));
   return SIMP_OK;
