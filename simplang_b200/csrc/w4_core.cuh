@@ -178,7 +178,7 @@ __device__ __forceinline__ void w4_mma_spans(const W4Tile& tl, int r0, int vrows
 
 // Streaming kernel.  A block owns tiles of TR consecutive rows; a tile is fetched by ONE bulk async copy
 // per matrix (cp.async.bulk global -> shared, completion on an mbarrier; rows of a row-major matrix are
-// contiguous) plus one for its scales, two tiles in flight.  The copies of the first two tiles are issued
+// contiguous) plus one for its scales, NS tiles in flight.  The copies of the first NS tiles are issued
 // before the kernel waits for the producer of its input vector, so under programmatic dependent launch
 // the weights of the next projection are already streaming while the previous kernel finishes.  The input
 // vector is then packed by every block for itself (no separate pack launch, no packed copy in global memory).
@@ -186,11 +186,11 @@ __device__ __forceinline__ void w4_mma_spans(const W4Tile& tl, int r0, int vrows
 // rows (TR == 8: one half-used slab), the NW warps split slabs x interleaved 128-weight spans, and the
 // per-warp partial sums of a row meet in a small shared array.  NW = 8 with up to three blocks per SM; for rows so
 // long that only 8-row tiles would fit that way, NW = 16 with 16-row tiles and one block per SM.
-template <int MODE, int TR, int NW>
+template <int MODE, int TR, int NW, int NS>
 __global__ void __launch_bounds__(NW * 32, NW == 8 ? 3 : 1) w4_gemv_kernel(const W4Args a) {
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ float sh_ss[NW];
-  __shared__ __align__(8) uint64_t bars[2];
+  __shared__ __align__(8) uint64_t bars[NS];
   __shared__ int abort_flag;
   constexpr int NM = MODE == W4_GATE_UP ? 2 : 1;
   constexpr int S_ROWS = TR;
@@ -225,7 +225,7 @@ __global__ void __launch_bounds__(NW * 32, NW == 8 ? 3 : 1) w4_gemv_kernel(const
     if (q >= my_steps) return;
     int s, row0, rows;
     locate(q, s, row0, rows);
-    const int st = q & 1;
+    const int st = q % NS;
     const int vr = min(S_ROWS, rows - row0);
     const uint32_t bar = ptx::smem_u32(&bars[st]);
     if (vr == S_ROWS) {
@@ -258,15 +258,15 @@ __global__ void __launch_bounds__(NW * 32, NW == 8 ? 3 : 1) w4_gemv_kernel(const
   };
 
   if (threadIdx.x == 0) {
-    ptx::mbar_init(ptx::smem_u32(&bars[0]), 1);
-    ptx::mbar_init(ptx::smem_u32(&bars[1]), 1);
+#pragma unroll
+    for (int k = 0; k < NS; ++k) ptx::mbar_init(ptx::smem_u32(&bars[k]), 1);
     abort_flag = 0;
     ptx::fence_barrier_init();
   }
   __syncthreads();
-  // Weights never change: the first two tiles are requested before waiting for the producer of the input.
-  issue(0);
-  issue(1);
+  // Weights never change: the first NS tiles are requested before waiting for the producer of the input.
+#pragma unroll
+  for (int k = 0; k < NS; ++k) issue(k);
   // Pack the input vector into this block's shared memory, four threads per chunk, W4_PACK_ROUNDS rounds of
   // loads in flight together.  The norm weights never change: the first batch is requested before waiting for
   // the producer of x (they miss in L2 once per layer).
@@ -329,8 +329,8 @@ __global__ void __launch_bounds__(NW * 32, NW == 8 ? 3 : 1) w4_gemv_kernel(const
   for (int q = 0; q < my_steps; ++q) {
     int s, row0, rows;
     locate(q, s, row0, rows);
-    const int st = q & 1;
-    if (!ptx::mbar_wait(ptx::smem_u32(&bars[st]), uint32_t(q >> 1) & 1u, &abort_flag, a.status, 10)) break;
+    const int st = q % NS, rb = q & 1;   // weight stage; buffer of the partial sums
+    if (!ptx::mbar_wait(ptx::smem_u32(&bars[st]), uint32_t(q / NS) & 1u, &abort_flag, a.status, 10)) break;
     float acc[NM][2];
 #pragma unroll
     for (int m = 0; m < NM; ++m) acc[m][0] = acc[m][1] = 0.0f;
@@ -350,17 +350,17 @@ __global__ void __launch_bounds__(NW * 32, NW == 8 ? 3 : 1) w4_gemv_kernel(const
         float v = acc[m][h];
         v += __shfl_xor_sync(0xffffffffu, v, 1);
         v += __shfl_xor_sync(0xffffffffu, v, 2);
-        if ((lane & 3) == 0) red[st][m][kpart][slab * 16 + (lane >> 2) + 8 * h] = v;
+        if ((lane & 3) == 0) red[rb][m][kpart][slab * 16 + (lane >> 2) + 8 * h] = v;
       }
     __syncthreads();  // partial sums published; every warp is done with stage st before it is refilled
-    issue(q + 2);
+    issue(q + NS);
     if (threadIdx.x < S_ROWS) {
       const int row = row0 + int(threadIdx.x);
       float v0 = 0.0f, v1 = 0.0f;
 #pragma unroll
       for (int k = 0; k < KP; ++k) {
-        v0 += red[st][0][k][threadIdx.x];
-        if (NM == 2) v1 += red[st][NM - 1][k][threadIdx.x];
+        v0 += red[rb][0][k][threadIdx.x];
+        if (NM == 2) v1 += red[rb][NM - 1][k][threadIdx.x];
       }
       v0 *= inv_r;
       v1 *= inv_r;
@@ -394,16 +394,25 @@ inline int w4_launch(W4Args a, cudaStream_t st, int sm_count, bool pdl = false) 
   // matrices of batch-1 decode.  Two tiles must fit in shared memory next to the packed input, with room for
   // 2-3 blocks per SM.
   const size_t xs_bytes = w4_packed_bytes(a.cols);
-  auto need = [&](int tr) { return xs_bytes + 2 * w4_stage_bytes(a.cols, a.groups_per_row, NM, zeros, tr); };
+  auto need = [&](int tr, int ns = 2) { return xs_bytes + ns * w4_stage_bytes(a.cols, a.groups_per_row, NM, zeros, tr); };
   int tr = 32;
   while (tr > 8 && need(tr) > 74 * 1024) tr >>= 1;
   if (tr == 8 && need(16) <= 112 * 1024) tr = 16;
-  while (tr > 8 && total_rows / tr < 2 * int64_t(sm_count)) tr >>= 1;
-  // long rows: 8-row tiles would use half of every MMA; 16-row tiles with 16 warps in one block per SM instead
-  const bool wide = !getenv("SIMP_W4_NO_WIDE") && tr == 8 && need(16) > 112 * 1024 && need(16) <= 220 * 1024 && total_rows / 16 >= int64_t(sm_count);
-  if (wide) tr = 16;
-  const int nw = wide ? 16 : W4_WARPS;
-  const size_t smem = need(tr);
+  while (tr > 8 && total_rows / tr < int64_t(sm_count)) tr >>= 1;
+  // Wide form: 16 warps on 16-row tiles, one block per SM, as many stages as fit (up to 4).  Chosen when rows are so
+  // long that three 8-warp blocks per SM would be left with 8-row tiles (half of every MMA unused, and every
+  // block packs the input vector for itself).
+  static const char* wide_env = getenv("SIMP_W4_WIDE");   // "all": whenever there is a 16-row tile per SM; "off": never
+  const bool wide_fit = need(16) <= 220 * 1024 && total_rows / 16 >= int64_t(sm_count);
+  bool wide = wide_fit && tr == 8 && need(16) > 112 * 1024;
+  if (wide_env && !strcmp(wide_env, "all")) wide = wide_fit;
+  if (wide_env && !strcmp(wide_env, "off")) wide = false;
+  int ns = 2;
+  if (wide) {
+    tr = 16;
+    while (ns < 4 && need(16, ns + 1) <= 200 * 1024) ++ns;
+  }
+  const size_t smem = need(tr, ns);
   if (smem > 220 * 1024) return set_error(SIMP_ERR_SHAPE, "w4_gemv: row too long for the shared-memory pipeline");
   int g = 0;
   for (int s = 0; s < nseg_tiles; ++s) {
@@ -417,19 +426,21 @@ inline int w4_launch(W4Args a, cudaStream_t st, int sm_count, bool pdl = false) 
   const int cap = sm_count * per_sm;
   const int grid = g < cap ? g : cap;
   cudaError_t e;
-#define W4_LAUNCH_TR(TRV, NWV)                                                                              \
+#define W4_LAUNCH_TR(TRV, NWV, NSV)                                                                         \
   do {                                                                                                      \
     static bool attr_set = false;                                                                           \
     if (!attr_set) {                                                                                        \
-      cudaFuncSetAttribute(w4_gemv_kernel<MODE, TRV, NWV>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024); \
+      cudaFuncSetAttribute(w4_gemv_kernel<MODE, TRV, NWV, NSV>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024); \
       attr_set = true;                                                                                      \
     }                                                                                                       \
-    e = launch_kernel(w4_gemv_kernel<MODE, TRV, NWV>, dim3(grid), dim3(NWV * 32), smem, st, pdl, a);        \
+    e = launch_kernel(w4_gemv_kernel<MODE, TRV, NWV, NSV>, dim3(grid), dim3(NWV * 32), smem, st, pdl, a);   \
   } while (0)
-  if (nw == 16) W4_LAUNCH_TR(16, 16);
-  else if (tr == 32) W4_LAUNCH_TR(32, 8);
-  else if (tr == 16) W4_LAUNCH_TR(16, 8);
-  else W4_LAUNCH_TR(8, 8);
+  if (wide && ns == 4) W4_LAUNCH_TR(16, 16, 4);
+  else if (wide && ns == 3) W4_LAUNCH_TR(16, 16, 3);
+  else if (wide) W4_LAUNCH_TR(16, 16, 2);
+  else if (tr == 32) W4_LAUNCH_TR(32, 8, 2);
+  else if (tr == 16) W4_LAUNCH_TR(16, 8, 2);
+  else W4_LAUNCH_TR(8, 8, 2);
 #undef W4_LAUNCH_TR
   if (e != cudaSuccess) return set_error(SIMP_ERR_CUDA, "w4_gemv launch failed: %s", cudaGetErrorString(e));
   return SIMP_OK;
