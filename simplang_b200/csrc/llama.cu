@@ -74,15 +74,37 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
   const int h = blockIdx.x, sp = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   pdl_launch_dependents();
-  pdl_wait();
+  // Before waiting for q/k/v: the position (written by the previous token's last kernel, long complete), the
+  // rotation angles, and a request for this block's cache rows -- written by earlier tokens and evicted from
+  // L2 by a token's worth of weights since -- so that they are on their way while the projection finishes.
+  __shared__ float rc[64], rs[64];
   const int pos = ctl[1];
   const int len = pos + 1;
   const int kvh = h / kv_mul;
+  float* kbase = kc + int64_t(layer) * seq_len * kv_dim + kvh * hs;
+  float* vbase = vc + int64_t(layer) * seq_len * kv_dim + kvh * hs;
+  const int per = (len + nsplit - 1) / nsplit;
+  const int t0 = sp * per, t1 = min(len, t0 + per);
   if (int(threadIdx.x) < hs / 2) {
     const int i = 2 * threadIdx.x;
     const float freq = 1.0f / powf(10000.0f, float(i) / float(hs));
     const float val = float(pos) * freq;
-    const float fcr = cosf(val), fci = sinf(val);
+    rc[threadIdx.x] = cosf(val);
+    rs[threadIdx.x] = sinf(val);
+  }
+  {
+    const int lines = (hs * 4 + 127) / 128 + 1;   // a row of hs floats may straddle one more 128-byte line
+    for (int t = t0 + warp; t < t1; t += ATT_WARPS)
+      if (t != pos && lane < 2 * lines) {
+        const float* row = (lane < lines ? kbase : vbase) + int64_t(t) * kv_dim;
+        const int ln = lane < lines ? lane : lane - lines;
+        if (ln * 32 < hs + 31) asm volatile("prefetch.global.L2 [%0];" ::"l"(row + min(ln * 32, hs - 1)));
+      }
+  }
+  pdl_wait();
+  if (int(threadIdx.x) < hs / 2) {
+    const int i = 2 * threadIdx.x;
+    const float fcr = rc[threadIdx.x], fci = rs[threadIdx.x];
     const float q0 = q[h * hs + i], q1 = q[h * hs + i + 1];
     qs[i] = q0 * fcr - q1 * fci;
     qs[i + 1] = q0 * fci + q1 * fcr;
@@ -93,16 +115,12 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
     vs[i + 1] = v[kvh * hs + i + 1];
   }
   __syncthreads();
-  float* kbase = kc + int64_t(layer) * seq_len * kv_dim + kvh * hs;
-  float* vbase = vc + int64_t(layer) * seq_len * kv_dim + kvh * hs;
   if (sp == 0 && h % kv_mul == 0) {
     for (int i = threadIdx.x; i < hs; i += blockDim.x) {
       kbase[int64_t(pos) * kv_dim + i] = ks[i];
       vbase[int64_t(pos) * kv_dim + i] = vs[i];
     }
   }
-  const int per = (len + nsplit - 1) / nsplit;
-  const int t0 = sp * per, t1 = min(len, t0 + per);
   const float div = sqrtf(float(hs));
   float qr[ATT_E], acc[ATT_E];
 #pragma unroll
