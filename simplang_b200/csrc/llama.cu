@@ -234,32 +234,33 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
 
 // Greedy argmax (strict '>', lowest index wins) + bookkeeping for the next step:
 // step++, pos++, token = pos < n_prompt ? prompt[pos] : argmax; generated tokens are recorded.
+// ARGMAX_BLOCKS blocks each reduce a contiguous slice of the logits to one (value, index) pair; the last block to
+// finish (ticket in ctl[8], reset for the next launch; nobody waits) reduces the pairs and does the bookkeeping.
+constexpr int ARGMAX_BLOCKS = 32;
+__device__ __forceinline__ void argmax_merge(float& best, int& idx, float ov, int oi) {
+  if (ov > best || (ov == best && oi < idx)) {
+    best = ov;
+    idx = oi;
+  }
+}
 __global__ void __launch_bounds__(1024) argmax_advance_kernel(const float* __restrict__ logits, int n, int* ctl,
                                                               const int32_t* __restrict__ prompt,
-                                                              int32_t* __restrict__ out_tokens) {
+                                                              int32_t* __restrict__ out_tokens, float* __restrict__ part_val,
+                                                              int* __restrict__ part_idx) {
   __shared__ float bv[32];
   __shared__ int bi[32];
+  __shared__ int is_last;
   pdl_launch_dependents();
   pdl_wait();
+  const int per = (n + gridDim.x - 1) / gridDim.x;
+  const int i0 = blockIdx.x * per, i1 = min(n, i0 + per);
   float best = -INFINITY;
   int idx = 0x7fffffff;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    const float v = logits[i];
-    if (v > best || (v == best && i < idx)) {
-      best = v;
-      idx = i;
-    }
-  }
+  for (int i = i0 + threadIdx.x; i < i1; i += blockDim.x) argmax_merge(best, idx, logits[i], i);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-    const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
-    if (ov > best || (ov == best && oi < idx)) {
-      best = ov;
-      idx = oi;
-    }
-  }
+  for (int o = 16; o > 0; o >>= 1)
+    argmax_merge(best, idx, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, idx, o));
   if (lane == 0) {
     bv[warp] = best;
     bi[warp] = idx;
@@ -269,23 +270,32 @@ __global__ void __launch_bounds__(1024) argmax_advance_kernel(const float* __res
     best = lane < (blockDim.x >> 5) ? bv[lane] : -INFINITY;
     idx = lane < (blockDim.x >> 5) ? bi[lane] : 0x7fffffff;
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-      const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
-      if (ov > best || (ov == best && oi < idx)) {
-        best = ov;
-        idx = oi;
-      }
-    }
+    for (int o = 16; o > 0; o >>= 1)
+      argmax_merge(best, idx, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, idx, o));
     if (lane == 0) {
-      if (idx == 0x7fffffff) idx = 0;  // all-NaN logits: the host loop would keep index 0
-      const int pos = ctl[1] + 1, n_prompt = ctl[2], step = ctl[3];
-      ctl[4] = idx;
-      if (out_tokens && pos >= n_prompt) out_tokens[pos - n_prompt] = idx;
-      ctl[0] = (prompt && pos < n_prompt) ? prompt[pos] : idx;
-      ctl[1] = pos;
-      ctl[3] = step + 1;
+      part_val[blockIdx.x] = best;
+      part_idx[blockIdx.x] = idx;
+      __threadfence();
+      is_last = atomicAdd(ctl + 8, 1) == int(gridDim.x) - 1;
     }
+  }
+  __syncthreads();
+  if (!is_last || warp != 0) return;
+  __threadfence();
+  best = lane < int(gridDim.x) ? __ldcg(part_val + lane) : -INFINITY;
+  idx = lane < int(gridDim.x) ? __ldcg(part_idx + lane) : 0x7fffffff;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1)
+    argmax_merge(best, idx, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, idx, o));
+  if (lane == 0) {
+    if (idx == 0x7fffffff) idx = 0;  // all-NaN logits: the host loop would keep index 0
+    const int pos = ctl[1] + 1, n_prompt = ctl[2], step = ctl[3];
+    ctl[4] = idx;
+    if (out_tokens && pos >= n_prompt) out_tokens[pos - n_prompt] = idx;
+    ctl[0] = (prompt && pos < n_prompt) ? prompt[pos] : idx;
+    ctl[1] = pos;
+    ctl[3] = step + 1;
+    ctl[8] = 0;
   }
 }
 
@@ -361,8 +371,8 @@ static int enqueue_token(LlamaModel& m, cudaStream_t st) {
     g.nseg = 1; g.k4 = dim / 4; g.x = m.xb;
     if (int rc = gemv_f32_launch<GEMV_STORE>(g, st, sms)) return rc;
   }
-  LAUNCH_OR_FAIL(argmax_advance_kernel, dim3(1), dim3(1024), 0, st, false, (const float*)m.logits, int(c.vocab_size),
-                 m.ctl, (const int32_t*)m.prompt, m.out_tokens);
+  LAUNCH_OR_FAIL(argmax_advance_kernel, dim3(ARGMAX_BLOCKS), dim3(1024), 0, st, false, (const float*)m.logits,
+                 int(c.vocab_size), m.ctl, (const int32_t*)m.prompt, m.out_tokens, m.pk_best_val, m.pk_best_idx);
   return SIMP_OK;
 }
 
@@ -450,8 +460,8 @@ static int enqueue_token_tp(LlamaModel& m, cudaStream_t st) {
     if (int rc = gemv_f32_launch<GEMV_STORE>(g, st, sms)) return rc;
   }
   if (int rc = gather(m.logits, V_l)) return rc;
-  LAUNCH_OR_FAIL(argmax_advance_kernel, dim3(1), dim3(1024), 0, st, false, (const float*)m.logits, int(c.vocab_size),
-                 m.ctl, (const int32_t*)m.prompt, m.out_tokens);
+  LAUNCH_OR_FAIL(argmax_advance_kernel, dim3(ARGMAX_BLOCKS), dim3(1024), 0, st, false, (const float*)m.logits,
+                 int(c.vocab_size), m.ctl, (const int32_t*)m.prompt, m.out_tokens, m.pk_best_val, m.pk_best_idx);
 #undef TP_CUDA
   return SIMP_OK;
 }
@@ -557,6 +567,7 @@ SIMP_API int simp_llama_create(const simp_llama_config* cfg, void** model) {
   A((void**)&m->attn_part, size_t(c.n_heads) * (m->nsplit > 4 ? m->nsplit : 4) * (hs + 2) * 4);
   A((void**)&m->attn_cnt, size_t(c.n_heads) * 4);
   A((void**)&m->ctl, 64);
+  if (rc == SIMP_OK && cudaMemset(m->ctl, 0, 64) != cudaSuccess) rc = SIMP_ERR_CUDA;   // ctl[8]: argmax ticket
   A((void**)&m->pk_bar, 64);
   A((void**)&m->pk_best_val, size_t(ctx().sm_count) * 4);
   A((void**)&m->pk_best_idx, size_t(ctx().sm_count) * 4);
