@@ -401,10 +401,11 @@ inline int w4_launch(W4Args a, cudaStream_t st, int sm_count, bool pdl = false) 
   while (tr > 8 && total_rows / tr < int64_t(sm_count)) tr >>= 1;
   // Wide form: 16 warps on 16-row tiles, one block per SM, as many stages as fit (up to 4).  Chosen when rows are so
   // long that three 8-warp blocks per SM would be left with 8-row tiles (half of every MMA unused, and every
-  // block packs the input vector for itself).
+  // block packs the input vector for itself), and for launches of a few tiles per SM (batch-1 decode), where the
+  // fixed costs of a launch dominate: one pack per SM instead of three, half the dependent rounds per tile.
   static const char* wide_env = getenv("SIMP_W4_WIDE");   // "all": whenever there is a 16-row tile per SM; "off": never
   const bool wide_fit = need(16) <= 220 * 1024 && total_rows / 16 >= int64_t(sm_count);
-  bool wide = wide_fit && tr == 8 && need(16) > 112 * 1024;
+  bool wide = wide_fit && ((tr == 8 && need(16) > 112 * 1024) || total_rows / 16 <= 8 * int64_t(sm_count));
   if (wide_env && !strcmp(wide_env, "all")) wide = wide_fit;
   if (wide_env && !strcmp(wide_env, "off")) wide = false;
   int ns = 2;
