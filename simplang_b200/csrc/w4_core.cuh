@@ -330,6 +330,9 @@ __global__ void __launch_bounds__(NW * 32, NW == 8 ? 3 : 1) w4_gemv_kernel(const
     int s, row0, rows;
     locate(q, s, row0, rows);
     const int st = q % NS, rb = q & 1;   // weight stage; buffer of the partial sums
+    // residual rows are requested before the tile's arithmetic so that their latency is not paid in the epilogue
+    float resid = 0.0f;
+    if (MODE == W4_ADD && int(threadIdx.x) < S_ROWS && row0 + int(threadIdx.x) < rows) resid = __ldcg(a.res + row0 + int(threadIdx.x));
     if (!ptx::mbar_wait(ptx::smem_u32(&bars[st]), uint32_t(q / NS) & 1u, &abort_flag, a.status, 10)) break;
     float acc[NM][2];
 #pragma unroll
@@ -366,7 +369,7 @@ __global__ void __launch_bounds__(NW * 32, NW == 8 ? 3 : 1) w4_gemv_kernel(const
       v1 *= inv_r;
       if (row < rows) {
         if (MODE == W4_STORE) a.seg[s].out[row] = v0;
-        if (MODE == W4_ADD) a.seg[s].out[row] = a.res[row] + v0;
+        if (MODE == W4_ADD) a.seg[s].out[row] = resid + v0;
         if (MODE == W4_GATE_UP) a.seg[0].out[row] = (v0 / (1.0f + expf(-v0))) * v1;
       }
     }
