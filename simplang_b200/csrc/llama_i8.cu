@@ -115,6 +115,9 @@ __global__ void __launch_bounds__(GI8_WARPS * 32) gemv_i8_kernel(const GemvI8Arg
     }
   }
   pdl_wait();
+  // residual rows are requested now so that their latency is not paid in the epilogue (lane r holds row r's)
+  float resid_pre = 0.0f;
+  if (EPI == EPI_RESID && active && lane < RPW) resid_pre = __ldcg(a.resid + r_in + lane);
   // ---- prologue: the int8 input vector in shared memory
   if (PRO == PRO_NORM) {
     // y = (x / r) * w, r = sqrt(mean(x^2) + 1e-5); v = y * 127 clamped, truncated (llama32_1b_int8_tensor.sl:93-103)
@@ -178,10 +181,11 @@ __global__ void __launch_bounds__(GI8_WARPS * 32) gemv_i8_kernel(const GemvI8Arg
       v0 += __shfl_xor_sync(0xffffffffu, v0, o);
       if (NM == 2) v1 += __shfl_xor_sync(0xffffffffu, v1, o);
     }
+    const float resid_r = __shfl_sync(0xffffffffu, resid_pre, r);
     if (lane == 0) {
       const int row = r_in + r;
       if (EPI == EPI_STORE) a.seg[s].out[row] = v0;
-      if (EPI == EPI_RESID) a.resid[row] = a.resid[row] + float(v0) / 65536.0f;
+      if (EPI == EPI_RESID) a.resid[row] = resid_r + float(v0) / 65536.0f;
       if (EPI == EPI_GATEUP) {
         const float gate_f = float(v0) / 65536.0f;
         const float silu = gate_f / (1.0f + expf(0.0f - gate_f));
