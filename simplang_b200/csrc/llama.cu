@@ -83,7 +83,11 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
   const int kvh = h / kv_mul;
   float* kbase = kc + int64_t(layer) * seq_len * kv_dim + kvh * hs;
   float* vbase = vc + int64_t(layer) * seq_len * kv_dim + kvh * hs;
-  const int per = (len + nsplit - 1) / nsplit;
+  // short sequences use fewer splits (one per 32 positions): the other blocks of the head leave at once and the
+  // merge reads only the partials that exist
+  const int eff = min(nsplit, max(1, (len + 31) >> 5));
+  if (sp >= eff) return;
+  const int per = (len + eff - 1) / eff;
   const int t0 = sp * per, t1 = min(len, t0 + per);
   if (int(threadIdx.x) < hs / 2) {
     const int i = 2 * threadIdx.x;
@@ -209,24 +213,36 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
   // last block of this head merges (writes above are published by the fence + atomic)
   __threadfence();
   __syncthreads();
-  if (threadIdx.x == 0) is_last = (atomicAdd(&counters[h], 1) == nsplit - 1);
+  if (threadIdx.x == 0) is_last = (atomicAdd(&counters[h], 1) == eff - 1);
   __syncthreads();
   if (!is_last) return;
   __threadfence();
+  // all partial maxima and sums are requested together, then all values of an element: one round trip each
+  constexpr int MAXS = 8;   // nsplit never exceeds 8
   const float* p = part + int64_t(h) * nsplit * (hs + 2);
+  float mm[MAXS], ssum[MAXS], ex[MAXS];
+#pragma unroll
+  for (int x = 0; x < MAXS; ++x) {
+    mm[x] = x < eff ? __ldcg(p + x * (hs + 2)) : -INFINITY;
+    ssum[x] = x < eff ? __ldcg(p + x * (hs + 2) + 1) : 0.0f;
+  }
   float M = -INFINITY;
-  for (int x = 0; x < nsplit; ++x) M = fmaxf(M, __ldcg(p + x * (hs + 2)));
+#pragma unroll
+  for (int x = 0; x < MAXS; ++x) M = fmaxf(M, mm[x]);
   float S = 0.0f;
-  for (int x = 0; x < nsplit; ++x) {
-    const float mm = __ldcg(p + x * (hs + 2));
-    if (mm != -INFINITY) S += __ldcg(p + x * (hs + 2) + 1) * expf(mm - M);
+#pragma unroll
+  for (int x = 0; x < MAXS; ++x) {
+    ex[x] = mm[x] != -INFINITY ? expf(mm[x] - M) : 0.0f;
+    if (mm[x] != -INFINITY) S += ssum[x] * ex[x];
   }
   for (int i = threadIdx.x; i < hs; i += blockDim.x) {
+    float val[MAXS];
+#pragma unroll
+    for (int x = 0; x < MAXS; ++x) val[x] = x < eff ? __ldcg(p + x * (hs + 2) + 2 + i) : 0.0f;
     float a = 0.0f;
-    for (int x = 0; x < nsplit; ++x) {
-      const float mm = __ldcg(p + x * (hs + 2));
-      if (mm != -INFINITY) a += __ldcg(p + x * (hs + 2) + 2 + i) * expf(mm - M);
-    }
+#pragma unroll
+    for (int x = 0; x < MAXS; ++x)
+      if (mm[x] != -INFINITY) a += val[x] * ex[x];
     out[h * hs + i] = a / S;
   }
   if (threadIdx.x == 0) counters[h] = 0;
