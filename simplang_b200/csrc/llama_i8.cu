@@ -352,20 +352,32 @@ __global__ void __launch_bounds__(AI8_WARPS * 32) attn_i8_kernel(const int32_t* 
   __syncthreads();
   if (!is_last) return;
   __threadfence();
+  // all partial maxima and sums are requested together, then all values of an element: one round trip each
+  constexpr int MAXS = 16;   // the number of sequence splits never exceeds 16
   const float* p0 = part + size_t(h) * nsplit * (hs + 2);
+  float mm[MAXS], ssum[MAXS], ex[MAXS];
+#pragma unroll
+  for (int x = 0; x < MAXS; ++x) {
+    mm[x] = x < nsplit ? __ldcg(p0 + x * (hs + 2)) : -INFINITY;
+    ssum[x] = x < nsplit ? __ldcg(p0 + x * (hs + 2) + 1) : 0.0f;
+  }
   float M = -INFINITY;
-  for (int x = 0; x < nsplit; ++x) M = fmaxf(M, __ldcg(p0 + x * (hs + 2)));
+#pragma unroll
+  for (int x = 0; x < MAXS; ++x) M = fmaxf(M, mm[x]);
   float total = 0.0f;
-  for (int x = 0; x < nsplit; ++x) {
-    const float mm = __ldcg(p0 + x * (hs + 2));
-    if (mm != -INFINITY) total += __ldcg(p0 + x * (hs + 2) + 1) * expf(mm - M);
+#pragma unroll
+  for (int x = 0; x < MAXS; ++x) {
+    ex[x] = mm[x] != -INFINITY ? expf(mm[x] - M) : 0.0f;
+    if (mm[x] != -INFINITY) total += ssum[x] * ex[x];
   }
   for (int d = threadIdx.x; d < hs; d += blockDim.x) {
+    float pv[MAXS];
+#pragma unroll
+    for (int x = 0; x < MAXS; ++x) pv[x] = x < nsplit ? __ldcg(p0 + x * (hs + 2) + 2 + d) : 0.0f;
     float val = 0.0f;
-    for (int x = 0; x < nsplit; ++x) {
-      const float mm = __ldcg(p0 + x * (hs + 2));
-      if (mm != -INFINITY) val += __ldcg(p0 + x * (hs + 2) + 2 + d) * expf(mm - M);
-    }
+#pragma unroll
+    for (int x = 0; x < MAXS; ++x)
+      if (mm[x] != -INFINITY) val += pv[x] * ex[x];
     const int32_t out = __float2int_rz(val / total);
     xb_i8[h * hs + d] = quant_clamped(float(out) / 256.0f);
   }
