@@ -172,7 +172,11 @@ int simp_gpu_event_destroy(void* event);
  * call of a few microseconds is dominated by its launch unless the sequence is replayed as one unit).
  * Between record_begin and record_end the calls are recorded, not executed; only the simp_gpu_* compute entry
  * points with device pointers may be called (no alloc / upload / download / sync, no first call of an op
- * family -- run the sequence once before recording it).  Pointers and shapes are frozen into the recording. */
+ * family -- run the sequence once before recording it).  Pointers and shapes are frozen into the recording,
+ * library scratch included: simp_gpu_matmul_i4 and simp_gpu_conv2d_f32 use it, so a recorded call of those that
+ * would need MORE scratch than any earlier call fails with SIMP_ERR_STATE (run it once first); scratch that a
+ * live recording uses is kept until the recording is destroyed, whatever later calls need.  Destroy every
+ * recording before simp_gpu_shutdown. */
 int simp_gpu_record_begin(void);
 int simp_gpu_record_end(void** recording);
 int simp_gpu_replay(void* recording, int64_t times);       /* enqueued on the library stream */
@@ -230,6 +234,9 @@ int simp_llama_forward(void* model, int64_t token, int64_t pos, float* logits_ho
  * device time of the whole generation in milliseconds. */
 int simp_llama_generate(void* model, const int32_t* prompt, int64_t n_prompt, int64_t n_new,
                         int32_t* tokens_out, float* logits_trace, float* ms_out);
+/* Number of kernel launches one token costs (kernel nodes of the captured token graph; valid after the first
+ * forward / generate).  A measurement aid: the reference's hosts count calls of the compiled forward function. */
+int simp_llama_kernels_per_token(void* model, int64_t* kernels);
 int simp_llama_destroy(void* model);
 
 /* ---- int8 LLaMA-3.2-1B-style token forward ---------------------------------------------------

@@ -25,10 +25,20 @@ _i8p = np.ctypeslib.ndpointer(dtype=np.int8, flags="C_CONTIGUOUS")
 _u8p = np.ctypeslib.ndpointer(dtype=np.uint8, flags="C_CONTIGUOUS")
 
 
+def reference_dir():
+    """Path of the reference checkout: $SIMP_REFERENCE_DIR, else a directory named ``reference`` beside this
+    repository; None when neither exists (the prebuilt oracle/_ref objects are then used as they are)."""
+    cand = os.environ.get("SIMP_REFERENCE_DIR") or os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
+    return cand if os.path.isdir(os.path.join(cand, "simptensor")) else None
+
+
 def build(with_ref: bool = True) -> None:
     """Compile the oracle (and oracle/_ref when the reference checkout is present)."""
-    subprocess.run(["make", "-C", _HERE, "all" if with_ref else "oracle"], check=True,
-                   stdout=subprocess.DEVNULL)
+    cmd = ["make", "-C", _HERE, "all" if with_ref else "oracle"]
+    ref_dir = reference_dir() if with_ref else None
+    if ref_dir:
+        cmd.append(f"REF={ref_dir}")
+    subprocess.run(cmd, check=True, stdout=subprocess.DEVNULL)
 
 
 def lib() -> C.CDLL:
@@ -40,6 +50,8 @@ def lib() -> C.CDLL:
         _LIB = C.CDLL(path)
         L = _LIB
         L.simp_oracle_max_threads.restype = C.c_int
+        L.simp_oracle_set_threads.argtypes = [C.c_int]
+        L.simp_oracle_set_threads.restype = C.c_int
         L.simp_oracle_matmul_f32.argtypes = [_f32p, i64, _f32p, i64, _f32p, i64, i64, i64, i64, C.c_int]
         L.simp_oracle_tensor_matmul_f32.argtypes = [_f32p, _f32p, _f32p, i64, i64, i64, C.c_int, C.c_int]
         L.simp_oracle_tensor_matmul_f64.argtypes = [_f64p, _f64p, _f64p, i64, i64, i64, C.c_int, C.c_int]
@@ -59,6 +71,17 @@ def lib() -> C.CDLL:
         L.simp_oracle_argmax.argtypes = [_f32p, i64]
         L.simp_oracle_argmax.restype = i64
     return _LIB
+
+
+def use_all_cores() -> int:
+    """Sets the OpenMP team size of this process to the cores it may run on (its affinity mask) and returns
+    that count.  torch.distributed.run exports OMP_NUM_THREADS=1 to every rank; the CPU baselines call this so
+    that they are timed on all host cores whatever launched them."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    return int(lib().simp_oracle_set_threads(n))
 
 
 def _ptr(a):

@@ -45,6 +45,19 @@ ORACLE_API int simp_oracle_max_threads() {
 #endif
 }
 
+// Sets the OpenMP team size used by later parallel regions started from the calling thread (every library
+// in the process that links the same OpenMP runtime follows it, the compiled reference kernels included).
+// Launchers that export OMP_NUM_THREADS=1 to every rank would otherwise pin the CPU legs to one core.
+ORACLE_API int simp_oracle_set_threads(int threads) {
+#ifdef _OPENMP
+  if (threads > 0) omp_set_num_threads(threads);
+  return omp_get_max_threads();
+#else
+  (void)threads;
+  return 1;
+#endif
+}
+
 // ---------------------------------------------------------------------------
 // simp.matmul : C[coff + i*n + j] += sum_p A[aoff + i*k + p] * B[boff + p*n + j]
 // Follows MatMulOpLowering (src/mlir/lowering/ConvertSimpToMemRef.cpp:1794-1920):

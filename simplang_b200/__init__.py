@@ -73,6 +73,7 @@ _SIGNATURES = {
     "simp_llama_set_w4_offsets": [vp, C.POINTER(i64)],
     "simp_llama_forward": [vp, i64, i64, vp],
     "simp_llama_generate": [vp, vp, i64, i64, vp, vp, C.POINTER(C.c_float)],
+    "simp_llama_kernels_per_token": [vp, C.POINTER(i64)],
     "simp_llama_destroy": [vp],
     "simp_llama_i8_create": [vp, C.POINTER(vp)],
     "simp_llama_i8_load": [vp, C.c_char_p, vp, C.c_size_t],
@@ -400,6 +401,11 @@ class Llama:
         check(lib().simp_llama_generate(self.h, prompt.ctypes.data, len(prompt), n_new, toks.ctypes.data,
                                         trace.ctypes.data if trace_logits else None, C.byref(ms)))
         return toks, trace, float(ms.value)
+
+    def kernels_per_token(self) -> int:
+        n = i64()
+        check(lib().simp_llama_kernels_per_token(self.h, C.byref(n)))
+        return int(n.value)
 
     def close(self):
         if self.h:

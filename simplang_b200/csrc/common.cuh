@@ -26,8 +26,13 @@ Context& ctx();
 int set_error(int code, const char* fmt, ...) __attribute__((format(printf, 2, 3)));
 int ensure_ready();
 
-// Scratch arena owned by the library (grows, never shrinks until shutdown).
+// Scratch arena owned by the library (grows, never shrinks until shutdown).  Recordings freeze the arena
+// pointers they saw: while one is being captured a slot does not grow (nullptr is returned and the call fails),
+// and while recordings are alive a slot that must grow keeps its old block until the last of them is destroyed.
 void* scratch(size_t bytes, int slot);
+int scratch_failed(const char* who); // status + message for a nullptr from scratch(): refused growth or out of memory
+void scratch_capture(bool on);      // a stream capture of the library stream begins / ends
+void scratch_recordings(int delta); // a recording was created (+1) / destroyed (-1)
 
 #define SIMP_CUDA(call)                                                                     \
   do {                                                                                      \

@@ -61,7 +61,7 @@ SIMP_API int simp_gpu_matmul_i4(const uint8_t* A_packed, const uint8_t* B_packed
   int8_t* a8 = static_cast<int8_t*>(scratch(size_t(M) * Kp, 8));
   int8_t* b8 = static_cast<int8_t*>(scratch(size_t(Kp) * Np, 9));
   int32_t* c32 = static_cast<int32_t*>(scratch(size_t(M) * Np * 4, 10));
-  SIMP_REQUIRE(a8 && b8 && c32, SIMP_ERR_CUDA, "matmul_i4: out of device memory for the unpacked operands");
+  if (!(a8 && b8 && c32)) return scratch_failed("matmul_i4 (unpacked operands)");
   auto blocks = [](int64_t n) { return unsigned((n + 255) / 256); };
   unpack_i4_kernel<<<blocks(M * (Kp / 2)), 256, 0, st>>>(A_packed, a8, M, K, M, Kp);
   unpack_i4_kernel<<<blocks(Kp * (Np / 2)), 256, 0, st>>>(B_packed, b8, K, N, Kp, Np);

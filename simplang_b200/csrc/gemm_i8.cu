@@ -625,9 +625,12 @@ int gemm_i8_run(const void* A, const int8_t* B, int32_t* C, int64_t M, int64_t K
   const bool tma_ok = a16 && b16 && (K % 16 == 0) && (b_transposed ? true : (N % 16 == 0)) &&
                       ((reinterpret_cast<uintptr_t>(C) & 15u) == 0);
   if (n_peers > 0)
-    SIMP_REQUIRE(tma_ok && N % 4 == 0 && ldc % 4 == 0 && col_offset % 4 == 0 && col_offset + N <= ldc, SIMP_ERR_SHAPE,
+    // The epilogue stores whole 32-column boxes at col_offset + c0 into the [M, ldc] maps of every rank, which are
+    // clipped at ldc only: a column block that is not a multiple of 32 would spill zero columns into the next
+    // rank's block.
+    SIMP_REQUIRE(tma_ok && N % 32 == 0 && ldc % 4 == 0 && col_offset % 4 == 0 && col_offset + N <= ldc, SIMP_ERR_SHAPE,
                  "matmul_i8: the fused all-gather form needs 16-byte aligned operands, K %% 16 == 0 and column "
-                 "blocks that are multiples of 16");
+                 "blocks that are multiples of 32 columns");
   // The tensor-core kernel pays a fixed pipeline fill per tile; tiny problems stay on dp4a.
   const bool tiny = n_peers == 0 && M * N * K < int64_t(64) * 64 * 64;
   if (tma_ok && !tiny) {

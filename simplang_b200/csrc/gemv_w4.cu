@@ -1,8 +1,8 @@
 // gemv_w4.cu -- matmul_quant entry point: out[rows] = W4[rows,cols] . x[cols]   (batch-1 decode GEMV)
 //
 // Semantics: MatMulQuantOpLowering (src/mlir/lowering/ConvertSimpToMemRef.cpp:3906-4005).
-// The streaming kernel and the packed-activation format live in w4_core.cuh; this file holds the
-// entry point (pack x into library scratch memory, then stream the weights) and the general
+// The streaming kernel and the packed-activation format live in w4_core.cuh (every block packs x in its
+// own shared memory: no scratch in global memory); this file holds the two entry points and the general
 // kernel that follows the lowering's index arithmetic literally for every (gs, cols, offset,
 // scale_mode) the streaming kernel does not take.
 #include "common.cuh"
@@ -46,31 +46,35 @@ __global__ void __launch_bounds__(256)
 
 using namespace simp;
 
-SIMP_API int simp_gpu_matmul_w4(const uint8_t* qw, const float* sc, const float* zr, const float* x, float* out,
-                                int64_t rows, int64_t cols, int64_t gs, int64_t offset, int scale_mode) {
-  if (int rc = ensure_ready()) return rc;
-  SIMP_REQUIRE(rows >= 0 && cols >= 0 && offset >= 0, SIMP_ERR_ARG, "matmul_w4: negative size or offset");
-  SIMP_REQUIRE(gs > 0, SIMP_ERR_ARG, "matmul_w4: group_size must be positive");
-  SIMP_REQUIRE(scale_mode == 0 || scale_mode == 1, SIMP_ERR_ARG, "matmul_w4: scale_mode must be 0 or 1");
+namespace {
+// Body shared by both entry points (`who` names the caller in error texts).  Neither path allocates: the
+// streaming kernel stages everything in shared memory and the general kernel reads the operands in place.
+int matmul_w4_run(const char* who, const uint8_t* qw, const float* sc, const float* zr, const float* x, float* out,
+                  int64_t rows, int64_t cols, int64_t gs, int64_t offset, int scale_mode) {
+  SIMP_REQUIRE(rows >= 0 && cols >= 0 && offset >= 0, SIMP_ERR_ARG, "%s: negative size or offset", who);
+  SIMP_REQUIRE(gs > 0, SIMP_ERR_ARG, "%s: group_size must be positive", who);
+  SIMP_REQUIRE(scale_mode == 0 || scale_mode == 1, SIMP_ERR_ARG, "%s: scale_mode must be 0 or 1", who);
   if (rows == 0) return SIMP_OK;
-  SIMP_REQUIRE(qw && sc && x && out, SIMP_ERR_ARG, "matmul_w4: null pointer");
+  SIMP_REQUIRE(qw && sc && x && out, SIMP_ERR_ARG, "%s: null pointer", who);
   SIMP_REQUIRE(scale_mode == 0 || cols % gs == 0, SIMP_ERR_SHAPE,
-               "matmul_w4: scale_mode 1 needs cols %% group_size == 0 (cols %lld, gs %lld)", (long long)cols,
-               (long long)gs);
+               "%s: scale_mode 1 needs cols %% group_size == 0 (cols %lld, gs %lld)", who, (long long)cols, (long long)gs);
   cudaStream_t st = ctx().stream;
   int log2_cpg = -1;
   for (int s = 0; s <= 5; ++s)
     if (gs == (int64_t(32) << s)) log2_cpg = s;
   const bool mode_ok = scale_mode == 1 ? (offset % gs == 0) : (gs == 128);
   const uint8_t* base = qw + offset / 2;
-  const int64_t soff_chk = scale_mode == 1 ? offset / gs : 0;
-  const bool sc_aligned = ((reinterpret_cast<uintptr_t>(sc + soff_chk) & 15u) == 0) &&
-                          (!zr || (reinterpret_cast<uintptr_t>(zr + soff_chk) & 15u) == 0);
-  const bool fast = sc_aligned && log2_cpg >= 0 && mode_ok && cols > 0 && cols % gs == 0 && cols <= 16384 && offset % 32 == 0 &&
-                    ((reinterpret_cast<uintptr_t>(base) & 15u) == 0) && ((reinterpret_cast<uintptr_t>(x) & 15u) == 0) &&
-                    rows <= 0x7fffffff;
+  const int64_t soff = scale_mode == 1 ? offset / gs : 0;
+  const bool sc_aligned = ((reinterpret_cast<uintptr_t>(sc + soff) & 15u) == 0) &&
+                          (!zr || (reinterpret_cast<uintptr_t>(zr + soff) & 15u) == 0);
+  bool fast = sc_aligned && log2_cpg >= 0 && mode_ok && cols > 0 && cols % gs == 0 && cols <= 16384 && offset % 32 == 0 &&
+              ((reinterpret_cast<uintptr_t>(base) & 15u) == 0) && ((reinterpret_cast<uintptr_t>(x) & 15u) == 0) &&
+              rows <= 0x7fffffff;
+  // the packed input plus two stages of the smallest (8-row) tile must fit in shared memory; very long rows with
+  // small groups and zeros (16384 columns, groups of 32) do not, and take the general kernel
+  if (fast && w4_packed_bytes(cols) + 2 * w4_stage_bytes(int(cols), int(cols / gs), 1, zr != nullptr, 8) > W4_SMEM_LIMIT)
+    fast = false;
   if (fast) {
-    const int64_t soff = scale_mode == 1 ? offset / gs : 0;
     W4Args a{};
     a.seg[0] = W4Seg{base, sc + soff, zr ? zr + soff : nullptr, out, int(rows)};
     a.nseg = 1;
@@ -86,10 +90,17 @@ SIMP_API int simp_gpu_matmul_w4(const uint8_t* qw, const float* sc, const float*
     return SIMP_OK;
   }
   const int64_t grid = cdiv(rows, 8);
-  SIMP_REQUIRE(grid <= 0x7fffffff, SIMP_ERR_SHAPE, "matmul_w4: too many rows");
+  SIMP_REQUIRE(grid <= 0x7fffffff, SIMP_ERR_SHAPE, "%s: too many rows", who);
   w4_gemv_general_kernel<<<int(grid), 256, 0, st>>>(qw, sc, zr, x, out, rows, cols, gs, offset, scale_mode);
   SIMP_LAUNCH_CHECK();
   return SIMP_OK;
+}
+}  // namespace
+
+SIMP_API int simp_gpu_matmul_w4(const uint8_t* qw, const float* sc, const float* zr, const float* x, float* out,
+                                int64_t rows, int64_t cols, int64_t gs, int64_t offset, int scale_mode) {
+  if (int rc = ensure_ready()) return rc;
+  return matmul_w4_run("matmul_w4", qw, sc, zr, x, out, rows, cols, gs, offset, scale_mode);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -98,9 +109,11 @@ SIMP_API int simp_gpu_matmul_w4(const uint8_t* qw, const float* sc, const float*
 // Some hosts may not allocate device memory when they call into this library: a serving process
 // that hands its whole memory budget to its own pool at start-up (a later cudaMalloc then fails or
 // fragments the pool), or code running where the CUDA runtime forbids allocation altogether.
-// The streaming kernel packs the input vector in every block's shared memory, so this entry point
-// needs no scratch in global memory at all: it only refuses to initialise the library (which
-// allocates) and shapes beyond SIMP_W4_NOALLOC_MAX_COLS columns.
+// The W4 kernels need no scratch in global memory (the streaming kernel packs the input vector in every
+// block's shared memory, the general kernel reads the operands in place), so what distinguishes this entry
+// point is what it refuses to do: it never initialises the library on demand (initialisation allocates the
+// stream and the status words) and it takes at most W4_NOALLOC_MAX_COLS columns, the documented limit of
+// the interface.
 constexpr int64_t W4_NOALLOC_MAX_COLS = 16384;
 
 SIMP_API int simp_gpu_matmul_w4_noalloc(const uint8_t* qw, const float* sc, const float* zr, const float* x,
@@ -108,46 +121,8 @@ SIMP_API int simp_gpu_matmul_w4_noalloc(const uint8_t* qw, const float* sc, cons
                                         int scale_mode) {
   SIMP_REQUIRE(ctx().ready, SIMP_ERR_STATE,
                "matmul_w4_noalloc: call simp_gpu_init first (initialisation allocates; this entry point must not)");
-  SIMP_REQUIRE(rows >= 0 && cols >= 0 && offset >= 0, SIMP_ERR_ARG, "matmul_w4_noalloc: negative size or offset");
-  SIMP_REQUIRE(gs > 0, SIMP_ERR_ARG, "matmul_w4_noalloc: group_size must be positive");
-  SIMP_REQUIRE(scale_mode == 0 || scale_mode == 1, SIMP_ERR_ARG, "matmul_w4_noalloc: scale_mode must be 0 or 1");
   SIMP_REQUIRE(cols <= W4_NOALLOC_MAX_COLS, SIMP_ERR_SHAPE,
-               "matmul_w4_noalloc: cols %lld exceeds the built-in scratch (max %lld); use simp_gpu_matmul_w4",
+               "matmul_w4_noalloc: cols %lld exceeds the limit of this entry point (%lld); use simp_gpu_matmul_w4",
                (long long)cols, (long long)W4_NOALLOC_MAX_COLS);
-  if (rows == 0) return SIMP_OK;
-  SIMP_REQUIRE(qw && sc && x && out, SIMP_ERR_ARG, "matmul_w4_noalloc: null pointer");
-  SIMP_REQUIRE(scale_mode == 0 || cols % gs == 0, SIMP_ERR_SHAPE,
-               "matmul_w4_noalloc: scale_mode 1 needs cols %% group_size == 0");
-  cudaStream_t st = ctx().stream;
-  int log2_cpg = -1;
-  for (int s = 0; s <= 5; ++s)
-    if (gs == (int64_t(32) << s)) log2_cpg = s;
-  const bool mode_ok = scale_mode == 1 ? (offset % gs == 0) : (gs == 128);
-  const uint8_t* base = qw + offset / 2;
-  const int64_t soff = scale_mode == 1 ? offset / gs : 0;
-  const bool sc_aligned = ((reinterpret_cast<uintptr_t>(sc + soff) & 15u) == 0) &&
-                          (!zr || (reinterpret_cast<uintptr_t>(zr + soff) & 15u) == 0);
-  const bool fast = sc_aligned && log2_cpg >= 0 && mode_ok && cols > 0 && cols % gs == 0 && offset % 32 == 0 &&
-                    ((reinterpret_cast<uintptr_t>(base) & 15u) == 0) && ((reinterpret_cast<uintptr_t>(x) & 15u) == 0) &&
-                    rows <= 0x7fffffff;
-  if (fast) {
-    W4Args a{};
-    a.seg[0] = W4Seg{base, sc + soff, zr ? zr + soff : nullptr, out, int(rows)};
-    a.nseg = 1;
-    a.cols = int(cols);
-    a.log2_cpg = log2_cpg;
-    a.groups_per_row = int(cols / gs);
-    a.x = x;
-    return w4_launch<W4_STORE>(a, st, ctx().sm_count);
-  }
-  // shapes outside the streaming kernel's domain use the general kernel, which needs no scratch at all
-  if (cols == 0) {
-    SIMP_CUDA(cudaMemsetAsync(out, 0, size_t(rows) * sizeof(float), st));
-    return SIMP_OK;
-  }
-  const int64_t grid = cdiv(rows, 8);
-  SIMP_REQUIRE(grid <= 0x7fffffff, SIMP_ERR_SHAPE, "matmul_w4_noalloc: too many rows");
-  w4_gemv_general_kernel<<<int(grid), 256, 0, st>>>(qw, sc, zr, x, out, rows, cols, gs, offset, scale_mode);
-  SIMP_LAUNCH_CHECK();
-  return SIMP_OK;
+  return matmul_w4_run("matmul_w4_noalloc", qw, sc, zr, x, out, rows, cols, gs, offset, scale_mode);
 }

@@ -7,6 +7,7 @@
 // once with simp_gpu_register_host(): later calls that pass a pointer inside a registered range
 // use the resident device mirror instead of copying.
 // Also here: pinned host memory and CUDA-event timing for the host drivers.
+#include <cstdint>
 #include <map>
 #include <mutex>
 #include <vector>
@@ -119,18 +120,21 @@ SIMP_API int simp_gpu_event_destroy(void* ev) {
 SIMP_API int simp_gpu_record_begin(void) {
   if (int rc = ensure_ready()) return rc;
   SIMP_CUDA(cudaStreamBeginCapture(ctx().stream, cudaStreamCaptureModeThreadLocal));
+  scratch_capture(true);
   return SIMP_OK;
 }
 SIMP_API int simp_gpu_record_end(void** recording) {
   SIMP_REQUIRE(recording != nullptr, SIMP_ERR_ARG, "record_end: null pointer");
   cudaGraph_t g = nullptr;
   cudaError_t e = cudaStreamEndCapture(ctx().stream, &g);
+  scratch_capture(false);
   SIMP_REQUIRE(e == cudaSuccess && g != nullptr, SIMP_ERR_CUDA, "record_end: capture failed: %s", cudaGetErrorString(e));
   cudaGraphExec_t ex = nullptr;
   e = cudaGraphInstantiate(&ex, g, 0);
   cudaGraphDestroy(g);
   SIMP_REQUIRE(e == cudaSuccess, SIMP_ERR_CUDA, "record_end: instantiate failed: %s", cudaGetErrorString(e));
   *recording = ex;
+  scratch_recordings(+1);
   return SIMP_OK;
 }
 SIMP_API int simp_gpu_replay(void* recording, int64_t times) {
@@ -139,7 +143,11 @@ SIMP_API int simp_gpu_replay(void* recording, int64_t times) {
   return SIMP_OK;
 }
 SIMP_API int simp_gpu_recording_destroy(void* recording) {
-  if (recording) SIMP_CUDA(cudaGraphExecDestroy(static_cast<cudaGraphExec_t>(recording)));
+  if (recording) {
+    SIMP_CUDA(cudaStreamSynchronize(ctx().stream));
+    SIMP_CUDA(cudaGraphExecDestroy(static_cast<cudaGraphExec_t>(recording)));
+    scratch_recordings(-1);
+  }
   return SIMP_OK;
 }
 
@@ -227,8 +235,21 @@ SIMP_API int simp_host_matmul_f32(const float* A, int64_t aoff, const float* B, 
 SIMP_API int simp_host_matmul_quant(const uint8_t* qw, size_t qw_bytes, const float* sc, const float* zr,
                                     size_t n_groups, const float* x, float* out, int64_t rows, int64_t cols,
                                     int64_t gs, int64_t offset, int scale_mode) {
+  SIMP_REQUIRE(qw && sc && x && out && rows >= 0 && cols >= 0 && offset >= 0 && gs > 0, SIMP_ERR_ARG,
+               "host matmul_quant: bad argument");
+  SIMP_REQUIRE(scale_mode == 0 || scale_mode == 1, SIMP_ERR_ARG, "host matmul_quant: scale_mode must be 0 or 1");
+  // The kernels index qw[(offset + row*cols + k) >> 1] and scales[(row*cols [+ offset]) / gs + g], g < cols / gs:
+  // a wrong offset / rows / cols must come back as an error, not as an out-of-range device read.
+  SIMP_REQUIRE(rows <= (INT64_MAX - offset) / (cols > 0 ? cols : 1), SIMP_ERR_SHAPE, "host matmul_quant: size overflow");
+  SIMP_REQUIRE(size_t(offset + rows * cols + 1) / 2 <= qw_bytes, SIMP_ERR_SHAPE,
+               "host matmul_quant: offset %lld + %lld x %lld weights need %zu bytes of qweights, the array holds %zu",
+               (long long)offset, (long long)rows, (long long)cols, size_t(offset + rows * cols + 1) / 2, qw_bytes);
+  if (cols >= gs) {
+    const int64_t last = ((scale_mode == 1 ? offset : 0) + (rows - 1) * cols) / gs + cols / gs - 1;
+    SIMP_REQUIRE(last >= 0 && size_t(last) < n_groups, SIMP_ERR_SHAPE,
+                 "host matmul_quant: the last group read is %lld, scales / zeros hold %zu groups", (long long)last, n_groups);
+  }
   if (int rc = ensure_ready()) return rc;
-  SIMP_REQUIRE(qw && sc && x && out && rows >= 0 && cols >= 0, SIMP_ERR_ARG, "host matmul_quant: bad argument");
   cudaStream_t st = ctx().stream;
   void *dq, *ds, *dz = nullptr, *dx;
   if (int rc = stage_in(qw, qw_bytes, 0, st, &dq)) return rc;

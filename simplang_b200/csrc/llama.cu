@@ -15,6 +15,7 @@
 // one (the reference's W4 model has none); W4 projections use scale_mode 1 (per-matrix scale index).
 #include <cstring>
 #include <string>
+#include <vector>
 
 #include "common.cuh"
 #include "gemv_f32_core.cuh"
@@ -503,6 +504,18 @@ static int ensure_graph(LlamaModel& m) {
     return rc;
   }
   SIMP_REQUIRE(e == cudaSuccess, SIMP_ERR_CUDA, "graph capture failed: %s", cudaGetErrorString(e));
+  {
+    size_t n_nodes = 0;
+    m.graph_kernels = 0;
+    if (cudaGraphGetNodes(g, nullptr, &n_nodes) == cudaSuccess && n_nodes > 0) {
+      std::vector<cudaGraphNode_t> nodes(n_nodes);
+      if (cudaGraphGetNodes(g, nodes.data(), &n_nodes) == cudaSuccess)
+        for (size_t i = 0; i < n_nodes; ++i) {
+          cudaGraphNodeType t;
+          if (cudaGraphNodeGetType(nodes[i], &t) == cudaSuccess && t == cudaGraphNodeTypeKernel) ++m.graph_kernels;
+        }
+    }
+  }
   e = cudaGraphInstantiate(&m.graph, g, 0);
   cudaGraphDestroy(g);
   SIMP_REQUIRE(e == cudaSuccess, SIMP_ERR_CUDA, "graph instantiate failed: %s", cudaGetErrorString(e));
@@ -769,6 +782,14 @@ SIMP_API int simp_llama_generate(void* model, const int32_t* prompt, int64_t n_p
   if (ms_out) SIMP_CUDA(cudaEventElapsedTime(ms_out, e0, e1));
   cudaEventDestroy(e0);
   cudaEventDestroy(e1);
+  return SIMP_OK;
+}
+
+SIMP_API int simp_llama_kernels_per_token(void* model, int64_t* kernels) {
+  SIMP_REQUIRE(model && kernels, SIMP_ERR_ARG, "llama_kernels_per_token: null pointer");
+  LlamaModel& m = *static_cast<LlamaModel*>(model);
+  SIMP_REQUIRE(m.graph != nullptr, SIMP_ERR_STATE, "llama_kernels_per_token: no token graph yet (run forward or generate first)");
+  *kernels = m.graph_kernels;
   return SIMP_OK;
 }
 

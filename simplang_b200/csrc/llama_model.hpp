@@ -36,6 +36,7 @@ struct LlamaModel {
   int* pk_best_idx = nullptr;
   bool pk_attr_done = false;   // the kernel's shared-memory attribute was set on this model's device
   cudaGraphExec_t graph = nullptr;
+  int graph_kernels = 0;       // kernel nodes of the captured token graph
   bool loaded_any = false;
 };
 

@@ -458,7 +458,7 @@ SIMP_API int simp_gpu_conv2d_f32(const float* input_dev, const float* weights_de
   SIMP_REQUIRE(in_h < (1 << 30) && in_w < (1 << 30) && in_c < (1 << 30) && out_c < (1 << 30) && total / 256 < 0x7fffffff,
                SIMP_ERR_SHAPE, "conv2d: dimension too large");
   float* wt = static_cast<float*>(simp::scratch(size_t(taps) * out_c * 4, 11));
-  SIMP_REQUIRE(wt != nullptr, SIMP_ERR_CUDA, "conv2d: out of device memory for the weight copy");
+  if (!wt) return simp::scratch_failed("conv2d (weight copy)");
   cudaStream_t st = simp::ctx().stream;
   simp::conv2d_weights_to_hwio_kernel<<<unsigned((taps * out_c + 255) / 256), 256, 0, st>>>(weights_dev, wt, out_c, taps);
   simp::conv2d_f32_kernel<<<unsigned((total + 255) / 256), 256, 0, st>>>(input_dev, wt, bias_dev, output_dev, total, int(in_h),

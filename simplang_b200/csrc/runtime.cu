@@ -19,6 +19,10 @@ struct Arena {
   size_t cap = 0;
 };
 static Arena g_arena[16];
+static bool g_capturing = false;          // the library stream is being captured into a recording
+static int g_recordings = 0;              // live recordings (their graphs hold arena pointers)
+static std::vector<void*> g_retired;      // outgrown arena blocks a live recording may still use
+static thread_local bool g_scratch_refused = false;
 
 Context& ctx() { return g_ctx; }
 
@@ -38,10 +42,22 @@ int ensure_ready() {
 void* scratch(size_t bytes, int slot) {
   std::lock_guard<std::mutex> lk(g_mu);
   Arena& a = g_arena[slot];
+  g_scratch_refused = false;
   if (a.cap < bytes) {
+    if (g_capturing) {
+      g_scratch_refused = true;
+      // growing would synchronise and free on the capturing stream, and the capture would keep a stale pointer
+      set_error(SIMP_ERR_STATE, "scratch slot %d must grow to %zu bytes while a recording is being captured: run the "
+                "same call once before simp_gpu_record_begin", slot, bytes);
+      return nullptr;
+    }
     if (a.p) {
-      cudaStreamSynchronize(g_ctx.stream);
-      cudaFree(a.p);
+      if (g_recordings > 0) {
+        g_retired.push_back(a.p);   // a recording may replay kernels that use this block
+      } else {
+        cudaStreamSynchronize(g_ctx.stream);
+        cudaFree(a.p);
+      }
       a.p = nullptr;
       a.cap = 0;
     }
@@ -53,6 +69,29 @@ void* scratch(size_t bytes, int slot) {
     a.cap = cap;
   }
   return a.p;
+}
+
+int scratch_failed(const char* who) {
+  if (g_scratch_refused) return SIMP_ERR_STATE;   // message already set by scratch()
+  return set_error(SIMP_ERR_CUDA, "%s: out of device memory for library scratch", who);
+}
+
+void scratch_capture(bool on) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  g_capturing = on;
+}
+
+void scratch_recordings(int delta) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  g_recordings += delta;
+  if (g_recordings <= 0) {
+    g_recordings = 0;
+    if (!g_retired.empty() && g_ctx.ready) {
+      cudaStreamSynchronize(g_ctx.stream);
+      for (void* p : g_retired) cudaFree(p);
+    }
+    g_retired.clear();
+  }
 }
 
 }  // namespace simp
@@ -96,6 +135,10 @@ SIMP_API int simp_gpu_shutdown(void) {
     if (a.p) cudaFree(a.p);
     a = Arena{};
   }
+  for (void* p : g_retired) cudaFree(p);
+  g_retired.clear();
+  g_recordings = 0;
+  g_capturing = false;
   cudaFree(g_ctx.dev_status);
   cudaFreeHost(g_ctx.host_status);
   cudaStreamDestroy(g_ctx.stream);

@@ -73,7 +73,10 @@ SIMP_API int32_t simp_rt_silu_f32(MEMREF1(float, x), MEMREF1(float, y), int64_t 
 SIMP_API int32_t simp_rt_matmul_quant(MEMREF1(int8_t, qw), MEMREF1(float, sc), MEMREF1(float, zr), MEMREF1(float, x),
                                       MEMREF1(float, out), int64_t rows, int64_t cols, int64_t group_size,
                                       int64_t offset) {
-  (void)qw_alloc; (void)sc_alloc; (void)zr_alloc; (void)x_alloc; (void)out_alloc; (void)x_size; (void)out_size;
+  (void)qw_alloc; (void)sc_alloc; (void)zr_alloc; (void)x_alloc; (void)out_alloc;
+  SIMP_REQUIRE(rows >= 0 && cols >= 0 && cols <= x_size && rows <= out_size, SIMP_ERR_SHAPE,
+               "matmul_quant: rows %lld / cols %lld exceed the out (%lld) / x (%lld) arrays", (long long)rows,
+               (long long)cols, (long long)out_size, (long long)x_size);
   if (int rc = check_contig1(qw_stride, "matmul_quant qweights")) return rc;
   if (int rc = check_contig1(sc_stride, "matmul_quant scales")) return rc;
   if (int rc = check_contig1(zr_stride, "matmul_quant zeros")) return rc;

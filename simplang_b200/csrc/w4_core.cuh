@@ -30,6 +30,8 @@ constexpr int W4_WARPS = 8;
 constexpr int W4_CHUNK_U4 = 5;  // uint4 per packed chunk
 constexpr int W4_PACK_ROUNDS = 3;   // rounds of input loads a thread keeps in flight while packing
 
+constexpr size_t W4_SMEM_LIMIT = 220 * 1024;   // dynamic shared memory a launch may ask for
+
 inline size_t w4_packed_bytes(int64_t cols) { return size_t(cols / 32) * W4_CHUNK_U4 * 16; }
 
 // Eight inputs of a chunk packed by one thread, the four threads of a chunk (adjacent lanes, j = lane & 3) sharing
@@ -417,7 +419,7 @@ inline int w4_launch(W4Args a, cudaStream_t st, int sm_count, bool pdl = false) 
     while (ns < 4 && need(16, ns + 1) <= 200 * 1024) ++ns;
   }
   const size_t smem = need(tr, ns);
-  if (smem > 220 * 1024) return set_error(SIMP_ERR_SHAPE, "w4_gemv: row too long for the shared-memory pipeline");
+  if (smem > W4_SMEM_LIMIT) return set_error(SIMP_ERR_SHAPE, "w4_gemv: row too long for the shared-memory pipeline");
   int g = 0;
   for (int s = 0; s < nseg_tiles; ++s) {
     a.seg_tile_start[s] = g;

@@ -58,3 +58,38 @@ def test_cpp_host_builds_and_reports_a_missing_library():
     exe = b.build_host()
     r = subprocess.run([exe, "/nonexistent/libsimp_gpu.so"], capture_output=True, text=True)
     assert r.returncode == 1 and "Failed to load library" in r.stderr
+
+
+def test_host_matmul_quant_rejects_out_of_range_shapes_before_touching_a_device():
+    """The host-pointer W4 entry and its memref shim know the real array sizes: a wrong offset / rows / cols must
+    come back as SIMP_ERR_SHAPE (-2) without any device work (none is possible here: no GPU)."""
+    import numpy as np
+    import simplang_b200 as sg
+    L = sg.lib()
+    rows, cols, gs = 8, 256, 64
+    qw = np.zeros(rows * cols // 2, np.uint8)
+    sc = np.ones(rows * cols // gs, np.float32)
+    x = np.zeros(cols, np.float32)
+    out = np.zeros(rows, np.float32)
+    p = lambda a: a.ctypes.data
+
+    def call(rows_, cols_, offset, mode, n_groups=sc.size, qw_bytes=qw.nbytes):
+        return L.simp_host_matmul_quant(p(qw), qw_bytes, p(sc), None, n_groups, p(x), p(out), rows_, cols_, gs, offset, mode)
+
+    assert call(rows + 1, cols, 0, 1) == -2 and b"qweights" in L.simp_gpu_last_error()
+    assert call(rows, cols, 64, 1) == -2                      # offset pushes the last row past the end
+    assert call(rows, cols, 0, 1, n_groups=sc.size - 1) == -2 and b"group" in L.simp_gpu_last_error()
+    assert call(rows, cols, 0, 2) == -1
+    assert call(rows, cols, -1, 1) == -1
+    # the shim takes rows / cols from the call and the lengths from the memref descriptors
+    i64 = ctypes.c_int64
+    def memref1(a):
+        return [ctypes.c_void_p(p(a)), ctypes.c_void_p(p(a)), i64(0), i64(a.size), i64(1)]
+    zr = np.zeros_like(sc)
+    L.simp_rt_matmul_quant.argtypes = None
+    rc = L.simp_rt_matmul_quant(*memref1(qw), *memref1(sc), *memref1(zr), *memref1(x), *memref1(out),
+                                i64(rows), i64(cols + 64), i64(gs), i64(0))
+    assert rc == -2 and b"exceed" in L.simp_gpu_last_error()
+    rc = L.simp_rt_matmul_quant(*memref1(qw), *memref1(sc), *memref1(zr), *memref1(x), *memref1(out),
+                                i64(rows + 1), i64(cols), i64(gs), i64(0))
+    assert rc == -2

@@ -1,6 +1,7 @@
 """GPU parity: matmul_quant / dequant_w4 vs the CPU oracle.
 
-Tolerance (north star): relative error 1e-3 for W4, taken against sum_k |w_k * x_k| of the row.
+Tolerance (north star): relative error 1e-3 for W4.  Two readings are asserted: against sum_k |w_k * x_k| of the
+row, and the stricter max|out - ref| <= 1e-3 * max|ref| over the whole result (the one the model tests use).
 """
 import numpy as np
 import pytest
@@ -45,6 +46,9 @@ def test_matmul_w4_per_matrix(gpu, oracle, rows, cols, gs, symmetric):
     ref = oracle.matmul_quant(qw, sc, zr, x, rows, cols, gs, offset, scale_mode=1, threads=0)
     err = np.abs(out.astype(np.float64) - ref) / row_scale(oracle, qw, sc, zr, x, rows, cols, gs, offset)
     assert err.max() <= 1e-3, err.max()
+    top = np.max(np.abs(out - ref)) / (np.max(np.abs(ref)) + 1e-30)
+    print(f"w4 {rows}x{cols} gs {gs} sym {symmetric}: max error / row scale = {err.max():.2e}, / max|ref| = {top:.2e}")
+    assert top <= 1e-3, top
 
 
 @pytest.mark.parametrize("rows,cols,gs,offset", [(1536, 1536, 128, 0), (64, 1536, 128, 1536 * 1536), (10, 200, 64, 0),

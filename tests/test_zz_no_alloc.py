@@ -1,16 +1,20 @@
-"""GPU test of simp_gpu_matmul_w4_noalloc, the W4 GEMV variant for callers that cannot allocate device
-memory (its packed-input scratch is a fixed array inside the library, not the growable arena).
+"""GPU test of simp_gpu_matmul_w4_noalloc, the W4 GEMV entry point for callers that may not allocate device
+memory when they call the library (a serving process whose own pool took the whole memory budget at start-up,
+or code running where the CUDA runtime forbids allocation).  The W4 kernels keep everything they stage in
+shared memory, so the entry point has no scratch in global memory; what it adds is that it never initialises
+the library on demand and that it refuses rows longer than its documented limit.
 
-It is called through the C-ABI twice in a row with different inputs -- the array is shared and keeps the
-previous call's contents, so the second call proves nothing stale leaks through -- and each result is
-compared with the regular entry point's on the same inputs (same kernels, so the W4 tolerance of 1e-3 is
-met with a wide margin).  The file name sorts last so that, if this addition ever fails, a run that stops at
-the first failure has already covered everything else.
+It is called through the C-ABI several times in a row with different shapes, and each result is compared
+both with the regular entry point's on the same inputs (same kernels: equal to rounding) and with the CPU oracle
+(the W4 tolerance of 1e-3 against the largest output).  The file name sorts last so that, if this addition
+ever fails, a run that stops at the first failure has already covered everything else.
 """
 import ctypes as C
 
 import numpy as np
 import pytest
+
+import oracle
 
 pytestmark = pytest.mark.gpu
 
@@ -28,13 +32,18 @@ def _case(gpu, rng, rows, cols, gs, symmetric):
     a, b = ref_out.to_numpy(np.float32, rows), new_out.to_numpy(np.float32, rows)
     assert np.all(np.isfinite(b))
     assert np.max(np.abs(a - b)) <= 1e-3 * np.max(np.abs(a))
+    want = oracle.matmul_quant(q, sc, zr, x, rows, cols, gs, 0, scale_mode=1, threads=0)
+    err = np.max(np.abs(b - want)) / np.max(np.abs(want))
+    print(f"w4_noalloc {rows}x{cols} gs {gs}: max error vs oracle / max|oracle| = {err:.2e}")
+    assert err <= 1e-3
 
 
 def test_two_calls_in_a_row_match_the_regular_entry_point(gpu):
     rng = np.random.default_rng(2024)
-    _case(gpu, rng, 3200, 8640, 64, True)    # fills most of the built-in scratch
-    _case(gpu, rng, 1000, 3200, 64, False)   # shorter input right after: stale tail must not matter
-    _case(gpu, rng, 96, 16384, 128, True)    # exactly the maximum
+    _case(gpu, rng, 3200, 8640, 64, True)
+    _case(gpu, rng, 1000, 3200, 64, False)   # a shorter input right after a longer one
+    _case(gpu, rng, 96, 16384, 128, True)    # exactly the maximum row length
+    _case(gpu, rng, 40, 16384, 32, False)    # too long for the shared-memory pipeline: the general kernel
 
 
 def test_rejects_what_it_cannot_hold(gpu):
