@@ -13,7 +13,7 @@ import os
 import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libsimp_gpu.so")
+LIB_PATH = os.environ.get("SIMP_GPU_LIB") or os.path.join(_HERE, "libsimp_gpu.so")   # SIMP_GPU_LIB: another build of the library
 _LIB = None
 
 i64 = C.c_int64

@@ -129,11 +129,15 @@ __device__ __forceinline__ uint4 ld_stream_u4(const void* p) {
                : "l"(p));
   return v;
 }
+// 16 bytes of a matrix that is read once per pass: not kept in L1, first in line for eviction from L2 (so that a
+// stream of weights does not push kernel code, launch parameters and activations out of L2).
 __device__ __forceinline__ float4 ld_stream_f4(const void* p) {
   float4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.f32 {%0,%1,%2,%3}, [%4];"
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.v4.f32 {%0,%1,%2,%3}, [%4], %5;"
                : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
-               : "l"(p));
+               : "l"(p), "l"(pol));
   return v;
 }
 #endif

@@ -13,6 +13,8 @@
 // Deviations from the .sl text (all mirrored by the CPU oracle): the score divisor is sqrt(head_size)
 // rather than the literal 8.0 (identical for head_size 64); the W4 model applies RoPE like the f32
 // one (the reference's W4 model has none); W4 projections use scale_mode 1 (per-matrix scale index).
+#include <cuda.h>
+
 #include <cstring>
 #include <string>
 #include <vector>
@@ -49,47 +51,131 @@ __global__ void __launch_bounds__(1024) dec_rmsnorm_kernel(const float* __restri
   for (int i = threadIdx.x; i < n; i += blockDim.x) y[i] = (x[i] / r) * w[i];
 }
 
-// Decode attention of one layer in a single launch: grid (heads, nsplit), one block per head and
-// slice of the sequence.
+// Decode attention of one layer in a single launch: grid (heads, nsplit), one block of 16 warps per head and
+// slice of the sequence.  Built for latency (at batch 1 the kernel is a dependency chain, not a stream):
+//   * everything that does not depend on this token's q/k/v happens BEFORE the wait for the projection kernel:
+//     the position, the rotation angles, and asynchronous copies (cp.async, no registers held) of ALL cached K and
+//     V rows of the block's slice into shared memory -- rows of earlier positions are final; they were evicted
+//     from L2 by a token's worth of weights, so their HBM latency is spent while the projection still runs;
 //   * RoPE on (even, odd) pairs of this head's q and k (examples/llama2/stories110M.sl:86-112:
 //     freq = 1 / 10000^((i % hs)/hs), angle = pos * freq), held in shared memory; the block (split 0, first
-//     head of a KV group) stores the rotated k and v into the caches at `pos` (stories110M.sl:115-121);
-//   * each warp walks timesteps t0+warp, t0+warp+4, ... four at a time (all k and v rows of a batch are
-//     requested before the first use); lanes split the head dimension (hs <= 128); the softmax is carried
-//     online (running max, running sum, running weighted value); timestep `pos` itself is served from the
-//     shared-memory copy, so no block depends on another block's cache write;
-//   * partials (m, s, acc[hs]) go to `part`; the last block of a head to finish (atomic counter, no
-//     waiting) merges the nsplit partials in split order and writes the normalised head output.
-constexpr int ATT_WARPS = 4;
-constexpr int ATT_E = 4;   // head elements per lane (hs <= 128)
-constexpr int ATT_UB = 4;  // timesteps per batch
+//     head of a KV group) stores the rotated k and v into the caches at `pos` (stories110M.sl:115-121) and every
+//     block whose slice holds `pos` puts them into its shared-memory rows, so no block depends on another
+//     block's cache write;
+//   * three short phases out of shared memory instead of an online softmax carried through every timestep (whose
+//     max / exp / rescale chain every lane of a warp repeats per timestep):
+//     (A) raw scores: four threads per timestep, a quarter of the head dimension each (a warp per timestep with a
+//         five-step shuffle reduction took 4.3 us for 143 timesteps);
+//     (B) softmax numerators, one thread per timestep: block maximum, expf, sum;
+//     (C) weighted values: thread (g, i) sums p[t] * v[t][i] over t = g, g+4, ...; the four partial sums of an
+//         element meet in shared memory;
+//   * a slice is at most `cap` positions (what fits in shared memory, at most 256): up to there a head is ONE
+//     block, which writes the normalised head output directly -- no partials in global memory, no counter, no
+//     second round trip.  Longer sequences use one block per `cap` positions (at most nsplit; beyond nsplit * cap a
+//     block walks its slice in rounds); their partials (m, s, acc[hs]) go to `part`, and the last block of a head
+//     to finish (atomic counter, no waiting) merges them in split order.
+constexpr int ATT_WARPS = 16;
+constexpr int ATT_MAX_CAP = 256;
+constexpr size_t ATT_SMEM_BUDGET = 200 * 1024;
+inline int att_cap(int hs) {   // timesteps per block and round
+  const int fit = int(ATT_SMEM_BUDGET / (size_t(hs) * 8));
+  return (fit < ATT_MAX_CAP ? fit : ATT_MAX_CAP) / 16 * 16;
+}
+inline size_t att_smem_bytes(int hs) { return size_t(att_cap(hs)) * hs * 8; }
+
+constexpr int ATT_BOX_ROWS = 16;   // rows per tiled load
 __global__ void __launch_bounds__(ATT_WARPS * 32)
-    attn_fused_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
+    attn_fused_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap, int use_tma,
+                      const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
                       float* __restrict__ kc, float* __restrict__ vc, float* __restrict__ part, int* __restrict__ counters,
                       float* __restrict__ out, const int* __restrict__ ctl, int hs, int kv_dim, int kv_mul, int seq_len,
-                      int layer, int nsplit) {
+                      int layer, int nsplit, int cap, int* status
+#ifdef SIMP_W4_TRACE
+                      , unsigned long long* trace
+#define ATT_MARK(k) do { if (trace && threadIdx.x == 0 && blockIdx.y == 0) trace[size_t(blockIdx.x) * 16 + (k)] = ptx::globaltimer_ns(); } while (0)
+#else
+#define ATT_MARK(k) do { } while (0)
+#endif
+                      ) {
+  ATT_MARK(0);
+  extern __shared__ __align__(128) float att_rows[];   // [cap][hs] K rows, then [cap][hs] V rows
+  __shared__ __align__(8) uint64_t row_bar;
+  __shared__ int abort_flag;
   __shared__ float qs[128], ks[128], vs[128];
-  __shared__ float sm_m[ATT_WARPS], sm_s[ATT_WARPS];
-  __shared__ float sm_acc[ATT_WARPS][128];
+  __shared__ float sc_s[ATT_MAX_CAP];            // scores, then softmax numerators, of the round's timesteps
+  __shared__ float red_m[ATT_WARPS], red_s[ATT_WARPS];
+  __shared__ float sm_acc[4][128];
   __shared__ int is_last;
+  __shared__ float rc[64], rs[64];
   const int h = blockIdx.x, sp = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   pdl_launch_dependents();
-  // Before waiting for q/k/v: the position (written by the previous token's last kernel, long complete), the
-  // rotation angles, and a request for this block's cache rows -- written by earlier tokens and evicted from
-  // L2 by a token's worth of weights since -- so that they are on their way while the projection finishes.
-  __shared__ float rc[64], rs[64];
-  const int pos = ctl[1];
+  const int pos = ctl[1];   // written by the previous token's last kernel, long complete
   const int len = pos + 1;
   const int kvh = h / kv_mul;
   float* kbase = kc + int64_t(layer) * seq_len * kv_dim + kvh * hs;
   float* vbase = vc + int64_t(layer) * seq_len * kv_dim + kvh * hs;
-  // short sequences use fewer splits (one per 32 positions): the other blocks of the head leave at once and the
-  // merge reads only the partials that exist
-  const int eff = min(nsplit, max(1, (len + 31) >> 5));
+  const int eff = min(nsplit, (len + cap - 1) / cap);
   if (sp >= eff) return;
   const int per = (len + eff - 1) / eff;
   const int t0 = sp * per, t1 = min(len, t0 + per);
+  const int nrounds = (per + cap - 1) / cap;   // > 1 only when nsplit blocks of `cap` cannot cover the sequence
+  float* ksm = att_rows;
+  float* vsm = att_rows + size_t(cap) * hs;
+  if (use_tma) {
+    if (threadIdx.x == 0) {
+      ptx::mbar_init(ptx::smem_u32(&row_bar), 1);
+      abort_flag = 0;
+      ptx::fence_barrier_init();
+      ptx::prefetch_tensormap(&kmap);
+      ptx::prefetch_tensormap(&vmap);
+    }
+    __syncthreads();
+  }
+  // async copies of the rows [r0, r0 + rn) (without `pos`) into shared memory; 16 bytes at a time when rows are
+  // 16-byte aligned (hs % 4 == 0 and an aligned cache), else 4 bytes
+  const bool vec16 = (hs & 3) == 0 && (kv_dim & 3) == 0 && ((reinterpret_cast<uintptr_t>(kbase) | reinterpret_cast<uintptr_t>(vbase)) & 15u) == 0;
+  // Tiled loads (TMA) of the rows [r0, r0 + rn) of this head: boxes of ATT_BOX_ROWS rows x hs floats straight into
+  // the row-major shared-memory arrays, one request per box by lane 0 of successive warps; the copy engine keeps
+  // far more bytes in flight per SM than per-thread copies do (those took 8 us for 115 KB).  The box that holds
+  // `pos` brings a stale row, which is overwritten after the loads have landed.
+  auto fetch_rows = [&](int r0, int rn) {
+    if (use_tma) {
+      const int nbox = (rn + ATT_BOX_ROWS - 1) / ATT_BOX_ROWS;
+      const uint32_t bar = ptx::smem_u32(&row_bar), box_bytes = uint32_t(ATT_BOX_ROWS * hs * 4);
+      if (threadIdx.x == 0) ptx::mbar_arrive_expect_tx(bar, uint32_t(nbox) * 2u * box_bytes);
+      if (lane == 0)
+        for (int b = warp; b < nbox; b += ATT_WARPS) {
+          const int y = layer * seq_len + r0 + b * ATT_BOX_ROWS;
+          ptx::tma_load_2d(ptx::smem_u32(ksm) + uint32_t(b) * box_bytes, &kmap, bar, kvh * hs, y);
+          ptx::tma_load_2d(ptx::smem_u32(vsm) + uint32_t(b) * box_bytes, &vmap, bar, kvh * hs, y);
+        }
+      return;
+    }
+    if (vec16) {
+      const int per_row = hs >> 2, n = rn * per_row;
+      for (int e = threadIdx.x; e < n; e += blockDim.x) {
+        const int r = e / per_row, c4 = e - r * per_row;
+        if (r0 + r == pos) continue;
+        const size_t go = size_t(r0 + r) * kv_dim + c4 * 4;
+        const uint32_t so = uint32_t(r * hs + c4 * 4) * 4u;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(ptx::smem_u32(ksm) + so), "l"(kbase + go) : "memory");
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(ptx::smem_u32(vsm) + so), "l"(vbase + go) : "memory");
+      }
+    } else {
+      const int n = rn * hs;
+      for (int e = threadIdx.x; e < n; e += blockDim.x) {
+        const int r = e / hs, c1 = e - r * hs;
+        if (r0 + r == pos) continue;
+        const size_t go = size_t(r0 + r) * kv_dim + c1;
+        const uint32_t so = uint32_t(r * hs + c1) * 4u;
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(ptx::smem_u32(ksm) + so), "l"(kbase + go) : "memory");
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(ptx::smem_u32(vsm) + so), "l"(vbase + go) : "memory");
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  fetch_rows(t0, min(cap, t1 - t0));   // in flight while the projection kernel finishes
   if (int(threadIdx.x) < hs / 2) {
     const int i = 2 * threadIdx.x;
     const float freq = 1.0f / powf(10000.0f, float(i) / float(hs));
@@ -97,29 +183,24 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
     rc[threadIdx.x] = cosf(val);
     rs[threadIdx.x] = sinf(val);
   }
-  {
-    const int lines = (hs * 4 + 127) / 128 + 1;   // a row of hs floats may straddle one more 128-byte line
-    for (int t = t0 + warp; t < t1; t += ATT_WARPS)
-      if (t != pos && lane < 2 * lines) {
-        const float* row = (lane < lines ? kbase : vbase) + int64_t(t) * kv_dim;
-        const int ln = lane < lines ? lane : lane - lines;
-        if (ln * 32 < hs + 31) asm volatile("prefetch.global.L2 [%0];" ::"l"(row + min(ln * 32, hs - 1)));
-      }
-  }
+  ATT_MARK(2);
   pdl_wait();
+  ATT_MARK(3);
   if (int(threadIdx.x) < hs / 2) {
     const int i = 2 * threadIdx.x;
     const float fcr = rc[threadIdx.x], fci = rs[threadIdx.x];
-    const float q0 = q[h * hs + i], q1 = q[h * hs + i + 1];
-    qs[i] = q0 * fcr - q1 * fci;
-    qs[i + 1] = q0 * fci + q1 * fcr;
-    const float k0 = k[kvh * hs + i], k1 = k[kvh * hs + i + 1];
-    ks[i] = k0 * fcr - k1 * fci;
-    ks[i + 1] = k0 * fci + k1 * fcr;
-    vs[i] = v[kvh * hs + i];
-    vs[i + 1] = v[kvh * hs + i + 1];
+    const float2 qq = __ldcg(reinterpret_cast<const float2*>(q + h * hs + i));
+    const float2 kk = __ldcg(reinterpret_cast<const float2*>(k + kvh * hs + i));
+    const float2 vv = __ldcg(reinterpret_cast<const float2*>(v + kvh * hs + i));
+    qs[i] = qq.x * fcr - qq.y * fci;
+    qs[i + 1] = qq.x * fci + qq.y * fcr;
+    ks[i] = kk.x * fcr - kk.y * fci;
+    ks[i + 1] = kk.x * fci + kk.y * fcr;
+    vs[i] = vv.x;
+    vs[i + 1] = vv.y;
   }
   __syncthreads();
+  ATT_MARK(4);
   if (sp == 0 && h % kv_mul == 0) {
     for (int i = threadIdx.x; i < hs; i += blockDim.x) {
       kbase[int64_t(pos) * kv_dim + i] = ks[i];
@@ -127,90 +208,95 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
     }
   }
   const float div = sqrtf(float(hs));
-  float qr[ATT_E], acc[ATT_E];
-#pragma unroll
-  for (int e = 0; e < ATT_E; ++e) {
-    const int i = lane + 32 * e;
-    qr[e] = i < hs ? qs[i] : 0.0f;
-    acc[e] = 0.0f;
-  }
-  float m = -INFINITY, s = 0.0f;
-  for (int tb = t0 + warp; tb < t1; tb += ATT_WARPS * ATT_UB) {
-    float kr[ATT_UB][ATT_E], vr[ATT_UB][ATT_E];
-#pragma unroll
-    for (int u = 0; u < ATT_UB; ++u) {
-      const int t = tb + u * ATT_WARPS;
-#pragma unroll
-      for (int e = 0; e < ATT_E; ++e) {
-        const int i = lane + 32 * e;
-        kr[u][e] = 0.0f;
-        vr[u][e] = 0.0f;
-        if (t < t1 && i < hs) {
-          if (t == pos) {
-            kr[u][e] = ks[i];
-            vr[u][e] = vs[i];
-          } else {
-            kr[u][e] = kbase[int64_t(t) * kv_dim + i];
-            vr[u][e] = vbase[int64_t(t) * kv_dim + i];
-          }
-        }
-      }
+  const int cg = threadIdx.x >> 7, ci = threadIdx.x & 127;   // phase C: group of timesteps, head element
+  float acc = 0.0f;                                          // running weighted value of element ci, timesteps = cg mod 4
+  float Mrun = -INFINITY, Srun = 0.0f;                       // running (max, sum) over the rounds
+  for (int rd = 0; rd < nrounds; ++rd) {
+    const int r0 = t0 + rd * cap;                  // first timestep of the round
+    const int rn = max(0, min(cap, t1 - r0));      // timesteps in the round
+    if (rd > 0) {
+      __syncthreads();   // the previous round's rows and scores are no longer read
+      fetch_rows(r0, rn);
     }
-#pragma unroll
-    for (int u = 0; u < ATT_UB; ++u) {
-      const int t = tb + u * ATT_WARPS;
-      if (t < t1) {  // warp-uniform
+    if (use_tma) {
+      if (!ptx::mbar_wait(ptx::smem_u32(&row_bar), uint32_t(rd) & 1u, &abort_flag, status, 70)) return;   // block-wide flag
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    ATT_MARK(7);
+    // the row of `pos` comes from this token's rotated k and v
+    if (pos >= r0 && pos < r0 + rn)
+      for (int i = threadIdx.x; i < hs; i += blockDim.x) {
+        ksm[(pos - r0) * hs + i] = ks[i];
+        vsm[(pos - r0) * hs + i] = vs[i];
+      }
+    __syncthreads();
+    // ---- (A) raw scores: four threads per timestep, each a quarter of the head dimension (row pitches of 64 or 100
+    // floats keep the 32 lanes of a warp on 32 different banks), two shuffles per timestep
+    {
+      const int part = threadIdx.x & 3, qsz = (hs + 3) >> 2;
+      const int i0 = part * qsz, i1 = min(hs, i0 + qsz);
+      for (int base = 0; base < rn; base += ATT_WARPS * 8) {   // warp-uniform trip count
+        const int r = base + int(threadIdx.x >> 2);
         float d = 0.0f;
-#pragma unroll
-        for (int e = 0; e < ATT_E; ++e) d = fmaf(qr[e], kr[u][e], d);
-        const float score = warp_sum(d) / div;
-        const float m_new = fmaxf(m, score);
-        const float corr = expf(m - m_new);  // 0 on the first step (m = -inf)
-        const float p = expf(score - m_new);
-        s = s * corr + p;
-#pragma unroll
-        for (int e = 0; e < ATT_E; ++e) acc[e] = acc[e] * corr + p * vr[u][e];
-        m = m_new;
+        if (r < rn) {
+          const float* kr = ksm + r * hs;
+          for (int i = i0; i < i1; ++i) d = fmaf(qs[i], kr[i], d);
+        }
+        d += __shfl_xor_sync(0xffffffffu, d, 1);
+        d += __shfl_xor_sync(0xffffffffu, d, 2);
+        if (r < rn && part == 0) sc_s[r] = d / div;
       }
     }
-  }
-  if (lane == 0) {
-    sm_m[warp] = m;
-    sm_s[warp] = s;
-  }
+    __syncthreads();
+    ATT_MARK(8);
+    // ---- (B) softmax numerators of the round: block maximum, expf, sum
+    const float x = int(threadIdx.x) < rn ? sc_s[threadIdx.x] : -INFINITY;
+    float mx = x;
 #pragma unroll
-  for (int e = 0; e < ATT_E; ++e) {
-    const int i = lane + 32 * e;
-    if (i < hs) sm_acc[warp][i] = acc[e];
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if (lane == 0) red_m[warp] = mx;
+    __syncthreads();
+    float M = red_m[0];
+#pragma unroll
+    for (int w = 1; w < ATT_WARPS; ++w) M = fmaxf(M, red_m[w]);
+    const float Mnew = fmaxf(Mrun, M);
+    const float pnum = int(threadIdx.x) < rn ? expf(x - Mnew) : 0.0f;
+    if (int(threadIdx.x) < rn) sc_s[threadIdx.x] = pnum;
+    const float ps = warp_sum(pnum);
+    if (lane == 0) red_s[warp] = ps;
+    __syncthreads();
+    float S = 0.0f;
+#pragma unroll
+    for (int w = 0; w < ATT_WARPS; ++w) S += red_s[w];
+    const float corr = Mrun == -INFINITY ? 0.0f : expf(Mrun - Mnew);   // rescales earlier rounds
+    Srun = Srun * corr + S;
+    Mrun = Mnew;
+    ATT_MARK(9);
+    // ---- (C) weighted values
+    acc *= corr;
+    if (ci < hs)
+      for (int r = cg; r < rn; r += 4) acc = fmaf(sc_s[r], vsm[r * hs + ci], acc);
   }
+  ATT_MARK(5);
+  if (ci < hs) sm_acc[cg][ci] = acc;
   __syncthreads();
   float* mine = part + (int64_t(h) * nsplit + sp) * (hs + 2);
-  if (warp == 0) {
-    float M = -INFINITY;
-#pragma unroll
-    for (int w = 0; w < ATT_WARPS; ++w) M = fmaxf(M, sm_m[w]);
-    float S = 0.0f;
-    float sc[ATT_WARPS];
-#pragma unroll
-    for (int w = 0; w < ATT_WARPS; ++w) {
-      sc[w] = sm_m[w] == -INFINITY ? 0.0f : expf(sm_m[w] - M);
-      S += sm_s[w] * sc[w];
-    }
-    if (lane == 0) {
-      mine[0] = M;
-      mine[1] = S;
-    }
-#pragma unroll
-    for (int e = 0; e < ATT_E; ++e) {
-      const int i = lane + 32 * e;
-      if (i < hs) {
-        float a = 0.0f;
-#pragma unroll
-        for (int w = 0; w < ATT_WARPS; ++w) a += sm_acc[w][i] * sc[w];
-        mine[2 + i] = a;
+  if (int(threadIdx.x) < hs) {
+    const int i = threadIdx.x;
+    const float a = (sm_acc[0][i] + sm_acc[1][i]) + (sm_acc[2][i] + sm_acc[3][i]);
+    if (eff == 1) {   // the whole sequence was this block's: normalised output, done
+      out[h * hs + i] = a / Srun;
+    } else {
+      if (i == 0) {
+        mine[0] = Mrun;
+        mine[1] = Srun;
       }
+      mine[2 + i] = a;
     }
   }
+  ATT_MARK(6);
+  if (eff == 1) return;
   // last block of this head merges (writes above are published by the fence + atomic)
   __threadfence();
   __syncthreads();
@@ -223,27 +309,27 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
   const float* p = part + int64_t(h) * nsplit * (hs + 2);
   float mm[MAXS], ssum[MAXS], ex[MAXS];
 #pragma unroll
-  for (int x = 0; x < MAXS; ++x) {
-    mm[x] = x < eff ? __ldcg(p + x * (hs + 2)) : -INFINITY;
-    ssum[x] = x < eff ? __ldcg(p + x * (hs + 2) + 1) : 0.0f;
+  for (int x2 = 0; x2 < MAXS; ++x2) {
+    mm[x2] = x2 < eff ? __ldcg(p + x2 * (hs + 2)) : -INFINITY;
+    ssum[x2] = x2 < eff ? __ldcg(p + x2 * (hs + 2) + 1) : 0.0f;
   }
   float M = -INFINITY;
 #pragma unroll
-  for (int x = 0; x < MAXS; ++x) M = fmaxf(M, mm[x]);
+  for (int x2 = 0; x2 < MAXS; ++x2) M = fmaxf(M, mm[x2]);
   float S = 0.0f;
 #pragma unroll
-  for (int x = 0; x < MAXS; ++x) {
-    ex[x] = mm[x] != -INFINITY ? expf(mm[x] - M) : 0.0f;
-    if (mm[x] != -INFINITY) S += ssum[x] * ex[x];
+  for (int x2 = 0; x2 < MAXS; ++x2) {
+    ex[x2] = mm[x2] != -INFINITY ? expf(mm[x2] - M) : 0.0f;
+    if (mm[x2] != -INFINITY) S += ssum[x2] * ex[x2];
   }
   for (int i = threadIdx.x; i < hs; i += blockDim.x) {
     float val[MAXS];
 #pragma unroll
-    for (int x = 0; x < MAXS; ++x) val[x] = x < eff ? __ldcg(p + x * (hs + 2) + 2 + i) : 0.0f;
+    for (int x2 = 0; x2 < MAXS; ++x2) val[x2] = x2 < eff ? __ldcg(p + x2 * (hs + 2) + 2 + i) : 0.0f;
     float a = 0.0f;
 #pragma unroll
-    for (int x = 0; x < MAXS; ++x)
-      if (mm[x] != -INFINITY) a += val[x] * ex[x];
+    for (int x2 = 0; x2 < MAXS; ++x2)
+      if (mm[x2] != -INFINITY) a += val[x2] * ex[x2];
     out[h * hs + i] = a / S;
   }
   if (threadIdx.x == 0) counters[h] = 0;
@@ -317,6 +403,31 @@ __global__ void __launch_bounds__(1024) argmax_advance_kernel(const float* __res
 }
 
 // ---------------------------------------------------------------------------------------------
+// Tensor map of a key / value cache viewed as [rows, kv_dim] f32 with boxes of ATT_BOX_ROWS rows x hs columns.
+static int make_cache_map(CUtensorMap* map, const float* base, int64_t rows, int64_t kv_dim, int64_t hs) {
+  typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  static EncodeFn enc = nullptr;
+  if (!enc) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      enc = reinterpret_cast<EncodeFn>(sym);
+  }
+  SIMP_REQUIRE(enc != nullptr, SIMP_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
+  cuuint64_t dims[2] = {cuuint64_t(kv_dim), cuuint64_t(rows)};
+  cuuint64_t strides[1] = {cuuint64_t(kv_dim) * 4};
+  cuuint32_t box[2] = {cuuint32_t(hs), cuuint32_t(ATT_BOX_ROWS)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  SIMP_REQUIRE(r == CUDA_SUCCESS, SIMP_ERR_CUDA, "cuTensorMapEncodeTiled (kv cache) failed with CUresult %d", int(r));
+  return SIMP_OK;
+}
+
 static int dev_alloc(void** p, size_t bytes) {
   SIMP_CUDA(cudaMalloc(p, bytes ? bytes : 16));
   return SIMP_OK;
@@ -361,9 +472,13 @@ static int enqueue_token(LlamaModel& m, cudaStream_t st) {
       g.nseg = 3; g.k4 = dim / 4; g.x = m.x; g.norm_w = m.rms_att + l * dim; g.eps = 1e-5f;
       if (int rc = gemv_f32_dec_launch<GEMV_STORE>(g, st, sms, pdl)) return rc;
     }
-    LAUNCH_OR_FAIL(attn_fused_kernel, dim3(unsigned(c.n_heads), unsigned(m.nsplit)), dim3(ATT_WARPS * 32), 0, st, pdl,
-                   (const float*)m.q, (const float*)m.k, (const float*)m.v, m.kc, m.vc, m.attn_part, m.attn_cnt, m.xb,
-                   (const int*)m.ctl, hs, kv, int(c.n_heads / c.n_kv_heads), int(c.seq_len), int(l), m.nsplit);
+    LAUNCH_OR_FAIL(attn_fused_kernel, dim3(unsigned(c.n_heads), unsigned(m.nsplit)), dim3(ATT_WARPS * 32), att_smem_bytes(hs), st, pdl,
+                   m.kmap, m.vmap, int(m.kv_tma), (const float*)m.q, (const float*)m.k, (const float*)m.v, m.kc, m.vc, m.attn_part, m.attn_cnt, m.xb,
+                   (const int*)m.ctl, hs, kv, int(c.n_heads / c.n_kv_heads), int(c.seq_len), int(l), m.nsplit, att_cap(hs), ctx().dev_status
+#ifdef SIMP_W4_TRACE
+                   , (unsigned long long*)nullptr
+#endif
+                   );
     {
       GemvDecArgs o{};
       o.seg[0] = GemvSeg{m.wo + l * dim * dim, m.x, dim};
@@ -397,8 +512,21 @@ static int enqueue_token(LlamaModel& m, cudaStream_t st) {
 // replicated input vector, and the row slices are exchanged with in-place all-gathers.  Every projection kernel
 // packs its (gathered) input vector itself and folds the preceding rmsnorm in, so each output element keeps the
 // single-GPU arithmetic.
+#ifdef SIMP_W4_TRACE
+static unsigned long long* g_w4_trace = nullptr;   // instrumented builds: [4 projections of layer 1][148 blocks][16 marks]
+#endif
+
 static int enqueue_token_tp(LlamaModel& m, cudaStream_t st) {
   const simp_llama_config& c = m.cfg;
+#ifdef SIMP_W4_TRACE
+  if (!g_w4_trace) {
+    cudaMalloc(&g_w4_trace, 5 * 148 * 16 * 8);
+    cudaMemset(g_w4_trace, 0, 5 * 148 * 16 * 8);
+  }
+#define W4_TRACE_SET(args, which) (args).trace = (l == 1) ? g_w4_trace + size_t(which) * 148 * 16 : nullptr
+#else
+#define W4_TRACE_SET(args, which) do { } while (0)
+#endif
   const int R = m.tp, rk = m.rank;
   const int dim = int(c.dim), hd = int(c.hidden_dim), kv = int(m.kv_dim), hs = int(m.head_size);
   const int dim_l = dim / R, kv_l = kv / R, hd_l = hd / R, V_l = int(c.vocab_size) / R, heads_l = int(c.n_heads) / R;
@@ -412,6 +540,17 @@ static int enqueue_token_tp(LlamaModel& m, cudaStream_t st) {
     const int64_t o = m.loff[fam] + layer * rows_l * cols;
     return W4Seg{m.qweights + o / 2, m.scales + o / c.group_size, m.zeros ? m.zeros + o / c.group_size : nullptr, out,
                  int(rows_l)};
+  };
+  // weights and scales of (family, layer) as L2 prefetch regions i, i+1 of a launch's arguments
+  static const bool x_nx = !getenv("SIMP_X_NX") || atoi(getenv("SIMP_X_NX")) != 0;
+  static const bool x_kv = !getenv("SIMP_X_KVPF") || atoi(getenv("SIMP_X_KVPF")) != 0;
+  auto next_weights = [&](W4Args& a, int i, int fam, int64_t layer, int64_t rows_l, int64_t cols) {
+    if (layer >= c.n_layers || m.zeros || !x_nx) return;
+    const int64_t o = m.loff[fam] + layer * rows_l * cols;
+    a.nx_base[i] = m.qweights + o / 2;
+    a.nx_bytes[i] = uint32_t(rows_l * cols / 2);
+    a.nx_base[i + 1] = reinterpret_cast<const uint8_t*>(m.scales + o / c.group_size);
+    a.nx_bytes[i + 1] = uint32_t(rows_l * cols / c.group_size * 4);
   };
   // input vector x; norm_w != nullptr folds rmsnorm(x, norm_w) into the projection
   auto w4args = [&](int cols, const float* x, const float* norm_w) {
@@ -438,17 +577,32 @@ static int enqueue_token_tp(LlamaModel& m, cudaStream_t st) {
       a.seg[1] = w4seg(1, l, kv_l, dim, m.k);
       a.seg[2] = w4seg(2, l, kv_l, dim, m.v);
       a.nseg = 3;
+      // the attention kernel that follows reads this layer's cached keys / values of all earlier positions; they were
+      // evicted from L2 by a token's worth of weights, so this launch requests them into L2 while it streams
+      a.pf_len = x_kv ? m.ctl + 1 : nullptr;
+      a.pf_base[0] = reinterpret_cast<const uint8_t*>(m.kc + size_t(l) * c.seq_len * kv_l);
+      a.pf_base[1] = reinterpret_cast<const uint8_t*>(m.vc + size_t(l) * c.seq_len * kv_l);
+      a.pf_row_bytes = kv_l * 4;
+      next_weights(a, 0, 3, l, dim_l, dim);   // wo
+      W4_TRACE_SET(a, 0);
       if (int rc = w4_launch<W4_STORE>(a, st, sms, chain_x)) return rc;
     }
-    LAUNCH_OR_FAIL(attn_fused_kernel, dim3(unsigned(heads_l), unsigned(m.nsplit)), dim3(ATT_WARPS * 32), 0, st, true,
-                   (const float*)m.q, (const float*)m.k, (const float*)m.v, m.kc, m.vc, m.attn_part, m.attn_cnt,
+    LAUNCH_OR_FAIL(attn_fused_kernel, dim3(unsigned(heads_l), unsigned(m.nsplit)), dim3(ATT_WARPS * 32), att_smem_bytes(hs), st, true,
+                   m.kmap, m.vmap, int(m.kv_tma), (const float*)m.q, (const float*)m.k, (const float*)m.v, m.kc, m.vc, m.attn_part, m.attn_cnt,
                    m.xb + rk * dim_l, (const int*)m.ctl, hs, kv_l, int(c.n_heads / c.n_kv_heads), int(c.seq_len), int(l),
-                   m.nsplit);
+                   m.nsplit, att_cap(hs), ctx().dev_status
+#ifdef SIMP_W4_TRACE
+                   , (unsigned long long*)(l == 1 ? g_w4_trace + size_t(4) * 148 * 16 : nullptr)
+#endif
+                   );
     if (int rc = gather(m.xb, dim_l)) return rc;
     {
       W4Args a = w4args(dim, m.xb, nullptr);
       a.seg[0] = w4seg(3, l, dim_l, dim, m.x + rk * dim_l);
       a.nseg = 1; a.res = m.x + rk * dim_l;
+      next_weights(a, 0, 4, l, hd_l, dim);    // gate
+      next_weights(a, 2, 6, l, hd_l, dim);    // up
+      W4_TRACE_SET(a, 1);
       if (int rc = w4_launch<W4_ADD>(a, st, sms, chain_x)) return rc;
     }
     if (int rc = gather(m.x, dim_l)) return rc;
@@ -457,6 +611,8 @@ static int enqueue_token_tp(LlamaModel& m, cudaStream_t st) {
       g.seg[0] = w4seg(4, l, hd_l, dim, m.hb + rk * hd_l);
       g.seg[1] = w4seg(6, l, hd_l, dim, nullptr);
       g.nseg = 2;
+      next_weights(g, 0, 5, l, dim_l, hd);    // down
+      W4_TRACE_SET(g, 2);
       if (int rc = w4_launch<W4_GATE_UP>(g, st, sms, chain_x)) return rc;
     }
     if (int rc = gather(m.hb, hd_l)) return rc;
@@ -464,6 +620,10 @@ static int enqueue_token_tp(LlamaModel& m, cudaStream_t st) {
       W4Args d = w4args(hd, m.hb, nullptr);
       d.seg[0] = w4seg(5, l, dim_l, hd, m.x + rk * dim_l);
       d.nseg = 1; d.res = m.x + rk * dim_l;
+      next_weights(d, 0, 0, l + 1, dim_l, dim);   // the next layer's q | k | v
+      next_weights(d, 2, 1, l + 1, kv_l, dim);
+      next_weights(d, 4, 2, l + 1, kv_l, dim);
+      W4_TRACE_SET(d, 3);
       if (int rc = w4_launch<W4_ADD>(d, st, sms, chain_x)) return rc;
     }
     if (int rc = gather(m.x, dim_l)) return rc;
@@ -486,6 +646,13 @@ static int enqueue_token_tp(LlamaModel& m, cudaStream_t st) {
 static int ensure_graph(LlamaModel& m) {
   if (m.graph) return SIMP_OK;
   cudaStream_t st = ctx().stream;
+  {
+    static bool att_attr_set = false;   // the attention kernel stages its K / V rows in dynamic shared memory
+    if (!att_attr_set) {
+      SIMP_CUDA(cudaFuncSetAttribute(attn_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(ATT_SMEM_BUDGET)));
+      att_attr_set = true;
+    }
+  }
   // one eager pass first (sets function attributes, surfaces launch errors outside capture); it
   // rewrites the same cache row the replay will write, so it is harmless
   int ctl_save[5];
@@ -600,6 +767,17 @@ SIMP_API int simp_llama_create(const simp_llama_config* cfg, void** model) {
   A((void**)&m->pk_bar, 64);
   A((void**)&m->pk_best_val, size_t(ctx().sm_count) * 4);
   A((void**)&m->pk_best_idx, size_t(ctx().sm_count) * 4);
+  if (rc == SIMP_OK) {
+    // tiled loads of cache rows need 16-byte multiples everywhere: head_size and the per-rank row length % 4 == 0
+    const int64_t kv_l = m->kv_dim / tp;
+    memset(&m->kmap, 0, sizeof(m->kmap));
+    memset(&m->vmap, 0, sizeof(m->vmap));
+    m->kv_tma = hs % 4 == 0 && kv_l % 4 == 0;
+    if (m->kv_tma) {
+      rc = make_cache_map(&m->kmap, m->kc, c.n_layers * c.seq_len, kv_l, hs);
+      if (rc == SIMP_OK) rc = make_cache_map(&m->vmap, m->vc, c.n_layers * c.seq_len, kv_l, hs);
+    }
+  }
   if (rc != SIMP_OK) { simp_llama_destroy(m); return rc; }
   cudaMemsetAsync(m->ctl, 0, 64, ctx().stream);
   cudaMemsetAsync(m->attn_cnt, 0, size_t(c.n_heads) * 4, ctx().stream);
@@ -734,7 +912,7 @@ SIMP_API int simp_llama_forward(void* model, int64_t token, int64_t pos, float* 
   if (logits_host)
     SIMP_CUDA(cudaMemcpyAsync(logits_host, m.logits, size_t(m.cfg.vocab_size) * 4, cudaMemcpyDeviceToHost, st));
   SIMP_CUDA(cudaStreamSynchronize(st));
-  return SIMP_OK;
+  return simp_gpu_check_device_status();
 }
 
 // Teacher-forces `prompt` (positions 0..n_prompt-1), then generates n_new tokens greedily.
@@ -782,7 +960,7 @@ SIMP_API int simp_llama_generate(void* model, const int32_t* prompt, int64_t n_p
   if (ms_out) SIMP_CUDA(cudaEventElapsedTime(ms_out, e0, e1));
   cudaEventDestroy(e0);
   cudaEventDestroy(e1);
-  return SIMP_OK;
+  return simp_gpu_check_device_status();   // a bounded device-side wait that gave up makes the tokens meaningless
 }
 
 SIMP_API int simp_llama_kernels_per_token(void* model, int64_t* kernels) {
@@ -811,3 +989,11 @@ SIMP_API int simp_llama_destroy(void* model) {
   delete m;
   return SIMP_OK;
 }
+
+#ifdef SIMP_W4_TRACE
+SIMP_API int simp_debug_w4_trace(unsigned long long* host_out, size_t words) {
+  SIMP_REQUIRE(simp::g_w4_trace != nullptr, SIMP_ERR_STATE, "no trace yet");
+  SIMP_CUDA(cudaMemcpy(host_out, simp::g_w4_trace, words * 8, cudaMemcpyDeviceToHost));
+  return SIMP_OK;
+}
+#endif

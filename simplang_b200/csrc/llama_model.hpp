@@ -1,6 +1,7 @@
 // llama_model.hpp -- device-resident state of one LLaMA decoder (shared by the per-op graph path in
 // llama.cu and the persistent per-token kernel in llama_persistent.cu).
 #pragma once
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <cstdint>
 
@@ -30,6 +31,10 @@ struct LlamaModel {
   int32_t *prompt = nullptr, *out_tokens = nullptr;
   int64_t prompt_cap = 0, out_cap = 0;
   int nsplit = 1;
+  // tensor maps of the key / value caches for the attention kernel's tiled loads: [n_layers * seq_len rows, kv_dim]
+  // f32, boxes of 16 rows x head_size (valid when head_size % 4 == 0)
+  CUtensorMap kmap, vmap;
+  bool kv_tma = false;
   // scratch of the persistent per-token kernels: grid-barrier words, per-block argmax candidates
   unsigned* pk_bar = nullptr;
   float* pk_best_val = nullptr;

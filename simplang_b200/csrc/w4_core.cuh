@@ -93,10 +93,29 @@ struct W4Args {
   int norm;
   float ss_div, eps;
   const float* res;        // W4_ADD: out[i] = res[i] + dot (segment 0 only)
+  // L2 prefetch on behalf of a later kernel: pf_len[0] rows of pf_row_bytes bytes from each of pf_base[0..1]
+  // (nullptr: none)
+  const int* pf_len;
+  const uint8_t* pf_base[2];
+  int pf_row_bytes;
+  // L2 prefetch of the NEXT launch's weights (regions of nx_bytes[i] bytes at nx_base[i], 16-byte aligned; unused
+  // entries have nx_bytes 0): every block requests a share right after its own tiles, so HBM keeps streaming
+  // through this launch's wait for its input, its arithmetic and the launch gap.
+  const uint8_t* nx_base[6];
+  uint32_t nx_bytes[6];
   int total_tiles;         // row tiles over all segments (W4_GATE_UP: over segment 0)
   int* status;             // device error word for bounded waits
   int seg_tile_start[4];
+#ifdef SIMP_W4_TRACE
+  unsigned long long* trace;   // instrumented builds: [gridDim.x][16] globaltimer marks of this launch, or nullptr
+#endif
 };
+
+#ifdef SIMP_W4_TRACE
+#define W4_MARK(k) do { if (a.trace && threadIdx.x == 0) a.trace[size_t(blockIdx.x) * 16 + (k)] = ptx::globaltimer_ns(); } while (0)
+#else
+#define W4_MARK(k) do { } while (0)
+#endif
 
 // Shared-memory footprint of one pipeline stage: TR rows of every streamed matrix with their scales (+zeros).
 inline size_t w4_stage_bytes(int cols, int groups_per_row, int nm, bool zeros, int tr) {
@@ -188,7 +207,7 @@ __device__ __forceinline__ void w4_mma_spans(const W4Tile& tl, int r0, int vrows
 // rows (TR == 8: one half-used slab), the NW warps split slabs x interleaved 128-weight spans, and the
 // per-warp partial sums of a row meet in a small shared array.  NW = 8 with up to three blocks per SM; for rows so
 // long that only 8-row tiles would fit that way, NW = 16 with 16-row tiles and one block per SM.
-template <int MODE, int TR, int NW, int NS>
+template <int MODE, int TR, int NW, int NS, bool BATCH>
 __global__ void __launch_bounds__(NW * 32, NW == 8 ? 3 : 1) w4_gemv_kernel(const W4Args a) {
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ float sh_ss[NW];
@@ -199,7 +218,8 @@ __global__ void __launch_bounds__(NW * 32, NW == 8 ? 3 : 1) w4_gemv_kernel(const
   constexpr int SL = TR == 32 ? 2 : 1;      // slabs per tile
   constexpr int KP = NW / SL;               // warps that split the spans of one slab
   constexpr bool HALF = TR == 8;
-  __shared__ float red[2][NM][KP][S_ROWS];
+  __shared__ float red[BATCH ? NS : 2][NM][KP][S_ROWS];
+  W4_MARK(0);
   const int nchunks = a.cols >> 5;
   const int row_bytes = a.cols >> 1;
   const int sc_row = a.groups_per_row;  // floats of scale per row
@@ -221,28 +241,39 @@ __global__ void __launch_bounds__(NW * 32, NW == 8 ? 3 : 1) w4_gemv_kernel(const
     row0 = (tile - a.seg_tile_start[s]) * S_ROWS;
     rows = a.seg[s].rows;
   };
-  // Requests tile q.  Full tiles: one elected thread issues bulk copies; a ragged last tile is copied with
-  // plain loads by every thread (bulk copies need 16-byte multiples) and published by the same barrier.
-  auto issue = [&](int q) {
-    if (q >= my_steps) return;
-    int s, row0, rows;
-    locate(q, s, row0, rows);
-    const int st = q % NS;
-    const int vr = min(S_ROWS, rows - row0);
-    const uint32_t bar = ptx::smem_u32(&bars[st]);
-    if (vr == S_ROWS) {
-      if (threadIdx.x == 0) {
-        ptx::mbar_arrive_expect_tx(bar, uint32_t(stage_bytes));
-#pragma unroll
-        for (int m = 0; m < NM; ++m) {
-          const W4Seg& sg = a.seg[MODE == W4_GATE_UP ? m : s];
-          uint8_t* dst = stage_ptr(st, m);
-          ptx::bulk_load(ptx::smem_u32(dst), sg.qw + size_t(row0) * row_bytes, uint32_t(mat_w), bar);
-          ptx::bulk_load(ptx::smem_u32(dst + mat_w), sg.sc + size_t(row0) * sc_row, uint32_t(mat_s), bar);
-          if (has_z) ptx::bulk_load(ptx::smem_u32(dst + mat_w + mat_s), sg.zr + size_t(row0) * sc_row, uint32_t(mat_s), bar);
-        }
-      }
-    } else {
+  // Requests of tiles.  A full tile is P = NM x (weights, scales[, zeros]) bulk copies onto the stage's barrier.
+  // One thread accepts ~2.5 M bulk-copy requests per second whatever their size, so a round of tiles is spread
+  // over the warps: request r of the round (tile r / P, piece r % P) is made by lane 0 of warp r % NW; the thread
+  // with piece 0 also posts the stage's byte count (a copy that completes before that only drives the barrier's
+  // byte count negative, which the barrier allows).  A ragged last tile (bulk copies need 16-byte multiples) is
+  // copied with plain loads by the whole block and published on the same barrier.
+  const int P = NM * (has_z ? 3 : 2);
+  auto issue_round = [&](int q_first, int count) {
+    for (int r = warp; r < count * P; r += NW) {
+      const int q = q_first + r / P, piece = r % P;
+      if (q >= my_steps || lane != 0) continue;
+      int s, row0, rows;
+      locate(q, s, row0, rows);
+      if (rows - row0 < S_ROWS) continue;   // ragged: below
+      const int st = q % NS;
+      const uint32_t bar = ptx::smem_u32(&bars[st]);
+      const int m = piece / (has_z ? 3 : 2), part = piece % (has_z ? 3 : 2);
+      const W4Seg& sg = a.seg[MODE == W4_GATE_UP ? m : s];
+      uint8_t* dst = stage_ptr(st, m);
+      if (piece == 0) ptx::mbar_arrive_expect_tx(bar, uint32_t(stage_bytes));
+      const uint64_t pol = ptx::l2_evict_first_policy();   // weights are read once per pass
+      if (part == 0) ptx::bulk_load_hint(ptx::smem_u32(dst), sg.qw + size_t(row0) * row_bytes, uint32_t(mat_w), bar, pol);
+      else if (part == 1) ptx::bulk_load_hint(ptx::smem_u32(dst + mat_w), sg.sc + size_t(row0) * sc_row, uint32_t(mat_s), bar, pol);
+      else ptx::bulk_load_hint(ptx::smem_u32(dst + mat_w + mat_s), sg.zr + size_t(row0) * sc_row, uint32_t(mat_s), bar, pol);
+    }
+    for (int j = 0; j < count; ++j) {   // block-uniform
+      const int q = q_first + j;
+      if (q >= my_steps) break;
+      int s, row0, rows;
+      locate(q, s, row0, rows);
+      const int vr = rows - row0;
+      if (vr >= S_ROWS) continue;
+      const int st = q % NS;
 #pragma unroll
       for (int m = 0; m < NM; ++m) {
         const W4Seg& sg = a.seg[MODE == W4_GATE_UP ? m : s];
@@ -255,24 +286,12 @@ __global__ void __launch_bounds__(NW * 32, NW == 8 ? 3 : 1) w4_gemv_kernel(const
         }
       }
       __syncthreads();
-      if (threadIdx.x == 0) ptx::mbar_arrive(bar);
+      if (threadIdx.x == 0) ptx::mbar_arrive(ptx::smem_u32(&bars[st]));
     }
   };
 
-  if (threadIdx.x == 0) {
-#pragma unroll
-    for (int k = 0; k < NS; ++k) ptx::mbar_init(ptx::smem_u32(&bars[k]), 1);
-    abort_flag = 0;
-    ptx::fence_barrier_init();
-  }
-  __syncthreads();
-  // Weights never change: the first NS tiles are requested before waiting for the producer of the input.
-#pragma unroll
-  for (int k = 0; k < NS; ++k) issue(k);
-  // Pack the input vector into this block's shared memory, four threads per chunk, W4_PACK_ROUNDS rounds of
-  // loads in flight together.  The norm weights never change: the first batch is requested before waiting for
-  // the producer of x (they miss in L2 once per layer).
-  pdl_launch_dependents();
+  // The norm weights never change either (they miss in L2 once per layer): they are requested FIRST, ahead of the
+  // weight tiles in the memory system's queues, so that they are at hand when the input vector arrives.
   const int ntask = nchunks * 4;
   float ssl = 0.0f;
   float4 mv[W4_PACK_ROUNDS][2];
@@ -285,7 +304,42 @@ __global__ void __launch_bounds__(NW * 32, NW == 8 ? 3 : 1) w4_gemv_kernel(const
       mv[r][1] = __ldg(reinterpret_cast<const float4*>(a.mul) + 2 * q + 1);
     }
   }
+  if (threadIdx.x == 0) {
+#pragma unroll
+    for (int k = 0; k < NS; ++k) ptx::mbar_init(ptx::smem_u32(&bars[k]), 1);
+    abort_flag = 0;
+    ptx::fence_barrier_init();
+  }
+  __syncthreads();
+  // Weights never change: the first NS tiles are requested before waiting for the producer of the input.
+  issue_round(0, NS);
+  W4_MARK(1);
+  pdl_launch_dependents();
+  // Optional: bring a read-only region that a LATER kernel needs (the attention kernel's key / value rows of
+  // earlier positions, evicted from L2 by a token's worth of weights) into L2 while this launch streams.
+  if (warp == NW - 1 && lane < 6 && a.nx_bytes[lane] != 0 && (reinterpret_cast<uintptr_t>(a.nx_base[lane]) & 15u) == 0) {
+    // this block's share of region `lane`, in 16-byte units; one request of at most 64 KB per loop trip
+    const uint32_t units = a.nx_bytes[lane] >> 4;
+    const uint32_t u0 = uint32_t(uint64_t(units) * blockIdx.x / gridDim.x), u1 = uint32_t(uint64_t(units) * (blockIdx.x + 1) / gridDim.x);
+    const uint64_t pol = ptx::l2_evict_first_policy();
+    for (uint32_t u = u0; u < u1; u += 4096)
+      ptx::bulk_prefetch_l2(a.nx_base[lane] + size_t(u) * 16, (min(u1, u + 4096) - u) * 16, pol);
+  }
+  if (a.pf_len) {
+    const int n = __ldg(a.pf_len) * a.pf_row_bytes;   // bytes per region
+    for (int o = (int(blockIdx.x) * int(blockDim.x) + int(threadIdx.x)) * 128; o < n; o += int(gridDim.x) * int(blockDim.x) * 128) {
+      // real loads whose values are never used (a prefetch instruction is only a hint and did not help here)
+      uint32_t d0, d1;
+      asm volatile("ld.global.cg.u32 %0, [%1];" : "=r"(d0) : "l"(a.pf_base[0] + o) : "memory");
+      asm volatile("ld.global.cg.u32 %0, [%1];" : "=r"(d1) : "l"(a.pf_base[1] + o) : "memory");
+    }
+  }
+  // Pack the input vector into this block's shared memory, four threads per chunk, W4_PACK_ROUNDS rounds of
+  // loads in flight together.
   pdl_wait();
+  W4_MARK(2);
+  // (The arithmetic of a round exists once in the code: a kernel of a decode step runs every instruction only a
+  // few times, so what it costs is largely fetching the instruction -- compact code beats unrolled code here.)
   for (int b0 = 0; b0 < ntask; b0 += W4_PACK_ROUNDS * int(blockDim.x)) {
     float4 xv[W4_PACK_ROUNDS][2];
 #pragma unroll
@@ -301,17 +355,20 @@ __global__ void __launch_bounds__(NW * 32, NW == 8 ? 3 : 1) w4_gemv_kernel(const
         }
       }
     }
-#pragma unroll
+    static_assert(W4_PACK_ROUNDS == 3, "the rotation below is written for three rounds");
+#pragma unroll 1
     for (int r = 0; r < W4_PACK_ROUNDS; ++r) {
+      if (b0 + r * int(blockDim.x) >= ntask) break;   // uniform over the block: whole warps take part in the shuffles
       const int q = b0 + r * int(blockDim.x) + int(threadIdx.x);
-      if (b0 + r * int(blockDim.x) < ntask) {   // uniform over the block: whole warps take part in the shuffles
-        float v[8] = {xv[r][0].x, xv[r][0].y, xv[r][0].z, xv[r][0].w, xv[r][1].x, xv[r][1].y, xv[r][1].z, xv[r][1].w};
+      float v[8] = {xv[0][0].x, xv[0][0].y, xv[0][0].z, xv[0][0].w, xv[0][1].x, xv[0][1].y, xv[0][1].z, xv[0][1].w};
 #pragma unroll
-        for (int i = 0; i < 8; ++i) ssl = fmaf(v[i], v[i], ssl);
-        v[0] *= mv[r][0].x; v[1] *= mv[r][0].y; v[2] *= mv[r][0].z; v[3] *= mv[r][0].w;
-        v[4] *= mv[r][1].x; v[5] *= mv[r][1].y; v[6] *= mv[r][1].z; v[7] *= mv[r][1].w;
-        w4_pack_quarter(v, q < ntask, q & 3, smem + size_t(q >> 2) * (W4_CHUNK_U4 * 16));
-      }
+      for (int i = 0; i < 8; ++i) ssl = fmaf(v[i], v[i], ssl);
+      v[0] *= mv[0][0].x; v[1] *= mv[0][0].y; v[2] *= mv[0][0].z; v[3] *= mv[0][0].w;
+      v[4] *= mv[0][1].x; v[5] *= mv[0][1].y; v[6] *= mv[0][1].z; v[7] *= mv[0][1].w;
+      w4_pack_quarter(v, q < ntask, q & 3, smem + size_t(q >> 2) * (W4_CHUNK_U4 * 16));
+      // the next round's values move into place (register moves)
+      xv[0][0] = xv[1][0]; xv[0][1] = xv[1][1]; xv[1][0] = xv[2][0]; xv[1][1] = xv[2][1];
+      mv[0][0] = mv[1][0]; mv[0][1] = mv[1][1]; mv[1][0] = mv[2][0]; mv[1][1] = mv[2][1];
     }
   }
   if (a.norm) {
@@ -327,55 +384,140 @@ __global__ void __launch_bounds__(NW * 32, NW == 8 ? 3 : 1) w4_gemv_kernel(const
     inv_r = 1.0f / sqrtf(ss / a.ss_div + a.eps);
   }
   const int slab = warp % SL, kpart = warp / SL;
+  W4_MARK(3);
+  const int nspans = (nchunks + 3) >> 2;
 
-  for (int q = 0; q < my_steps; ++q) {
-    int s, row0, rows;
-    locate(q, s, row0, rows);
-    const int st = q % NS, rb = q & 1;   // weight stage; buffer of the partial sums
-    // residual rows are requested before the tile's arithmetic so that their latency is not paid in the epilogue
-    float resid = 0.0f;
-    if (MODE == W4_ADD && int(threadIdx.x) < S_ROWS && row0 + int(threadIdx.x) < rows) resid = __ldcg(a.res + row0 + int(threadIdx.x));
-    if (!ptx::mbar_wait(ptx::smem_u32(&bars[st]), uint32_t(q / NS) & 1u, &abort_flag, a.status, 10)) break;
-    float acc[NM][2];
+  if constexpr (!BATCH) {
+    // Streaming form (a block owns more tiles than there are stages): one tile at a time, the other stages in flight.
+    for (int q = 0; q < my_steps; ++q) {
+      int s, row0, rows;
+      locate(q, s, row0, rows);
+      const int st = q % NS, rb = q & 1;   // weight stage; buffer of the partial sums
+      // residual rows are requested before the tile's arithmetic so that their latency is not paid in the epilogue
+      float resid = 0.0f;
+      if (MODE == W4_ADD && int(threadIdx.x) < S_ROWS && row0 + int(threadIdx.x) < rows) resid = __ldcg(a.res + row0 + int(threadIdx.x));
+      if (!ptx::mbar_wait(ptx::smem_u32(&bars[st]), uint32_t(q / NS) & 1u, &abort_flag, a.status, 10)) break;
+      float acc[NM][2];
 #pragma unroll
-    for (int m = 0; m < NM; ++m) acc[m][0] = acc[m][1] = 0.0f;
-    W4Tile tl;
-    tl.base = stage_ptr(st, 0);
-    tl.mat_bytes = mat_bytes;
-    tl.mat_w = mat_w;
-    tl.mat_s = mat_s;
-    tl.row_bytes = row_bytes;
-    tl.sc_row = sc_row;
-    tl.has_z = has_z;
-    if (row0 + slab * 16 < rows) w4_mma_spans<NM, HALF>(tl, slab * 16, S_ROWS, xs, nchunks, a.log2_cpg, kpart, KP, lane, acc);
+      for (int m = 0; m < NM; ++m) acc[m][0] = acc[m][1] = 0.0f;
+      W4Tile tl;
+      tl.base = stage_ptr(st, 0);
+      tl.mat_bytes = mat_bytes;
+      tl.mat_w = mat_w;
+      tl.mat_s = mat_s;
+      tl.row_bytes = row_bytes;
+      tl.sc_row = sc_row;
+      tl.has_z = has_z;
+      if (row0 + slab * 16 < rows) w4_mma_spans<NM, HALF>(tl, slab * 16, S_ROWS, xs, nchunks, a.log2_cpg, kpart, KP, lane, acc);
 #pragma unroll
-    for (int m = 0; m < NM; ++m)
+      for (int m = 0; m < NM; ++m)
 #pragma unroll
-      for (int h = 0; h < (HALF ? 1 : 2); ++h) {
-        float v = acc[m][h];
-        v += __shfl_xor_sync(0xffffffffu, v, 1);
-        v += __shfl_xor_sync(0xffffffffu, v, 2);
-        if ((lane & 3) == 0) red[rb][m][kpart][slab * 16 + (lane >> 2) + 8 * h] = v;
+        for (int h = 0; h < (HALF ? 1 : 2); ++h) {
+          float v = acc[m][h];
+          v += __shfl_xor_sync(0xffffffffu, v, 1);
+          v += __shfl_xor_sync(0xffffffffu, v, 2);
+          if ((lane & 3) == 0) red[rb][m][kpart][slab * 16 + (lane >> 2) + 8 * h] = v;
+        }
+      __syncthreads();  // partial sums published; every warp is done with stage st before it is refilled
+      issue_round(q + NS, 1);
+      if (threadIdx.x < S_ROWS) {
+        const int row = row0 + int(threadIdx.x);
+        float v0 = 0.0f, v1 = 0.0f;
+#pragma unroll
+        for (int k = 0; k < KP; ++k) {
+          v0 += red[rb][0][k][threadIdx.x];
+          if (NM == 2) v1 += red[rb][NM - 1][k][threadIdx.x];
+        }
+        v0 *= inv_r;
+        v1 *= inv_r;
+        if (row < rows) {
+          if (MODE == W4_STORE) a.seg[s].out[row] = v0;
+          if (MODE == W4_ADD) a.seg[s].out[row] = resid + v0;
+          if (MODE == W4_GATE_UP) a.seg[0].out[row] = (v0 / (1.0f + expf(-v0))) * v1;
+        }
       }
-    __syncthreads();  // partial sums published; every warp is done with stage st before it is refilled
-    issue(q + NS);
-    if (threadIdx.x < S_ROWS) {
-      const int row = row0 + int(threadIdx.x);
+    }
+    W4_MARK(15);
+    return;
+  }
+  // Batched form (decode-sized launches: a block owns no more tiles than there are stages, all of them requested
+  // before the input vector was even available).  One tile at a time (wait, spans, block-wide sync, cross-warp sum,
+  // store, next tile) would be a chain of short dependent steps; here every warp runs its spans over ALL tiles of
+  // the block back to back, and one block-wide sync and one round of cross-warp sums serve them all.
+  const int bsz = NS;
+  for (int q0 = 0; q0 < my_steps; q0 += bsz) {
+    const int nb = min(bsz, my_steps - q0);
+    // residual rows are requested before the arithmetic so that their latency is not paid in the epilogue
+    float resid = 0.0f;
+    int e_s = 0, e_row0 = 0, e_rows = 0;
+    const int e_tile = int(threadIdx.x) / S_ROWS, e_r = int(threadIdx.x) % S_ROWS;
+    if (e_tile < nb) {
+      locate(q0 + e_tile, e_s, e_row0, e_rows);
+      if (MODE == W4_ADD && e_row0 + e_r < e_rows) resid = __ldcg(a.res + e_row0 + e_r);
+    }
+    bool ok = true;
+#pragma unroll 1
+    for (int j = 0; j < nb && ok; ++j) {
+      {
+        const int q = q0 + j;
+        int s, row0, rows;
+        locate(q, s, row0, rows);
+        const int st = q % NS;
+        if (!ptx::mbar_wait(ptx::smem_u32(&bars[st]), uint32_t(q / NS) & 1u, &abort_flag, a.status, 10)) ok = false;
+        if (ok) {
+          if (j == 0) W4_MARK(4);
+          float acc[NM][2];
+#pragma unroll
+          for (int m = 0; m < NM; ++m) acc[m][0] = acc[m][1] = 0.0f;
+          W4Tile tl;
+          tl.base = stage_ptr(st, 0);
+          tl.mat_bytes = mat_bytes;
+          tl.mat_w = mat_w;
+          tl.mat_s = mat_s;
+          tl.row_bytes = row_bytes;
+          tl.sc_row = sc_row;
+          tl.has_z = has_z;
+          // first span of this warp in tile j: the round-robin over the KP warps of a slab continues across tiles,
+          // so e.g. 25 spans per tile over 16 warps still balance over the batch
+          const int s0 = (kpart + KP - (j * nspans) % KP) % KP;
+          if (row0 + slab * 16 < rows)
+            w4_mma_spans<NM, HALF>(tl, slab * 16, S_ROWS, xs, nchunks, a.log2_cpg, s0, KP, lane, acc);
+#pragma unroll
+          for (int m = 0; m < NM; ++m)
+#pragma unroll
+            for (int h = 0; h < (HALF ? 1 : 2); ++h) {
+              float v = acc[m][h];
+              v += __shfl_xor_sync(0xffffffffu, v, 1);
+              v += __shfl_xor_sync(0xffffffffu, v, 2);
+              if ((lane & 3) == 0) red[j][m][kpart][slab * 16 + (lane >> 2) + 8 * h] = v;
+            }
+        }
+      }
+    }
+    if (!ok) break;   // abort_flag is block-wide: every thread's wait has failed
+    __syncthreads();  // partial sums published; every warp is done with the stages before they are refilled
+    W4_MARK(5);
+    // the stages of this batch are refilled (every thread makes the call: a ragged tile is copied by the whole block)
+    issue_round(q0 + NS, nb);
+    if (e_tile < nb) {
+      const int row = e_row0 + e_r;
       float v0 = 0.0f, v1 = 0.0f;
 #pragma unroll
       for (int k = 0; k < KP; ++k) {
-        v0 += red[rb][0][k][threadIdx.x];
-        if (NM == 2) v1 += red[rb][NM - 1][k][threadIdx.x];
+        v0 += red[e_tile][0][k][e_r];
+        if (NM == 2) v1 += red[e_tile][NM - 1][k][e_r];
       }
       v0 *= inv_r;
       v1 *= inv_r;
-      if (row < rows) {
-        if (MODE == W4_STORE) a.seg[s].out[row] = v0;
-        if (MODE == W4_ADD) a.seg[s].out[row] = resid + v0;
+      if (row < e_rows) {
+        if (MODE == W4_STORE) a.seg[e_s].out[row] = v0;
+        if (MODE == W4_ADD) a.seg[e_s].out[row] = resid + v0;
         if (MODE == W4_GATE_UP) a.seg[0].out[row] = (v0 / (1.0f + expf(-v0))) * v1;
       }
     }
+    if (q0 + bsz < my_steps) __syncthreads();   // `red` is rewritten by the next batch
   }
+  W4_MARK(15);
 }
 
 // Fills the tile bookkeeping, sizes the stages and launches.  All pointers are device pointers.
@@ -416,7 +558,12 @@ inline int w4_launch(W4Args a, cudaStream_t st, int sm_count, bool pdl = false) 
   int ns = 2;
   if (wide) {
     tr = 16;
-    while (ns < 4 && need(16, ns + 1) <= 200 * 1024) ++ns;
+    // as many stages as fit, up to 4 -- or up to 6 when that lets every block hold its whole share of a decode-sized
+    // launch at once (9600 rows are 600 tiles on 148 SMs: eight blocks own five)
+    const int64_t tiles16 = (total_rows + 15) / 16;
+    const int share = int((tiles16 + sm_count - 1) / sm_count);
+    const int want = share > 4 && share <= 6 ? share : 4;
+    while (ns < want && need(16, ns + 1) <= 200 * 1024) ++ns;
   }
   const size_t smem = need(tr, ns);
   if (smem > W4_SMEM_LIMIT) return set_error(SIMP_ERR_SHAPE, "w4_gemv: row too long for the shared-memory pipeline");
@@ -432,22 +579,32 @@ inline int w4_launch(W4Args a, cudaStream_t st, int sm_count, bool pdl = false) 
   const int cap = sm_count * per_sm;
   const int grid = g < cap ? g : cap;
   cudaError_t e;
-#define W4_LAUNCH_TR(TRV, NWV, NSV)                                                                         \
+  // decode-sized launches (a block owns at most two rounds of stages) take the batched form of the kernel
+  const bool batch = int64_t(g) <= int64_t(grid) * ns * 2;
+#define W4_LAUNCH_B(TRV, NWV, NSV, BV)                                                                      \
   do {                                                                                                      \
     static bool attr_set = false;                                                                           \
     if (!attr_set) {                                                                                        \
-      cudaFuncSetAttribute(w4_gemv_kernel<MODE, TRV, NWV, NSV>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024); \
+      cudaFuncSetAttribute(w4_gemv_kernel<MODE, TRV, NWV, NSV, BV>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024); \
       attr_set = true;                                                                                      \
     }                                                                                                       \
-    e = launch_kernel(w4_gemv_kernel<MODE, TRV, NWV, NSV>, dim3(grid), dim3(NWV * 32), smem, st, pdl, a);   \
+    e = launch_kernel(w4_gemv_kernel<MODE, TRV, NWV, NSV, BV>, dim3(grid), dim3(NWV * 32), smem, st, pdl, a); \
   } while (0)
-  if (wide && ns == 4) W4_LAUNCH_TR(16, 16, 4);
+#define W4_LAUNCH_TR(TRV, NWV, NSV)                                                                         \
+  do {                                                                                                      \
+    if (batch) W4_LAUNCH_B(TRV, NWV, NSV, true);                                                            \
+    else W4_LAUNCH_B(TRV, NWV, NSV, false);                                                                 \
+  } while (0)
+  if (wide && ns == 6) W4_LAUNCH_TR(16, 16, 6);
+  else if (wide && ns == 5) W4_LAUNCH_TR(16, 16, 5);
+  else if (wide && ns == 4) W4_LAUNCH_TR(16, 16, 4);
   else if (wide && ns == 3) W4_LAUNCH_TR(16, 16, 3);
   else if (wide) W4_LAUNCH_TR(16, 16, 2);
   else if (tr == 32) W4_LAUNCH_TR(32, 8, 2);
   else if (tr == 16) W4_LAUNCH_TR(16, 8, 2);
   else W4_LAUNCH_TR(8, 8, 2);
 #undef W4_LAUNCH_TR
+#undef W4_LAUNCH_B
   if (e != cudaSuccess) return set_error(SIMP_ERR_CUDA, "w4_gemv launch failed: %s", cudaGetErrorString(e));
   return SIMP_OK;
 }
