@@ -300,8 +300,12 @@ int simp_dist_matmul_i8_nsharded(const void* A_dev, const int8_t* B_local_dev, i
  * memory and TMA-stored into every rank's copy of the full row-major C[M, N_local*world] (own HBM and, over
  * NVLink, the peers'), so the all-gather overlaps the main loop tile by tile and C arrives in the layout
  * tensor_matmul defines.  C_symm_dev must come from simp_dist_symm_alloc (a collective that allocates
- * `bytes` on every rank and maps all ranks' buffers through CUDA IPC); the call ends with simp_dist_barrier,
- * which orders every rank's stores before later work on the stream. */
+ * `bytes` on every rank and maps all ranks' buffers through CUDA IPC).  N_local must be a multiple of 32 (whole
+ * 32-column boxes are stored; a narrower block would spill into the neighbour's).  The call ends with a rendezvous
+ * of all ranks on the library stream (epoch words exchanged by peer stores, bounded waits), which orders every
+ * rank's stores before later work on the stream; its first use allocates the epoch words (a collective): make the
+ * first call outside any stream capture.  Buffer re-use: a rank may overwrite C_symm (or anything a peer stores
+ * into) only after a rendezvous that follows its own last read of it. */
 int simp_dist_symm_alloc(size_t bytes, void** local_ptr);
 int simp_dist_symm_free(void* local_ptr);
 int simp_dist_barrier(void);

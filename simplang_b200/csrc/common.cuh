@@ -76,11 +76,68 @@ inline cudaError_t launch_kernel(void (*kern)(KArgs...), dim3 grid, dim3 block, 
   return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
 }
 
+// ---- tensor-parallel exchange fused into the producing / consuming kernels --------------------
+// Every rank holds the exchanged activation vectors in a symmetric arena (same layout on every rank, all ranks'
+// arenas mapped through CUDA IPC).  In such a vector every element is one 64-bit word { value (low 32 bits), tag
+// (high 32 bits) }, written with ONE 64-bit store and read with ONE 64-bit load.  A kernel that produces a slice
+// stores its words into EVERY rank's copy (over NVLink for the peers); a kernel that consumes the vector polls the
+// words of its own copy until they carry the tag of the launch that produces them.  Data and flag travel together:
+// no fence, no atomic, no exchange kernel, no collective call -- an exchange costs one NVLink store latency.
+// tag = tokens completed * per_token + id, id = 1 for the embedding, 2 + 4 * layer + k for the four exchanged vectors
+// of a layer (attention output, x after wo, hidden, x after down): strictly increasing, never 0.
+typedef unsigned long long ll_word;
+struct TpLL {
+  int n = 0, rank = 0;          // ranks (0 or 1: plain vectors, no exchange), this rank
+  uint8_t* arena[8] = {};       // arena base of every rank as seen from this process (arena[rank] = local)
+  const int* tokens = nullptr;  // tokens completed so far (device word, advanced once per token)
+  uint32_t per_token = 0;       // tags per token
+};
+
 // ---- device helpers -------------------------------------------------------------------------
 #ifdef __CUDACC__
 // Programmatic dependent launch: no-ops when the kernel was launched without the attribute.
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// First tag of the current token (add the id of a vector).  The token counter is written by the previous token's
+// last kernel, so a kernel may read it before it waits for its predecessor.
+__device__ __forceinline__ uint32_t ll_tag_base(const TpLL& t) { return t.n > 1 ? uint32_t(__ldcg(t.tokens)) * t.per_token : 0u; }
+__device__ __forceinline__ void ll_store_sys(ll_word* p, float v, uint32_t tag) {
+  const ll_word w = (ll_word(tag) << 32) | ll_word(__float_as_uint(v));
+  asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
+}
+// One value to the same word of every rank's copy (byte offset `off` inside the arena).
+__device__ __forceinline__ void ll_store_all(const TpLL& t, uint32_t off, float v, uint32_t tag) {
+#pragma unroll
+  for (int r = 0; r < 8; ++r)   // fixed trip count: the arena table stays in the parameter bank
+    if (r < t.n) ll_store_sys(reinterpret_cast<ll_word*>(t.arena[r] + off), v, tag);
+}
+__device__ __forceinline__ ll_word ll_load_sys(const ll_word* p) {
+  ll_word w;
+  asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
+  return w;
+}
+// Polls `p` until it carries `tag` (bounded: 1 s, then the library status word is set and 0 is returned).
+static __device__ __noinline__ float ll_spin(const ll_word* p, uint32_t tag, int* status, int site) {
+  unsigned long long t0;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+  for (unsigned spin = 1;; ++spin) {
+    const ll_word w = ll_load_sys(p);
+    if (uint32_t(w >> 32) == tag) return __uint_as_float(uint32_t(w));
+    if ((spin & 63u) == 0) {
+      unsigned long long t1;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+      if (t1 - t0 > 1000000000ull || *reinterpret_cast<volatile int*>(status) == 1) {
+        if (atomicCAS(status, 0, 1) == 0) status[1] = site;
+        return 0.0f;
+      }
+    }
+  }
+}
+__device__ __forceinline__ float ll_get(const ll_word* p, uint32_t tag, int* status, int site) {
+  const ll_word w = ll_load_sys(p);
+  if (uint32_t(w >> 32) == tag) return __uint_as_float(uint32_t(w));
+  return ll_spin(p, tag, status, site);
+}
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -129,15 +186,11 @@ __device__ __forceinline__ uint4 ld_stream_u4(const void* p) {
                : "l"(p));
   return v;
 }
-// 16 bytes of a matrix that is read once per pass: not kept in L1, first in line for eviction from L2 (so that a
-// stream of weights does not push kernel code, launch parameters and activations out of L2).
 __device__ __forceinline__ float4 ld_stream_f4(const void* p) {
   float4 v;
-  uint64_t pol;
-  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
-  asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.v4.f32 {%0,%1,%2,%3}, [%4], %5;"
+  asm volatile("ld.global.nc.L1::no_allocate.v4.f32 {%0,%1,%2,%3}, [%4];"
                : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
-               : "l"(p), "l"(pol));
+               : "l"(p));
   return v;
 }
 #endif

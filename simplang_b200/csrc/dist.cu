@@ -74,7 +74,8 @@ struct SymmBuf {
 static std::vector<SymmBuf> g_symm;
 
 int gemm_i8_run(const void* A, const int8_t* B, int32_t* C, int64_t M, int64_t K, int64_t N, int a_unsigned,
-                int b_transposed, int32_t* const* peer_c, int n_peers, int64_t ldc, int64_t col_offset);
+                int b_transposed, int32_t* const* peer_c, int n_peers, int64_t ldc, int64_t col_offset, int self_rank);
+int dist_rendezvous();
 
 // ---- peer-store all-gather ---------------------------------------------------------------------
 // In-place all-gather of a small vector that lives in a symmetric buffer: every rank stores its slice straight
@@ -214,9 +215,9 @@ SIMP_API int simp_dist_matmul_i8_nsharded_fused(const void* A_dev, const int8_t*
   int32_t* peers[8];
   for (int r = 0; r < g_world; ++r) peers[r] = static_cast<int32_t*>(sb->peer[r]);
   if (int rc = gemm_i8_run(A_dev, B_local_dev, nullptr, M, K, N_local, a_unsigned, b_transposed, peers, g_world, ldc,
-                           int64_t(g_rank) * N_local))
+                           int64_t(g_rank) * N_local, g_rank))
     return rc;
-  return simp_dist_barrier();
+  return dist_rendezvous();
 }
 
 SIMP_API int simp_dist_unique_id(void* id_out, size_t bytes) {
@@ -286,14 +287,9 @@ SIMP_API int simp_dist_allgather(const void* send_dev, void* recv_dev, size_t by
 // [offset, offset + world * slice) of `symm_local` hold every rank's slice; this rank's slice must already be at
 // offset + rank * slice.  Every rank calls it in the same order.  The first call allocates the flag words
 // (a collective): make it outside stream capture.
-SIMP_API int simp_dist_allgather_peer(void* symm_local, size_t offset, size_t slice) {
-  if (int rc = ensure_ready()) return rc;
-  if (g_world == 1 || slice == 0) return SIMP_OK;
-  const SymmBuf* sb = nullptr;
-  for (const auto& b : g_symm)
-    if (b.local == symm_local) sb = &b;
-  SIMP_REQUIRE(sb != nullptr, SIMP_ERR_ARG, "dist_allgather_peer: buffer must come from simp_dist_symm_alloc");
-  SIMP_REQUIRE(offset + slice * size_t(g_world) <= sb->bytes, SIMP_ERR_SHAPE, "dist_allgather_peer: range outside the buffer");
+// The epoch words of the peer exchange (a collective on first use: allocates, so the first call must come
+// outside any stream capture).
+static int ll_flags_ready(const SymmBuf** fb_out) {
   if (!g_ll_flags) {
     void* f = nullptr;
     if (int rc = simp_dist_symm_alloc(256, &f)) return rc;
@@ -303,13 +299,53 @@ SIMP_API int simp_dist_allgather_peer(void* symm_local, size_t offset, size_t sl
     g_ll_flags = static_cast<unsigned*>(f);
     if (int rc = simp_dist_barrier()) return rc;   // every rank's flags are zero before anyone publishes
     SIMP_CUDA(cudaStreamSynchronize(ctx().stream));
-    for (const auto& b : g_symm)   // g_symm may have been reallocated by the push: look the buffer up again
-      if (b.local == symm_local) sb = &b;
   }
   const SymmBuf* fb = nullptr;
   for (const auto& b : g_symm)
     if (b.local == g_ll_flags) fb = &b;
-  SIMP_REQUIRE(fb != nullptr, SIMP_ERR_STATE, "dist_allgather_peer: flag buffer missing");
+  SIMP_REQUIRE(fb != nullptr, SIMP_ERR_STATE, "peer exchange: flag buffer missing");
+  *fb_out = fb;
+  return SIMP_OK;
+}
+
+namespace simp {
+// The addresses of all ranks' copies of a symmetric buffer (peers[rank] = local); false if `local` is unknown.
+bool dist_symm_peers(const void* local, uint8_t** peers8) {
+  for (const auto& b : g_symm)
+    if (b.local == local) {
+      for (int r = 0; r < 8; ++r) peers8[r] = static_cast<uint8_t*>(b.peer[r]);
+      return true;
+    }
+  return false;
+}
+// Rendezvous on the library stream without NCCL: the one-block exchange kernel with empty slices publishes this
+// rank's next epoch to every peer and waits (bounded) for theirs.  Work queued before it on this stream has
+// completed, with its stores to peer memory performed, before the epoch is published.
+int dist_rendezvous() {
+  if (g_world == 1) return SIMP_OK;
+  const SymmBuf* fb = nullptr;
+  if (int rc = ll_flags_ready(&fb)) return rc;
+  LlPeers peers{};
+  for (int r = 0; r < g_world; ++r) {
+    peers.buf[r] = static_cast<uint8_t*>(fb->peer[r]);   // not touched: the slices are empty
+    peers.flags[r] = static_cast<unsigned*>(fb->peer[r]);
+  }
+  ll_allgather_kernel<<<1, 256, 0, ctx().stream>>>(peers, g_ll_seq, g_rank, g_world, 0, 0, ctx().dev_status);
+  SIMP_LAUNCH_CHECK();
+  return SIMP_OK;
+}
+}  // namespace simp
+
+SIMP_API int simp_dist_allgather_peer(void* symm_local, size_t offset, size_t slice) {
+  if (int rc = ensure_ready()) return rc;
+  if (g_world == 1 || slice == 0) return SIMP_OK;
+  const SymmBuf* fb = nullptr;
+  if (int rc = ll_flags_ready(&fb)) return rc;
+  const SymmBuf* sb = nullptr;
+  for (const auto& b : g_symm)
+    if (b.local == symm_local) sb = &b;
+  SIMP_REQUIRE(sb != nullptr, SIMP_ERR_ARG, "dist_allgather_peer: buffer must come from simp_dist_symm_alloc");
+  SIMP_REQUIRE(offset + slice * size_t(g_world) <= sb->bytes, SIMP_ERR_SHAPE, "dist_allgather_peer: range outside the buffer");
   LlPeers peers{};
   for (int r = 0; r < g_world; ++r) {
     peers.buf[r] = static_cast<uint8_t*>(sb->peer[r]);

@@ -12,7 +12,7 @@
 namespace simp {
 
 int gemm_i8_run(const void* A, const int8_t* B, int32_t* C, int64_t M, int64_t K, int64_t N, int a_unsigned,
-                int b_transposed, int32_t* const* peer_c, int n_peers, int64_t ldc, int64_t col_offset);
+                int b_transposed, int32_t* const* peer_c, int n_peers, int64_t ldc, int64_t col_offset, int self_rank = 0);
 
 // src: [rows, ceil(cols / 2)] bytes, low nibble = even column.  dst: [rows_p, cols_p] s8, zero outside [rows, cols).
 __global__ void unpack_i4_kernel(const uint8_t* __restrict__ src, int8_t* __restrict__ dst, int64_t rows, int64_t cols,

@@ -40,9 +40,12 @@ constexpr int TMEM_COLS = 512;
 constexpr int EPI_BYTES = 4 * 2 * 4096;      // per epilogue warp: two 32x32 i32 staging tiles for TMA stores
 constexpr size_t GEMM_SMEM = size_t(STAGES) * STAGE_BYTES + EPI_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 
-// Tensor maps of the C buffers a tile is stored to when the all-gather is fused into the epilogue.
+// The C buffers a tile is stored to when the all-gather is fused into the epilogue: m[self] is the tensor map of
+// this rank's own copy (TMA store), c[r] the row-major [M, ldc] copies of the peers (plain stores over NVLink).
 struct PeerMaps {
   CUtensorMap m[8];
+  int32_t* c[8];
+  int self, ldc;
 };
 
 struct GemmParams {
@@ -168,15 +171,40 @@ __device__ __forceinline__ void epilogue_rows(const CUtensorMap* tmap_c, const P
         __syncwarp();
         if (lane == 0) {
           if (p.n_peers > 0) {
-            // fused all-gather: the same staged tile goes to every rank's copy of C (own memory and, over
-            // NVLink, the peers'); plain TMA stores, no multicast
-            for (int r = 0; r < p.n_peers; ++r) tma_store_2d(&peers->m[r], buf, c0 + p.col_offset, row0);
+            // fused all-gather, own copy: TMA store of the staged tile
+            tma_store_2d(&peers->m[peers->self], buf, c0 + p.col_offset, row0);
           } else if (partial) {
             tma_reduce_add_2d(tmap_c, buf, c0, row0);
           } else {
             tma_store_2d(tmap_c, buf, c0, row0);
           }
           tma_store_commit();
+        }
+        if (p.n_peers > 1) {
+          // fused all-gather, peers' copies: the warp reads the staged tile back (eight lanes per 128-byte row, four
+          // rows per instruction) and stores whole 128-byte lines into every peer's C over NVLink.  Plain stores on
+          // the load/store path: when the link pushes back only this epilogue warp waits -- TMA stores to peers sat
+          // in the same queue as the operand loads of the main loop and stalled it (0.282 ms per step on 2 GPUs
+          // where math and link each need 0.19).  Peers are visited from rank + 1 on, so that at any moment the
+          // ranks target different destinations.
+          const int prow = lane >> 3, pj = lane & 7;
+          int4 v[8];
+#pragma unroll
+          for (int it = 0; it < 8; ++it) {
+            const int r = it * 4 + prow;
+            const uint32_t addr = buf + uint32_t(r) * 128u + (uint32_t(pj ^ (r & 7)) << 4);
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v[it].x), "=r"(v[it].y), "=r"(v[it].z), "=r"(v[it].w) : "r"(addr));
+          }
+          for (int k = 1; k < p.n_peers; ++k) {
+            int dst = peers->self + k;
+            if (dst >= p.n_peers) dst -= p.n_peers;
+            int32_t* cp = peers->c[dst] + int64_t(row0) * peers->ldc + c0 + p.col_offset + pj * 4;
+#pragma unroll
+            for (int it = 0; it < 8; ++it) {
+              const int r = it * 4 + prow;
+              if (row0 + r < p.M) *reinterpret_cast<int4*>(cp + int64_t(r) * peers->ldc) = v[it];
+            }
+          }
         }
       }
     } else if (row < p.M && c0 < p.N) {
@@ -605,10 +633,10 @@ static int make_map_u8(CUtensorMap* map, const void* base, int64_t inner, int64_
 
 namespace simp {
 // Shared by simp_gpu_matmul_i8 (n_peers == 0: C is [M,N] in this GPU's memory) and the fused N-sharded GEMM
-// (n_peers > 0: peer_c[r] are the row-major [M, ldc] copies of the full result on every rank, this rank's
-// column block starts at col_offset).
+// (n_peers > 0: peer_c[r] are the row-major [M, ldc] copies of the full result on every rank, peer_c[self_rank]
+// this rank's own; this rank's column block starts at col_offset).
 int gemm_i8_run(const void* A, const int8_t* B, int32_t* C, int64_t M, int64_t K, int64_t N, int a_unsigned,
-                int b_transposed, int32_t* const* peer_c, int n_peers, int64_t ldc, int64_t col_offset) {
+                int b_transposed, int32_t* const* peer_c, int n_peers, int64_t ldc, int64_t col_offset, int self_rank) {
   if (int rc = ensure_ready()) return rc;
   SIMP_REQUIRE(M >= 0 && K >= 0 && N >= 0, SIMP_ERR_ARG, "matmul_i8: negative size");
   if (M == 0 || N == 0) return SIMP_OK;
@@ -634,9 +662,7 @@ int gemm_i8_run(const void* A, const int8_t* B, int32_t* C, int64_t M, int64_t K
   // The tensor-core kernel pays a fixed pipeline fill per tile; tiny problems stay on dp4a.
   const bool tiny = n_peers == 0 && M * N * K < int64_t(64) * 64 * 64;
   if (tma_ok && !tiny) {
-    // Kernel choice: the 2-CTA kernel for problems with at least one full wave of 256x256 tiles on the
-    // 74 CTA pairs; the 1-CTA kernel otherwise.  SIMP_GEMM_I8_KERNEL=1cta|2cta overrides (testing).
-    // Kernel choice: the 2-CTA kernel when 256x256 tiles fill its waves well (at least one wave on the 74 CTA
+    // Kernel choice (SIMP_GEMM_I8_KERNEL=1cta|2cta overrides it, for the tests): the 2-CTA kernel when 256x256 tiles fill its waves well (at least one wave on the 74 CTA
     // pairs and a last wave that is not nearly empty: 76 tiles would take two waves for 1.03 waves of work);
     // otherwise the 1-CTA kernel, whose hybrid stream-K mode spreads a partial last wave over all SMs.
     const int64_t tiles2 = cdiv(M, 256) * cdiv(N, 256);
@@ -661,8 +687,6 @@ int gemm_i8_run(const void* A, const int8_t* B, int32_t* C, int64_t M, int64_t K
     p.C = C;
     p.status = ctx().dev_status;
     p.tma_store = (N % 4 == 0) ? 1 : 0;
-    if (const char* env = getenv("SIMP_GEMM_I8_EPILOGUE"))
-      if (!strcmp(env, "direct")) p.tma_store = 0;
     CUtensorMap mc = ma;  // placeholder when unused
     PeerMaps peers;
     for (auto& pm : peers.m) pm = ma;
@@ -672,13 +696,19 @@ int gemm_i8_run(const void* A, const int8_t* B, int32_t* C, int64_t M, int64_t K
     p.mma_only = 0;
     if (const char* env = getenv("SIMP_GEMM_I8_ABLATE"))
       if (!strcmp(env, "mma") && n_peers == 0) p.mma_only = 1;
+    for (auto& pc : peers.c) pc = nullptr;
+    peers.self = 0;
+    peers.ldc = int(ldc);
     if (n_peers > 0) {
       p.tma_store = 1;
+      SIMP_REQUIRE(self_rank >= 0 && self_rank < n_peers, SIMP_ERR_ARG, "matmul_i8: bad rank %d of %d", self_rank, n_peers);
+      peers.self = self_rank;
       for (int r = 0; r < n_peers; ++r) {
         SIMP_REQUIRE(peer_c[r] != nullptr && (reinterpret_cast<uintptr_t>(peer_c[r]) & 15u) == 0, SIMP_ERR_ARG,
                      "matmul_i8: peer C pointer %d is null or misaligned", r);
-        if (int rc = make_map_c_i32(&peers.m[r], peer_c[r], ldc, M)) return rc;
+        peers.c[r] = peer_c[r];
       }
+      if (int rc = make_map_c_i32(&peers.m[self_rank], peer_c[self_rank], ldc, M)) return rc;
     } else if (p.tma_store) {
       if (int rc = make_map_c_i32(&mc, C, N, M)) return rc;
     }
@@ -725,10 +755,6 @@ int gemm_i8_run(const void* A, const int8_t* B, int32_t* C, int64_t M, int64_t K
       const int64_t tm1 = cdiv(M, BM);
       if (n_peers == 0 && M > 256 && tm1 * cdiv(N, BN) * cdiv(K, BK) < int64_t(ctx().sm_count) * 4)
         while (bn > 64 && tm1 * cdiv(N, bn) * 2 <= ctx().sm_count) bn >>= 1;
-      if (const char* env = getenv("SIMP_GEMM_I8_BN")) {
-        const int v = atoi(env);
-        if (v >= 32 && v <= 256 && v % 32 == 0) bn = v;
-      }
     }
     if (b_transposed) {  // the K-major B box height follows the tile width
       if (int rc = make_map_u8(&mb, B, K, N, BK, bn)) return rc;
@@ -789,5 +815,5 @@ int gemm_i8_run(const void* A, const int8_t* B, int32_t* C, int64_t M, int64_t K
 
 SIMP_API int simp_gpu_matmul_i8(const void* A, const int8_t* B, int32_t* C, int64_t M, int64_t K, int64_t N,
                                 int a_unsigned, int b_transposed) {
-  return simp::gemm_i8_run(A, B, C, M, K, N, a_unsigned, b_transposed, nullptr, 0, N, 0);
+  return simp::gemm_i8_run(A, B, C, M, K, N, a_unsigned, b_transposed, nullptr, 0, N, 0, 0);
 }

@@ -29,22 +29,40 @@ namespace simp {
 
 // ---------------------------------------------------------------------------------------------
 // x = embedding row of the current token.
+// (Tensor parallel: x is a vector of tagged words, see TpLL; every rank fills its own copy, tag id 1.)
 __global__ void __launch_bounds__(256) embed_kernel(float* __restrict__ x, const float* __restrict__ table,
-                                                    const int* __restrict__ ctl, int dim) {
+                                                    const int* __restrict__ ctl, int dim, const TpLL tp) {
   pdl_launch_dependents();
   pdl_wait();
   const int64_t token = ctl[0];
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i < dim) x[i] = table[token * dim + i];
+  if (i >= dim) return;
+  if (tp.n > 1) ll_store_sys(reinterpret_cast<ll_word*>(x) + i, table[token * dim + i], ll_tag_base(tp) + 1u);
+  else x[i] = table[token * dim + i];
 }
 
 // rmsnorm of one row before the classifier: y = (x / sqrt(ss/n + eps)) * w (the arithmetic of rmsnorm_any_kernel).
 __global__ void __launch_bounds__(1024) dec_rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w,
-                                                           float* __restrict__ y, int n, float eps) {
+                                                           float* __restrict__ y, int n, float eps, const TpLL tp, uint32_t id_x,
+                                                           int* status) {
   __shared__ float red[33];
+  extern __shared__ float xs_ll[];   // tensor parallel: x as it arrives (n floats)
   pdl_launch_dependents();
+  const uint32_t tbase = ll_tag_base(tp);
   pdl_wait();
   float ss = 0.0f;
+  if (tp.n > 1) {   // x is a vector of tagged words that the peers fill
+    const uint32_t tag = tbase + id_x;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      const float v = ll_get(reinterpret_cast<const ll_word*>(x) + i, tag, status, 81);
+      xs_ll[i] = v;
+      ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    const float r = sqrtf(ss / float(n) + eps);
+    for (int i = threadIdx.x; i < n; i += blockDim.x) y[i] = (xs_ll[i] / r) * w[i];
+    return;
+  }
   for (int i = threadIdx.x; i < n; i += blockDim.x) ss += x[i] * x[i];
   ss = block_sum(ss, red);
   const float r = sqrtf(ss / float(n) + eps);
@@ -89,7 +107,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
                       const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
                       float* __restrict__ kc, float* __restrict__ vc, float* __restrict__ part, int* __restrict__ counters,
                       float* __restrict__ out, const int* __restrict__ ctl, int hs, int kv_dim, int kv_mul, int seq_len,
-                      int layer, int nsplit, int cap, int* status
+                      int layer, int nsplit, int cap, int* status, const TpLL tp, uint32_t id_out, uint32_t out_off
 #ifdef SIMP_W4_TRACE
                       , unsigned long long* trace
 #define ATT_MARK(k) do { if (trace && threadIdx.x == 0 && blockIdx.y == 0) trace[size_t(blockIdx.x) * 16 + (k)] = ptx::globaltimer_ns(); } while (0)
@@ -111,6 +129,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   pdl_launch_dependents();
   const int pos = ctl[1];   // written by the previous token's last kernel, long complete
+  const uint32_t tag_out = ll_tag_base(tp) + id_out;
   const int len = pos + 1;
   const int kvh = h / kv_mul;
   float* kbase = kc + int64_t(layer) * seq_len * kv_dim + kvh * hs;
@@ -286,7 +305,9 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
     const int i = threadIdx.x;
     const float a = (sm_acc[0][i] + sm_acc[1][i]) + (sm_acc[2][i] + sm_acc[3][i]);
     if (eff == 1) {   // the whole sequence was this block's: normalised output, done
-      out[h * hs + i] = a / Srun;
+      const float val = a / Srun;
+      if (tp.n > 1) ll_store_all(tp, out_off + uint32_t(h * hs + i) * 8u, val, tag_out);   // every rank's copy
+      else out[h * hs + i] = val;
     } else {
       if (i == 0) {
         mine[0] = Mrun;
@@ -330,7 +351,9 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
 #pragma unroll
     for (int x2 = 0; x2 < MAXS; ++x2)
       if (mm[x2] != -INFINITY) a += val[x2] * ex[x2];
-    out[h * hs + i] = a / S;
+    const float res = a / S;
+    if (tp.n > 1) ll_store_all(tp, out_off + uint32_t(h * hs + i) * 8u, res, tag_out);
+    else out[h * hs + i] = res;
   }
   if (threadIdx.x == 0) counters[h] = 0;
 }
@@ -399,6 +422,7 @@ __global__ void __launch_bounds__(1024) argmax_advance_kernel(const float* __res
     ctl[1] = pos;
     ctl[3] = step + 1;
     ctl[8] = 0;
+    ctl[10] = ctl[10] + 1;   // tokens completed since the model was created (never reset: arrival counts build on it)
   }
 }
 
@@ -443,26 +467,26 @@ static int dev_alloc(void** p, size_t bytes) {
 // Enqueues one token.  Every launch after the first uses programmatic dependent launch: each kernel
 // requests its first weights, then waits for its predecessor before touching activations.
 static int enqueue_token_tp(LlamaModel& m, cudaStream_t st);
+bool dist_symm_peers(const void* local, uint8_t** peers8);   // dist.cu
 
 // Decode form on one GPU.  f32 model: the single cooperative kernel per token whenever the model fits its
-// shared-memory plan, unless SIMP_DECODE_MODE=graph asks for the per-op kernels.  W4 model: the per-op
-// kernels (faster today), unless SIMP_DECODE_MODE=persistent asks for the cooperative kernel.
-// Tensor-parallel models always use per-op kernels.
+// shared-memory plan, unless SIMP_DECODE_MODE=graph asks for the per-op kernels.  W4 model and tensor-parallel
+// models: the per-op kernels (a cooperative W4 kernel was built and measured at 1333 us per 3B token against
+// 1049 for the per-op graph of that time; it was removed).
 static bool use_persistent(const LlamaModel& m) {
   const char* e = getenv("SIMP_DECODE_MODE");
   if (e && !strcmp(e, "graph")) return false;
-  if (m.cfg.w4) return e && !strcmp(e, "persistent") && persistent_w4_supported(m);
-  return persistent_f32_supported(m);
+  return !m.cfg.w4 && persistent_f32_supported(m);
 }
 
 static int enqueue_token(LlamaModel& m, cudaStream_t st) {
   const simp_llama_config& c = m.cfg;
-  if (use_persistent(m)) return c.w4 ? enqueue_token_persistent_w4(m, st) : enqueue_token_persistent_f32(m, st);
+  if (use_persistent(m)) return enqueue_token_persistent_f32(m, st);
   if (c.w4) return enqueue_token_tp(m, st);  // the per-op W4 path is shared by 1 and R ranks
   const int dim = int(c.dim), hd = int(c.hidden_dim), kv = int(m.kv_dim), hs = int(m.head_size);
   const int sms = ctx().sm_count;
   const bool pdl = true;
-  LAUNCH_OR_FAIL(embed_kernel, dim3((dim + 255) / 256), dim3(256), 0, st, false, m.x, m.tok_emb, m.ctl, dim);
+  LAUNCH_OR_FAIL(embed_kernel, dim3((dim + 255) / 256), dim3(256), 0, st, false, m.x, m.tok_emb, m.ctl, dim, TpLL{});
   for (int64_t l = 0; l < c.n_layers; ++l) {
     {
       GemvDecArgs g{};
@@ -474,7 +498,7 @@ static int enqueue_token(LlamaModel& m, cudaStream_t st) {
     }
     LAUNCH_OR_FAIL(attn_fused_kernel, dim3(unsigned(c.n_heads), unsigned(m.nsplit)), dim3(ATT_WARPS * 32), att_smem_bytes(hs), st, pdl,
                    m.kmap, m.vmap, int(m.kv_tma), (const float*)m.q, (const float*)m.k, (const float*)m.v, m.kc, m.vc, m.attn_part, m.attn_cnt, m.xb,
-                   (const int*)m.ctl, hs, kv, int(c.n_heads / c.n_kv_heads), int(c.seq_len), int(l), m.nsplit, att_cap(hs), ctx().dev_status
+                   (const int*)m.ctl, hs, kv, int(c.n_heads / c.n_kv_heads), int(c.seq_len), int(l), m.nsplit, att_cap(hs), ctx().dev_status, TpLL{}, 0u, 0u
 #ifdef SIMP_W4_TRACE
                    , (unsigned long long*)nullptr
 #endif
@@ -496,7 +520,7 @@ static int enqueue_token(LlamaModel& m, cudaStream_t st) {
     }
   }
   LAUNCH_OR_FAIL(dec_rmsnorm_kernel, dim3(1), dim3(1024), 0, st, pdl, (const float*)m.x, (const float*)m.rms_final, m.xb,
-                 dim, 1e-5f);
+                 dim, 1e-5f, TpLL{}, 0u, ctx().dev_status);
   {
     GemvArgs g{};
     g.seg[0] = GemvSeg{m.wcls, m.logits, int(c.vocab_size)};
@@ -532,20 +556,34 @@ static int enqueue_token_tp(LlamaModel& m, cudaStream_t st) {
   const int dim_l = dim / R, kv_l = kv / R, hd_l = hd / R, V_l = int(c.vocab_size) / R, heads_l = int(c.n_heads) / R;
   const int sms = ctx().sm_count;
   const int log2_cpg = __builtin_ctzll(uint64_t(c.group_size / 32));
-  const bool chain = R == 1;  // no exchange kernels in between: every launch can be a programmatic dependent
-  // projections that follow an exchange: programmatic dependents of the peer-store kernel, plain launches after NCCL
-  const bool chain_x = chain || (m.tp_arena && !m.tp_nccl);
-  LAUNCH_OR_FAIL(embed_kernel, dim3((dim + 255) / 256), dim3(256), 0, st, false, m.x, m.tok_emb, m.ctl, dim);
+  // Tensor parallel: x, xb and hb are vectors of tagged words inside the symmetric arena; every producing kernel
+  // stores its slice into every rank's copy and every consuming kernel polls its own copy (see TpLL).  No exchange
+  // kernels in between, so every launch can be a programmatic dependent, as on one GPU.
+  const bool chain = true;
+  TpLL tp;
+  if (R > 1) {
+    tp.n = R; tp.rank = rk;
+    for (int r = 0; r < R; ++r) tp.arena[r] = m.tp_peer[r];
+    tp.tokens = m.ctl + 10;
+    tp.per_token = uint32_t(4 * c.n_layers + 2);
+  }
+  auto arena_off = [&](const float* p) { return uint32_t(reinterpret_cast<const uint8_t*>(p) - static_cast<const uint8_t*>(m.tp_arena)); };
+  // tag ids of a token: 1 = embedding; per layer: attention output, x after wo, hidden, x after down
+  auto id_xb = [](int64_t l) { return uint32_t(2 + 4 * l); };
+  auto id_xwo = [](int64_t l) { return uint32_t(3 + 4 * l); };
+  auto id_hb = [](int64_t l) { return uint32_t(4 + 4 * l); };
+  auto id_xdn = [](int64_t l) { return l < 0 ? 1u : uint32_t(5 + 4 * l); };
+  // a slice of a vector that holds 4-byte floats on one GPU and 8-byte tagged words under tensor parallelism
+  auto slice = [&](float* vec, int64_t first) { return R > 1 ? vec + 2 * first : vec + first; };
+  LAUNCH_OR_FAIL(embed_kernel, dim3((dim + 255) / 256), dim3(256), 0, st, false, m.x, m.tok_emb, m.ctl, dim, tp);
   auto w4seg = [&](int fam, int64_t layer, int64_t rows_l, int64_t cols, float* out) {
     const int64_t o = m.loff[fam] + layer * rows_l * cols;
     return W4Seg{m.qweights + o / 2, m.scales + o / c.group_size, m.zeros ? m.zeros + o / c.group_size : nullptr, out,
                  int(rows_l)};
   };
   // weights and scales of (family, layer) as L2 prefetch regions i, i+1 of a launch's arguments
-  static const bool x_nx = !getenv("SIMP_X_NX") || atoi(getenv("SIMP_X_NX")) != 0;
-  static const bool x_kv = !getenv("SIMP_X_KVPF") || atoi(getenv("SIMP_X_KVPF")) != 0;
   auto next_weights = [&](W4Args& a, int i, int fam, int64_t layer, int64_t rows_l, int64_t cols) {
-    if (layer >= c.n_layers || m.zeros || !x_nx) return;
+    if (layer >= c.n_layers || m.zeros) return;
     const int64_t o = m.loff[fam] + layer * rows_l * cols;
     a.nx_base[i] = m.qweights + o / 2;
     a.nx_bytes[i] = uint32_t(rows_l * cols / 2);
@@ -558,16 +596,15 @@ static int enqueue_token_tp(LlamaModel& m, cudaStream_t st) {
     a.cols = cols; a.log2_cpg = log2_cpg; a.groups_per_row = int(cols / c.group_size);
     a.x = x; a.mul = norm_w; a.norm = norm_w != nullptr;
     a.eps = 1e-5f; a.ss_div = float(dim);
+    a.tp = tp;
     return a;
   };
   // exchange of this rank's slice [rk * n, (rk + 1) * n) of an activation vector: peer stores inside the model's
   // symmetric arena (default) or an in-place NCCL all-gather (SIMP_TP_ALLGATHER=nccl, or no arena)
-  auto gather = [&](float* vec, int64_t n_per_rank) -> int {
+  // the logits (plain floats, once per token) are gathered by the one-block peer-store exchange kernel
+  auto gather_logits = [&]() -> int {
     if (R == 1) return SIMP_OK;
-    if (m.tp_arena && !m.tp_nccl)
-      return simp_dist_allgather_peer(m.tp_arena, size_t(reinterpret_cast<uint8_t*>(vec) - reinterpret_cast<uint8_t*>(m.tp_arena)),
-                                      size_t(n_per_rank) * 4);
-    return simp_dist_allgather(vec + rk * n_per_rank, vec, size_t(n_per_rank) * 4);
+    return simp_dist_allgather_peer(m.tp_arena, arena_off(m.logits), size_t(V_l) * 4);
   };
 #define TP_CUDA(e) do { cudaError_t e__ = (e); if (e__ != cudaSuccess) return set_error(SIMP_ERR_CUDA, "tp decode launch failed: %s", cudaGetErrorString(e__)); } while (0)
   for (int64_t l = 0; l < c.n_layers; ++l) {
@@ -579,64 +616,69 @@ static int enqueue_token_tp(LlamaModel& m, cudaStream_t st) {
       a.nseg = 3;
       // the attention kernel that follows reads this layer's cached keys / values of all earlier positions; they were
       // evicted from L2 by a token's worth of weights, so this launch requests them into L2 while it streams
-      a.pf_len = x_kv ? m.ctl + 1 : nullptr;
+      a.pf_len = m.ctl + 1;
       a.pf_base[0] = reinterpret_cast<const uint8_t*>(m.kc + size_t(l) * c.seq_len * kv_l);
       a.pf_base[1] = reinterpret_cast<const uint8_t*>(m.vc + size_t(l) * c.seq_len * kv_l);
       a.pf_row_bytes = kv_l * 4;
+      a.id_x = id_xdn(l - 1);
       next_weights(a, 0, 3, l, dim_l, dim);   // wo
       W4_TRACE_SET(a, 0);
-      if (int rc = w4_launch<W4_STORE>(a, st, sms, chain_x)) return rc;
+      if (int rc = w4_launch<W4_STORE>(a, st, sms, chain)) return rc;
     }
     LAUNCH_OR_FAIL(attn_fused_kernel, dim3(unsigned(heads_l), unsigned(m.nsplit)), dim3(ATT_WARPS * 32), att_smem_bytes(hs), st, true,
                    m.kmap, m.vmap, int(m.kv_tma), (const float*)m.q, (const float*)m.k, (const float*)m.v, m.kc, m.vc, m.attn_part, m.attn_cnt,
                    m.xb + rk * dim_l, (const int*)m.ctl, hs, kv_l, int(c.n_heads / c.n_kv_heads), int(c.seq_len), int(l),
-                   m.nsplit, att_cap(hs), ctx().dev_status
+                   m.nsplit, att_cap(hs), ctx().dev_status, tp, id_xb(l), R > 1 ? arena_off(slice(m.xb, rk * dim_l)) : 0u
 #ifdef SIMP_W4_TRACE
                    , (unsigned long long*)(l == 1 ? g_w4_trace + size_t(4) * 148 * 16 : nullptr)
 #endif
                    );
-    if (int rc = gather(m.xb, dim_l)) return rc;
     {
       W4Args a = w4args(dim, m.xb, nullptr);
-      a.seg[0] = w4seg(3, l, dim_l, dim, m.x + rk * dim_l);
-      a.nseg = 1; a.res = m.x + rk * dim_l;
+      a.seg[0] = w4seg(3, l, dim_l, dim, slice(m.x, rk * dim_l));
+      a.nseg = 1; a.res = slice(m.x, rk * dim_l);
+      a.id_x = id_xb(l); a.id_res = id_xdn(l - 1); a.id_out = id_xwo(l);
+      a.out_off = R > 1 ? arena_off(slice(m.x, rk * dim_l)) : 0u;
       next_weights(a, 0, 4, l, hd_l, dim);    // gate
       next_weights(a, 2, 6, l, hd_l, dim);    // up
       W4_TRACE_SET(a, 1);
-      if (int rc = w4_launch<W4_ADD>(a, st, sms, chain_x)) return rc;
+      if (int rc = w4_launch<W4_ADD>(a, st, sms, chain)) return rc;
     }
-    if (int rc = gather(m.x, dim_l)) return rc;
     {
       W4Args g = w4args(dim, m.x, m.rms_ffn + l * dim);
-      g.seg[0] = w4seg(4, l, hd_l, dim, m.hb + rk * hd_l);
+      g.seg[0] = w4seg(4, l, hd_l, dim, slice(m.hb, rk * hd_l));
       g.seg[1] = w4seg(6, l, hd_l, dim, nullptr);
       g.nseg = 2;
+      g.id_x = id_xwo(l); g.id_out = id_hb(l);
+      g.out_off = R > 1 ? arena_off(slice(m.hb, rk * hd_l)) : 0u;
       next_weights(g, 0, 5, l, dim_l, hd);    // down
       W4_TRACE_SET(g, 2);
-      if (int rc = w4_launch<W4_GATE_UP>(g, st, sms, chain_x)) return rc;
+      if (int rc = w4_launch<W4_GATE_UP>(g, st, sms, chain)) return rc;
     }
-    if (int rc = gather(m.hb, hd_l)) return rc;
     {
       W4Args d = w4args(hd, m.hb, nullptr);
-      d.seg[0] = w4seg(5, l, dim_l, hd, m.x + rk * dim_l);
-      d.nseg = 1; d.res = m.x + rk * dim_l;
+      d.seg[0] = w4seg(5, l, dim_l, hd, slice(m.x, rk * dim_l));
+      d.nseg = 1; d.res = slice(m.x, rk * dim_l);
+      d.id_x = id_hb(l); d.id_res = id_xwo(l); d.id_out = id_xdn(l);
+      d.out_off = R > 1 ? arena_off(slice(m.x, rk * dim_l)) : 0u;
       next_weights(d, 0, 0, l + 1, dim_l, dim);   // the next layer's q | k | v
       next_weights(d, 2, 1, l + 1, kv_l, dim);
       next_weights(d, 4, 2, l + 1, kv_l, dim);
       W4_TRACE_SET(d, 3);
-      if (int rc = w4_launch<W4_ADD>(d, st, sms, chain_x)) return rc;
+      if (int rc = w4_launch<W4_ADD>(d, st, sms, chain)) return rc;
     }
-    if (int rc = gather(m.x, dim_l)) return rc;
   }
-  LAUNCH_OR_FAIL(dec_rmsnorm_kernel, dim3(1), dim3(1024), 0, st, chain, (const float*)m.x, (const float*)m.rms_final,
-                 m.xb, dim, 1e-5f);
+  // final rmsnorm into a plain vector (under tensor parallelism its own buffer: xb holds tagged words there)
+  float* xn = R > 1 ? m.tp_xn : m.xb;
+  LAUNCH_OR_FAIL(dec_rmsnorm_kernel, dim3(1), dim3(1024), R > 1 ? size_t(dim) * 4 : 0, st, chain, (const float*)m.x,
+                 (const float*)m.rms_final, xn, dim, 1e-5f, tp, id_xdn(c.n_layers - 1), ctx().dev_status);
   {
     GemvArgs g{};
     g.seg[0] = GemvSeg{m.wcls, m.logits + int64_t(rk) * V_l, V_l};
-    g.nseg = 1; g.k4 = dim / 4; g.x = m.xb;
+    g.nseg = 1; g.k4 = dim / 4; g.x = xn;
     if (int rc = gemv_f32_launch<GEMV_STORE>(g, st, sms)) return rc;
   }
-  if (int rc = gather(m.logits, V_l)) return rc;
+  if (int rc = gather_logits()) return rc;
   LAUNCH_OR_FAIL(argmax_advance_kernel, dim3(ARGMAX_BLOCKS), dim3(1024), 0, st, false, (const float*)m.logits,
                  int(c.vocab_size), m.ctl, (const int32_t*)m.prompt, m.out_tokens, m.pk_best_val, m.pk_best_idx);
 #undef TP_CUDA
@@ -657,6 +699,8 @@ static int ensure_graph(LlamaModel& m) {
   // rewrites the same cache row the replay will write, so it is harmless
   int ctl_save[5];
   SIMP_CUDA(cudaMemcpyAsync(ctl_save, m.ctl, sizeof(ctl_save), cudaMemcpyDeviceToHost, st));
+  if (m.tp > 1)
+    if (int rc = simp_dist_barrier()) return rc;   // the eager pass exchanges with the peers: start it together
   SIMP_CUDA(cudaStreamSynchronize(st));
   if (int rc = (m.tp > 1 ? enqueue_token_tp(m, st) : enqueue_token(m, st))) return rc;
   SIMP_CUDA(cudaStreamSynchronize(st));
@@ -735,23 +779,29 @@ SIMP_API int simp_llama_create(const simp_llama_config* cfg, void** model) {
   auto A = [&](void** p, size_t n) { if (rc == SIMP_OK) rc = dev_alloc(p, n); };
   const size_t mx = size_t(c.dim > c.hidden_dim ? c.dim : c.hidden_dim);
   if (tp > 1) {
-    // the exchanged vectors (x, xb, hb, logits) live in one symmetric arena so that ranks can store their slices
-    // straight into each other's copies
+    // the exchanged vectors live in one symmetric arena so that ranks can store their slices straight into each
+    // other's copies: x, xb and hb as tagged 64-bit words (see TpLL; zero = no tag yet), the logits as plain floats
     auto al = [](size_t v) { return (v + 255) & ~size_t(255); };
-    const size_t o_xb = al(size_t(c.dim) * 4), o_hb = o_xb + al(mx * 4), o_lg = o_hb + al(size_t(c.hidden_dim) * 4);
+    const size_t o_xb = al(size_t(c.dim) * 8), o_hb = o_xb + al(size_t(c.dim) * 8), o_lg = o_hb + al(size_t(c.hidden_dim) * 8);
     const size_t total = o_lg + al(size_t(c.vocab_size) * 4);
-    const char* e = getenv("SIMP_TP_ALLGATHER");
-    m->tp_nccl = e && !strcmp(e, "nccl");
     if (rc == SIMP_OK) rc = simp_dist_symm_alloc(total, &m->tp_arena);
+    if (rc == SIMP_OK && !dist_symm_peers(m->tp_arena, m->tp_peer)) rc = set_error(SIMP_ERR_STATE, "llama_create: arena peers missing");
+    if (rc == SIMP_OK) {
+      // nobody may store into a peer's copy before every rank's words are zero
+      if (cudaMemsetAsync(m->tp_arena, 0, total, ctx().stream) != cudaSuccess) rc = SIMP_ERR_CUDA;
+      if (rc == SIMP_OK) rc = simp_dist_barrier();
+      if (rc == SIMP_OK && cudaStreamSynchronize(ctx().stream) != cudaSuccess) rc = SIMP_ERR_CUDA;
+    }
     if (rc == SIMP_OK) {
       uint8_t* base = static_cast<uint8_t*>(m->tp_arena);
       m->x = reinterpret_cast<float*>(base);
       m->xb = reinterpret_cast<float*>(base + o_xb);
       m->hb = reinterpret_cast<float*>(base + o_hb);
       m->logits = reinterpret_cast<float*>(base + o_lg);
-      // first use of the peer exchange allocates its flag words (a collective): do it here, outside any capture
-      if (!m->tp_nccl) rc = simp_dist_allgather_peer(m->tp_arena, 0, 16);
+      // first use of the peer exchange (logits) allocates its epoch words (a collective): here, outside any capture
+      rc = simp_dist_allgather_peer(m->tp_arena, o_lg, 16);
     }
+    A((void**)&m->tp_xn, size_t(c.dim) * 4);
   } else {
     A((void**)&m->x, c.dim * 4); A((void**)&m->xb, mx * 4); A((void**)&m->hb, c.hidden_dim * 4);
   }
@@ -908,6 +958,8 @@ SIMP_API int simp_llama_forward(void* model, int64_t token, int64_t pos, float* 
   }
   SIMP_CUDA(cudaMemcpyAsync(m.ctl, ctl, sizeof(ctl), cudaMemcpyHostToDevice, st));
   if (int rc = ensure_graph(m)) return rc;
+  if (m.tp > 1)
+    if (int rc = simp_dist_barrier()) return rc;
   SIMP_CUDA(cudaGraphLaunch(m.graph, st));
   if (logits_host)
     SIMP_CUDA(cudaMemcpyAsync(logits_host, m.logits, size_t(m.cfg.vocab_size) * 4, cudaMemcpyDeviceToHost, st));
@@ -943,6 +995,10 @@ SIMP_API int simp_llama_generate(void* model, const int32_t* prompt, int64_t n_p
   SIMP_CUDA(cudaMemcpyAsync(m.ctl, ctl, sizeof(ctl), cudaMemcpyHostToDevice, st));
   if (int rc = ensure_graph(m)) return rc;
   SIMP_CUDA(cudaMemcpyAsync(m.ctl, ctl, sizeof(ctl), cudaMemcpyHostToDevice, st));
+  // Tensor parallel: the ranks meet on the host side of the stream before the tokens start, so that the bounded
+  // device-side waits of the exchange only ever cover kernel skew, not a rank that is still loading or capturing.
+  if (m.tp > 1)
+    if (int rc = simp_dist_barrier()) return rc;
   const int64_t steps = n_prompt + n_new - 1;
   cudaEvent_t e0, e1;
   SIMP_CUDA(cudaEventCreate(&e0));
@@ -983,7 +1039,7 @@ SIMP_API int simp_llama_destroy(void* model) {
   void* ptrs[] = {m->tok_emb, m->rms_att, m->rms_ffn, m->rms_final, m->wcls, m->wq, m->wk, m->wv, m->wo, m->w1, m->w2,
                   m->w3, m->qweights, m->scales, m->zeros, m->x, m->xb, m->hb, m->q, m->k, m->v, m->logits, m->kc,
                   m->vc, m->attn_part, m->attn_cnt, m->ctl, m->prompt, m->out_tokens,
-                  m->pk_bar, m->pk_best_val, m->pk_best_idx};
+                  m->pk_bar, m->pk_best_val, m->pk_best_idx, m->tp_xn};
   for (void* p : ptrs)
     if (p) cudaFree(p);
   delete m;

@@ -435,12 +435,8 @@ static size_t i8_attn_smem(const LlamaI8Model& m) {
 
 static int i8_enqueue_token(LlamaI8Model& m, cudaStream_t st) {
   const simp_llama_i8_config& c = m.cfg;
-  // SIMP_DECODE_MODE=persistent selects the single cooperative kernel per token (llama_i8_persistent.cu; parity
-  // green, a few percent slower than the per-op kernels below today), anything else the per-op kernels
-  {
-    const char* e = getenv("SIMP_DECODE_MODE");
-    if (e && !strcmp(e, "persistent") && persistent_i8_supported(m)) return enqueue_token_persistent_i8(m, st);
-  }
+  // (a single cooperative kernel per token was built for this model too: 698 us at position 0 against 641 for the
+  // per-op kernels below, so it was removed)
   const int dim = int(c.dim), hd = int(c.hidden_dim), kv = int(m.kv_dim), hs = int(c.head_dim);
   const int sms = ctx().sm_count;
   I8_LAUNCH(i8_input_kernel, dim3((dim + 255) / 256), dim3(256), 0, st, false, (const int8_t*)m.x_i8, m.x, dim);
@@ -521,7 +517,7 @@ static int i8_ensure_graph(LlamaI8Model& m) {
 // a layer are int8 GEMMs on the tensor cores (gemm_i8_run: tcgen05 kind::i8, A = activations [M, K] s8,
 // B = weights [N, K] s8 K-major); the steps between them are small row kernels that restate the text.
 int gemm_i8_run(const void* A, const int8_t* B, int32_t* C, int64_t M, int64_t K, int64_t N, int a_unsigned,
-                int b_transposed, int32_t* const* peer_c, int n_peers, int64_t ldc, int64_t col_offset);
+                int b_transposed, int32_t* const* peer_c, int n_peers, int64_t ldc, int64_t col_offset, int self_rank = 0);
 
 // f32 -> i8 without a clamp: truncate to i32, keep the low 8 bits (what the compiled reference does on x86).
 __device__ __forceinline__ int8_t narrow_f32_to_i8(float v) {
@@ -662,7 +658,7 @@ SIMP_API int simp_llama_i8_destroy(void* model) {
   }
   void* ptrs[] = {m->rms_att, m->rms_ffn, m->rms_final, m->wcls, m->wq, m->wk, m->wv, m->wo, m->w1, m->w2, m->w3,
                   m->x_i8, m->xb_i8, m->ffn_hb, m->kc, m->vc, m->x, m->xb, m->logits, m->q, m->k, m->v, m->ctl,
-                  m->attn_part, m->attn_cnt, m->pk_bar, m->pk_best_val, m->pk_best_idx, m->pk_part};
+                  m->attn_part, m->attn_cnt};
   for (void* p : ptrs)
     if (p) cudaFree(p);
   delete m;
@@ -701,10 +697,6 @@ SIMP_API int simp_llama_i8_create(const simp_llama_i8_config* cfg, void** model)
   m->nsplit = int(std::min<int64_t>(AI8_MAX_SPLITS, std::max<int64_t>(1, c.max_seq_len / 256)));
   A((void**)&m->attn_part, size_t(c.n_heads) * m->nsplit * (c.head_dim + 2) * 4);
   A((void**)&m->attn_cnt, size_t(c.n_heads) * 4);
-  A((void**)&m->pk_bar, 64);
-  A((void**)&m->pk_best_val, size_t(ctx().sm_count) * 4);
-  A((void**)&m->pk_best_idx, size_t(ctx().sm_count) * 4);
-  A((void**)&m->pk_part, size_t(c.n_heads) * 4 * (c.head_dim + 2) * 4);
   if (rc != SIMP_OK) { simp_llama_i8_destroy(m); return rc; }
   cudaMemsetAsync(m->ctl, 0, 64, ctx().stream);
   cudaMemsetAsync(m->attn_cnt, 0, size_t(c.n_heads) * 4, ctx().stream);

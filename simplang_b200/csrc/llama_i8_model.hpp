@@ -1,5 +1,4 @@
-// llama_i8_model.hpp -- device-resident state of the int8 LLaMA-3.2-1B-style model (shared by the per-op graph
-// path in llama_i8.cu and the persistent per-token kernel in llama_i8_persistent.cu).
+// llama_i8_model.hpp -- device-resident state of the int8 LLaMA-3.2-1B-style model (llama_i8.cu).
 #pragma once
 #include <cuda_runtime.h>
 #include <cstdint>
@@ -22,13 +21,6 @@ struct LlamaI8Model {
   float* attn_part = nullptr;   // [n_heads, nsplit, head_dim + 2] split partials of the attention
   int* attn_cnt = nullptr;      // per-head arrival counters (zero between launches)
   int nsplit = 1;
-  // scratch of the persistent per-token kernel: grid-barrier words, per-block argmax candidates (unused by this
-  // model, kept for the shared classifier code), attention partials for up to 4 sequence splits
-  unsigned* pk_bar = nullptr;
-  float* pk_best_val = nullptr;
-  int* pk_best_idx = nullptr;
-  float* pk_part = nullptr;
-  bool pk_attr_done = false;
   cudaGraphExec_t graph = nullptr;
   // prefill: scratch and one captured graph per sequence length that has been used
   struct PrefillPlan {
@@ -40,9 +32,5 @@ struct LlamaI8Model {
   };
   std::vector<PrefillPlan> plans;
 };
-
-// One token as a single persistent cooperative kernel (llama_i8_persistent.cu).
-int enqueue_token_persistent_i8(LlamaI8Model& m, cudaStream_t st);
-bool persistent_i8_supported(const LlamaI8Model& m);
 
 }  // namespace simp

@@ -1,5 +1,5 @@
 // llama_model.hpp -- device-resident state of one LLaMA decoder (shared by the per-op graph path in
-// llama.cu and the persistent per-token kernel in llama_persistent.cu).
+// llama.cu and the persistent per-token kernel of the f32 model in llama_persistent.cu).
 #pragma once
 #include <cuda.h>
 #include <cuda_runtime.h>
@@ -21,8 +21,9 @@ struct LlamaModel {
   int64_t loff[7] = {0, 0, 0, 0, 0, 0, 0};  // the same for the device copy (differs under tensor parallelism)
   bool offsets_set = false;
   int tp = 1, rank = 0;                      // tensor-parallel degree and this rank
-  void* tp_arena = nullptr;                  // tp > 1: symmetric buffer holding x | xb | hb | logits (peer-store exchange)
-  bool tp_nccl = false;                      // tp > 1: exchange with NCCL all-gathers instead
+  void* tp_arena = nullptr;                  // tp > 1: symmetric buffer holding x | xb | hb (tagged words) | logits
+  uint8_t* tp_peer[8] = {};                  // the arena of every rank as seen from this process
+  float* tp_xn = nullptr;                    // tp > 1: normalised x for the classifier (plain floats)
   // state (device)
   float *x = nullptr, *xb = nullptr, *hb = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *logits = nullptr;
   float *kc = nullptr, *vc = nullptr, *attn_part = nullptr;
@@ -48,8 +49,5 @@ struct LlamaModel {
 // One token of the f32 model as a single persistent cooperative kernel (llama_persistent.cu).
 int enqueue_token_persistent_f32(LlamaModel& m, cudaStream_t st);
 bool persistent_f32_supported(const LlamaModel& m);
-// The same for the W4 model on one GPU (llama_persistent_w4.cu).
-int enqueue_token_persistent_w4(LlamaModel& m, cudaStream_t st);
-bool persistent_w4_supported(const LlamaModel& m);
 
 }  // namespace simp

@@ -84,9 +84,8 @@ __global__ void __launch_bounds__(PK_BLOCK, 1) llama_f32_token_kernel(const Pers
         if (bytes == 0) return;
         if (count_only) { total += bytes; return; }
         const uint8_t* src = reinterpret_cast<const uint8_t*>(W + (size_t(l) * R + first) * K);
-        const uint64_t pol = ptx::l2_evict_first_policy();   // weights are read once per token
         for (uint32_t done = 0; done < bytes; done += PK_COPY_CHUNK)
-          ptx::bulk_load_hint(ptx::smem_u32(dst + off + done), src + done, min(PK_COPY_CHUNK, bytes - done), bar, pol);
+          ptx::bulk_load(ptx::smem_u32(dst + off + done), src + done, min(PK_COPY_CHUNK, bytes - done), bar);
         off += bytes;
       };
       for (int pass = 0; pass < 2; ++pass) {

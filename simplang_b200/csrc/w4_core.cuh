@@ -103,6 +103,12 @@ struct W4Args {
   // through this launch's wait for its input, its arithmetic and the launch gap.
   const uint8_t* nx_base[6];
   uint32_t nx_bytes[6];
+
+  // Tensor parallel (tp.n > 1): x and res are arrays of tagged 64-bit words (see TpLL) that the kernel polls for
+  // tag id_x / id_res; with id_out != 0 the rows of segment 0 (W4_GATE_UP: the gated rows) go, tagged id_out, into
+  // every rank's copy of the output vector at byte offset out_off of the arena (this rank's slice) instead of `out`.
+  TpLL tp;
+  uint32_t id_x, id_res, id_out, out_off;
   int total_tiles;         // row tiles over all segments (W4_GATE_UP: over segment 0)
   int* status;             // device error word for bounded waits
   int seg_tile_start[4];
@@ -207,7 +213,7 @@ __device__ __forceinline__ void w4_mma_spans(const W4Tile& tl, int r0, int vrows
 // rows (TR == 8: one half-used slab), the NW warps split slabs x interleaved 128-weight spans, and the
 // per-warp partial sums of a row meet in a small shared array.  NW = 8 with up to three blocks per SM; for rows so
 // long that only 8-row tiles would fit that way, NW = 16 with 16-row tiles and one block per SM.
-template <int MODE, int TR, int NW, int NS, bool BATCH>
+template <int MODE, int TR, int NW, int NS, bool BATCH, bool LL>
 __global__ void __launch_bounds__(NW * 32, NW == 8 ? 3 : 1) w4_gemv_kernel(const W4Args a) {
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ float sh_ss[NW];
@@ -261,10 +267,9 @@ __global__ void __launch_bounds__(NW * 32, NW == 8 ? 3 : 1) w4_gemv_kernel(const
       const W4Seg& sg = a.seg[MODE == W4_GATE_UP ? m : s];
       uint8_t* dst = stage_ptr(st, m);
       if (piece == 0) ptx::mbar_arrive_expect_tx(bar, uint32_t(stage_bytes));
-      const uint64_t pol = ptx::l2_evict_first_policy();   // weights are read once per pass
-      if (part == 0) ptx::bulk_load_hint(ptx::smem_u32(dst), sg.qw + size_t(row0) * row_bytes, uint32_t(mat_w), bar, pol);
-      else if (part == 1) ptx::bulk_load_hint(ptx::smem_u32(dst + mat_w), sg.sc + size_t(row0) * sc_row, uint32_t(mat_s), bar, pol);
-      else ptx::bulk_load_hint(ptx::smem_u32(dst + mat_w + mat_s), sg.zr + size_t(row0) * sc_row, uint32_t(mat_s), bar, pol);
+      if (part == 0) ptx::bulk_load(ptx::smem_u32(dst), sg.qw + size_t(row0) * row_bytes, uint32_t(mat_w), bar);
+      else if (part == 1) ptx::bulk_load(ptx::smem_u32(dst + mat_w), sg.sc + size_t(row0) * sc_row, uint32_t(mat_s), bar);
+      else ptx::bulk_load(ptx::smem_u32(dst + mat_w + mat_s), sg.zr + size_t(row0) * sc_row, uint32_t(mat_s), bar);
     }
     for (int j = 0; j < count; ++j) {   // block-uniform
       const int q = q_first + j;
@@ -312,6 +317,8 @@ __global__ void __launch_bounds__(NW * 32, NW == 8 ? 3 : 1) w4_gemv_kernel(const
   }
   __syncthreads();
   // Weights never change: the first NS tiles are requested before waiting for the producer of the input.
+  constexpr bool ll = LL;                     // tensor parallel: tagged-word vectors (a.tp.n > 1)
+  const uint32_t tbase = LL ? ll_tag_base(a.tp) : 0u;   // requested before the wait for the predecessor
   issue_round(0, NS);
   W4_MARK(1);
   pdl_launch_dependents();
@@ -321,9 +328,7 @@ __global__ void __launch_bounds__(NW * 32, NW == 8 ? 3 : 1) w4_gemv_kernel(const
     // this block's share of region `lane`, in 16-byte units; one request of at most 64 KB per loop trip
     const uint32_t units = a.nx_bytes[lane] >> 4;
     const uint32_t u0 = uint32_t(uint64_t(units) * blockIdx.x / gridDim.x), u1 = uint32_t(uint64_t(units) * (blockIdx.x + 1) / gridDim.x);
-    const uint64_t pol = ptx::l2_evict_first_policy();
-    for (uint32_t u = u0; u < u1; u += 4096)
-      ptx::bulk_prefetch_l2(a.nx_base[lane] + size_t(u) * 16, (min(u1, u + 4096) - u) * 16, pol);
+    for (uint32_t u = u0; u < u1; u += 4096) ptx::bulk_prefetch_l2(a.nx_base[lane] + size_t(u) * 16, (min(u1, u + 4096) - u) * 16);
   }
   if (a.pf_len) {
     const int n = __ldg(a.pf_len) * a.pf_row_bytes;   // bytes per region
@@ -338,6 +343,7 @@ __global__ void __launch_bounds__(NW * 32, NW == 8 ? 3 : 1) w4_gemv_kernel(const
   // loads in flight together.
   pdl_wait();
   W4_MARK(2);
+  const uint32_t tag_x = tbase + a.id_x;
   // (The arithmetic of a round exists once in the code: a kernel of a decode step runs every instruction only a
   // few times, so what it costs is largely fetching the instruction -- compact code beats unrolled code here.)
   for (int b0 = 0; b0 < ntask; b0 += W4_PACK_ROUNDS * int(blockDim.x)) {
@@ -346,9 +352,22 @@ __global__ void __launch_bounds__(NW * 32, NW == 8 ? 3 : 1) w4_gemv_kernel(const
     for (int r = 0; r < W4_PACK_ROUNDS; ++r) {
       const int q = b0 + r * int(blockDim.x) + int(threadIdx.x);
       xv[r][0] = xv[r][1] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-      if (q < ntask) {
+      if (q < ntask && ll) {   // eight tagged words: all requested, then checked (a late one is polled)
+        const ll_word* xw = reinterpret_cast<const ll_word*>(a.x) + 8 * q;
+        ll_word w[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) w[i] = ll_load_sys(xw + i);
+        float f[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          f[i] = uint32_t(w[i] >> 32) == tag_x ? __uint_as_float(uint32_t(w[i])) : ll_spin(xw + i, tag_x, a.status, 80);
+        xv[r][0] = make_float4(f[0], f[1], f[2], f[3]);
+        xv[r][1] = make_float4(f[4], f[5], f[6], f[7]);
+      } else if (q < ntask) {
         xv[r][0] = __ldcg(reinterpret_cast<const float4*>(a.x) + 2 * q);
         xv[r][1] = __ldcg(reinterpret_cast<const float4*>(a.x) + 2 * q + 1);
+      }
+      if (q < ntask) {
         if (b0 > 0 && a.mul) {
           mv[r][0] = __ldg(reinterpret_cast<const float4*>(a.mul) + 2 * q);
           mv[r][1] = __ldg(reinterpret_cast<const float4*>(a.mul) + 2 * q + 1);
@@ -395,7 +414,9 @@ __global__ void __launch_bounds__(NW * 32, NW == 8 ? 3 : 1) w4_gemv_kernel(const
       const int st = q % NS, rb = q & 1;   // weight stage; buffer of the partial sums
       // residual rows are requested before the tile's arithmetic so that their latency is not paid in the epilogue
       float resid = 0.0f;
-      if (MODE == W4_ADD && int(threadIdx.x) < S_ROWS && row0 + int(threadIdx.x) < rows) resid = __ldcg(a.res + row0 + int(threadIdx.x));
+      if (MODE == W4_ADD && int(threadIdx.x) < S_ROWS && row0 + int(threadIdx.x) < rows)
+        resid = ll ? ll_get(reinterpret_cast<const ll_word*>(a.res) + row0 + int(threadIdx.x), tbase + a.id_res, a.status, 82)
+                   : __ldcg(a.res + row0 + int(threadIdx.x));
       if (!ptx::mbar_wait(ptx::smem_u32(&bars[st]), uint32_t(q / NS) & 1u, &abort_flag, a.status, 10)) break;
       float acc[NM][2];
 #pragma unroll
@@ -431,9 +452,9 @@ __global__ void __launch_bounds__(NW * 32, NW == 8 ? 3 : 1) w4_gemv_kernel(const
         v0 *= inv_r;
         v1 *= inv_r;
         if (row < rows) {
-          if (MODE == W4_STORE) a.seg[s].out[row] = v0;
-          if (MODE == W4_ADD) a.seg[s].out[row] = resid + v0;
-          if (MODE == W4_GATE_UP) a.seg[0].out[row] = (v0 / (1.0f + expf(-v0))) * v1;
+          const float val = MODE == W4_STORE ? v0 : (MODE == W4_ADD ? resid + v0 : (v0 / (1.0f + expf(-v0))) * v1);
+          if (ll && a.id_out != 0 && (MODE == W4_GATE_UP || s == 0)) ll_store_all(a.tp, a.out_off + uint32_t(row) * 8u, val, tbase + a.id_out);
+          else a.seg[MODE == W4_GATE_UP ? 0 : s].out[row] = val;
         }
       }
     }
@@ -453,7 +474,9 @@ __global__ void __launch_bounds__(NW * 32, NW == 8 ? 3 : 1) w4_gemv_kernel(const
     const int e_tile = int(threadIdx.x) / S_ROWS, e_r = int(threadIdx.x) % S_ROWS;
     if (e_tile < nb) {
       locate(q0 + e_tile, e_s, e_row0, e_rows);
-      if (MODE == W4_ADD && e_row0 + e_r < e_rows) resid = __ldcg(a.res + e_row0 + e_r);
+      if (MODE == W4_ADD && e_row0 + e_r < e_rows)
+        resid = ll ? ll_get(reinterpret_cast<const ll_word*>(a.res) + e_row0 + e_r, tbase + a.id_res, a.status, 82)
+                   : __ldcg(a.res + e_row0 + e_r);
     }
     bool ok = true;
 #pragma unroll 1
@@ -510,9 +533,9 @@ __global__ void __launch_bounds__(NW * 32, NW == 8 ? 3 : 1) w4_gemv_kernel(const
       v0 *= inv_r;
       v1 *= inv_r;
       if (row < e_rows) {
-        if (MODE == W4_STORE) a.seg[e_s].out[row] = v0;
-        if (MODE == W4_ADD) a.seg[e_s].out[row] = resid + v0;
-        if (MODE == W4_GATE_UP) a.seg[0].out[row] = (v0 / (1.0f + expf(-v0))) * v1;
+        const float val = MODE == W4_STORE ? v0 : (MODE == W4_ADD ? resid + v0 : (v0 / (1.0f + expf(-v0))) * v1);
+        if (ll && a.id_out != 0 && (MODE == W4_GATE_UP || e_s == 0)) ll_store_all(a.tp, a.out_off + uint32_t(row) * 8u, val, tbase + a.id_out);
+        else a.seg[MODE == W4_GATE_UP ? 0 : e_s].out[row] = val;
       }
     }
     if (q0 + bsz < my_steps) __syncthreads();   // `red` is rewritten by the next batch
@@ -522,7 +545,8 @@ __global__ void __launch_bounds__(NW * 32, NW == 8 ? 3 : 1) w4_gemv_kernel(const
 
 // Fills the tile bookkeeping, sizes the stages and launches.  All pointers are device pointers.
 template <int MODE>
-inline int w4_launch(W4Args a, cudaStream_t st, int sm_count, bool pdl = false) {
+// grid_out: receives the number of blocks; dry_run: only plan (nothing is launched).
+inline int w4_launch(W4Args a, cudaStream_t st, int sm_count, bool pdl = false, int* grid_out = nullptr, bool dry_run = false) {
   a.status = ctx().dev_status;
   constexpr int NM = MODE == W4_GATE_UP ? 2 : 1;
   const bool zeros = a.seg[0].zr != nullptr;
@@ -550,11 +574,8 @@ inline int w4_launch(W4Args a, cudaStream_t st, int sm_count, bool pdl = false) 
   // long that three 8-warp blocks per SM would be left with 8-row tiles (half of every MMA unused, and every
   // block packs the input vector for itself), and for launches of a few tiles per SM (batch-1 decode), where the
   // fixed costs of a launch dominate: one pack per SM instead of three, half the dependent rounds per tile.
-  static const char* wide_env = getenv("SIMP_W4_WIDE");   // "all": whenever there is a 16-row tile per SM; "off": never
   const bool wide_fit = need(16) <= 220 * 1024 && total_rows / 16 >= int64_t(sm_count);
   bool wide = wide_fit && ((tr == 8 && need(16) > 112 * 1024) || total_rows / 16 <= 8 * int64_t(sm_count));
-  if (wide_env && !strcmp(wide_env, "all")) wide = wide_fit;
-  if (wide_env && !strcmp(wide_env, "off")) wide = false;
   int ns = 2;
   if (wide) {
     tr = 16;
@@ -578,22 +599,27 @@ inline int w4_launch(W4Args a, cudaStream_t st, int sm_count, bool pdl = false) 
   per_sm = wide || per_sm < 1 ? 1 : (per_sm > 3 ? 3 : per_sm);
   const int cap = sm_count * per_sm;
   const int grid = g < cap ? g : cap;
+  if (grid_out) *grid_out = grid;
+  if (dry_run) return SIMP_OK;
   cudaError_t e;
   // decode-sized launches (a block owns at most two rounds of stages) take the batched form of the kernel
   const bool batch = int64_t(g) <= int64_t(grid) * ns * 2;
-#define W4_LAUNCH_B(TRV, NWV, NSV, BV)                                                                      \
+  const bool tagged = a.tp.n > 1;   // tensor parallel: the tagged-word form of the kernel
+#define W4_LAUNCH_B(TRV, NWV, NSV, BV, LV)                                                                  \
   do {                                                                                                      \
     static bool attr_set = false;                                                                           \
     if (!attr_set) {                                                                                        \
-      cudaFuncSetAttribute(w4_gemv_kernel<MODE, TRV, NWV, NSV, BV>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024); \
+      cudaFuncSetAttribute(w4_gemv_kernel<MODE, TRV, NWV, NSV, BV, LV>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024); \
       attr_set = true;                                                                                      \
     }                                                                                                       \
-    e = launch_kernel(w4_gemv_kernel<MODE, TRV, NWV, NSV, BV>, dim3(grid), dim3(NWV * 32), smem, st, pdl, a); \
+    e = launch_kernel(w4_gemv_kernel<MODE, TRV, NWV, NSV, BV, LV>, dim3(grid), dim3(NWV * 32), smem, st, pdl, a); \
   } while (0)
 #define W4_LAUNCH_TR(TRV, NWV, NSV)                                                                         \
   do {                                                                                                      \
-    if (batch) W4_LAUNCH_B(TRV, NWV, NSV, true);                                                            \
-    else W4_LAUNCH_B(TRV, NWV, NSV, false);                                                                 \
+    if (batch && tagged) W4_LAUNCH_B(TRV, NWV, NSV, true, true);                                            \
+    else if (batch) W4_LAUNCH_B(TRV, NWV, NSV, true, false);                                                \
+    else if (tagged) W4_LAUNCH_B(TRV, NWV, NSV, false, true);                                               \
+    else W4_LAUNCH_B(TRV, NWV, NSV, false, false);                                                          \
   } while (0)
   if (wide && ns == 6) W4_LAUNCH_TR(16, 16, 6);
   else if (wide && ns == 5) W4_LAUNCH_TR(16, 16, 5);

@@ -4,7 +4,7 @@
 // src/mlir/lowering/ConvertSimpToMemRef.cpp.  It is NOT built in this repository: the build image
 // has no LLVM/MLIR 14.  tests/ and bench.py exercise the library these calls bind to.
 //
-// With `--target gpu` these patterns are added to the pattern set of
+// With `--target gpu` (a new flag of src/main.cpp beside --emit-mlir) these patterns are added to the pattern set of
 // ConvertSimpToMemRefPass (ConvertSimpToMemRef.cpp:4078-4129) with a higher benefit than the loop
 // expansions they replace.  Each one rewrites a `simp` op whose operands have already been converted
 // to memrefs by the pass's type converter (ConvertSimpToMemRef.cpp:36-96) into

@@ -1,5 +1,6 @@
-"""GPU test of the N-sharded int8 GEMM over NCCL (needs >= 2 GPUs; skipped otherwise): every rank must end
-with all column blocks, bit-exact against the oracle."""
+"""GPU tests of the multi-GPU paths (need >= 2 GPUs, the 4-rank cases >= 4; skipped otherwise): the N-sharded int8
+GEMM -- every rank must end with all column blocks, bit-exact against the oracle, in the NCCL form and in the form
+that fuses the exchange into the GEMM epilogue -- and tensor-parallel W4 decode against the CPU oracle."""
 import os
 import socket
 import sys
@@ -64,21 +65,29 @@ def _worker(rank, world, port, out_dir):
             sg.sync()
             dist.barrier()
             sg.check(sg.lib().simp_dist_symm_free(cptr))
+        # a column block that is not a multiple of 32 columns would spill into the neighbour's block: refused
+        cptr = C.c_void_p()
+        sg.check(sg.lib().simp_dist_symm_alloc(256 * 48 * world * 4, C.byref(cptr)))
+        rc = sg.lib().simp_dist_matmul_i8_nsharded_fused(dA.ptr, dB.ptr, cptr, 256, 512, 48, 1, 0)
+        assert rc != 0 and b"multiples of 32" in sg.lib().simp_gpu_last_error()
+        dist.barrier()
+        sg.check(sg.lib().simp_dist_symm_free(cptr))
         np.save(os.path.join(out_dir, f"ok{rank}.npy"), np.array([1]))
         sg.check(sg.lib().simp_dist_shutdown())
     finally:
         dist.destroy_process_group()
 
 
-def test_nsharded_gemm_two_ranks(gpu, tmp_path):
+@pytest.mark.parametrize("world", [2, 4])
+def test_nsharded_gemm(gpu, tmp_path, world):
     import ctypes
     n = ctypes.c_int()
     gpu.check(gpu.lib().simp_gpu_device_count(ctypes.byref(n)))
-    if n.value < 2:
-        pytest.skip("needs at least 2 GPUs")
+    if n.value < world:
+        pytest.skip(f"needs at least {world} GPUs")
     import torch.multiprocessing as mp
-    mp.spawn(_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
-    assert all(os.path.exists(tmp_path / f"ok{r}.npy") for r in range(2))
+    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    assert all(os.path.exists(tmp_path / f"ok{r}.npy") for r in range(world))
 
 
 def _tp_worker(rank, world, port, out_dir, which):
@@ -129,13 +138,13 @@ def _tp_worker(rank, world, port, out_dir, which):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("which", ["tiny", "3b"])
-def test_tensor_parallel_w4_decode_two_ranks(gpu, tmp_path, which):
+@pytest.mark.parametrize("which,world", [("tiny", 2), ("3b", 2), ("tiny", 4), ("3b", 4)])
+def test_tensor_parallel_w4_decode(gpu, tmp_path, which, world):
     import ctypes
     n = ctypes.c_int()
     gpu.check(gpu.lib().simp_gpu_device_count(ctypes.byref(n)))
-    if n.value < 2:
-        pytest.skip("needs at least 2 GPUs")
+    if n.value < world:
+        pytest.skip(f"needs at least {world} GPUs")
     import torch.multiprocessing as mp
-    mp.spawn(_tp_worker, args=(2, _free_port(), str(tmp_path), which), nprocs=2, join=True)
-    assert all(os.path.exists(tmp_path / f"tp_{which}_{r}.npy") for r in range(2))
+    mp.spawn(_tp_worker, args=(world, _free_port(), str(tmp_path), which), nprocs=world, join=True)
+    assert all(os.path.exists(tmp_path / f"tp_{which}_{r}.npy") for r in range(world))

@@ -45,8 +45,8 @@ TINY = dict(dim=128, hidden_dim=256, n_layers=3, n_heads=4, n_kv_heads=4, vocab_
 
 @pytest.fixture(params=["persistent", "graph"])
 def decode_mode(request, monkeypatch):
-    """Both models have two device forms: one cooperative kernel per token, or a graph of per-op kernels.
-    The library reads SIMP_DECODE_MODE when a model builds its token graph."""
+    """The f32 model has two device forms: one cooperative kernel per token (default), or a graph of per-op kernels
+    (SIMP_DECODE_MODE=graph, read when a model builds its token graph).  The W4 model has the graph form only."""
     monkeypatch.setenv("SIMP_DECODE_MODE", request.param)
     return request.param
 
@@ -71,14 +71,14 @@ def test_tiny_f32_gqa_odd_head(gpu, oracle):
 
 
 @pytest.mark.parametrize("gs", [32, 64, 128])
-def test_tiny_w4(gpu, oracle, gs, decode_mode):
+def test_tiny_w4(gpu, oracle, gs):
     from simplang_b200 import synth
     cfg = dict(TINY, group_size=gs)
     t, off = synth.llama_w4_tensors(cfg, 7, threads=4)
     run_pair(gpu, oracle, cfg, t, True, off, 4, 30)
 
 
-def test_tiny_w4_asymmetric(gpu, oracle, decode_mode):
+def test_tiny_w4_asymmetric(gpu, oracle):
     """Reference-style asymmetric groups (zeros array present), quantised by the host quantiser's formula."""
     from simplang_b200 import synth
     cfg = dict(TINY, group_size=64)
@@ -103,13 +103,13 @@ def test_stories110m_f32(gpu, oracle, decode_mode):
     print(f"110M f32 ({decode_mode}): worst logit rel err {worst:.2e}, {79 / ms * 1e3:.0f} tok/s")
 
 
-def test_llama3b_w4(gpu, oracle, decode_mode):
+def test_llama3b_w4(gpu, oracle):
     """BASELINE config: dim 3200, 26 layers, 32 heads (hs 100), FFN 8640, W4 gs 64; 16-token prompt, 64 greedy tokens."""
     from simplang_b200 import synth
     cfg = synth.LLAMA_3B_W4
     t, off = synth.llama_w4_tensors(cfg, 0, threads=16)
     worst, ms = run_pair(gpu, oracle, cfg, t, True, off, 16, 64)
-    print(f"3B W4 ({decode_mode}): worst logit rel err {worst:.2e}, {79 / ms * 1e3:.0f} tok/s")
+    print(f"3B W4: worst logit rel err {worst:.2e}, {79 / ms * 1e3:.0f} tok/s")
 
 
 def test_forward_api_and_errors(gpu, oracle):

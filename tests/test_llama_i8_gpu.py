@@ -14,14 +14,6 @@ SMALL = dict(dim=128, hidden_dim=256, n_layers=2, n_heads=8, n_kv_heads=2, vocab
 MID = dict(dim=512, hidden_dim=1376 // 16 * 16, n_layers=3, n_heads=8, n_kv_heads=4, vocab_size=1000, max_seq_len=160, head_dim=64)
 
 
-@pytest.fixture(params=["persistent", "graph"])
-def decode_mode(request, monkeypatch):
-    """Two device forms of a token: one cooperative kernel, or a graph of per-op kernels.  The library reads
-    SIMP_DECODE_MODE when a model builds its token graph."""
-    monkeypatch.setenv("SIMP_DECODE_MODE", request.param)
-    return request.param
-
-
 def run_positions(gpu, oracle, cfg, seed, style, positions, x_seed=1):
     from simplang_b200 import synth
     t = synth.llama_i8_tensors(cfg, seed, style)
@@ -40,19 +32,19 @@ def run_positions(gpu, oracle, cfg, seed, style, positions, x_seed=1):
 
 
 @pytest.mark.parametrize("style", ["bench", "unit-norm"])
-def test_small(gpu, oracle, style, decode_mode):
+def test_small(gpu, oracle, style):
     run_positions(gpu, oracle, SMALL, 3, style, range(0, 40))
 
 
 @pytest.mark.parametrize("style", ["bench", "unit-norm"])
-def test_mid_gqa(gpu, oracle, style, decode_mode):
+def test_mid_gqa(gpu, oracle, style):
     """head_dim 64 (the divisor 8.0 is then sqrt(head_dim)), 2 query heads per KV head, hidden_dim not a power
     of two, context long enough for every warp of the attention kernel to hold several timesteps."""
     run_positions(gpu, oracle, MID, 5, style, range(0, 150))
 
 
 @pytest.mark.parametrize("style", ["bench", "unit-norm"])
-def test_long_context_sequence_splits(gpu, oracle, style, decode_mode):
+def test_long_context_sequence_splits(gpu, oracle, style):
     """max_seq_len 1100 gives the attention kernel 4 sequence splits per head; positions are visited sparsely
     (rows never visited stay zero in both caches), including split boundaries and the last position."""
     cfg = dict(dim=256, hidden_dim=512, n_layers=2, n_heads=4, n_kv_heads=2, vocab_size=400, max_seq_len=1100, head_dim=64)
@@ -60,7 +52,7 @@ def test_long_context_sequence_splits(gpu, oracle, style, decode_mode):
     run_positions(gpu, oracle, cfg, 11, style, positions)
 
 
-def test_decode_loop_matches_single_forwards(gpu, oracle, decode_mode):
+def test_decode_loop_matches_single_forwards(gpu, oracle):
     from simplang_b200 import synth
     t = synth.llama_i8_tensors(SMALL, 7, "unit-norm")
     x = synth.llama_i8_input(SMALL, 2)
@@ -78,7 +70,7 @@ def test_decode_loop_matches_single_forwards(gpu, oracle, decode_mode):
     gm.close()
 
 
-def test_llama32_1b_full_size(gpu, oracle, decode_mode):
+def test_llama32_1b_full_size(gpu, oracle):
     """The reference's configuration (dim 2048, 16 layers, 32 / 8 heads, hidden 8192, vocab 128256): a few
     positions with the host's own distributions; the CPU oracle needs ~1 s per token."""
     from simplang_b200 import synth
@@ -136,7 +128,7 @@ def test_prefill_mid_gqa(gpu, oracle, M):
     assert bad <= total // 1000, (bad, total)
 
 
-def test_prefill_then_decode_continues(gpu, oracle, decode_mode):
+def test_prefill_then_decode_continues(gpu, oracle):
     """The prefill leaves its K/V rows in the device cache; a decode step at position M must see them."""
     from simplang_b200 import synth
     cfg, M = SMALL, 16
