@@ -479,6 +479,50 @@ def run_ours(args):
                 "peer_copy_gb_s": 770.0, "link_floor_ms": link_ms, "math_ms": ms_local,
                 "frac_of_max_math_link": max(link_ms, ms_local) / ms_step}
 
+    # ---- N > 1: the largest cube of the sweep, 16384^3, where the math per exchanged byte is twice that of 8192^3
+    cube16k = None
+    if world > 1 and not args.no_big and S == 8192:
+        import ctypes as C
+        S2 = 16384
+        Nl2 = S2 // world
+        rng2 = np.random.default_rng(77)
+        A2 = rng2.integers(0, 256, (S2, S2), dtype=np.uint8)
+        B2 = rng2.integers(-128, 128, (S2, S2), dtype=np.int8)
+        dA2 = sg.DeviceBuffer.from_numpy(A2)
+        dB2 = sg.DeviceBuffer.from_numpy(np.ascontiguousarray(B2[:, rank * Nl2:(rank + 1) * Nl2]))
+        cp2 = C.c_void_p()
+        sg.check(sg.lib().simp_dist_symm_alloc(S2 * S2 * 4, C.byref(cp2)))
+
+        def step2():
+            sg.check(sg.lib().simp_dist_matmul_i8_nsharded_fused(dA2.ptr, dB2.ptr, cp2.value, S2, S2, Nl2, 1, 0))
+
+        for _ in range(3):
+            step2()
+        n2 = max(3, min(args.steps, 10))
+        ms2, _ = timed(step2, n2)
+        ms2 /= n2
+        sg.check(sg.lib().simp_gpu_check_device_status())
+        # every rank checks 3 rows of a 2048-column slice that ANOTHER rank computed
+        src = (rank + 1) % world
+        c_lo = src * Nl2
+        rows2 = [(5 * rank + 1) % S2, S2 // 2 + rank, S2 - 1 - rank]
+        got2 = np.empty((3, 2048), np.int32)
+        for i, r in enumerate(rows2):
+            sg.check(sg.lib().simp_gpu_download(got2[i].ctypes.data, cp2.value + 4 * (r * S2 + c_lo), 4 * 2048))
+        exact2 = (A2[rows2].astype(np.float64) @ B2[:, c_lo:c_lo + 2048].astype(np.float64)).astype(np.int64).astype(np.int32)
+        ok2 = float(np.array_equal(got2, exact2))
+        if max_over_ranks(1.0 - ok2) != 0.0:
+            raise SystemExit("bench: 16384^3 gathered result differs from the exact product")
+        ops2 = 2.0 * S2 ** 3
+        out2 = 4.0 * S2 * Nl2 * (world - 1)
+        cube16k = {"value": ops2 / (ms2 * 1e-3) / 1e12, "unit": "TOPS", "ms_per_step": ms2, "steps": n2,
+                   "workload": "int8 tensor_matmul 16384^3, N-sharded, all-gather fused into the GEMM epilogue",
+                   "bytes_out_per_gpu_per_step": int(out2), "achieved_gb_s_per_gpu": out2 / (ms2 * 1e-3) / 1e9,
+                   "link_floor_ms": out2 / 770e9 * 1e3, "check": "3 rows x 2048 columns of a peer's block exact on every rank"}
+        dA2.free(); dB2.free()
+        sg.check(sg.lib().simp_dist_symm_free(cp2.value))
+        del A2, B2
+
     # ---- e2e through the host-pointer entry point (every rank computes its shard; max over ranks)
     hA = sg.pinned_empty((M, K), np.uint8); hA[...] = A
     hB = sg.pinned_empty((K, Nl), np.int8); hB[...] = B_local
@@ -569,6 +613,8 @@ def run_ours(args):
     if without_gather:
         line["without_gather"] = without_gather
         line["link"] = link
+    if cube16k:
+        line["cube_16384"] = cube16k
     if decode:
         line["decode"] = decode
     if world == 1 and not args.no_cpu:
@@ -593,6 +639,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-decode", action="store_true", help="skip the LLaMA decode legs")
     ap.add_argument("--no-sustained", action="store_true", help="skip the 2-second pass of the GEMM step")
+    ap.add_argument("--no-big", action="store_true", help="skip the 16384^3 sub-record of the multi-GPU arm")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)

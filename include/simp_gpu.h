@@ -62,6 +62,11 @@ int simp_gpu_check_device_status(void);
 int simp_gpu_matmul_f32(const float* A_dev, int64_t aoff, const float* B_dev, int64_t boff,
                         float* C_dev, int64_t coff, int64_t m, int64_t k, int64_t n,
                         int accumulate, int b_transposed);
+/* The 3-D (batched) form of tensor_matmul on f32: C[b] = A[b] . B[b], A [batch, m, k], B [batch, k, n] (b_transposed:
+ * [batch, n, k]), C [batch, m, n] fresh -- linalg.batch_matmul in TensorMatMulOpLowering
+ * (ConvertSimpToMemRef.cpp:3286-3291). */
+int simp_gpu_matmul_f32_batched(const float* A_dev, const float* B_dev, float* C_dev, int64_t batch, int64_t m,
+                                int64_t k, int64_t n, int b_transposed);
 
 /* ---- tensor_matmul on i8 -> i32 ------------------------------------------------------------
  * C[M,N] (i32, wrap-around) = A[M,K] . B, bit-exact.

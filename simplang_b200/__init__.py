@@ -38,6 +38,7 @@ _SIGNATURES = {
     "simp_gpu_sync": [],
     "simp_gpu_check_device_status": [],
     "simp_gpu_matmul_f32": [vp, i64, vp, i64, vp, i64, i64, i64, i64, C.c_int, C.c_int],
+    "simp_gpu_matmul_f32_batched": [vp, vp, vp, i64, i64, i64, i64, C.c_int],
     "simp_gpu_matmul_i8": [vp, vp, vp, i64, i64, i64, C.c_int, C.c_int],
     "simp_gpu_matmul_w4": [vp, vp, vp, vp, vp, i64, i64, i64, i64, C.c_int],
     "simp_gpu_dequant_w4": [vp, vp, vp, i64, i64, i64, vp],

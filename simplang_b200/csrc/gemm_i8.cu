@@ -22,6 +22,7 @@
 
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 
 #include "common.cuh"
 #include "sm100_ptx.cuh"
@@ -598,9 +599,46 @@ static EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
+// Encoded tensor maps are kept per (kind, address, extents, box): a map depends on nothing else, an encode costs
+// about a microsecond, and a small GEMM (1024^3 is 6 us of device time) makes three per call.
+struct MapKey {
+  int kind;
+  const void* base;
+  int64_t inner, outer;
+  int box_inner, box_outer;
+  bool operator==(const MapKey& o) const {
+    return kind == o.kind && base == o.base && inner == o.inner && outer == o.outer && box_inner == o.box_inner && box_outer == o.box_outer;
+  }
+};
+struct MapCache {
+  static constexpr int N = 32;
+  MapKey key[N];
+  CUtensorMap map[N];
+  int used = 0, next = 0;
+  std::mutex mu;
+};
+static MapCache g_maps;
+static bool map_lookup(const MapKey& k, CUtensorMap* out) {
+  std::lock_guard<std::mutex> lk(g_maps.mu);
+  for (int i = 0; i < g_maps.used; ++i)
+    if (g_maps.key[i] == k) {
+      *out = g_maps.map[i];
+      return true;
+    }
+  return false;
+}
+static void map_insert(const MapKey& k, const CUtensorMap& m) {
+  std::lock_guard<std::mutex> lk(g_maps.mu);
+  const int slot = g_maps.used < MapCache::N ? g_maps.used++ : (g_maps.next++ % MapCache::N);
+  g_maps.key[slot] = k;
+  g_maps.map[slot] = m;
+}
+
 // 2-D u8 tensor map: `inner` contiguous bytes per row, `outer` rows, 128-byte swizzle.
 // 2-D i32 tensor map for C stores: 32 x 32 boxes (128-byte rows), 128-byte swizzle.
 static int make_map_c_i32(CUtensorMap* map, const void* base, int64_t n, int64_t m) {
+  const MapKey key{1, base, n, m, 32, 32};
+  if (map_lookup(key, map)) return SIMP_OK;
   EncodeTiledFn enc = get_encode_fn();
   SIMP_REQUIRE(enc != nullptr, SIMP_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
   cuuint64_t dims[2] = {cuuint64_t(n), cuuint64_t(m)};
@@ -611,11 +649,14 @@ static int make_map_c_i32(CUtensorMap* map, const void* base, int64_t n, int64_t
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   SIMP_REQUIRE(r == CUDA_SUCCESS, SIMP_ERR_CUDA, "cuTensorMapEncodeTiled (C) failed with CUresult %d", int(r));
+  map_insert(key, *map);
   return SIMP_OK;
 }
 
 static int make_map_u8(CUtensorMap* map, const void* base, int64_t inner, int64_t outer, int box_inner,
                        int box_outer) {
+  const MapKey key{0, base, inner, outer, box_inner, box_outer};
+  if (map_lookup(key, map)) return SIMP_OK;
   EncodeTiledFn enc = get_encode_fn();
   SIMP_REQUIRE(enc != nullptr, SIMP_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
   cuuint64_t dims[2] = {cuuint64_t(inner), cuuint64_t(outer)};
@@ -626,6 +667,7 @@ static int make_map_u8(CUtensorMap* map, const void* base, int64_t inner, int64_
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   SIMP_REQUIRE(r == CUDA_SUCCESS, SIMP_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", int(r));
+  map_insert(key, *map);
   return SIMP_OK;
 }
 

@@ -29,11 +29,15 @@ __global__ void __launch_bounds__(256) gemv_f32_any_kernel(const float* __restri
 
 // General shapes: 64x64 output tile, K step 16, 256 threads x (4x4) micro-tile, FFMA.
 // B is [k,n] (b_t == 0) or [n,k] (b_t == 1).  Scalar, bounds-checked loads: any alignment.
+// blockIdx.z = batch index of the 3-D form (strides m*k, k*n, m*n; linalg.batch_matmul).
 __global__ void __launch_bounds__(256) gemm_f32_tile_kernel(const float* __restrict__ A, const float* __restrict__ B,
                                                             float* __restrict__ C, int64_t m, int64_t k, int64_t n,
                                                             int accumulate, int b_t) {
   __shared__ float As[16][64 + 4];
   __shared__ float Bs[16][64 + 4];
+  A += int64_t(blockIdx.z) * m * k;
+  B += int64_t(blockIdx.z) * k * n;
+  C += int64_t(blockIdx.z) * m * n;
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
   const int64_t m0 = int64_t(blockIdx.y) * 64, n0 = int64_t(blockIdx.x) * 64;
   float acc[4][4] = {};
@@ -126,6 +130,28 @@ SIMP_API int simp_gpu_matmul_f32(const float* A, int64_t aoff, const float* B, i
     gemm_f32_tile_kernel<<<dim3(unsigned(gx), unsigned(gy)), 256, 0, st>>>(a, b, c, m, k, n, accumulate,
                                                                          b_transposed);
   }
+  SIMP_LAUNCH_CHECK();
+  return SIMP_OK;
+}
+
+// Batched (3-D) tensor_matmul on f32: C[b] = A[b] . B[b] for b < batch, A [batch, m, k], B [batch, k, n] (or
+// [batch, n, k] with b_transposed), C [batch, m, n] fresh -- the linalg.batch_matmul case of TensorMatMulOpLowering
+// (src/mlir/lowering/ConvertSimpToMemRef.cpp:3286-3291).  One launch of the tile kernel with the batch in grid.z.
+SIMP_API int simp_gpu_matmul_f32_batched(const float* A, const float* B, float* C, int64_t batch, int64_t m, int64_t k,
+                                         int64_t n, int b_transposed) {
+  if (int rc = ensure_ready()) return rc;
+  SIMP_REQUIRE(batch >= 0 && m >= 0 && k >= 0 && n >= 0, SIMP_ERR_ARG, "matmul_f32_batched: negative size");
+  if (batch == 0 || m == 0 || n == 0) return SIMP_OK;
+  SIMP_REQUIRE(A && B && C, SIMP_ERR_ARG, "matmul_f32_batched: null pointer");
+  cudaStream_t st = ctx().stream;
+  if (k == 0) {
+    SIMP_CUDA(cudaMemsetAsync(C, 0, size_t(batch) * size_t(m) * size_t(n) * sizeof(float), st));
+    return SIMP_OK;
+  }
+  const int64_t gx = cdiv(n, 64), gy = cdiv(m, 64);
+  SIMP_REQUIRE(gx <= 0x7fffffff && gy <= 65535 && batch <= 65535, SIMP_ERR_SHAPE,
+               "matmul_f32_batched: shape too large for the tile kernel");
+  gemm_f32_tile_kernel<<<dim3(unsigned(gx), unsigned(gy), unsigned(batch)), 256, 0, st>>>(A, B, C, m, k, n, 0, b_transposed);
   SIMP_LAUNCH_CHECK();
   return SIMP_OK;
 }

@@ -2,7 +2,7 @@
 int8 GEMM at the configured shapes.  Prints one JSON line per case with the achieved GB/s (or TOPS), the
 algorithmic bytes used, and the fraction of the measured roofline.
 
-    python -m simplang_b200.opbench [--iters 50] [--only gemv_f32,w4,rowops,gemm_i8,gemm_i4,mma_peak,decode110m,decode3b,decode_i8,prefill_i8]
+    python -m simplang_b200.opbench [--iters 50] [--only gemv_f32,gemm_f32,w4,rowops,gemm_i8,gemm_i4,mma_peak,decode110m,decode3b,decode_i8,prefill_i8]
 
 Each case rotates over enough independent operand copies that the working set exceeds twice the
 126 MB L2, so every iteration streams from HBM the way consecutive layers of a decode step do.
@@ -81,6 +81,28 @@ def bench_gemv_f32(iters):
         ms = timed(lambda i: sg.matmul_f32(bufs[i], 0, x, 0, y, 0, rows, cols, 1, accumulate=False), nc, iters)
         emit("gemv_f32", [rows, cols], ms, nb, {"copies": nc})
         del bufs
+
+
+def bench_gemm_f32(iters):
+    """tensor_matmul on f32 with more than one right-hand side: the projection shapes of
+    examples/llama2/llama32_1b_fp32_prefill.sl:51-199 (M tokens x [2048 -> 2048 / 512 / 8192, 8192 -> 2048]).
+    Plain FFMA (never TF32): the bound is the FP32 pipe (148 SMs x 128 FMA per clock) for tall M and the weight
+    stream for M = 8."""
+    rng = np.random.default_rng(5)
+    ffma_peak = 148 * 128 * 2 * 1.965e9 / 1e12   # TFLOP/s at the maximum clock
+    for m, k, n in [(8, 2048, 2048), (8, 2048, 8192), (64, 2048, 2048), (512, 2048, 2048), (512, 2048, 8192), (512, 8192, 2048)]:
+        if not want((m, k, n)):
+            continue
+        nb = 4 * (m * k + k * n + m * n)
+        nc = copies_for(4 * k * n)
+        A = sg.DeviceBuffer.from_numpy(rng.standard_normal(m * k).astype(np.float32))
+        Bs = [sg.DeviceBuffer.from_numpy((0.02 * rng.standard_normal(k * n)).astype(np.float32)) for _ in range(min(nc, 8))]
+        Cb = sg.DeviceBuffer(m * n * 4)
+        ms = timed(lambda i: sg.matmul_f32(A, 0, Bs[i % len(Bs)], 0, Cb, 0, m, k, n, accumulate=False), len(Bs), iters)
+        tf = 2.0 * m * k * n / (ms * 1e-3) / 1e12
+        emit("tensor_matmul_f32", [m, k, n], ms, nb, {"tflops": round(tf, 2), "frac_of_ffma_peak": round(tf / ffma_peak, 3),
+                                                      "ffma_peak_tflops": round(ffma_peak, 1)})
+        del Bs
 
 
 def bench_w4(iters):
@@ -316,6 +338,8 @@ def main():
     which = set(args.only.split(","))
     if "gemv_f32" in which:
         bench_gemv_f32(args.iters)
+    if "gemm_f32" in which:
+        bench_gemm_f32(args.iters)
     if "w4" in which:
         bench_w4(args.iters)
     if "rowops" in which:

@@ -90,3 +90,26 @@ def test_linearity_large(gpu):
     rows = [0, 1, 127, 128, 2049, 4095]
     exact = A1[rows].astype(np.int64) @ B.astype(np.int64)
     assert np.array_equal(c1[rows], exact.astype(np.int32))
+
+
+def test_16384_cube_sampled_rows_exact(gpu):
+    """The largest cube of the sweep (16384^3, u8 x s8, B as [K, N]): too large for the CPU oracle as a whole, so rows
+    and columns are sampled -- every 2048-column slice gets 4 of the rows checked bit for bit against an exact product
+    (partial sums stay below 2^53, so a float64 BLAS product of the sample is exact)."""
+    S = 16384
+    rng = np.random.default_rng(16384)
+    A = rng.integers(0, 256, (S, S), dtype=np.uint8)
+    B = rng.integers(-128, 128, (S, S), dtype=np.int8)
+    dA, dB = gpu.DeviceBuffer.from_numpy(A), gpu.DeviceBuffer.from_numpy(B)
+    dC = gpu.DeviceBuffer(S * S * 4)
+    gpu.matmul_i8(dA, dB, dC, S, S, S, a_unsigned=True, b_transposed=False)
+    gpu.sync()
+    for s in range(S // 2048):
+        rows = sorted(int(r) for r in rng.choice(S, 4, replace=False)) + [0, S - 1][s % 2:s % 2 + 1]
+        cols = slice(s * 2048, (s + 1) * 2048)
+        exact = (A[rows].astype(np.float64) @ B[:, cols].astype(np.float64)).astype(np.int64).astype(np.int32)
+        got = np.empty((len(rows), 2048), np.int32)
+        for i, r in enumerate(rows):
+            gpu.check(gpu.lib().simp_gpu_download(got[i].ctypes.data, dC.ptr + 4 * (r * S + s * 2048), 4 * 2048))
+        bad = np.argwhere(got != exact)
+        assert bad.size == 0, f"slice {s}: {len(bad)} mismatches, first at {bad[:3].tolist()}"

@@ -76,3 +76,19 @@ def test_known_answers(gpu):
     dC = gpu.DeviceBuffer(32)
     gpu.matmul_f32(dA, 0, dB, 0, dC, 0, 4, 3, 2, accumulate=False)
     assert dC.to_numpy(np.float32, (4, 2))[0, 0] == 22.0
+
+
+@pytest.mark.parametrize("batch,m,k,n", [(3, 8, 2048, 512), (5, 33, 70, 41), (1, 64, 64, 64), (12, 16, 64, 16)])
+@pytest.mark.parametrize("b_t", [False, True])
+def test_batched_tensor_matmul(gpu, oracle, batch, m, k, n, b_t):
+    """3-D tensor_matmul (linalg.batch_matmul, ConvertSimpToMemRef.cpp:3286-3291): every batch entry equals the 2-D op."""
+    rng = np.random.default_rng(batch * 1000 + m * k + n)
+    A = rng.standard_normal((batch, m, k)).astype(np.float32)
+    B = rng.standard_normal((batch, k, n)).astype(np.float32)
+    Bg = np.ascontiguousarray(B.transpose(0, 2, 1)) if b_t else B
+    dA, dB = gpu.DeviceBuffer.from_numpy(A), gpu.DeviceBuffer.from_numpy(Bg)
+    dC = gpu.DeviceBuffer(batch * m * n * 4)
+    gpu.check(gpu.lib().simp_gpu_matmul_f32_batched(dA.ptr, dB.ptr, dC.ptr, batch, m, k, n, int(b_t)))
+    out = dC.to_numpy(np.float32, (batch, m, n))
+    for b in range(batch):
+        check(out[b], A[b], B[b], oracle.tensor_matmul_f32(A[b], Bg[b], b_transposed=b_t))
