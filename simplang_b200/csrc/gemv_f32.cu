@@ -8,6 +8,8 @@
 // Other shapes run a 64x64 FFMA tile kernel (plain f32 FMA, never TF32).
 // Semantics: MatMulOpLowering (src/mlir/lowering/ConvertSimpToMemRef.cpp:1890-1913, accumulates)
 // and TensorMatMulOpLowering f32 (ConvertSimpToMemRef.cpp:2926-2933, 3280-3291, fresh result).
+#include <algorithm>
+
 #include "common.cuh"
 #include "gemv_f32_core.cuh"
 
@@ -86,6 +88,72 @@ __global__ void __launch_bounds__(256) gemm_f32_tile_kernel(const float* __restr
     }
 }
 
+// Skinny left operand (m <= 64 rows; the prefill of a few tokens, examples/llama2/llama32_1b_fp32_prefill.sl:47-60:
+// f32<8, 2048> x f32<2048, 2048>): the op streams B once and is bound by that stream, not by arithmetic.  B is
+// [k, n] row-major, so a thread owns four neighbouring columns (one 16-byte load per row of B, coalesced across the
+// block) and up to SK_ROWS rows of A, whose values it reads from shared memory as broadcasts.  The k range is cut
+// into `splits` slices over grid.y so that every SM streams a share; slice s writes its partial [m, n] block to
+// scratch and gemm_f32_skinny_reduce adds the slices in slice order (fixed order: run-to-run identical results).
+constexpr int SK_ROWS = 8;
+constexpr int SK_THREADS = 128;
+constexpr int SK_KCHUNK = 64;   // rows of B per shared-memory refill of the A panel
+__global__ void __launch_bounds__(SK_THREADS) gemm_f32_skinny_kernel(const float* __restrict__ A, const float* __restrict__ B,
+                                                                     float* __restrict__ part, int m, int k, int n,
+                                                                     int k_per_split) {
+  __shared__ float As[SK_ROWS][SK_KCHUNK];
+  const int j = (int(blockIdx.x) * SK_THREADS + int(threadIdx.x)) * 4;   // first of this thread's four columns
+  const int k0 = int(blockIdx.y) * k_per_split, k1 = min(k, k0 + k_per_split);
+  const int r0 = int(blockIdx.z) * SK_ROWS, nr = min(SK_ROWS, m - r0);
+  float acc[SK_ROWS][4];
+#pragma unroll
+  for (int r = 0; r < SK_ROWS; ++r) acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0.0f;
+  for (int p0 = k0; p0 < k1; p0 += SK_KCHUNK) {
+    const int pc = min(SK_KCHUNK, k1 - p0);
+    __syncthreads();
+    for (int e = threadIdx.x; e < SK_ROWS * SK_KCHUNK; e += SK_THREADS) {
+      const int r = e / SK_KCHUNK, c = e - r * SK_KCHUNK;
+      As[r][c] = (r < nr && c < pc) ? A[int64_t(r0 + r) * k + p0 + c] : 0.0f;
+    }
+    __syncthreads();
+    if (j < n) {
+#pragma unroll 4
+      for (int c = 0; c < pc; ++c) {
+        const float4 b = ld_stream_f4(B + int64_t(p0 + c) * n + j);
+#pragma unroll
+        for (int r = 0; r < SK_ROWS; ++r) {
+          const float a = As[r][c];
+          acc[r][0] = fmaf(a, b.x, acc[r][0]);
+          acc[r][1] = fmaf(a, b.y, acc[r][1]);
+          acc[r][2] = fmaf(a, b.z, acc[r][2]);
+          acc[r][3] = fmaf(a, b.w, acc[r][3]);
+        }
+      }
+    }
+  }
+  if (j < n) {
+    float* dst = part + (int64_t(blockIdx.y) * m + r0) * n + j;
+#pragma unroll
+    for (int r = 0; r < SK_ROWS; ++r)
+      if (r < nr) *reinterpret_cast<float4*>(dst + int64_t(r) * n) = make_float4(acc[r][0], acc[r][1], acc[r][2], acc[r][3]);
+  }
+}
+__global__ void __launch_bounds__(256) gemm_f32_skinny_reduce(const float* __restrict__ part, float* __restrict__ C, int64_t mn,
+                                                              int splits, int accumulate) {
+  const int64_t i = (int64_t(blockIdx.x) * 256 + threadIdx.x) * 4;
+  if (i >= mn) return;
+  float4 s = *reinterpret_cast<const float4*>(part + i);
+  for (int q = 1; q < splits; ++q) {
+    const float4 t = *reinterpret_cast<const float4*>(part + int64_t(q) * mn + i);
+    s.x += t.x; s.y += t.y; s.z += t.z; s.w += t.w;
+  }
+  float4* c = reinterpret_cast<float4*>(C + i);
+  if (accumulate) {
+    const float4 o = *c;
+    s.x += o.x; s.y += o.y; s.z += o.z; s.w += o.w;
+  }
+  *c = s;
+}
+
 }  // namespace simp
 
 using namespace simp;
@@ -124,6 +192,19 @@ SIMP_API int simp_gpu_matmul_f32(const float* A, int64_t aoff, const float* B, i
       SIMP_REQUIRE(grid <= 0x7fffffff, SIMP_ERR_SHAPE, "matmul_f32: too many rows");
       gemv_f32_any_kernel<<<int(grid), 256, 0, st>>>(a, b, c, m, k, accumulate);
     }
+  } else if (!b_transposed && m <= 64 && n % 4 == 0 && n >= 512 && k >= 256 && k <= 0x7fffffff && n <= 0x7fffffff &&
+             ((reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(c)) & 15u) == 0) {
+    // skinny left operand: stream B once, k split over the SMs, partial blocks in library scratch
+    const int col_blocks = int(cdiv(n / 4, SK_THREADS)), row_blocks = int(cdiv(m, SK_ROWS));
+    int splits = int(cdiv(int64_t(ctx().sm_count) * 2, int64_t(col_blocks) * row_blocks));
+    splits = int(std::max<int64_t>(1, std::min<int64_t>(splits, k / 64)));
+    const int k_per_split = int(cdiv(cdiv(k, splits), 4) * 4);
+    splits = int(cdiv(k, k_per_split));
+    float* part = static_cast<float*>(scratch(size_t(splits) * size_t(m) * size_t(n) * 4, 12));
+    if (!part) return scratch_failed("matmul_f32 (k-slice partial sums)");
+    gemm_f32_skinny_kernel<<<dim3(unsigned(col_blocks), unsigned(splits), unsigned(row_blocks)), SK_THREADS, 0, st>>>(
+        a, b, part, int(m), int(k), int(n), k_per_split);
+    gemm_f32_skinny_reduce<<<unsigned(cdiv(m * n / 4, 256)), 256, 0, st>>>(part, c, m * n, splits, accumulate);
   } else {
     const int64_t gx = cdiv(n, 64), gy = cdiv(m, 64);
     SIMP_REQUIRE(gx <= 0x7fffffff && gy <= 65535, SIMP_ERR_SHAPE, "matmul_f32: shape too large for the tile kernel");

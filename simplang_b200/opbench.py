@@ -230,10 +230,14 @@ def bench_gemm_i4(iters):
                           "giops_replayed": round(2.0 * n ** 3 / (ms_r * 1e-3) / 1e9, 1)}), flush=True)
 
 
-def bench_decode(which, n_new=128):
+DECODE_TOKENS = 128
+
+
+def bench_decode(which, n_new=None):
     """Greedy decode tokens/s of the two model configurations (random init), device-timed over the
     whole generation (prompt of 16 teacher-forced tokens + n_new generated)."""
     from simplang_b200 import synth
+    n_new = n_new or DECODE_TOKENS
     peak, src = hbm_peak()
     if which == "110m":
         cfg = synth.STORIES_110M
@@ -323,8 +327,10 @@ def main():
     ap.add_argument("--iters", type=int, default=50)
     ap.add_argument("--only", default="gemv_f32,w4,rowops,gemm_i8")
     ap.add_argument("--shape", default=None, help="run only the case with this shape, e.g. 32000x3200")
+    ap.add_argument("--tokens", type=int, default=128, help="generated tokens of the decode workloads (small for profiler runs)")
     args = ap.parse_args()
-    global SHAPE_FILTER
+    global SHAPE_FILTER, DECODE_TOKENS
+    DECODE_TOKENS = args.tokens
     if args.shape:
         SHAPE_FILTER = [int(v) for v in args.shape.lower().split("x")]
     sg.init(int(os.environ.get("LOCAL_RANK", "0")))

@@ -46,7 +46,9 @@ def test_gemv(gpu, oracle, m, k, accumulate):
     check((out[coff:] - base)[:, None], Am, x[:, None], (ref[coff:] - base)[:, None])
 
 
-@pytest.mark.parametrize("m,k,n", [(64, 64, 64), (100, 37, 53), (4, 3, 2), (2, 2, 2), (512, 768, 96), (1, 300, 200)])
+@pytest.mark.parametrize("m,k,n", [(64, 64, 64), (100, 37, 53), (4, 3, 2), (2, 2, 2), (512, 768, 96), (1, 300, 200),
+                                   # skinny left operand: the k-split streaming kernel (m <= 64, n % 4 == 0, n >= 512, k >= 256)
+                                   (8, 2048, 2048), (64, 512, 1024), (5, 300, 512), (17, 1000, 516), (8, 2048, 8192)])
 @pytest.mark.parametrize("b_t", [False, True])
 def test_gemm_tile(gpu, oracle, m, k, n, b_t):
     rng = np.random.default_rng(m * k + n)
@@ -58,6 +60,19 @@ def test_gemm_tile(gpu, oracle, m, k, n, b_t):
     gpu.matmul_f32(dA, 0, dB, 0, dC, 0, m, k, n, accumulate=False, b_transposed=b_t)
     out = dC.to_numpy(np.float32, (m, n))
     check(out, A, B, oracle.tensor_matmul_f32(A, Bg, b_transposed=b_t))
+
+
+def test_skinny_accumulates_like_simp_matmul(gpu, oracle):
+    """simp.matmul semantics (C += A . B) on the k-split kernel."""
+    rng = np.random.default_rng(9)
+    m, k, n = 8, 1024, 768
+    A = rng.standard_normal((m, k)).astype(np.float32)
+    B = (0.05 * rng.standard_normal((k, n))).astype(np.float32)
+    C0 = rng.standard_normal((m, n)).astype(np.float32)
+    dA, dB, dC = (gpu.DeviceBuffer.from_numpy(a) for a in (A, B, C0))
+    gpu.matmul_f32(dA, 0, dB, 0, dC, 0, m, k, n, accumulate=True)
+    out = dC.to_numpy(np.float32, (m, n))
+    check(out - C0, A, B, oracle.tensor_matmul_f32(A, B))
 
 
 def test_known_answers(gpu):
