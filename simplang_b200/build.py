@@ -1,9 +1,13 @@
 """Builds ``libsimp_gpu.so`` (the C-ABI CUDA library) in-tree with nvcc for sm_100a.
 
-    python -m simplang_b200.build [--force] [--verbose]
+    python -m simplang_b200.build [--force] [--verbose] [--trace]
 
 One object per ``csrc/*.cu`` (compiled in parallel, skipped when up to date), linked into
 ``simplang_b200/libsimp_gpu.so``.  nvcc cross-compiles without a GPU.
+``--trace`` builds a second, instrumented library ``libsimp_gpu_trace.so`` (-DSIMP_W4_TRACE: the W4 projection and
+attention kernels of a decode step write %globaltimer marks from thread 0 of every block); load it with
+``SIMP_GPU_LIB=simplang_b200/libsimp_gpu_trace.so python -m simplang_b200.opbench --only decode3b_marks``.
+It is a measurement aid: its timings are not the product's.
 """
 from __future__ import annotations
 
@@ -35,13 +39,13 @@ def _newer(target, deps):
     return all(os.path.getmtime(d) <= t for d in deps)
 
 
-def _compile(src, force, verbose):
-    obj = os.path.join(OBJ, os.path.basename(src)[:-3] + ".o")
+def _compile(src, force, verbose, obj_dir=None, extra=()):
+    obj = os.path.join(obj_dir or OBJ, os.path.basename(src)[:-3] + ".o")
     headers = glob.glob(os.path.join(CSRC, "*.cuh")) + glob.glob(os.path.join(CSRC, "*.hpp")) + \
         glob.glob(os.path.join(ROOT, "include", "*.h"))
     if not force and _newer(obj, [src] + headers):
         return obj, ""
-    cmd = [NVCC] + FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", src, "-o", obj]
+    cmd = [NVCC] + FLAGS + list(extra) + (["-Xptxas", "-v"] if verbose else []) + ["-c", src, "-o", obj]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"nvcc failed for {src}:\n{r.stdout}\n{r.stderr}")
@@ -67,6 +71,21 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
+def build_trace() -> str:
+    """The instrumented library (see the module docstring)."""
+    obj_dir = os.path.join(HERE, "build_trace")
+    os.makedirs(obj_dir, exist_ok=True)
+    lib = os.path.join(HERE, "libsimp_gpu_trace.so")
+    srcs = sorted(glob.glob(os.path.join(CSRC, "*.cu")))
+    with cf.ThreadPoolExecutor(max_workers=min(8, len(srcs))) as ex:
+        objs = [o for o, _ in ex.map(lambda s: _compile(s, False, False, obj_dir, ("-DSIMP_W4_TRACE",)), srcs)]
+    r = subprocess.run([NVCC, "-shared", "-ccbin", HOST_CXX, "-o", lib] + objs + ["-lcudart_static", "-ldl", "-lpthread", "-lrt"],
+                       capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+    return lib
+
+
 def build_host() -> str:
     """Compiles the C++ host example (plain g++, links only -ldl: it dlopen()s the runtime library)."""
     host_dir = os.path.join(HERE, "host")
@@ -81,3 +100,5 @@ def build_host() -> str:
 
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    if "--trace" in sys.argv:
+        print(build_trace())

@@ -272,6 +272,47 @@ def bench_decode(which, n_new=None):
     m.close()
 
 
+def bench_decode_marks():
+    """Block-level time marks of one layer of the 3B W4 token graph.  Needs the instrumented library
+    (`python -m simplang_b200.build --trace`, loaded through SIMP_GPU_LIB): thread 0 of every block of the four
+    projection launches and of the attention launch of layer 1 writes %globaltimer marks; printed for the last token of
+    the run as min / median / max over blocks, ns relative to the first block of the q/k/v launch."""
+    import ctypes as C
+    from simplang_b200 import synth
+    L = sg.lib()
+    if not hasattr(L, "simp_debug_w4_trace"):
+        raise SystemExit("decode3b_marks needs the instrumented library: python -m simplang_b200.build --trace, then "
+                         "SIMP_GPU_LIB=simplang_b200/libsimp_gpu_trace.so")
+    cfg = synth.LLAMA_3B_W4
+    t, off = synth.llama_w4_tensors(cfg, 0, threads=16)
+    m = sg.Llama(cfg, t, w4=True, offsets=off)
+    prompt = synth.prompt_tokens(16, cfg["vocab_size"])
+    m.generate(prompt, 8)
+    _, _, ms = m.generate(prompt, DECODE_TOKENS)
+    print(json.dumps({"op": "llama 3B W4 decode (instrumented build)", "us_per_token": round(ms * 1e3 / (15 + DECODE_TOKENS), 1)}))
+    n = 5 * 148 * 16
+    buf = np.zeros(n, np.uint64)
+    L.simp_debug_w4_trace.argtypes = [C.c_void_p, C.c_size_t]
+    sg.check(L.simp_debug_w4_trace(buf.ctypes.data, n))
+    marks = buf.reshape(5, 148, 16).astype(np.int64)
+    base = marks[0, :, 0].min()
+    proj = {0: "start", 1: "weights requested", 2: "predecessor done", 3: "input packed", 4: "first tile ready", 5: "batch done", 15: "end"}
+    for k, name in enumerate(["q/k/v", "wo", "gate/up", "down"]):
+        for mk, what in proj.items():
+            v = marks[k, :, mk]
+            v = v[v > 0] - base
+            if len(v):
+                print(json.dumps({"launch": name, "mark": what, "min_ns": int(v.min()), "median_ns": int(np.median(v)), "max_ns": int(v.max()), "blocks": int(len(v))}))
+    att = {0: "start", 2: "rows requested", 3: "predecessor done", 4: "q/k/v staged", 7: "rows landed", 8: "scores done", 9: "softmax done",
+           5: "values done", 6: "output stored"}
+    for mk, what in att.items():
+        v = marks[4, :cfg["n_heads"], mk]
+        v = v[v > 0] - base
+        if len(v):
+            print(json.dumps({"launch": "attention", "mark": what, "min_ns": int(v.min()), "median_ns": int(np.median(v)), "max_ns": int(v.max()), "blocks": int(len(v))}))
+    m.close()
+
+
 def bench_decode_i8():
     """The int8 LLaMA-3.2-1B-style model as its host times it (bench_llama32_1b_int8.cpp): forwards of one
     int8 input at positions 0 / 127 / 511 / 1023 / 2047 / 4095 (5 each) and a 64-token loop from position 128."""
@@ -358,6 +399,8 @@ def main():
         bench_mma_peak(args.iters)
     if "decode110m" in which:
         bench_decode("110m")
+    if "decode3b_marks" in which:
+        bench_decode_marks()
     if "decode3b" in which:
         bench_decode("3b")
     if "decode_i8" in which:
