@@ -75,7 +75,7 @@ static std::vector<SymmBuf> g_symm;
 
 int gemm_i8_run(const void* A, const int8_t* B, int32_t* C, int64_t M, int64_t K, int64_t N, int a_unsigned,
                 int b_transposed, int32_t* const* peer_c, int n_peers, int64_t ldc, int64_t col_offset, int self_rank);
-int dist_rendezvous();
+int dist_rendezvous(bool pdl = false);
 
 // ---- peer-store all-gather ---------------------------------------------------------------------
 // In-place all-gather of a small vector that lives in a symmetric buffer: every rank stores its slice straight
@@ -103,6 +103,7 @@ __global__ void __launch_bounds__(256) ll_allgather_kernel(LlPeers peers, unsign
   // a consumer launched as a programmatic dependent may start its prologue (weight requests) now; its
   // griddepcontrol.wait still returns only when this exchange has completed
   pdl_launch_dependents();
+  pdl_wait();   // launched as a programmatic dependent by the fused GEMM: the predecessor's stores have been performed
   const unsigned epoch = *seq + 1u;
   const uint8_t* mine = peers.buf[rank] + offset + size_t(rank) * slice;
   const bool vec = ((reinterpret_cast<uintptr_t>(mine) | slice) & 15u) == 0;
@@ -217,7 +218,7 @@ SIMP_API int simp_dist_matmul_i8_nsharded_fused(const void* A_dev, const int8_t*
   if (int rc = gemm_i8_run(A_dev, B_local_dev, nullptr, M, K, N_local, a_unsigned, b_transposed, peers, g_world, ldc,
                            int64_t(g_rank) * N_local, g_rank))
     return rc;
-  return dist_rendezvous();
+  return dist_rendezvous(true);   // resident early; its wait returns when the GEMM's stores have been performed
 }
 
 SIMP_API int simp_dist_unique_id(void* id_out, size_t bytes) {
@@ -321,7 +322,7 @@ bool dist_symm_peers(const void* local, uint8_t** peers8) {
 // Rendezvous on the library stream without NCCL: the one-block exchange kernel with empty slices publishes this
 // rank's next epoch to every peer and waits (bounded) for theirs.  Work queued before it on this stream has
 // completed, with its stores to peer memory performed, before the epoch is published.
-int dist_rendezvous() {
+int dist_rendezvous(bool pdl) {
   if (g_world == 1) return SIMP_OK;
   const SymmBuf* fb = nullptr;
   if (int rc = ll_flags_ready(&fb)) return rc;
@@ -330,8 +331,8 @@ int dist_rendezvous() {
     peers.buf[r] = static_cast<uint8_t*>(fb->peer[r]);   // not touched: the slices are empty
     peers.flags[r] = static_cast<unsigned*>(fb->peer[r]);
   }
-  ll_allgather_kernel<<<1, 256, 0, ctx().stream>>>(peers, g_ll_seq, g_rank, g_world, 0, 0, ctx().dev_status);
-  SIMP_LAUNCH_CHECK();
+  SIMP_CUDA(launch_kernel(ll_allgather_kernel, dim3(1), dim3(256), 0, ctx().stream, pdl, peers, g_ll_seq, g_rank, g_world,
+                          size_t(0), size_t(0), ctx().dev_status));
   return SIMP_OK;
 }
 }  // namespace simp

@@ -57,6 +57,7 @@ struct GemmParams {
   int32_t* C;
   int* status;
   int tma_store;    // 1: epilogue goes through shared memory + TMA stores (needs N % 4 == 0)
+  uint32_t link_ns; // fused all-gather, 2-CTA kernel: time the link needs for everything this rank sends (0: no pacing)
   int n_peers;      // > 0: every C tile is TMA-stored into n_peers buffers (own + peer GPUs) at column col_offset
   int col_offset;
   int streamk;      // 1: the tiles x K-blocks work units are split evenly over the CTAs; partial tiles are
@@ -142,7 +143,8 @@ __global__ void zero_tiles_kernel(int32_t* __restrict__ C, int M, int N, int til
 __device__ __forceinline__ void epilogue_rows(const CUtensorMap* tmap_c, const PeerMaps* peers, const GemmParams& p,
                                               uint32_t tmem_acc,
                                               int q, int lane, int row0, int n0, uint32_t stage_smem,
-                                              uint32_t& nstore, bool partial = false) {
+                                              uint32_t& nstore, bool partial = false, uint64_t* pace_next = nullptr,
+                                              uint32_t pace_ns = 0) {
   const int row = row0 + lane;
   int32_t* crow = p.C + int64_t(row) * p.N + n0;
   const bool vec_ok = (p.N % 4) == 0;
@@ -195,6 +197,12 @@ __device__ __forceinline__ void epilogue_rows(const CUtensorMap* tmap_c, const P
             const int r = it * 4 + prow;
             const uint32_t addr = buf + uint32_t(r) * 128u + (uint32_t(pj ^ (r & 7)) << 4);
             asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v[it].x), "=r"(v[it].y), "=r"(v[it].z), "=r"(v[it].w) : "r"(addr));
+          }
+          if (pace_ns != 0) {
+            // the warp's share of the link: this chunk's stores leave no earlier than the previous chunk's slot ended
+            uint64_t now = globaltimer_ns();
+            while (now < *pace_next) now = globaltimer_ns();   // bounded: the slot is never more than pace_ns ahead
+            *pace_next = now + pace_ns;
           }
           for (int k = 1; k < p.n_peers; ++k) {
             int dst = peers->self + k;
@@ -384,7 +392,21 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
 constexpr int P_STAGES = 6;
 constexpr int P_A_BYTES = 128 * BK, P_B_BYTES = 128 * BK;
 constexpr int P_STAGE_BYTES = P_A_BYTES + P_B_BYTES;
+// Rate at which plain stores issued by the SMs fill the peers' memory over NVLink on this machine, in bytes per
+// nanosecond: between two GPUs a store kernel alone reaches 675-680 GB/s whatever the store shape (copy engines 740),
+// and the fused GEMM is fastest paced at 700 (690: +1 %, 720: +4 %, 740 and more: as slow as unpaced, +12 %); with
+// four GPUs the best pace is 650.
+constexpr double PEER_STORE_GBS_PAIR = 700.0, PEER_STORE_GBS_SWITCHED = 650.0;
+constexpr double KB_NS = 383.0;   // one 256 x 256 x 128 K-block of the 2-CTA main loop at full speed (24.5 us per 8192-deep tile)
 constexpr size_t GEMM2_SMEM = size_t(P_STAGES) * P_STAGE_BYTES + EPI_BYTES + 1024 + 256;
+
+#ifdef SIMP_W4_TRACE
+// instrumented builds: [CTA pair][tile of the pair][accumulator free, last MMA issued, accumulator complete, tile stored]
+__device__ unsigned long long g_gemm_trace[74 * 16 * 4];
+#define GEMM_MARK(it, k) do { if (pair < 74 && (it) < 16) g_gemm_trace[(pair * 16 + (it)) * 4 + (k)] = globaltimer_ns(); } while (0)
+#else
+#define GEMM_MARK(it, k) do { } while (0)
+#endif
 
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
     gemm_i8_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -402,6 +424,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_generic + 8 * (2 * P_STAGES + 4));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_generic + 8 * (2 * P_STAGES + 4) + 8);
 
+  if (p.n_peers > 0) pdl_launch_dependents();  // the rendezvous kernel may become resident; its wait covers this grid
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t cta_rank = cluster_ctarank();  // 0: even CTA (issues MMAs), 1: odd CTA
   const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
@@ -430,6 +453,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
   cluster_sync_all();  // the peer's barriers are initialised before anything signals them
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  // Fused all-gather form: launched as a programmatic dependent of the rendezvous that closes the previous step, so
+  // everything above ran while that step drained; nothing below touches global memory before the wait returns.
+  if (p.n_peers > 0) pdl_wait();
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer (both CTAs)
@@ -467,6 +493,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
         if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, 12)) { ok = false; break; }
         tc_fence_after_sync();
+        GEMM_MARK((tile - pair) / num_pairs, 0);
         const uint32_t d_tmem = tmem_base + uint32_t(acc * BN);
         for (int kb = 0; kb < p.num_kb; ++kb) {
           if (!p.mma_only && !mbar_wait(full_bar(stage), phase, abort_flag, p.status, 13)) { ok = false; break; }
@@ -484,6 +511,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         }
         if (!ok) break;
         mma_commit_pair(tfull_bar(acc));
+        GEMM_MARK((tile - pair) / num_pairs, 1);
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1u;
       }
@@ -495,16 +523,33 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     uint32_t acc_phase = 0;
     const uint32_t my_stage = epi_base + uint32_t(warp - 2) * 8192u;
     uint32_t nstore = 0;
+    uint64_t pace_next = 0;
+    uint32_t pace_ns = 0;
+    {
+      // Pacing of the stores to the peers: the link carries everything this rank sends in link_ns; a pair that owns
+      // n tiles spreads its 8 * n chunks per warp evenly over that time, so that all pairs finish together and the
+      // stores never queue up in front of the operand loads (unpaced, a wave of finished tiles floods the path to
+      // the link and the main loops behind it run up to 1.8x longer).
+      const int my_tiles = (num_tiles - pair + num_pairs - 1) / num_pairs;
+      if (p.link_ns != 0 && my_tiles > 0) pace_ns = p.link_ns / uint32_t(my_tiles * (BN / 32));
+    }
     for (int tile = pair; tile < num_tiles; tile += num_pairs) {
       int tm, tn;
       tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
       if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, 14)) break;
       tc_fence_after_sync();
+#ifdef SIMP_W4_TRACE
+      const bool marker = warp == 2 && lane == 0 && cta_rank == 0;
+      if (marker) GEMM_MARK((tile - pair) / num_pairs, 2);
+#endif
       if (!p.mma_only)
         epilogue_rows(&tmap_c, &peers, p, tmem_base + uint32_t(acc * BN), q, lane,
-                      tm * 256 + int(cta_rank) * 128 + q * 32, tn * BN, my_stage, nstore);
+                      tm * 256 + int(cta_rank) * 128 + q * 32, tn * BN, my_stage, nstore, false, &pace_next, pace_ns);
       tc_fence_before_sync();
       __syncwarp();
+#ifdef SIMP_W4_TRACE
+      if (marker) GEMM_MARK((tile - pair) / num_pairs, 3);
+#endif
       if (lane == 0) mbar_arrive_even_cta(tempty_bar(acc));
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
@@ -722,7 +767,7 @@ int gemm_i8_run(const void* A, const int8_t* B, int32_t* C, int64_t M, int64_t K
     } else {
       if (int rc = make_map_u8(&mb, B, N, K, 128, BK)) return rc;
     }
-    GemmParams p;
+    GemmParams p{};
     p.M = int(M); p.N = int(N); p.K = int(K);
     p.num_kb = int(cdiv(K, BK));
     p.b_mn_major = b_transposed ? 0 : 1;
@@ -770,18 +815,34 @@ int gemm_i8_run(const void* A, const int8_t* B, int32_t* C, int64_t M, int64_t K
       SIMP_REQUIRE(tiles <= 0x7fffffff, SIMP_ERR_SHAPE, "matmul_i8: too many tiles");
       const int max_pairs = ctx().sm_count / 2;
       const int pairs = int(tiles < max_pairs ? tiles : max_pairs);
+      p.link_ns = 0;
+      if (n_peers > 1) {
+        // SIMP_PEER_STORE_GBS overrides the measured rate of this machine (0 switches pacing off)
+        double gbs = n_peers == 2 ? PEER_STORE_GBS_PAIR : PEER_STORE_GBS_SWITCHED;
+        if (const char* env = getenv("SIMP_PEER_STORE_GBS")) gbs = atof(env);
+        const double ns = gbs > 0 ? double(M) * double(N) * 4.0 * (n_peers - 1) / gbs : 0.0;
+        // Pacing protects the main loops from the flood of stores.  Where the link needs much longer than the math
+        // (8192^3 on 4 ranks: 3x) the main loops have slack and the unpaced epilogue keeps the link as busy (354 us
+        // either way), so pacing is used only up to a ratio of 2.5 (16384^3 on 4 ranks, 1.8x: 1402 -> 1316 us).
+        const double math_ns = double(cdiv(tiles, pairs)) * double(p.num_kb) * KB_NS;
+        p.link_ns = (ns > 0 && ns < 4.0e9 && ns < 2.5 * math_ns) ? uint32_t(ns) : 0u;
+      }
       cudaLaunchConfig_t cfg = {};
       cfg.gridDim = dim3(unsigned(2 * pairs));
       cfg.blockDim = dim3(GEMM_THREADS);
       cfg.dynamicSmemBytes = GEMM2_SMEM;
       cfg.stream = st;
-      cudaLaunchAttribute at[1];
+      cudaLaunchAttribute at[2];
       at[0].id = cudaLaunchAttributeClusterDimension;
       at[0].val.clusterDim.x = 2;
       at[0].val.clusterDim.y = 1;
       at[0].val.clusterDim.z = 1;
+      // fused all-gather form: the prologue (barriers, TMEM, tensor-map fetch) runs while the previous kernel on the
+      // stream -- the rendezvous of the previous step -- is still waiting for the peers
+      at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      at[1].val.programmaticStreamSerializationAllowed = 1;
       cfg.attrs = at;
-      cfg.numAttrs = 1;
+      cfg.numAttrs = n_peers > 0 ? 2 : 1;
       SIMP_CUDA(cudaLaunchKernelEx(&cfg, gemm_i8_tcgen05_2cta_kernel, ma, mb, mc, peers, p));
       return SIMP_OK;
     }
@@ -859,3 +920,11 @@ SIMP_API int simp_gpu_matmul_i8(const void* A, const int8_t* B, int32_t* C, int6
                                 int a_unsigned, int b_transposed) {
   return simp::gemm_i8_run(A, B, C, M, K, N, a_unsigned, b_transposed, nullptr, 0, N, 0, 0);
 }
+
+#ifdef SIMP_W4_TRACE
+// Instrumented builds: the per-tile time marks of the last 2-CTA GEMM launch (74 pairs x 16 tiles x 4 marks).
+SIMP_API int simp_debug_gemm_trace(unsigned long long* host_out) {
+  SIMP_CUDA(cudaMemcpyFromSymbol(host_out, simp::g_gemm_trace, sizeof(unsigned long long) * 74 * 16 * 4));
+  return SIMP_OK;
+}
+#endif
