@@ -108,6 +108,12 @@ def _tp_worker(rank, world, port, out_dir, which):
             cfg = dict(dim=256, hidden_dim=512, n_layers=3, n_heads=8, n_kv_heads=8, vocab_size=320, seq_len=64,
                        group_size=64)
             n_prompt, n_new = 4, 24
+        elif which == "ragged":
+            # per-rank row counts that are not whole 16-row tiles (as the 3B model's 8640 / 8 = 1080 hidden rows on 8
+            # ranks): 2144 / 4 = 536 hidden rows and 88 classifier rows per rank
+            cfg = dict(dim=512, hidden_dim=2144, n_layers=2, n_heads=8, n_kv_heads=8, vocab_size=88 * world, seq_len=64,
+                       group_size=32)
+            n_prompt, n_new = 4, 20
         else:
             cfg = synth.LLAMA_3B_W4
             n_prompt, n_new = 16, 16
@@ -138,7 +144,7 @@ def _tp_worker(rank, world, port, out_dir, which):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("which,world", [("tiny", 2), ("3b", 2), ("tiny", 4), ("3b", 4)])
+@pytest.mark.parametrize("which,world", [("tiny", 2), ("ragged", 2), ("3b", 2), ("tiny", 4), ("ragged", 4), ("3b", 4)])
 def test_tensor_parallel_w4_decode(gpu, tmp_path, which, world):
     import ctypes
     n = ctypes.c_int()
