@@ -160,6 +160,49 @@ __device__ __forceinline__ void w4_mma_spans(const W4Tile& tl, int r0, int vrows
   const bool bsel = t == (g >> 1);
   const int plane = g & 1;
   const int nspans = (nchunks + 3) >> 2;
+  if constexpr (!HALF) {
+    // Lean loop for the common case (a whole 16-row slab, symmetric weights, whole spans): the same arithmetic in the
+    // same order, with 32-bit shared-memory addresses that advance by a constant per span and nothing predicated
+    // but the B operand.  A decode launch runs this loop a handful of times per warp, so its length in instructions
+    // is what it costs.
+    if (!tl.has_z && r0 + 16 <= vrows) {
+      const int nfull = nchunks >> 2;
+      const uint32_t tile = ptx::smem_u32(tl.base);
+      uint32_t xa = ptx::smem_u32(xs) + uint32_t(4 * s0 + t) * (W4_CHUNK_U4 * 16);
+      uint32_t wa_addr = tile + uint32_t(r0 + g) * uint32_t(tl.row_bytes) + uint32_t(4 * s0 + t) * 16u;
+      const uint32_t sc_addr = tile + uint32_t(tl.mat_w) + uint32_t(r0 + g) * uint32_t(tl.sc_row) * 4u;
+      const uint32_t xstep = uint32_t(sstep) * (4 * W4_CHUNK_U4 * 16), wstep = uint32_t(sstep) * 64u;
+      const uint32_t wb_off = 8u * uint32_t(tl.row_bytes), sb_off = 8u * uint32_t(tl.sc_row) * 4u;
+      const uint32_t xsel = uint32_t(plane) * 32u;
+      uint4 xb0 = make_uint4(0, 0, 0, 0), xb1 = xb0;
+      int s = s0;
+      for (; s < nfull; s += sstep, xa += xstep, wa_addr += wstep) {
+        const uint4 meta = ptx::lds128(xa + 64u);
+        if (bsel) {
+          xb0 = ptx::lds128(xa + xsel);
+          xb1 = ptx::lds128(xa + xsel + 16u);
+        }
+        const float sx = __uint_as_float(meta.x);
+        const int m8 = -8 * int(meta.z);
+        const uint32_t grp4 = uint32_t((4 * s + t) >> log2_cpg) << 2;
+#pragma unroll
+        for (int m = 0; m < NM; ++m) {
+          const uint32_t mo = uint32_t(m) * uint32_t(tl.mat_bytes);
+          const uint4 wa = ptx::lds128(wa_addr + mo), wb = ptx::lds128(wa_addr + mo + wb_off);
+          const float sa = ptx::lds_f32(sc_addr + mo + grp4), sb = ptx::lds_f32(sc_addr + mo + sb_off + grp4);
+          int cc[4] = {0, 0, 0, 0};
+          constexpr uint32_t MK = 0x0F0F0F0Fu;
+          mma_u8s8(cc, wa.x & MK, wb.x & MK, (wa.x >> 4) & MK, (wb.x >> 4) & MK, xb0.x, xb0.y);
+          mma_u8s8(cc, wa.y & MK, wb.y & MK, (wa.y >> 4) & MK, (wb.y >> 4) & MK, xb0.z, xb0.w);
+          mma_u8s8(cc, wa.z & MK, wb.z & MK, (wa.z >> 4) & MK, (wb.z >> 4) & MK, xb1.x, xb1.y);
+          mma_u8s8(cc, wa.w & MK, wb.w & MK, (wa.w >> 4) & MK, (wb.w >> 4) & MK, xb1.z, xb1.w);
+          acc[m][0] = fmaf(float(cc[0] * 256 + cc[1] + m8) * sx, sa, acc[m][0]);
+          acc[m][1] = fmaf(float(cc[2] * 256 + cc[3] + m8) * sx, sb, acc[m][1]);
+        }
+      }
+      s0 = s;   // a ragged last span (cols % 128 != 0), if it is this warp's, goes through the general loop below
+    }
+  }
   for (int s = s0; s < nspans; s += sstep) {
     const int c = 4 * s + t;
     const bool valid = c < nchunks;
