@@ -47,7 +47,8 @@ def _worker(rank, world, port, out_dir):
         assert np.array_equal(full, oracle.tensor_matmul_i8(A, B))
         # fused form: TMA stores from the epilogue into every rank's row-major C (CUDA IPC peers)
         import ctypes as C
-        for (M2, K2, N2) in ((256, 512, 1024), (1024, 2048, 4096), (300, 256, 96 * world)):
+        # (2048, 4096, 8192): two waves of 256 x 256 tiles per rank; on 2 ranks the stores to the peer are paced
+        for (M2, K2, N2) in ((256, 512, 1024), (1024, 2048, 4096), (300, 256, 96 * world), (2048, 4096, 8192)):
             A2 = rng.integers(0, 256, (M2, K2), dtype=np.uint8)
             B2 = rng.integers(-128, 128, (K2, N2), dtype=np.int8)
             lo2, hi2 = sd.column_shard(N2, world, rank)
