@@ -716,6 +716,26 @@ static int make_map_u8(CUtensorMap* map, const void* base, int64_t inner, int64_
   return SIMP_OK;
 }
 
+// 2-D f32 tensor maps for the tensor-core f32 GEMM (gemm_f32_tc.cu): operand planes [outer, inner] with boxes of
+// 32 floats (128 bytes) x box_outer rows, and C with 32 x 32 boxes; 128-byte swizzle.
+int make_map_f32(CUtensorMap* map, const void* base, int64_t inner, int64_t outer, int box_outer, bool operand) {
+  const MapKey key{operand ? 2 : 3, base, inner, outer, 32, box_outer};
+  if (map_lookup(key, map)) return SIMP_OK;
+  EncodeTiledFn enc = get_encode_fn();
+  SIMP_REQUIRE(enc != nullptr, SIMP_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
+  cuuint64_t dims[2] = {cuuint64_t(inner), cuuint64_t(outer)};
+  cuuint64_t strides[1] = {cuuint64_t(inner) * 4};
+  cuuint32_t box[2] = {32, cuuint32_t(box_outer)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   operand ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  SIMP_REQUIRE(r == CUDA_SUCCESS, SIMP_ERR_CUDA, "cuTensorMapEncodeTiled (f32) failed with CUresult %d", int(r));
+  map_insert(key, *map);
+  return SIMP_OK;
+}
+
 }  // namespace simp
 
 namespace simp {

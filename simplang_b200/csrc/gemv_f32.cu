@@ -156,6 +156,10 @@ __global__ void __launch_bounds__(256) gemm_f32_skinny_reduce(const float* __res
 
 }  // namespace simp
 
+namespace simp {
+int gemm_f32_tc_run(const float* a, const float* b, float* c, int64_t m, int64_t k, int64_t n, int accumulate,
+                    int b_transposed);
+}
 using namespace simp;
 
 SIMP_API int simp_gpu_matmul_f32(const float* A, int64_t aoff, const float* B, int64_t boff, float* C,
@@ -206,10 +210,15 @@ SIMP_API int simp_gpu_matmul_f32(const float* A, int64_t aoff, const float* B, i
         a, b, part, int(m), int(k), int(n), k_per_split);
     gemm_f32_skinny_reduce<<<unsigned(cdiv(m * n / 4, 256)), 256, 0, st>>>(part, c, m * n, splits, accumulate);
   } else {
-    const int64_t gx = cdiv(n, 64), gy = cdiv(m, 64);
-    SIMP_REQUIRE(gx <= 0x7fffffff && gy <= 65535, SIMP_ERR_SHAPE, "matmul_f32: shape too large for the tile kernel");
-    gemm_f32_tile_kernel<<<dim3(unsigned(gx), unsigned(gy)), 256, 0, st>>>(a, b, c, m, k, n, accumulate,
-                                                                         b_transposed);
+    // GEMM-sized shapes: 3 x TF32 on the tensor cores (gemm_f32_tc.cu); everything else: the FFMA tile kernel
+    const int tc = gemm_f32_tc_run(a, b, c, m, k, n, accumulate, b_transposed);
+    if (tc < 0) return tc;
+    if (tc == 1) {
+      const int64_t gx = cdiv(n, 64), gy = cdiv(m, 64);
+      SIMP_REQUIRE(gx <= 0x7fffffff && gy <= 65535, SIMP_ERR_SHAPE, "matmul_f32: shape too large for the tile kernel");
+      gemm_f32_tile_kernel<<<dim3(unsigned(gx), unsigned(gy)), 256, 0, st>>>(a, b, c, m, k, n, accumulate,
+                                                                           b_transposed);
+    }
   }
   SIMP_LAUNCH_CHECK();
   return SIMP_OK;
@@ -228,6 +237,19 @@ SIMP_API int simp_gpu_matmul_f32_batched(const float* A, const float* B, float* 
   if (k == 0) {
     SIMP_CUDA(cudaMemsetAsync(C, 0, size_t(batch) * size_t(m) * size_t(n) * sizeof(float), st));
     return SIMP_OK;
+  }
+  // GEMM-sized matrices: one tensor-core GEMM per batch entry (the split planes live in library scratch, reused in
+  // stream order)
+  {
+    const int first = gemm_f32_tc_run(A, B, C, m, k, n, 0, b_transposed);
+    if (first < 0) return first;
+    if (first == 0) {
+      for (int64_t i = 1; i < batch; ++i) {
+        const int rc = gemm_f32_tc_run(A + i * m * k, B + i * k * n, C + i * m * n, m, k, n, 0, b_transposed);
+        if (rc != 0) return rc < 0 ? rc : set_error(SIMP_ERR_CUDA, "matmul_f32_batched: scratch lost between batch entries");
+      }
+      return SIMP_OK;
+    }
   }
   const int64_t gx = cdiv(n, 64), gy = cdiv(m, 64);
   SIMP_REQUIRE(gx <= 0x7fffffff && gy <= 65535 && batch <= 65535, SIMP_ERR_SHAPE,

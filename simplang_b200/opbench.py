@@ -90,7 +90,8 @@ def bench_gemm_f32(iters):
     stream for M = 8."""
     rng = np.random.default_rng(5)
     ffma_peak = 148 * 128 * 2 * 1.965e9 / 1e12   # TFLOP/s at the maximum clock
-    for m, k, n in [(8, 2048, 2048), (8, 2048, 8192), (64, 2048, 2048), (512, 2048, 2048), (512, 2048, 8192), (512, 8192, 2048)]:
+    for m, k, n in [(8, 2048, 2048), (8, 2048, 8192), (64, 2048, 2048), (512, 2048, 2048), (512, 2048, 8192), (512, 8192, 2048),
+                    (4096, 4096, 4096), (8192, 8192, 8192)]:
         if not want((m, k, n)):
             continue
         nb = 4 * (m * k + k * n + m * n)

@@ -62,6 +62,31 @@ def test_gemm_tile(gpu, oracle, m, k, n, b_t):
     check(out, A, B, oracle.tensor_matmul_f32(A, Bg, b_transposed=b_t))
 
 
+@pytest.mark.parametrize("m,k,n", [(512, 768, 2304), (300, 520, 516), (1024, 1024, 1024), (128, 4096, 128), (2048, 64, 2048),
+                                   (256, 16384, 128),
+                                   # fewer tiles than CTA pairs: the K chunks of a tile go to different pairs (split K)
+                                   (512, 8192, 2048), (256, 2048, 256)])
+@pytest.mark.parametrize("b_t", [False, True])
+@pytest.mark.parametrize("accumulate", [False, True])
+def test_gemm_tensor_core(gpu, oracle, m, k, n, b_t, accumulate):
+    """GEMM-sized shapes run as 3 x TF32 on the tensor cores (operands split into two TF32 planes each): edge tiles in m
+    and n, k that is not a multiple of the 32-float K block, B in both layouts, and C += through the TMA reduce-add.
+    The error must stay at f32 level -- a plain TF32 product would be ~1e-3."""
+    rng = np.random.default_rng(m + 3 * k + 7 * n)
+    A = rng.standard_normal((m, k)).astype(np.float32)
+    B = rng.standard_normal((k, n)).astype(np.float32)
+    C0 = rng.standard_normal((m, n)).astype(np.float32)
+    Bg = np.ascontiguousarray(B.T) if b_t else B
+    dA, dB, dC = gpu.DeviceBuffer.from_numpy(A), gpu.DeviceBuffer.from_numpy(Bg), gpu.DeviceBuffer.from_numpy(C0)
+    gpu.matmul_f32(dA, 0, dB, 0, dC, 0, m, k, n, accumulate=accumulate, b_transposed=b_t)
+    out = dC.to_numpy(np.float32, (m, n))
+    if accumulate:
+        out = out - C0
+    check(out, A, B, oracle.tensor_matmul_f32(A, Bg, b_transposed=b_t))
+    exact = A.astype(np.float64) @ B.astype(np.float64)
+    assert np.max(np.abs(out - exact)) / np.max(np.abs(exact)) <= 2e-5
+
+
 def test_skinny_accumulates_like_simp_matmul(gpu, oracle):
     """simp.matmul semantics (C += A . B) on the k-split kernel."""
     rng = np.random.default_rng(9)
@@ -93,7 +118,8 @@ def test_known_answers(gpu):
     assert dC.to_numpy(np.float32, (4, 2))[0, 0] == 22.0
 
 
-@pytest.mark.parametrize("batch,m,k,n", [(3, 8, 2048, 512), (5, 33, 70, 41), (1, 64, 64, 64), (12, 16, 64, 16)])
+@pytest.mark.parametrize("batch,m,k,n", [(3, 8, 2048, 512), (5, 33, 70, 41), (1, 64, 64, 64), (12, 16, 64, 16),
+                                         (2, 256, 512, 512)])
 @pytest.mark.parametrize("b_t", [False, True])
 def test_batched_tensor_matmul(gpu, oracle, batch, m, k, n, b_t):
     """3-D tensor_matmul (linalg.batch_matmul, ConvertSimpToMemRef.cpp:3286-3291): every batch entry equals the 2-D op."""
