@@ -43,16 +43,27 @@ __device__ __forceinline__ void split2(float x, float& hi, float& lo) {
   lo = to_tf32(x - hi);
 }
 
-// src [rows, k] row-major (row pitch ld) -> hi, lo [rows, kp]; columns k..kp-1 are zero.  One thread per element.
+// src [rows, k] row-major (row pitch ld) -> hi, lo [rows, kp]; columns k..kp-1 are zero.  One thread per four
+// elements (kp is a multiple of 32; `vec`: k % 4 == 0 and src 16-byte aligned, so the loads are 16-byte loads too).
 __global__ void __launch_bounds__(256) split_rows_kernel(const float* __restrict__ src, int64_t rows, int64_t k, int64_t ld,
-                                                         float* __restrict__ hi, float* __restrict__ lo, int64_t kp) {
-  const int64_t col = int64_t(blockIdx.x) * 256 + threadIdx.x;
-  const int64_t row = blockIdx.y;
+                                                         float* __restrict__ hi, float* __restrict__ lo, int64_t kp, int vec) {
+  const int64_t col = (int64_t(blockIdx.y) * 256 + threadIdx.x) * 4;
+  const int64_t row = blockIdx.x;
   if (col >= kp) return;
-  float h = 0.0f, l = 0.0f;
-  if (col < k) split2(__ldg(src + row * ld + col), h, l);
-  hi[row * kp + col] = h;
-  lo[row * kp + col] = l;
+  float x[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+  if (vec && col + 4 <= k) {
+    const float4 v = __ldg(reinterpret_cast<const float4*>(src + row * ld + col));
+    x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      if (col + i < k) x[i] = __ldg(src + row * ld + col + i);
+  }
+  float h[4], l[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) split2(x[i], h[i], l[i]);
+  *reinterpret_cast<float4*>(hi + row * kp + col) = make_float4(h[0], h[1], h[2], h[3]);
+  *reinterpret_cast<float4*>(lo + row * kp + col) = make_float4(l[0], l[1], l[2], l[3]);
 }
 
 // src [k, n] row-major -> hi, lo [n, kp] (transposed), zero fill for k..kp-1.  32 x 32 tiles through shared memory.
@@ -358,6 +369,7 @@ int gemm_f32_tc_run(const float* a, const float* b, float* c, int64_t m, int64_t
   if (double(m) * double(n) * double(k) < double(int64_t(1) << 26)) return 1;   // too small to pay for the split pass
   if (m > 0x3fffffff || n > 0x3fffffff || k > 0x3fffffff) return 1;
   const int64_t kp = cdiv(k, F_BK) * F_BK;
+  if (kp / 32 > 65535) return 1;   // grid limit of the transposing split
   const size_t a_plane = size_t(m) * size_t(kp) * 4, b_plane = size_t(n) * size_t(kp) * 4;
   if (2 * (a_plane + b_plane) > (size_t(8) << 30)) return 1;
   float* pa = static_cast<float*>(scratch(2 * a_plane, 13));
@@ -365,9 +377,11 @@ int gemm_f32_tc_run(const float* a, const float* b, float* c, int64_t m, int64_t
   if (!pa || !pb) return 1;
   float *a_hi = pa, *a_lo = pa + size_t(m) * kp, *b_hi = pb, *b_lo = pb + size_t(n) * kp;
   cudaStream_t st = ctx().stream;
-  split_rows_kernel<<<dim3(unsigned(cdiv(kp, 256)), unsigned(m)), 256, 0, st>>>(a, m, k, k, a_hi, a_lo, kp);
+  const int va = (k % 4 == 0 && (reinterpret_cast<uintptr_t>(a) & 15u) == 0) ? 1 : 0;
+  const int vb = (k % 4 == 0 && (reinterpret_cast<uintptr_t>(b) & 15u) == 0) ? 1 : 0;
+  split_rows_kernel<<<dim3(unsigned(m), unsigned(cdiv(kp, 1024))), 256, 0, st>>>(a, m, k, k, a_hi, a_lo, kp, va);
   if (b_transposed)
-    split_rows_kernel<<<dim3(unsigned(cdiv(kp, 256)), unsigned(n)), 256, 0, st>>>(b, n, k, k, b_hi, b_lo, kp);
+    split_rows_kernel<<<dim3(unsigned(n), unsigned(cdiv(kp, 1024))), 256, 0, st>>>(b, n, k, k, b_hi, b_lo, kp, vb);
   else
     split_transpose_kernel<<<dim3(unsigned(cdiv(n, 32)), unsigned(kp / 32)), 256, 0, st>>>(b, k, n, b_hi, b_lo, kp);
   SIMP_LAUNCH_CHECK();

@@ -65,7 +65,7 @@ def test_gemm_tile(gpu, oracle, m, k, n, b_t):
 @pytest.mark.parametrize("m,k,n", [(512, 768, 2304), (300, 520, 516), (1024, 1024, 1024), (128, 4096, 128), (2048, 64, 2048),
                                    (256, 16384, 128),
                                    # fewer tiles than CTA pairs: the K chunks of a tile go to different pairs (split K)
-                                   (512, 8192, 2048), (256, 2048, 256)])
+                                   (256, 8192, 512), (256, 2048, 256)])
 @pytest.mark.parametrize("b_t", [False, True])
 @pytest.mark.parametrize("accumulate", [False, True])
 def test_gemm_tensor_core(gpu, oracle, m, k, n, b_t, accumulate):
