@@ -57,8 +57,13 @@ int simp_gpu_check_device_status(void);
  * accumulate == 0: tensor_matmul / tensor_matmul_into / tensor_matvecmul on f32, C = A.B
  *   (ConvertSimpToMemRef.cpp:2884-2950, 3280-3291, 3490-3627, 3632-3792).
  * b_transposed != 0: tensor_matmul_nt, B given as [n,k] (ConvertSimpToMemRef.cpp:3373-3486).
- * n == 1 runs the streaming GEMV kernel; other shapes run the FFMA tile kernel.  f32 FMA
- * arithmetic throughout (no TF32). */
+ * n == 1 runs the streaming GEMV kernel, a skinny left operand (m <= 64) the k-split streaming kernel, small shapes
+ * the FFMA tile kernel: f32 FMA arithmetic.  GEMM-sized shapes (m, n >= 128, k >= 32, n % 4 == 0, m*n*k >= 2^26) run
+ * on the tensor cores as 3 x TF32 (each operand split into two TF32 numbers, three products per step, f32
+ * accumulation: error at f32 level, never a single TF32 product); that path keeps the split operands in library
+ * scratch (2 x the operand bytes; grown on first use -- inside a recording it falls back to the FFMA kernel if the
+ * scratch would have to grow), and for shapes with fewer than 37 tiles of 256 x 256 it splits K over the SMs and adds
+ * the parts into C in no fixed order (results may differ in the last bits from run to run). */
 int simp_gpu_matmul_f32(const float* A_dev, int64_t aoff, const float* B_dev, int64_t boff,
                         float* C_dev, int64_t coff, int64_t m, int64_t k, int64_t n,
                         int accumulate, int b_transposed);

@@ -86,8 +86,8 @@ def bench_gemv_f32(iters):
 def bench_gemm_f32(iters):
     """tensor_matmul on f32 with more than one right-hand side: the projection shapes of
     examples/llama2/llama32_1b_fp32_prefill.sl:51-199 (M tokens x [2048 -> 2048 / 512 / 8192, 8192 -> 2048]).
-    Plain FFMA (never TF32): the bound is the FP32 pipe (148 SMs x 128 FMA per clock) for tall M and the weight
-    stream for M = 8."""
+    M = 8 / 64: f32 FMA kernels bound by the weight stream; M >= 128: 3 x TF32 on the tensor cores (f32 accuracy), whose
+    rate is also reported against the FP32 pipe's own peak (148 SMs x 128 FMA per clock) for comparison."""
     rng = np.random.default_rng(5)
     ffma_peak = 148 * 128 * 2 * 1.965e9 / 1e12   # TFLOP/s at the maximum clock
     for m, k, n in [(8, 2048, 2048), (8, 2048, 8192), (64, 2048, 2048), (512, 2048, 2048), (512, 2048, 8192), (512, 8192, 2048),
