@@ -17,6 +17,8 @@
 //     TMA-loads its own 128 rows of the four planes (128-byte swizzle, 3 stages of 64 KB), the even CTA issues
 //     tcgen05.mma.cta_group::2.kind::tf32 (M 256, N 256, K 8), accumulators double-buffered in TMEM, four epilogue
 //     warps per CTA move TMEM -> registers -> swizzled shared tile -> TMA store (TMA f32 reduce-add for `accumulate`).
+//     K is accumulated in TMEM in chunks of 2048 (F_CHUNK_KB) that are added into C one after the other; shapes with
+//     few tiles deal (tile, chunk) units to the CTA pairs instead (split K, see F32Params::splitk).
 // All waits are bounded (mbar_wait): on expiry the library status word is set and the kernel drains.
 #include <cuda.h>
 
@@ -222,7 +224,6 @@ __global__ void __launch_bounds__(F_THREADS, 1)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t cta_rank = cluster_ctarank();  // 0: even CTA (issues the MMAs), 1: odd CTA
   const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
-  const int num_tiles = p.tiles_m * p.tiles_n;  // 256 x 256 tiles
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < F_STAGES; ++s) {
