@@ -385,7 +385,7 @@ def run_ours(args):
         dC_local = sg.DeviceBuffer(M * Nl * 4)
 
         def step():
-            if fused:  # all-gather fused into the GEMM epilogue (TMA stores to every rank's C)
+            if fused:  # all-gather fused into the GEMM epilogue (stores to every rank's C)
                 sg.check(sg.lib().simp_dist_matmul_i8_nsharded_fused(dA.ptr, dB.ptr, c_ptr, M, K, Nl, 1, 0))
             else:      # GEMM, then NCCL all-gather of the column blocks
                 sg.check(sg.lib().simp_dist_matmul_i8_nsharded(dA.ptr, dB.ptr, dC.ptr, M, K, Nl, 1, 0))
@@ -586,7 +586,7 @@ def run_ours(args):
         "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "u8", "data": "synthetic",
         "config": {"workload": f"int8 tensor_matmul {S}^3: u8[M,K] x s8[K,N] -> i32, seeded uniform, row-major",
-                   "sharding": "single GPU" if world == 1 else (f"N-sharded over {world} ranks, all-gather of C fused into the GEMM epilogue (TMA stores to peer HBM over NVLink)"
+                   "sharding": "single GPU" if world == 1 else (f"N-sharded over {world} ranks, all-gather of C fused into the GEMM epilogue (every tile stored to all peers over NVLink by the kernel itself)"
                                                                    if fused else f"N-sharded over {world} ranks + NCCL all-gather of the column blocks of C"),
                    "l2": "384 MB touched per step at 8192^3 (> 126 MB L2): no flush between steps",
                    "decode": "second half of the metric: see the `decode` record (f32 110M on one GPU; W4 3B tensor-parallel over all ranks)"},

@@ -307,9 +307,9 @@ int simp_dist_matmul_i8_nsharded(const void* A_dev, const int8_t* B_local_dev, i
                                  int64_t M, int64_t K, int64_t N_local, int a_unsigned,
                                  int b_transposed);
 /* The same GEMM with the exchange fused into the tensor-core kernel: every C tile is staged once in shared
- * memory and TMA-stored into every rank's copy of the full row-major C[M, N_local*world] (own HBM and, over
- * NVLink, the peers'), so the all-gather overlaps the main loop tile by tile and C arrives in the layout
- * tensor_matmul defines.  C_symm_dev must come from simp_dist_symm_alloc (a collective that allocates
+ * memory and written into every rank's copy of the full row-major C[M, N_local*world] (own HBM by TMA store; the
+ * peers', over NVLink, by plain stores paced at the link's rate), so the all-gather overlaps the main loop tile by
+ * tile and C arrives in the layout tensor_matmul defines.  C_symm_dev must come from simp_dist_symm_alloc (a collective that allocates
  * `bytes` on every rank and maps all ranks' buffers through CUDA IPC).  N_local must be a multiple of 32 (whole
  * 32-column boxes are stored; a narrower block would spill into the neighbour's).  The call ends with a rendezvous
  * of all ranks on the library stream (epoch words exchanged by peer stores, bounded waits), which orders every

@@ -58,7 +58,8 @@ struct GemmParams {
   int* status;
   int tma_store;    // 1: epilogue goes through shared memory + TMA stores (needs N % 4 == 0)
   uint32_t link_ns; // fused all-gather, 2-CTA kernel: time the link needs for everything this rank sends (0: no pacing)
-  int n_peers;      // > 0: every C tile is TMA-stored into n_peers buffers (own + peer GPUs) at column col_offset
+  int n_peers;      // > 0: every C tile is written into n_peers buffers (own copy by TMA store, the peer GPUs' by plain
+                    //      stores) at column col_offset
   int col_offset;
   int streamk;      // 1: the tiles x K-blocks work units are split evenly over the CTAs; partial tiles are
                     //    added into a zeroed C with TMA reduce-add (integer adds: exact in any order)

@@ -45,7 +45,7 @@ def _worker(rank, world, port, out_dir):
         sg.check(sg.lib().simp_dist_matmul_i8_nsharded(dA.ptr, dB.ptr, dC.ptr, M, K, hi - lo, 1, 0))
         full = sd.assemble_column_blocks(dC.to_numpy(np.int32, (world, M, hi - lo)))
         assert np.array_equal(full, oracle.tensor_matmul_i8(A, B))
-        # fused form: TMA stores from the epilogue into every rank's row-major C (CUDA IPC peers)
+        # fused form: the epilogue writes every tile into every rank's row-major C (CUDA IPC peers)
         import ctypes as C
         # (2048, 4096, 8192): two waves of 256 x 256 tiles per rank; on 2 ranks the stores to the peer are paced
         for (M2, K2, N2) in ((256, 512, 1024), (1024, 2048, 4096), (300, 256, 96 * world), (2048, 4096, 8192)):
