@@ -593,7 +593,7 @@ def run_ours(args):
         "clocks": clocks,
         "e2e": {"value": e2e_tops, "unit": "TOPS", "h2d_bytes_per_step": int(M * K + K * Nl) * world,
                 "d2h_bytes_per_step": int(4 * M * Nl) * world, "ms_per_step": 1e3 * t_e2e, "steps": e2e_steps,
-                "api": "simp_host_tensor_matmul_i8 (pinned host operands, chunked upload/compute/download)"},
+                "api": "simp_host_tensor_matmul_i8 (pinned host operands; C in row chunks x column blocks, upload / compute / download overlapped)"},
         "gpu_launches": args.steps,
         "roofline": {"bound": "tensor", "achieved": tops / world, "peak": peak_int8, "unit": "TOP/s",
                      "frac": tops / world / peak_int8,

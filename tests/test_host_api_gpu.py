@@ -114,6 +114,26 @@ def test_host_gemm_chunked_pipeline_and_registered_weights(gpu, oracle):
     assert gpu.lib().simp_gpu_unregister_host(Bt.ctypes.data) != 0
 
 
+@pytest.mark.parametrize("nt", [False, True])
+@pytest.mark.parametrize("a_dtype", [np.uint8, np.int8])
+def test_host_gemm_blocked_pipeline(gpu, oracle, nt, a_dtype):
+    """Large host-to-host products are cut into row chunks x column blocks of C (uploads ordered so that the first block
+    leaves early): ragged last row chunk, both layouts of B, pageable and pinned host buffers."""
+    rng = np.random.default_rng(14)
+    M, K, N = 2100, 4096, 4096   # 16 MB of B: 9 row chunks (the last one ragged) x 4 column blocks
+    lo, hi = (0, 256) if a_dtype == np.uint8 else (-128, 128)
+    A = rng.integers(lo, hi, (M, K)).astype(a_dtype)
+    B = rng.integers(-128, 128, (K, N), dtype=np.int8)
+    Bg = np.ascontiguousarray(B.T) if nt else B
+    ref = oracle.tensor_matmul_i8(A, Bg, b_transposed=nt)
+    assert np.array_equal(gpu.host_tensor_matmul_i8(A, Bg, b_transposed=nt), ref)
+    Ap, Bp, Cp = gpu.pinned_empty(A.shape, A.dtype), gpu.pinned_empty(Bg.shape, Bg.dtype), gpu.pinned_empty((M, N), np.int32)
+    Ap[...] = A
+    Bp[...] = Bg
+    Cp[...] = -1
+    assert np.array_equal(gpu.host_tensor_matmul_i8(Ap, Bp, out=Cp, b_transposed=nt), ref)
+
+
 def test_cpp_host_driver(gpu):
     """The C++ host (GpuKernelRunner / ProfiledGpuKernelRunner) loads the library, runs and verifies a GEMM."""
     import os
