@@ -110,6 +110,8 @@ struct W4Args {
   TpLL tp;
   uint32_t id_x, id_res, id_out, out_off;
   int total_tiles;         // row tiles over all segments (W4_GATE_UP: over segment 0)
+  int any_ragged;          // some segment's row count is not a multiple of the tile height (its last tile is copied
+                           // with plain loads instead of bulk copies)
   int* status;             // device error word for bounded waits
   int seg_tile_start[4];
 #ifdef SIMP_W4_TRACE
@@ -282,13 +284,33 @@ __global__ void __launch_bounds__(NW * 32, NW == 8 ? 3 : 1) w4_gemv_kernel(const
   auto stage_ptr = [&](int st, int m) { return smem + xs_bytes + st * stage_bytes + m * mat_bytes; };
 
   const int my_steps = int(blockIdx.x) < a.total_tiles ? (a.total_tiles - 1 - int(blockIdx.x)) / int(gridDim.x) + 1 : 0;
-  auto locate = [&](int q, int& s, int& row0, int& rows) {
+  auto locate_tile = [&](int q, int& s, int& row0, int& rows) {
     const int tile = int(blockIdx.x) + q * int(gridDim.x);
     s = 0;
     if (MODE != W4_GATE_UP)
       while (s + 1 < a.nseg && tile >= a.seg_tile_start[s + 1]) ++s;
     row0 = (tile - a.seg_tile_start[s]) * S_ROWS;
     rows = a.seg[s].rows;
+  };
+  // Batched form: a block owns at most 2 * NS tiles; where they lie is worked out once (one thread per tile, while
+  // the kernel has nothing else to do) and looked up afterwards -- every warp asks for every tile several times, and
+  // in a decode launch 16 warps x a few dozen instructions per question is time on the critical path.
+  __shared__ int t_seg[BATCH ? 2 * NS : 1], t_row0[BATCH ? 2 * NS : 1], t_rows[BATCH ? 2 * NS : 1];
+  if (BATCH && int(threadIdx.x) < 2 * NS && int(threadIdx.x) < my_steps) {
+    int s, row0, rows;
+    locate_tile(int(threadIdx.x), s, row0, rows);
+    t_seg[threadIdx.x] = s;
+    t_row0[threadIdx.x] = row0;
+    t_rows[threadIdx.x] = rows;
+  }
+  auto locate = [&](int q, int& s, int& row0, int& rows) {
+    if (BATCH) {
+      s = t_seg[q];
+      row0 = t_row0[q];
+      rows = t_rows[q];
+    } else {
+      locate_tile(q, s, row0, rows);
+    }
   };
   // Requests of tiles.  A full tile is P = NM x (weights, scales[, zeros]) bulk copies onto the stage's barrier.
   // One thread accepts ~2.5 M bulk-copy requests per second whatever their size, so a round of tiles is spread
@@ -314,6 +336,7 @@ __global__ void __launch_bounds__(NW * 32, NW == 8 ? 3 : 1) w4_gemv_kernel(const
       else if (part == 1) ptx::bulk_load(ptx::smem_u32(dst + mat_w), sg.sc + size_t(row0) * sc_row, uint32_t(mat_s), bar);
       else ptx::bulk_load(ptx::smem_u32(dst + mat_w + mat_s), sg.zr + size_t(row0) * sc_row, uint32_t(mat_s), bar);
     }
+    if (a.any_ragged)
     for (int j = 0; j < count; ++j) {   // block-uniform
       const int q = q_first + j;
       if (q >= my_steps) break;
@@ -638,6 +661,9 @@ inline int w4_launch(W4Args a, cudaStream_t st, int sm_count, bool pdl = false, 
   }
   a.seg_tile_start[nseg_tiles] = g;
   a.total_tiles = g;
+  a.any_ragged = 0;
+  for (int s = 0; s < nseg_tiles; ++s)
+    if (a.seg[s].rows % tr != 0) a.any_ragged = 1;
   int per_sm = int((227 * 1024) / (smem + 4096));
   per_sm = wide || per_sm < 1 ? 1 : (per_sm > 3 ? 3 : per_sm);
   const int cap = sm_count * per_sm;
