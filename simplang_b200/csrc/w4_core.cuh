@@ -462,7 +462,8 @@ __global__ void __launch_bounds__(NW * 32, NW == 8 ? 3 : 1) w4_gemv_kernel(const
   }
   __syncthreads();
   float inv_r = 1.0f;
-  if (a.norm) {
+  // only the threads that will write results need the norm factor (the first S_ROWS per tile of a batch)
+  if (a.norm && int(threadIdx.x) < (BATCH ? NS : 1) * S_ROWS) {
     float ss = 0.0f;
 #pragma unroll
     for (int w = 0; w < NW; ++w) ss += sh_ss[w];
